@@ -1,0 +1,159 @@
+// Host side of the tcgen05 GEMM: builds the TMA tensor maps and launches the persistent kernel.
+#include "gemm_sm100.cuh"
+#include "opk_api.h"
+
+#include <cudaTypedefs.h>
+#include <mutex>
+#include <stdio.h>
+#include <string.h>
+
+namespace {
+
+thread_local char g_err[512] = "";
+void set_err(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+  });
+  return fn;
+}
+
+// 3-D bf16 map {inner, rows, batch} with a {64, box_rows, 1} box and 128-byte swizzle.
+bool make_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t rows, uint64_t batch, uint64_t ld,
+              uint64_t batch_stride, uint32_t box_rows) {
+  EncodeFn enc = get_encode();
+  if (!enc) { set_err("cuTensorMapEncodeTiled not available"); return false; }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) { set_err("TMA operand base must be 16-byte aligned"); return false; }
+  if ((ld * 2) % 16 != 0) { set_err("TMA operand row pitch must be a multiple of 8 elements"); return false; }
+  if (batch > 1 && (batch_stride * 2) % 16 != 0) { set_err("TMA batch stride must be a multiple of 8 elements"); return false; }
+  cuuint64_t dims[3] = {inner, rows, batch};
+  cuuint64_t bs = batch > 1 ? batch_stride * 2 : rows * ld * 2;
+  cuuint64_t strides[2] = {ld * 2, bs};
+  cuuint32_t box[3] = {64, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[160];
+    snprintf(buf, sizeof(buf), "cuTensorMapEncodeTiled failed (%d): inner=%llu rows=%llu batch=%llu ld=%llu", (int)r,
+             (unsigned long long)inner, (unsigned long long)rows, (unsigned long long)batch, (unsigned long long)ld);
+    set_err(buf);
+    return false;
+  }
+  return true;
+}
+
+int g_num_sms = 0;
+int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+template <bool A_MN, bool B_MN, int BN, int EPI>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const opk::GemmParams& p, int max_ctas, cudaStream_t st) {
+  using Cfg = opk::GemmCfg<BN>;
+  auto kern = opk::gemm_bf16_kernel<A_MN, B_MN, BN, EPI>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) { set_err(cudaGetErrorString(e)); return (int)e; }
+    attr_done = true;
+  }
+  const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN) * p.batch;
+  int grid = max_ctas > 0 ? max_ctas : num_sms();
+  if (grid > tiles) grid = tiles;
+  kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(ta, tb, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_err(cudaGetErrorString(e)); return (int)e; }
+  return 0;
+}
+
+int pick_bn(int N, int epilogue) {
+  if (epilogue == opk::EPI_LCE_FWD || epilogue == opk::EPI_LCE_BWD || epilogue == opk::EPI_SWIGLU) return 256;
+  return N <= 128 ? 128 : 256;
+}
+
+}  // namespace
+
+extern "C" const char* opk_last_error(void) { return g_err; }
+extern "C" int opk_num_sms(void) { return num_sms(); }
+extern "C" int opk_gemm_tiles_n(int N, int epilogue) {
+  const int bn = pick_bn(N, epilogue);
+  return (N + bn - 1) / bn;
+}
+
+extern "C" int opk_gemm(const OpkGemmArgs* a, void* stream) {
+  if (!a || a->M <= 0 || a->N <= 0 || a->K <= 0 || a->batch <= 0) { set_err("opk_gemm: bad sizes"); return -1; }
+  const int bn = pick_bn(a->N, a->epilogue);
+  CUtensorMap ta, tb;
+  // A: K-major -> {K, M, batch} box {64, 128}; MN-major -> {M, K, batch} box {64, 64}
+  if (a->a_mn) {
+    if (!make_map(&ta, a->A, a->M, a->K, a->batch, a->lda, a->strideA, 64)) return -2;
+  } else {
+    if (!make_map(&ta, a->A, a->K, a->M, a->batch, a->lda, a->strideA, 128)) return -2;
+  }
+  const int bdiv = a->b_batch_div > 0 ? a->b_batch_div : 1;
+  const int bbatch = (a->batch + bdiv - 1) / bdiv;
+  if (a->b_mn) {
+    if (!make_map(&tb, a->B, a->N, a->K, bbatch, a->ldb, a->strideB, 64)) return -2;
+  } else {
+    if (!make_map(&tb, a->B, a->K, a->N, bbatch, a->ldb, a->strideB, bn)) return -2;
+  }
+  opk::GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = a->M; p.N = a->N; p.K = a->K; p.batch = a->batch; p.b_batch_div = bdiv;
+  p.ldc = a->ldc; p.strideC = a->strideC; p.C = a->C; p.R = a->R; p.bias = a->bias;
+  p.alpha = a->alpha; p.sumsq = a->sumsq; p.act = a->act; p.ld_act = a->ld_act; p.labels = a->labels;
+  p.pmax = a->pmax; p.psum = a->psum; p.tgt = a->tgt; p.lse = a->lse; p.coef = a->coef; p.softcap = a->softcap;
+  p.err = a->err;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int key = (a->a_mn ? 1 : 0) | (a->b_mn ? 2 : 0);
+  const int mc = a->max_ctas;
+  switch (a->epilogue) {
+    case opk::EPI_STORE:
+      if (key == 0) return bn == 256 ? launch<false, false, 256, opk::EPI_STORE>(ta, tb, p, mc, st)
+                                     : launch<false, false, 128, opk::EPI_STORE>(ta, tb, p, mc, st);
+      if (key == 2) return bn == 256 ? launch<false, true, 256, opk::EPI_STORE>(ta, tb, p, mc, st)
+                                     : launch<false, true, 128, opk::EPI_STORE>(ta, tb, p, mc, st);
+      if (key == 3) return bn == 256 ? launch<true, true, 256, opk::EPI_STORE>(ta, tb, p, mc, st)
+                                     : launch<true, true, 128, opk::EPI_STORE>(ta, tb, p, mc, st);
+      break;
+    case opk::EPI_SUMSQ:
+      if (!a->sumsq) { set_err("opk_gemm: sumsq pointer required"); return -1; }
+      if (key == 3) return bn == 256 ? launch<true, true, 256, opk::EPI_SUMSQ>(ta, tb, p, mc, st)
+                                     : launch<true, true, 128, opk::EPI_SUMSQ>(ta, tb, p, mc, st);
+      break;
+    case opk::EPI_SWIGLU:
+      if (!a->act || (a->N & 1)) { set_err("opk_gemm: swiglu needs act and even N"); return -1; }
+      if (key == 0) return launch<false, false, 256, opk::EPI_SWIGLU>(ta, tb, p, mc, st);
+      break;
+    case opk::EPI_LCE_FWD:
+      if (!a->labels || !a->pmax || !a->psum || !a->tgt) { set_err("opk_gemm: lce fwd buffers required"); return -1; }
+      if (key == 0) return launch<false, false, 256, opk::EPI_LCE_FWD>(ta, tb, p, mc, st);
+      break;
+    case opk::EPI_LCE_BWD:
+      if (!a->labels || !a->lse || !a->coef) { set_err("opk_gemm: lce bwd buffers required"); return -1; }
+      if (key == 0) return launch<false, false, 256, opk::EPI_LCE_BWD>(ta, tb, p, mc, st);
+      break;
+    default: break;
+  }
+  set_err("opk_gemm: unsupported (layout, epilogue) combination");
+  return -3;
+}

@@ -1,0 +1,98 @@
+"""ctypes binding of ``libopake_kernels.so`` (the hand-written sm_100a kernels).
+
+The library is built in-tree by :mod:`opake_b200._build`. On a machine with a GPU a missing library is a hard
+error: no op silently falls back to eager PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_double, c_float, c_int32, c_int64, c_void_p
+from functools import lru_cache
+
+import torch
+
+from .._build import KERNEL_LIB, build_kernels
+
+
+class GemmArgs(Structure):
+    _fields_ = [
+        ("A", c_void_p), ("B", c_void_p), ("C", c_void_p), ("R", c_void_p), ("bias", c_void_p),
+        ("M", c_int32), ("N", c_int32), ("K", c_int32), ("batch", c_int32),
+        ("a_mn", c_int32), ("b_mn", c_int32), ("epilogue", c_int32), ("b_batch_div", c_int32),
+        ("lda", c_int64), ("ldb", c_int64), ("ldc", c_int64),
+        ("strideA", c_int64), ("strideB", c_int64), ("strideC", c_int64),
+        ("alpha", c_float), ("softcap", c_float),
+        ("sumsq", c_void_p), ("act", c_void_p), ("ld_act", c_int64),
+        ("labels", c_void_p), ("pmax", c_void_p), ("psum", c_void_p), ("tgt", c_void_p),
+        ("lse", c_void_p), ("coef", c_void_p), ("err", c_void_p), ("max_ctas", c_int32),
+    ]
+
+
+class KernelLibraryError(RuntimeError):
+    pass
+
+
+@lru_cache(maxsize=1)
+def lib() -> ctypes.CDLL:
+    path = KERNEL_LIB
+    if not path.exists():
+        try:
+            build_kernels()
+        except Exception as exc:  # pragma: no cover - build environment specific
+            raise KernelLibraryError(f"{path} is missing and could not be built: {exc}") from exc
+    L = ctypes.CDLL(str(path))
+    L.opk_last_error.restype = c_char_p
+    L.opk_gemm.argtypes = [POINTER(GemmArgs), c_void_p]
+    L.opk_gemm.restype = c_int32
+    L.opk_gemm_tiles_n.argtypes = [c_int32, c_int32]
+    L.opk_gemm_tiles_n.restype = c_int32
+    L.opk_num_sms.restype = c_int32
+    _declare_optional(L)
+    return L
+
+
+def _declare_optional(L: ctypes.CDLL) -> None:
+    """Attach prototypes for the non-GEMM kernels (declared in csrc/kernels/opk_api.h)."""
+    from ._protos import PROTOTYPES
+
+    for name, (restype, argtypes) in PROTOTYPES.items():
+        fn = getattr(L, name, None)
+        if fn is None:
+            raise KernelLibraryError(f"symbol {name} missing from {KERNEL_LIB}; rebuild with opake_b200._build")
+        fn.restype = restype
+        fn.argtypes = argtypes
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        msg = lib().opk_last_error().decode("utf-8", "replace")
+        raise KernelLibraryError(f"{what} failed (code {code}): {msg}")
+
+
+def stream_ptr(device: torch.device | None = None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+_ERR: dict[int, torch.Tensor] = {}
+
+
+def err_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 that kernels set to 1 when one of their bounded waits expires."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _ERR.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _ERR[idx] = t
+    return t
+
+
+def raise_if_device_error(device: torch.device) -> None:
+    """Synchronising check of the error word; raises :class:`KernelLibraryError` when a kernel gave up a wait."""
+    t = err_word(device)
+    if int(t.item()) != 0:
+        t.zero_()
+        raise KernelLibraryError("a device-side bounded wait expired (kernel aborted cleanly)")

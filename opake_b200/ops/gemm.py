@@ -1,0 +1,121 @@
+"""bf16 tensor-core matrix products on the tcgen05 GEMM kernel (csrc/kernels/gemm_sm100.cuh).
+
+All functions take 2-D (or batched 3-D) row-major bf16 CUDA tensors whose row pitch is a multiple of 8 elements
+and return bf16. They correspond to the cuBLAS/ATen matmuls the reference runs under ``vmap(grad)``
+(reference: packages/opake-patches/src/opake/api/patches/kernels — "everything else on GPU" path).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+EPI_STORE, EPI_SUMSQ, EPI_SWIGLU, EPI_LCE_FWD, EPI_LCE_BWD = range(5)
+
+
+def _check2d(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.bfloat16 or not t.is_cuda:
+        raise TypeError(f"{name}: expected a CUDA bf16 tensor, got {t.dtype} on {t.device}")
+    if t.stride(-1) != 1:
+        raise ValueError(f"{name}: last dimension must be contiguous")
+    if t.stride(-2) % 8 != 0 or t.data_ptr() % 16 != 0:
+        raise ValueError(f"{name}: row pitch must be a multiple of 8 elements and the base 16-byte aligned")
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    out: torch.Tensor | None = None,
+    residual: torch.Tensor | None = None,
+    bias: torch.Tensor | None = None,
+    alpha: float = 1.0,
+    epilogue: int = EPI_STORE,
+    sumsq: torch.Tensor | None = None,
+    act: torch.Tensor | None = None,
+    labels: torch.Tensor | None = None,
+    pmax: torch.Tensor | None = None,
+    psum: torch.Tensor | None = None,
+    tgt: torch.Tensor | None = None,
+    lse: torch.Tensor | None = None,
+    coef: torch.Tensor | None = None,
+    softcap: float = 0.0,
+    b_batch_div: int = 1,
+    max_ctas: int = 0,
+) -> torch.Tensor | None:
+    """General entry: ``out[b] = alpha * op(a[b]) @ op(b[b // b_batch_div])^T`` with an epilogue.
+
+    ``a_mn=False``: ``a`` is ``[M, K]``; ``a_mn=True``: ``a`` is ``[K, M]`` (used as its transpose).
+    ``b_mn=False``: ``b`` is ``[N, K]``; ``b_mn=True``: ``b`` is ``[K, N]``.
+    """
+    _check2d(a, "a")
+    _check2d(b, "b")
+    batched = a.dim() == 3
+    batch = a.shape[0] if batched else 1
+    if a_mn:
+        K, M = a.shape[-2], a.shape[-1]
+    else:
+        M, K = a.shape[-2], a.shape[-1]
+    if b_mn:
+        Kb, N = b.shape[-2], b.shape[-1]
+    else:
+        N, Kb = b.shape[-2], b.shape[-1]
+    if K != Kb:
+        raise ValueError(f"reduction sizes differ: {K} vs {Kb}")
+    need_out = epilogue != EPI_LCE_FWD
+    if out is None and need_out:
+        shape = (batch, M, N) if batched else (M, N)
+        out = torch.empty(shape, dtype=torch.bfloat16, device=a.device)
+    args = _lib.GemmArgs()
+    args.A, args.B = a.data_ptr(), b.data_ptr()
+    args.C = out.data_ptr() if out is not None else None
+    if out is not None:
+        _check2d(out, "out")
+        args.ldc = out.stride(-2)
+        args.strideC = out.stride(0) if batched else 0
+    if residual is not None:
+        if residual.shape != out.shape or residual.stride() != out.stride():
+            raise ValueError("residual must have the layout of out")
+        args.R = residual.data_ptr()
+    args.bias = _lib.ptr(bias)
+    args.M, args.N, args.K, args.batch = M, N, K, batch
+    args.a_mn, args.b_mn, args.epilogue, args.b_batch_div = int(a_mn), int(b_mn), epilogue, b_batch_div
+    args.lda, args.ldb = a.stride(-2), b.stride(-2)
+    args.strideA = a.stride(0) if batched else 0
+    args.strideB = b.stride(0) if b.dim() == 3 else 0
+    args.alpha, args.softcap = alpha, softcap
+    args.sumsq = _lib.ptr(sumsq)
+    if act is not None:
+        args.act, args.ld_act = act.data_ptr(), act.stride(-2)
+    args.labels, args.pmax, args.psum, args.tgt = map(_lib.ptr, (labels, pmax, psum, tgt))
+    args.lse, args.coef = _lib.ptr(lse), _lib.ptr(coef)
+    args.err = _lib.err_word(a.device).data_ptr()
+    args.max_ctas = max_ctas
+    _lib.check(_lib.lib().opk_gemm(args, _lib.stream_ptr(a.device)), "opk_gemm")
+    return out
+
+
+def linear_fwd(x: torch.Tensor, w: torch.Tensor, *, bias=None, residual=None, out=None) -> torch.Tensor:
+    """``y = x @ w.T (+bias) (+residual)`` with ``x [T, K]``, ``w [N, K]``."""
+    return gemm(x, w, out=out, bias=bias, residual=residual)
+
+
+def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, *, out=None, residual=None) -> torch.Tensor:
+    """``dx = dy @ w`` with ``dy [T, N]``, ``w [N, K]`` (weight consumed in place, no transposed copy)."""
+    return gemm(dy, w, b_mn=True, out=out, residual=residual)
+
+
+def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, *, out=None, sumsq: torch.Tensor | None = None) -> torch.Tensor:
+    """``dw = dy.T @ x`` with ``dy [T, N]``, ``x [T, K]`` -> ``[N, K]``.
+
+    With ``sumsq`` (a float64 scalar tensor) the kernel also adds ``sum(dw**2)`` of the stored bf16 values to it,
+    which is the per-example squared gradient norm contribution of this weight.
+    """
+    epi = EPI_SUMSQ if sumsq is not None else EPI_STORE
+    return gemm(dy, x, a_mn=True, b_mn=True, out=out, epilogue=epi, sumsq=sumsq)
+
+
+def lce_tiles(n_vocab: int) -> int:
+    return _lib.lib().opk_gemm_tiles_n(n_vocab, EPI_LCE_FWD)
