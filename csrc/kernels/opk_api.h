@@ -41,6 +41,101 @@ int opk_gemm_tiles_n(int N, int epilogue);  // number of column tiles the kernel
 int opk_num_sms(void);
 const char* opk_last_error(void);
 
+// ---- normalisation / rotary / activation / embedding (csrc/kernels/elementwise.cu) -------------------------
+// y = x * rsqrt(mean(x^2) + eps) * (w + offset); rstd[T] saved for backward. x, y, w bf16.
+int opk_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int D, float eps, float w_offset,
+                    void* stream);
+// s = x + r (stored to sum_out), then RMSNorm of s.
+int opk_add_rmsnorm_fwd(const void* x, const void* r, const void* w, void* sum_out, void* y, float* rstd, int T, int D,
+                        float eps, float w_offset, void* stream);
+// dx_out = dres (optional) + d(rmsnorm)/dx ; dw[D] (fp32) += sum_t dy * xhat.  dw must be zeroed by the caller.
+int opk_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx_out,
+                    float* dw, int T, int D, float w_offset, void* stream);
+// LayerNorm (GPT-2): y = (x - mean) * rstd * w + b
+int opk_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int T, int D,
+                      float eps, void* stream);
+int opk_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                      const void* dres, void* dx_out, float* dw, float* db, int T, int D, void* stream);
+// In-place rotary embedding on the first n_rot_heads heads of each row (heads are head_dim wide, row pitch ld).
+// cs = [T][head_dim/2][2] fp32 (cos, sin); pos = optional int32 [T] row -> table row. sign = +1 forward, -1 backward.
+int opk_rope(void* qk, const float* cs, const int32_t* pos, int T, int n_rot_heads, int head_dim, int64_t ld,
+             float sign, void* stream);
+// SwiGLU on interleaved (gate, up) columns. fwd: act[T][F]; bwd: dgu[T][2F] from dact[T][F] and gu[T][2F].
+int opk_swiglu_fwd(const void* gu, void* act, int T, int F, void* stream);
+int opk_swiglu_bwd(const void* dact, const void* gu, void* dgu, int T, int F, void* stream);
+// GEGLU (tanh approximation when approx != 0), same interleaved layout.
+int opk_geglu_fwd(const void* gu, void* act, int T, int F, int approx, void* stream);
+int opk_geglu_bwd(const void* dact, const void* gu, void* dgu, int T, int F, int approx, void* stream);
+// GELU (GPT-2 "gelu_new" tanh form): y = gelu(x); backward dx = dy * gelu'(x).
+int opk_gelu_fwd(const void* x, void* y, int64_t n, void* stream);
+int opk_gelu_bwd(const void* dy, const void* x, void* dx, int64_t n, void* stream);
+// out[t] = table[tok[t]] (+ pos_table[t] when given)
+int opk_embedding_fwd(const int32_t* tok, const void* table, const void* pos_table, void* out, int T, int D,
+                      void* stream);
+// Per-example embedding gradient without a dense [V][D] buffer: rows with equal tokens are summed into the row of
+// their first occurrence. first_pos is an int32 [V] scratch that must hold INT32_MAX on entry and is restored.
+// Outputs: rep[T] (first position of the same token), gc[T][D] fp32 (zeroed here), sumsq += sum(bf16(gc)^2).
+int opk_embedding_bwd_compact(const int32_t* tok, const void* dx, int32_t* first_pos, int32_t* rep, float* gc,
+                              double* sumsq, int T, int D, void* stream);
+// acc[tok[t]] += bf16(gc[t] * scale) for the representative rows (rep[t] == t).
+int opk_embedding_accumulate(const int32_t* tok, const int32_t* rep, const float* gc, const float* scale, float* acc,
+                             int T, int D, void* stream);
+// Fused linear-cross-entropy finalisation: lse[t] from the per-tile partials, nll[t] = lse - tgt (0 if ignored).
+int opk_lce_finalize(const float* pmax, const float* psum, const float* tgt, const int32_t* labels, float* lse,
+                     float* nll, int T, int tiles, void* stream);
+// Row-wise cross entropy over materialised logits (bf16 or fp32): nll[t], optional lse[t]; softcap / scale as LCE.
+int opk_cross_entropy_fwd(const void* logits, int is_fp32, const int32_t* labels, float* nll, float* lse, int T, int V,
+                          int64_t ld, float scale, float softcap, void* stream);
+int opk_cross_entropy_bwd(const void* logits, int is_fp32, const int32_t* labels, const float* lse, const float* coef,
+                          void* dlogits, int T, int V, int64_t ld, float scale, float softcap, void* stream);
+// sum(x^2) of a bf16/fp32 vector (x rounded to bf16 first when round_bf16) added to *sumsq (double).
+int opk_sumsq(const void* x, int is_fp32, int round_bf16, int64_t n, double* sumsq, void* stream);
+// out_bf16 = bf16(in_fp32)
+int opk_cast_f32_bf16(const float* in, void* out, int64_t n, void* stream);
+
+// ---- DP clipping / noise / optimizer (csrc/kernels/dp_step.cu) ---------------------------------------------
+// scale = guarded min(1, C / sqrt(sumsq)) (fixed) or R / (sqrt(sumsq) + gamma) (auto); see dp_step.cu.
+// Also: norm_out[0] = sqrt(sumsq), counters[0] += (norm > C), and *sumsq is reset to 0 when reset != 0.
+int opk_clip_scale(double* sumsq, float clip, int mode_auto, float gamma, int n_leaves, int64_t widest_leaf,
+                   float* scale_out, float* norm_out, int32_t* counters, int reset, void* stream);
+// acc[i] += float(bf16(float(g[i]) * scale)) with bf16 subnormals that rounded up flushed to zero.
+int opk_clip_accumulate(const void* g, const float* scale, float* acc, int64_t n, void* stream);
+// Gaussian noise from Philox4x32-10: out[i] (+)= sigma * N(0,1)_{key, stream, step, offset + i}.
+int opk_philox_normal(float* out, int64_t n, uint64_t seed, uint32_t stream_id, uint32_t step, uint64_t offset,
+                      float sigma, int accumulate, void* stream);
+
+typedef struct OpkDpStepArgs {
+  // gradient sources: n_src buffers (this rank's and its peers') of the fp32 clipped-gradient sum, all same layout
+  const float* const* grad_src;  // device array of n_src pointers (element 0.. = ranks in rank order)
+  int32_t n_src;
+  int64_t shard_begin;   // first element of the global flat parameter vector owned by this rank
+  int64_t shard_len;     // number of owned elements
+  float inv_batch;       // 1 / normalize_by
+  float sigma;           // noise std in the normalised units (noise_multiplier * C / B)
+  uint64_t seed;         // RngKey.seed of the step key
+  uint32_t stream_id;    // Philox stream (0 = gradient noise)
+  uint32_t step;
+  // optimizer state for the shard (length shard_len)
+  float* m;
+  float* v;
+  float* master;         // optional fp32 master weights for the shard (may be NULL)
+  // parameter outputs: n_dst full-size bf16 parameter buffers (own + peers); shard is written at shard_begin
+  void* const* param_dst;
+  int32_t n_dst;
+  const void* param_src; // this rank's bf16 parameters (full-size), read when master == NULL
+  float lr, beta1, beta2, eps, weight_decay;
+  float bc1, bc2;        // 1 - beta^t
+  float phi_hat;         // bias-corrected noise second moment (0 disables the correction)
+  int32_t zero_grad;     // zero this rank's shard region in every grad_src after reading
+  // optional correlated-noise (BLT) state for DP-FTRL: nbuf buffers of shard_len fp32
+  float* blt_state;
+  int32_t blt_nbuf;
+  const float* blt_decay;  // device [nbuf]
+  const float* blt_scale;  // device [nbuf]
+  int32_t sgd_mode;      // 1: plain SGD update p -= lr * g (no moments)
+} OpkDpStepArgs;
+int opk_dp_step(const OpkDpStepArgs* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
