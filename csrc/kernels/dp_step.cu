@@ -1,0 +1,307 @@
+// Differential-privacy step kernels for sm_100a:
+//   * guarded clip scale from a per-example squared norm (conservative rounding: the stored clipped
+//     gradient never exceeds the clipping norm),
+//   * clipped accumulation  acc += bf16(g * scale),
+//   * counter-based Philox4x32-10 Gaussian noise indexed by the global element offset, so every
+//     sharding of the parameter vector draws the same global noise tensor exactly once,
+//   * the fused step: reduce-scatter of the clipped-gradient sums over peer memory (plain P2P loads),
+//     normalisation, noise (optionally correlated through a buffered-linear-Toeplitz state), DP-AdamW with
+//     noise bias correction, and the all-gather of the updated bf16 parameters as P2P stores.
+#include "opk_api.h"
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+namespace {
+
+#define OPK_LAUNCH_CHECK()                                   \
+  do {                                                       \
+    cudaError_t e__ = cudaGetLastError();                    \
+    if (e__ != cudaSuccess) return (int)e__;                 \
+  } while (0)
+
+// ------------------------------------------------------------------------------------------- Philox4x32-10
+struct U4 { uint32_t x, y, z, w; };
+__host__ __device__ __forceinline__ U4 philox4x32_10(U4 c, uint32_t k0, uint32_t k1) {
+  const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t p0 = (uint64_t)M0 * c.x, p1 = (uint64_t)M1 * c.z;
+    U4 n;
+    n.x = (uint32_t)(p1 >> 32) ^ c.y ^ k0;
+    n.y = (uint32_t)p1;
+    n.z = (uint32_t)(p0 >> 32) ^ c.w ^ k1;
+    n.w = (uint32_t)p0;
+    c = n;
+    k0 += W0;
+    k1 += W1;
+  }
+  return c;
+}
+// Four standard normals for the aligned group of four elements with index q = element / 4.
+__device__ __forceinline__ void normal4(uint64_t q, uint64_t seed, uint32_t stream_id, uint32_t step, float (&z)[4]) {
+  U4 c{(uint32_t)q, (uint32_t)(q >> 32), step, stream_id};
+  const U4 r = philox4x32_10(c, (uint32_t)seed, (uint32_t)(seed >> 32));
+  const float k = 2.3283064365386963e-10f;  // 2^-32
+  const float u1 = ((float)r.x + 1.0f) * k, u2 = (float)r.y * k;
+  const float u3 = ((float)r.z + 1.0f) * k, u4 = (float)r.w * k;
+  const float ra = sqrtf(-2.0f * logf(fminf(u1, 1.0f))), rb = sqrtf(-2.0f * logf(fminf(u3, 1.0f)));
+  float s, co;
+  sincospif(2.0f * u2, &s, &co);
+  z[0] = ra * co;
+  z[1] = ra * s;
+  sincospif(2.0f * u4, &s, &co);
+  z[2] = rb * co;
+  z[3] = rb * s;
+}
+
+__global__ void philox_normal_kernel(float* __restrict__ out, long long n, uint64_t seed, uint32_t stream_id,
+                                     uint32_t step, uint64_t offset, float sigma, int accumulate) {
+  // thread handles one aligned quad of the GLOBAL index space; elements outside [offset, offset+n) are skipped
+  const uint64_t q0 = offset >> 2;
+  const uint64_t q1 = (offset + (uint64_t)n + 3) >> 2;
+  for (uint64_t q = q0 + blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; q < q1; q += (uint64_t)gridDim.x * blockDim.x) {
+    float z[4];
+    normal4(q, seed, stream_id, step, z);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint64_t e = q * 4 + j;
+      if (e >= offset && e < offset + (uint64_t)n) {
+        const long long i = (long long)(e - offset);
+        out[i] = accumulate ? out[i] + sigma * z[j] : sigma * z[j];
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------- clip scale
+// Conservative clip factor (fixed clipping): the factor is shrunk by the worst-case rounding of the norm
+// accumulation, of the fp32 multiply and of the bf16 store, so that the norm of the *stored* clipped gradient
+// is <= clip. AUTO-S (mode_auto): R / (norm + gamma) with the same guard and no clamp to one.
+__global__ void clip_scale_kernel(double* sumsq, float clip, int mode_auto, float gamma, int n_leaves,
+                                  long long widest_leaf, float* scale_out, float* norm_out, int* counters, int reset) {
+  const double sq = *sumsq;
+  if (reset) *sumsq = 0.0;
+  const double norm = sqrt(sq > 0.0 ? sq : 0.0);
+  if (norm_out) *norm_out = (float)norm;
+  const double c = clip > 0.f ? (double)clip : 0.0;
+  double ratio;
+  if (mode_auto) ratio = c / (norm + (double)gamma);
+  else ratio = norm > 0.0 ? c / norm : INFINITY;
+  if (counters && !mode_auto && norm > c) atomicAdd(counters, 1);
+  // unit roundoffs
+  const double u_acc = 1.1920928955078125e-07 / 2.0;   // fp32
+  const double u_sq = 2.220446049250313e-16 / 2.0;     // fp64
+  const double n_red = widest_leaf > 4096 ? 2048.0 + ceil((double)widest_leaf / 2048.0) : (double)widest_leaf;
+  // the tile epilogues add 256 squares per thread in fp32 plus a 5-level shuffle tree before going to fp64
+  const double tile_slack = 264.0 * u_acc;
+  const double roundoff = (u_acc + ((double)(n_leaves > 1 ? n_leaves : 1) + n_red) * u_sq + tile_slack) / 2.0;
+  const double store_eps = 0.0078125, mult_eps = 1.1920928955078125e-07;  // bf16 store, fp32 multiply
+  const double rounding = store_eps / 2.0 + mult_eps;
+  double s = ratio * (1.0 - rounding - 2.0 * roundoff) - 1.1754943508222875e-38 * store_eps;
+  if (!mode_auto && s > 1.0) s = 1.0;
+  if (!isfinite(s)) s = (!mode_auto && ratio > 0) ? 1.0 : 0.0;
+  if (s < 0.0) s = 0.0;
+  if (clip <= 0.f) s = 0.0;
+  // round the fp32 factor toward zero so the cast itself cannot enlarge it
+  float sf = (float)s;
+  if ((double)sf > s) sf = nextafterf(sf, 0.0f);
+  *scale_out = sf;
+}
+
+struct alignas(16) bf16x8 { __nv_bfloat162 h[4]; };
+
+__device__ __forceinline__ float clip_store(float g, float s) {
+  const float scaled = g * s;
+  float stored = __bfloat162float(__float2bfloat16(scaled));
+  // a value that rounded *up* into (or within) the subnormal range would break the bound: flush it
+  if (fabsf(stored) <= 1.1754943508222875e-38f && fabsf(stored) > fabsf(scaled)) stored = 0.f;
+  return stored;
+}
+
+__global__ void __launch_bounds__(256) clip_accumulate_kernel(const bf16x8* __restrict__ g, const float* __restrict__ scale,
+                                                              float4* __restrict__ acc, long long nvec, int overwrite) {
+  const float s = *scale;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < nvec; i += (long long)gridDim.x * 256) {
+    const bf16x8 v = g[i];
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = __bfloat1622float2(v.h[j]);
+      f[2 * j] = t.x;
+      f[2 * j + 1] = t.y;
+    }
+    float4 a0, a1;
+    if (overwrite) {
+      a0 = make_float4(0.f, 0.f, 0.f, 0.f);
+      a1 = a0;
+    } else {
+      a0 = acc[2 * i];
+      a1 = acc[2 * i + 1];
+    }
+    a0.x += clip_store(f[0], s); a0.y += clip_store(f[1], s); a0.z += clip_store(f[2], s); a0.w += clip_store(f[3], s);
+    a1.x += clip_store(f[4], s); a1.y += clip_store(f[5], s); a1.z += clip_store(f[6], s); a1.w += clip_store(f[7], s);
+    acc[2 * i] = a0;
+    acc[2 * i + 1] = a1;
+  }
+}
+__global__ void clip_accumulate_tail_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ scale,
+                                            float* __restrict__ acc, long long begin, long long n, int overwrite) {
+  const float s = *scale;
+  const long long i = begin + blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i < n) acc[i] = (overwrite ? 0.f : acc[i]) + clip_store(__bfloat162float(g[i]), s);
+}
+
+// ------------------------------------------------------------------------------------------- fused DP step
+struct StepParams {
+  OpkDpStepArgs a;
+};
+
+constexpr int MAX_PEERS = 16;
+struct PeerTable {
+  const float* grad[MAX_PEERS];
+  __nv_bfloat16* param[MAX_PEERS];
+};
+
+__global__ void __launch_bounds__(256) dp_step_kernel(const OpkDpStepArgs a, const PeerTable pt) {
+  // Each thread owns aligned quads of the shard; shard_begin is a multiple of 4 (checked on the host).
+  const long long nq = (a.shard_len + 3) >> 2;
+  for (long long q = blockIdx.x * 256ll + threadIdx.x; q < nq; q += (long long)gridDim.x * 256) {
+    const long long i0 = q << 2;
+    const long long e0 = a.shard_begin + i0;
+    const int cnt = (int)((a.shard_len - i0) < 4 ? (a.shard_len - i0) : 4);
+    float g[4] = {0.f, 0.f, 0.f, 0.f};
+    if (cnt == 4) {
+      // reduce-scatter: sum the owned quad over every rank's buffer (peer reads travel over NVLink)
+#pragma unroll 4
+      for (int r = 0; r < a.n_src; ++r) {
+        const float4 v = *reinterpret_cast<const float4*>(pt.grad[r] + e0);
+        g[0] += v.x; g[1] += v.y; g[2] += v.z; g[3] += v.w;
+      }
+    } else {
+      for (int r = 0; r < a.n_src; ++r)
+        for (int j = 0; j < cnt; ++j) g[j] += pt.grad[r][e0 + j];
+    }
+    float z[4] = {0.f, 0.f, 0.f, 0.f};
+    if (a.sigma != 0.f) normal4((uint64_t)e0 >> 2, a.seed, a.stream_id, a.step, z);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j >= cnt) break;
+      const long long i = i0 + j;
+      float noise = z[j];
+      if (a.blt_nbuf > 0) {
+        // streaming multiply by C^{-1} of a buffered linear Toeplitz factor: xhat = z - <scale, state>;
+        // state_k = decay_k * state_k + xhat
+        float rd = 0.f;
+        for (int k = 0; k < a.blt_nbuf; ++k) rd += a.blt_scale[k] * a.blt_state[(long long)k * a.shard_len + i];
+        noise = z[j] - rd;
+        for (int k = 0; k < a.blt_nbuf; ++k) {
+          float* sp = &a.blt_state[(long long)k * a.shard_len + i];
+          *sp = a.blt_decay[k] * (*sp) + noise;
+        }
+      }
+      const float grad = g[j] * a.inv_batch + a.sigma * noise;
+      float p_old;
+      if (a.master) p_old = a.master[i];
+      else p_old = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.param_src)[e0 + j]);
+      float upd;
+      if (a.sgd_mode) {
+        upd = grad + a.weight_decay * p_old;
+      } else {
+        const float m = a.beta1 * a.m[i] + (1.f - a.beta1) * grad;
+        const float v = a.beta2 * a.v[i] + (1.f - a.beta2) * grad * grad;
+        a.m[i] = m;
+        a.v[i] = v;
+        const float mh = m / a.bc1, vh = v / a.bc2;
+        const float d = vh - a.phi_hat;
+        const float den = sqrtf(d > 0.f ? d : vh) + a.eps;
+        upd = mh / den + a.weight_decay * p_old;
+      }
+      const float p_new = p_old - a.lr * upd;
+      if (a.master) a.master[i] = p_new;
+      g[j] = p_new;
+    }
+    // all-gather: write the updated bf16 quad into every rank's parameter buffer
+    if (cnt == 4) {
+      uint2 o;
+      __nv_bfloat162 lo = __floats2bfloat162_rn(g[0], g[1]), hi = __floats2bfloat162_rn(g[2], g[3]);
+      o.x = *reinterpret_cast<uint32_t*>(&lo);
+      o.y = *reinterpret_cast<uint32_t*>(&hi);
+#pragma unroll 4
+      for (int r = 0; r < a.n_dst; ++r) *reinterpret_cast<uint2*>(pt.param[r] + e0) = o;
+    } else {
+      for (int r = 0; r < a.n_dst; ++r)
+        for (int j = 0; j < cnt; ++j) pt.param[r][e0 + j] = __float2bfloat16(g[j]);
+    }
+    if (a.zero_grad) {
+      if (cnt == 4) *reinterpret_cast<float4*>(const_cast<float*>(pt.grad[0]) + e0) = make_float4(0.f, 0.f, 0.f, 0.f);
+      else for (int j = 0; j < cnt; ++j) const_cast<float*>(pt.grad[0])[e0 + j] = 0.f;
+    }
+  }
+}
+
+inline int grid_for(long long n, int block, int cap_blocks) {
+  long long g = (n + block - 1) / block;
+  if (g > cap_blocks) g = cap_blocks;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+}  // namespace
+
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+
+extern "C" int opk_philox_normal(float* out, int64_t n, uint64_t seed, uint32_t stream_id, uint32_t step,
+                                 uint64_t offset, float sigma, int accumulate, void* stream) {
+  if (n <= 0) return 0;
+  philox_normal_kernel<<<grid_for((n + 3) / 4 + 1, 256, 148 * 8), 256, 0, ST(stream)>>>(out, n, seed, stream_id, step,
+                                                                                      offset, sigma, accumulate);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int opk_clip_scale(double* sumsq, float clip, int mode_auto, float gamma, int n_leaves, int64_t widest_leaf,
+                              float* scale_out, float* norm_out, int32_t* counters, int reset, void* stream) {
+  clip_scale_kernel<<<1, 1, 0, ST(stream)>>>(sumsq, clip, mode_auto, gamma, n_leaves, widest_leaf, scale_out, norm_out,
+                                            counters, reset);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int opk_clip_accumulate(const void* g, const float* scale, float* acc, int64_t n, void* stream);
+extern "C" int opk_clip_accumulate2(const void* g, const float* scale, float* acc, int64_t n, int overwrite,
+                                    void* stream) {
+  if (n <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(g) & 15) || (reinterpret_cast<uintptr_t>(acc) & 15)) return -1;
+  const long long nvec = n >> 3;
+  if (nvec > 0)
+    clip_accumulate_kernel<<<grid_for(nvec, 256, 148 * 16), 256, 0, ST(stream)>>>(
+        reinterpret_cast<const bf16x8*>(g), scale, reinterpret_cast<float4*>(acc), nvec, overwrite);
+  const long long tail = n - (nvec << 3);
+  if (tail > 0)
+    clip_accumulate_tail_kernel<<<1, 32, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(g), scale, acc,
+                                                         nvec << 3, n, overwrite);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_clip_accumulate(const void* g, const float* scale, float* acc, int64_t n, void* stream) {
+  return opk_clip_accumulate2(g, scale, acc, n, 0, stream);
+}
+
+// grad_src / param_dst are HOST arrays of device pointers here (copied into the kernel's parameter space).
+extern "C" int opk_dp_step(const OpkDpStepArgs* args, void* stream) {
+  if (!args || args->shard_len <= 0) return 0;
+  if (args->n_src < 1 || args->n_src > MAX_PEERS || args->n_dst < 0 || args->n_dst > MAX_PEERS) return -1;
+  if (args->shard_begin & 3) return -2;
+  PeerTable pt;
+  for (int r = 0; r < MAX_PEERS; ++r) {
+    pt.grad[r] = r < args->n_src ? args->grad_src[r] : nullptr;
+    pt.param[r] = r < args->n_dst ? reinterpret_cast<__nv_bfloat16*>(args->param_dst[r]) : nullptr;
+  }
+  const long long nq = (args->shard_len + 3) >> 2;
+  dp_step_kernel<<<grid_for(nq, 256, 148 * 8), 256, 0, ST(stream)>>>(*args, pt);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}

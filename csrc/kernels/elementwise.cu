@@ -1,0 +1,727 @@
+// Bandwidth-bound model kernels for sm_100a: RMSNorm / LayerNorm, rotary embedding, SwiGLU / GEGLU / GELU,
+// embedding gather and per-example compact embedding gradient, cross-entropy helpers.
+// All activations are bf16 in memory with fp32 arithmetic; rows are processed with 16-byte vector accesses.
+#include "opk_api.h"
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <limits.h>
+#include <math.h>
+#include <stdio.h>
+
+namespace {
+
+#define OPK_LAUNCH_CHECK()                                   \
+  do {                                                       \
+    cudaError_t e__ = cudaGetLastError();                    \
+    if (e__ != cudaSuccess) return (int)e__;                 \
+  } while (0)
+
+struct alignas(16) bf16x8 {
+  __nv_bfloat162 h[4];
+};
+
+__device__ __forceinline__ void unpack8(const bf16x8& v, float (&f)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(v.h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ bf16x8 pack8(const float (&f)[8]) {
+  bf16x8 v;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v.h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+
+template <int NT>
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float r = (threadIdx.x < NT / 32) ? sh[threadIdx.x] : 0.f;
+  if (w == 0) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    if (l == 0) sh[0] = r;
+  }
+  __syncthreads();
+  return sh[0];
+}
+
+constexpr int NT = 256;
+
+// ------------------------------------------------------------------------------------------- RMSNorm
+template <bool ADD>
+__global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                         const __nv_bfloat16* __restrict__ r,
+                                                         const __nv_bfloat16* __restrict__ w,
+                                                         __nv_bfloat16* __restrict__ sum_out,
+                                                         __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
+                                                         int D, float eps, float w_off) {
+  __shared__ float sh[32];
+  const long long row = blockIdx.x;
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * D);
+  const bf16x8* rr = ADD ? reinterpret_cast<const bf16x8*>(r + row * D) : nullptr;
+  bf16x8* sr = ADD ? reinterpret_cast<bf16x8*>(sum_out + row * D) : nullptr;
+  const int nv = D >> 3;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < nv; i += NT) {
+    float f[8];
+    unpack8(xr[i], f);
+    if (ADD) {
+      float g[8];
+      unpack8(rr[i], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += g[j];
+      bf16x8 s = pack8(f);
+      sr[i] = s;
+      unpack8(s, f);  // normalise the stored (rounded) residual stream
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  }
+  const float tot = block_sum<NT>(ss, sh);
+  const float rs = rsqrtf(tot / (float)D + eps);
+  if (threadIdx.x == 0 && rstd) rstd[row] = rs;
+  const bf16x8* src = ADD ? reinterpret_cast<const bf16x8*>(sum_out + row * D) : xr;
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * D);
+  for (int i = threadIdx.x; i < nv; i += NT) {
+    float f[8], g[8];
+    unpack8(src[i], f);
+    unpack8(wr[i], g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = f[j] * rs * (g[j] + w_off);
+    yr[i] = pack8(f);
+  }
+}
+
+// One CTA walks rows blockIdx.x, +gridDim.x, ...; column ownership is fixed per thread so the weight gradient
+// partial stays in registers until a single atomicAdd per column at the end.
+constexpr int MAX_COL_ITERS = 8;  // D <= 8 * 2048
+__global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                         const __nv_bfloat16* __restrict__ x,
+                                                         const __nv_bfloat16* __restrict__ w,
+                                                         const float* __restrict__ rstd,
+                                                         const __nv_bfloat16* __restrict__ dres,
+                                                         __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, int T,
+                                                         int D, float w_off) {
+  __shared__ float sh[32];
+  const int nv = D >> 3;
+  float dwp[MAX_COL_ITERS][8];
+#pragma unroll
+  for (int c = 0; c < MAX_COL_ITERS; ++c)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwp[c][j] = 0.f;
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  for (long long row = blockIdx.x; row < T; row += gridDim.x) {
+    const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + row * D);
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * D);
+    const float rs = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int c = 0; c < MAX_COL_ITERS; ++c) {
+      const int i = threadIdx.x + c * NT;
+      if (i < nv) {
+        float g[8], xv[8], wv[8];
+        unpack8(dyr[i], g);
+        unpack8(xr[i], xv);
+        unpack8(wr[i], wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = xv[j] * rs;
+          dwp[c][j] += g[j] * xh;
+          dot += g[j] * (wv[j] + w_off) * xh;
+        }
+      }
+    }
+    const float mean_dot = block_sum<NT>(dot, sh) / (float)D;
+    const bf16x8* drr = dres ? reinterpret_cast<const bf16x8*>(dres + row * D) : nullptr;
+    bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + row * D);
+#pragma unroll
+    for (int c = 0; c < MAX_COL_ITERS; ++c) {
+      const int i = threadIdx.x + c * NT;
+      if (i < nv) {
+        float g[8], xv[8], wv[8], o[8];
+        unpack8(dyr[i], g);
+        unpack8(xr[i], xv);
+        unpack8(wr[i], wv);
+        if (drr) unpack8(drr[i], o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = xv[j] * rs;
+          const float d = rs * (g[j] * (wv[j] + w_off) - xh * mean_dot);
+          o[j] = drr ? o[j] + d : d;
+        }
+        dxr[i] = pack8(o);
+      }
+    }
+  }
+  if (dw) {
+#pragma unroll
+    for (int c = 0; c < MAX_COL_ITERS; ++c) {
+      const int i = threadIdx.x + c * NT;
+      if (i < nv) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) atomicAdd(&dw[i * 8 + j], dwp[c][j]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------- LayerNorm
+__global__ void __launch_bounds__(NT) layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                           const __nv_bfloat16* __restrict__ w,
+                                                           const __nv_bfloat16* __restrict__ b,
+                                                           __nv_bfloat16* __restrict__ y, float* __restrict__ mean,
+                                                           float* __restrict__ rstd, int D, float eps) {
+  __shared__ float sh[32];
+  const long long row = blockIdx.x;
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * D);
+  const int nv = D >> 3;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < nv; i += NT) {
+    float f[8];
+    unpack8(xr[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += f[j];
+  }
+  const float mu = block_sum<NT>(s, sh) / (float)D;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < nv; i += NT) {
+    float f[8];
+    unpack8(xr[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += (f[j] - mu) * (f[j] - mu);
+  }
+  const float rs = rsqrtf(block_sum<NT>(ss, sh) / (float)D + eps);
+  if (threadIdx.x == 0) {
+    if (mean) mean[row] = mu;
+    if (rstd) rstd[row] = rs;
+  }
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  const bf16x8* br = b ? reinterpret_cast<const bf16x8*>(b) : nullptr;
+  bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * D);
+  for (int i = threadIdx.x; i < nv; i += NT) {
+    float f[8], g[8], bb[8];
+    unpack8(xr[i], f);
+    unpack8(wr[i], g);
+    if (br) unpack8(br[i], bb);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = (f[j] - mu) * rs * g[j] + (br ? bb[j] : 0.f);
+    yr[i] = pack8(f);
+  }
+}
+
+__global__ void __launch_bounds__(NT) layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                           const __nv_bfloat16* __restrict__ x,
+                                                           const __nv_bfloat16* __restrict__ w,
+                                                           const float* __restrict__ mean,
+                                                           const float* __restrict__ rstd,
+                                                           const __nv_bfloat16* __restrict__ dres,
+                                                           __nv_bfloat16* __restrict__ dx, float* __restrict__ dw,
+                                                           float* __restrict__ db, int T, int D) {
+  __shared__ float sh[32];
+  const int nv = D >> 3;
+  float dwp[MAX_COL_ITERS][8], dbp[MAX_COL_ITERS][8];
+#pragma unroll
+  for (int c = 0; c < MAX_COL_ITERS; ++c)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { dwp[c][j] = 0.f; dbp[c][j] = 0.f; }
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  for (long long row = blockIdx.x; row < T; row += gridDim.x) {
+    const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + row * D);
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * D);
+    const float rs = rstd[row], mu = mean[row];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < MAX_COL_ITERS; ++c) {
+      const int i = threadIdx.x + c * NT;
+      if (i < nv) {
+        float g[8], xv[8], wv[8];
+        unpack8(dyr[i], g);
+        unpack8(xr[i], xv);
+        unpack8(wr[i], wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = (xv[j] - mu) * rs;
+          dwp[c][j] += g[j] * xh;
+          dbp[c][j] += g[j];
+          const float gw = g[j] * wv[j];
+          s1 += gw;
+          s2 += gw * xh;
+        }
+      }
+    }
+    const float m1 = block_sum<NT>(s1, sh) / (float)D;
+    const float m2 = block_sum<NT>(s2, sh) / (float)D;
+    const bf16x8* drr = dres ? reinterpret_cast<const bf16x8*>(dres + row * D) : nullptr;
+    bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + row * D);
+#pragma unroll
+    for (int c = 0; c < MAX_COL_ITERS; ++c) {
+      const int i = threadIdx.x + c * NT;
+      if (i < nv) {
+        float g[8], xv[8], wv[8], o[8];
+        unpack8(dyr[i], g);
+        unpack8(xr[i], xv);
+        unpack8(wr[i], wv);
+        if (drr) unpack8(drr[i], o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = (xv[j] - mu) * rs;
+          const float d = rs * (g[j] * wv[j] - m1 - xh * m2);
+          o[j] = drr ? o[j] + d : d;
+        }
+        dxr[i] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < MAX_COL_ITERS; ++c) {
+    const int i = threadIdx.x + c * NT;
+    if (i < nv) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (dw) atomicAdd(&dw[i * 8 + j], dwp[c][j]);
+        if (db) atomicAdd(&db[i * 8 + j], dbp[c][j]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------- RoPE
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ qk, const float* __restrict__ cs,
+                            const int* __restrict__ pos, int T, int n_heads, int hd, long long ld, float sign) {
+  const int half = hd >> 1;
+  const long long total = (long long)T * n_heads * half;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int i = idx % half;
+    const long long th = idx / half;
+    const int h = th % n_heads;
+    const long long t = th / n_heads;
+    const long long p = pos ? pos[t] : t;
+    const float c = cs[(p * half + i) * 2], s = cs[(p * half + i) * 2 + 1] * sign;
+    __nv_bfloat16* base = qk + t * ld + (long long)h * hd;
+    const float x1 = __bfloat162float(base[i]), x2 = __bfloat162float(base[i + half]);
+    base[i] = __float2bfloat16(x1 * c - x2 * s);
+    base[i + half] = __float2bfloat16(x2 * c + x1 * s);
+  }
+}
+
+// ------------------------------------------------------------------------------------------- gated activations
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k = 0.7978845608028654f;
+  return 0.5f * x * (1.f + tanhf(k * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float gelu_tanh_grad(float x) {
+  const float k = 0.7978845608028654f;
+  const float u = k * (x + 0.044715f * x * x * x);
+  const float t = tanhf(u);
+  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * k * (1.f + 3.f * 0.044715f * x * x);
+}
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.7071067811865476f)); }
+__device__ __forceinline__ float gelu_erf_grad(float x) {
+  return 0.5f * (1.f + erff(x * 0.7071067811865476f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
+
+// MODE 0 = SwiGLU, 1 = GEGLU exact, 2 = GEGLU tanh
+template <int MODE>
+__device__ __forceinline__ float gate_fn(float g) {
+  return MODE == 0 ? g * sigmoidf_(g) : (MODE == 1 ? gelu_erf(g) : gelu_tanh(g));
+}
+template <int MODE>
+__device__ __forceinline__ float gate_grad(float g) {
+  if (MODE == 0) {
+    const float s = sigmoidf_(g);
+    return s * (1.f + g * (1.f - s));
+  }
+  return MODE == 1 ? gelu_erf_grad(g) : gelu_tanh_grad(g);
+}
+
+template <int MODE>
+__global__ void glu_fwd_kernel(const __nv_bfloat162* __restrict__ gu, __nv_bfloat16* __restrict__ act, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float2 p = __bfloat1622float2(gu[i]);
+    act[i] = __float2bfloat16(gate_fn<MODE>(p.x) * p.y);
+  }
+}
+template <int MODE>
+__global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloat162* __restrict__ gu,
+                               __nv_bfloat162* __restrict__ dgu, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float2 p = __bfloat1622float2(gu[i]);
+    const float d = __bfloat162float(dact[i]);
+    dgu[i] = __floats2bfloat162_rn(d * p.y * gate_grad<MODE>(p.x), d * gate_fn<MODE>(p.x));
+  }
+}
+__global__ void gelu_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    y[i] = __float2bfloat16(gelu_tanh(__bfloat162float(x[i])));
+}
+__global__ void gelu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                __nv_bfloat16* __restrict__ dx, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    dx[i] = __float2bfloat16(__bfloat162float(dy[i]) * gelu_tanh_grad(__bfloat162float(x[i])));
+}
+
+// ------------------------------------------------------------------------------------------- embedding
+__global__ void embedding_fwd_kernel(const int* __restrict__ tok, const __nv_bfloat16* __restrict__ table,
+                                     const __nv_bfloat16* __restrict__ pos_table, __nv_bfloat16* __restrict__ out,
+                                     int D) {
+  const long long t = blockIdx.x;
+  const bf16x8* src = reinterpret_cast<const bf16x8*>(table + (long long)tok[t] * D);
+  const bf16x8* ps = pos_table ? reinterpret_cast<const bf16x8*>(pos_table + t * D) : nullptr;
+  bf16x8* dst = reinterpret_cast<bf16x8*>(out + t * D);
+  for (int i = threadIdx.x; i < (D >> 3); i += blockDim.x) {
+    if (ps) {
+      float a[8], b[8];
+      unpack8(src[i], a);
+      unpack8(ps[i], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] += b[j];
+      dst[i] = pack8(a);
+    } else {
+      dst[i] = src[i];
+    }
+  }
+}
+__global__ void emb_first_pos_kernel(const int* __restrict__ tok, int* __restrict__ first_pos, int T) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < T) atomicMin(&first_pos[tok[t]], t);
+}
+__global__ void emb_scatter_kernel(const int* __restrict__ tok, const __nv_bfloat16* __restrict__ dx,
+                                   const int* __restrict__ first_pos, int* __restrict__ rep, float* __restrict__ gc,
+                                   int D) {
+  const long long t = blockIdx.x;
+  const int r = first_pos[tok[t]];
+  if (threadIdx.x == 0) rep[t] = r;
+  const __nv_bfloat16* src = dx + t * D;
+  float* dst = gc + (long long)r * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) atomicAdd(&dst[d], __bfloat162float(src[d]));
+}
+__global__ void emb_reset_kernel(const int* __restrict__ tok, int* __restrict__ first_pos, int T) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < T) first_pos[tok[t]] = INT_MAX;
+}
+__global__ void emb_accumulate_kernel(const int* __restrict__ tok, const int* __restrict__ rep,
+                                      const float* __restrict__ gc, const float* __restrict__ scale,
+                                      float* __restrict__ acc, int D) {
+  const long long t = blockIdx.x;
+  if (rep[t] != (int)t) return;
+  const float s = *scale;
+  const float* src = gc + t * D;
+  float* dst = acc + (long long)tok[t] * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float g = __bfloat162float(__float2bfloat16(src[d]));            // the stored per-example gradient
+    dst[d] += __bfloat162float(__float2bfloat16(g * s));                   // clipped in storage precision
+  }
+}
+
+// ------------------------------------------------------------------------------------------- reductions
+template <bool FP32, bool ROUND>
+__global__ void __launch_bounds__(NT) sumsq_kernel(const void* __restrict__ x, long long n, double* out) {
+  __shared__ float sh[32];
+  double acc = 0.0;
+  float part = 0.f;
+  int cnt = 0;
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n; i += (long long)gridDim.x * NT) {
+    float v = FP32 ? reinterpret_cast<const float*>(x)[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[i]);
+    if (ROUND) v = __bfloat162float(__float2bfloat16(v));
+    part += v * v;
+    if (++cnt == 64) { acc += (double)part; part = 0.f; cnt = 0; }
+  }
+  acc += (double)part;
+  // fp64 block reduction through two fp32 words would lose bits; reduce doubles with shuffles directly
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  __shared__ double shd[NT / 32];
+  if ((threadIdx.x & 31) == 0) shd[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < NT / 32; ++w) t += shd[w];
+    atomicAdd(out, t);
+  }
+  (void)sh;
+}
+
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    out[i] = __float2bfloat16(in[i]);
+}
+
+// ------------------------------------------------------------------------------------------- cross entropy
+__global__ void lce_finalize_kernel(const float* __restrict__ pmax, const float* __restrict__ psum,
+                                    const float* __restrict__ tgt, const int* __restrict__ labels,
+                                    float* __restrict__ lse, float* __restrict__ nll, int T, int tiles) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= T) return;
+  const float* pm = pmax + (long long)row * tiles;
+  const float* ps = psum + (long long)row * tiles;
+  float m = -INFINITY;
+  for (int i = lane; i < tiles; i += 32) m = fmaxf(m, pm[i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  float s = 0.f;
+  for (int i = lane; i < tiles; i += 32) s += ps[i] * __expf(pm[i] - m);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) {
+    const float l = m + logf(s);
+    lse[row] = l;
+    if (nll) nll[row] = labels[row] >= 0 ? l - tgt[row] : 0.f;
+  }
+}
+
+template <bool FP32>
+__device__ __forceinline__ float load_logit(const void* p, long long i) {
+  return FP32 ? reinterpret_cast<const float*>(p)[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+__device__ __forceinline__ float cap(float z, float scale, float softcap) {
+  z *= scale;
+  return softcap > 0.f ? softcap * tanhf(z / softcap) : z;
+}
+
+template <bool FP32>
+__global__ void __launch_bounds__(NT) ce_fwd_kernel(const void* __restrict__ logits, const int* __restrict__ labels,
+                                                    float* __restrict__ nll, float* __restrict__ lse, int V,
+                                                    long long ld, float scale, float softcap) {
+  __shared__ float sh[32];
+  const long long row = blockIdx.x;
+  const long long base = row * ld;
+  float m = -INFINITY, s = 0.f;
+  for (int i = threadIdx.x; i < V; i += NT) {
+    const float z = cap(load_logit<FP32>(logits, base + i), scale, softcap);
+    const float nm = fmaxf(m, z);
+    s = s * __expf(m - nm) + __expf(z - nm);
+    m = nm;
+  }
+  // combine (m, s) pairs: first the max, then rescaled sums
+  float gm = m;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, o));
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = gm;
+  __syncthreads();
+  float bm = sh[0];
+  for (int w = 1; w < NT / 32; ++w) bm = fmaxf(bm, sh[w]);
+  const float tot = block_sum<NT>(m == -INFINITY ? 0.f : s * __expf(m - bm), sh);
+  if (threadIdx.x == 0) {
+    const float l = bm + logf(tot);
+    if (lse) lse[row] = l;
+    const int lab = labels[row];
+    nll[row] = lab >= 0 ? l - cap(load_logit<FP32>(logits, base + lab), scale, softcap) : 0.f;
+  }
+}
+
+template <bool FP32>
+__global__ void __launch_bounds__(NT) ce_bwd_kernel(const void* __restrict__ logits, const int* __restrict__ labels,
+                                                    const float* __restrict__ lse, const float* __restrict__ coef,
+                                                    void* __restrict__ dlogits, int V, long long ld, float scale,
+                                                    float softcap) {
+  const long long row = blockIdx.x;
+  const long long base = row * ld;
+  const float l = lse[row], c = coef[row];
+  const int lab = labels[row];
+  for (int i = threadIdx.x; i < V; i += NT) {
+    const float raw = load_logit<FP32>(logits, base + i) * scale;
+    float z = raw, dz = scale;
+    if (softcap > 0.f) {
+      const float th = tanhf(raw / softcap);
+      z = softcap * th;
+      dz = scale * (1.f - th * th);
+    }
+    const float g = (__expf(z - l) - (i == lab ? 1.f : 0.f)) * c * dz;
+    if (FP32) reinterpret_cast<float*>(dlogits)[base + i] = g;
+    else reinterpret_cast<__nv_bfloat16*>(dlogits)[base + i] = __float2bfloat16(g);
+  }
+}
+
+inline int grid_for(long long n, int block, int cap_blocks = 148 * 16) {
+  long long g = (n + block - 1) / block;
+  if (g > cap_blocks) g = cap_blocks;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+}  // namespace
+
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+#define BF(p) reinterpret_cast<const __nv_bfloat16*>(p)
+#define BFM(p) reinterpret_cast<__nv_bfloat16*>(p)
+
+extern "C" int opk_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int D, float eps,
+                               float w_offset, void* stream) {
+  if (T <= 0) return 0;
+  if (D % 8) return -1;
+  rmsnorm_fwd_kernel<false><<<T, NT, 0, ST(stream)>>>(BF(x), nullptr, BF(w), nullptr, BFM(y), rstd, D, eps, w_offset);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_add_rmsnorm_fwd(const void* x, const void* r, const void* w, void* sum_out, void* y, float* rstd,
+                                   int T, int D, float eps, float w_offset, void* stream) {
+  if (T <= 0) return 0;
+  if (D % 8) return -1;
+  rmsnorm_fwd_kernel<true><<<T, NT, 0, ST(stream)>>>(BF(x), BF(r), BF(w), BFM(sum_out), BFM(y), rstd, D, eps, w_offset);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
+                               void* dx_out, float* dw, int T, int D, float w_offset, void* stream) {
+  if (T <= 0) return 0;
+  if (D % 8 || D > MAX_COL_ITERS * NT * 8) return -1;
+  const int grid = T < 148 * 2 ? T : 148 * 2;
+  rmsnorm_bwd_kernel<<<grid, NT, 0, ST(stream)>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx_out), dw, T, D, w_offset);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int T,
+                                 int D, float eps, void* stream) {
+  if (T <= 0) return 0;
+  if (D % 8) return -1;
+  layernorm_fwd_kernel<<<T, NT, 0, ST(stream)>>>(BF(x), BF(w), BF(b), BFM(y), mean, rstd, D, eps);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                                 const void* dres, void* dx_out, float* dw, float* db, int T, int D, void* stream) {
+  if (T <= 0) return 0;
+  if (D % 8 || D > MAX_COL_ITERS * NT * 8) return -1;
+  const int grid = T < 148 * 2 ? T : 148 * 2;
+  layernorm_bwd_kernel<<<grid, NT, 0, ST(stream)>>>(BF(dy), BF(x), BF(w), mean, rstd, BF(dres), BFM(dx_out), dw, db, T, D);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_rope(void* qk, const float* cs, const int32_t* pos, int T, int n_rot_heads, int head_dim, int64_t ld,
+                        float sign, void* stream) {
+  const long long n = (long long)T * n_rot_heads * (head_dim / 2);
+  if (n <= 0) return 0;
+  rope_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(BFM(qk), cs, pos, T, n_rot_heads, head_dim, ld, sign);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_swiglu_fwd(const void* gu, void* act, int T, int F, void* stream) {
+  const long long n = (long long)T * F;
+  if (n <= 0) return 0;
+  glu_fwd_kernel<0><<<grid_for(n, 256), 256, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat162*>(gu), BFM(act), n);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_swiglu_bwd(const void* dact, const void* gu, void* dgu, int T, int F, void* stream) {
+  const long long n = (long long)T * F;
+  if (n <= 0) return 0;
+  glu_bwd_kernel<0><<<grid_for(n, 256), 256, 0, ST(stream)>>>(BF(dact), reinterpret_cast<const __nv_bfloat162*>(gu),
+                                                             reinterpret_cast<__nv_bfloat162*>(dgu), n);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_geglu_fwd(const void* gu, void* act, int T, int F, int approx, void* stream) {
+  const long long n = (long long)T * F;
+  if (n <= 0) return 0;
+  if (approx) glu_fwd_kernel<2><<<grid_for(n, 256), 256, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat162*>(gu), BFM(act), n);
+  else glu_fwd_kernel<1><<<grid_for(n, 256), 256, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat162*>(gu), BFM(act), n);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_geglu_bwd(const void* dact, const void* gu, void* dgu, int T, int F, int approx, void* stream) {
+  const long long n = (long long)T * F;
+  if (n <= 0) return 0;
+  if (approx)
+    glu_bwd_kernel<2><<<grid_for(n, 256), 256, 0, ST(stream)>>>(BF(dact), reinterpret_cast<const __nv_bfloat162*>(gu),
+                                                               reinterpret_cast<__nv_bfloat162*>(dgu), n);
+  else
+    glu_bwd_kernel<1><<<grid_for(n, 256), 256, 0, ST(stream)>>>(BF(dact), reinterpret_cast<const __nv_bfloat162*>(gu),
+                                                               reinterpret_cast<__nv_bfloat162*>(dgu), n);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_gelu_fwd(const void* x, void* y, int64_t n, void* stream) {
+  if (n <= 0) return 0;
+  gelu_fwd_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(BF(x), BFM(y), n);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_gelu_bwd(const void* dy, const void* x, void* dx, int64_t n, void* stream) {
+  if (n <= 0) return 0;
+  gelu_bwd_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(BF(dy), BF(x), BFM(dx), n);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_embedding_fwd(const int32_t* tok, const void* table, const void* pos_table, void* out, int T, int D,
+                                 void* stream) {
+  if (T <= 0) return 0;
+  if (D % 8) return -1;
+  embedding_fwd_kernel<<<T, 128, 0, ST(stream)>>>(tok, BF(table), BF(pos_table), BFM(out), D);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_embedding_bwd_compact(const int32_t* tok, const void* dx, int32_t* first_pos, int32_t* rep,
+                                         float* gc, double* sumsq, int T, int D, void* stream) {
+  if (T <= 0) return 0;
+  cudaStream_t st = ST(stream);
+  cudaError_t e = cudaMemsetAsync(gc, 0, sizeof(float) * (size_t)T * D, st);
+  if (e != cudaSuccess) return (int)e;
+  emb_first_pos_kernel<<<(T + 255) / 256, 256, 0, st>>>(tok, first_pos, T);
+  emb_scatter_kernel<<<T, 256, 0, st>>>(tok, BF(dx), first_pos, rep, gc, D);
+  emb_reset_kernel<<<(T + 255) / 256, 256, 0, st>>>(tok, first_pos, T);
+  if (sumsq) sumsq_kernel<true, true><<<grid_for((long long)T * D, NT, 148 * 4), NT, 0, st>>>(gc, (long long)T * D, sumsq);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_embedding_accumulate(const int32_t* tok, const int32_t* rep, const float* gc, const float* scale,
+                                        float* acc, int T, int D, void* stream) {
+  if (T <= 0) return 0;
+  emb_accumulate_kernel<<<T, 256, 0, ST(stream)>>>(tok, rep, gc, scale, acc, D);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_lce_finalize(const float* pmax, const float* psum, const float* tgt, const int32_t* labels,
+                                float* lse, float* nll, int T, int tiles, void* stream) {
+  if (T <= 0) return 0;
+  lce_finalize_kernel<<<(T + 7) / 8, 256, 0, ST(stream)>>>(pmax, psum, tgt, labels, lse, nll, T, tiles);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_cross_entropy_fwd(const void* logits, int is_fp32, const int32_t* labels, float* nll, float* lse,
+                                     int T, int V, int64_t ld, float scale, float softcap, void* stream) {
+  if (T <= 0) return 0;
+  if (is_fp32) ce_fwd_kernel<true><<<T, NT, 0, ST(stream)>>>(logits, labels, nll, lse, V, ld, scale, softcap);
+  else ce_fwd_kernel<false><<<T, NT, 0, ST(stream)>>>(logits, labels, nll, lse, V, ld, scale, softcap);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_cross_entropy_bwd(const void* logits, int is_fp32, const int32_t* labels, const float* lse,
+                                     const float* coef, void* dlogits, int T, int V, int64_t ld, float scale,
+                                     float softcap, void* stream) {
+  if (T <= 0) return 0;
+  if (is_fp32) ce_bwd_kernel<true><<<T, NT, 0, ST(stream)>>>(logits, labels, lse, coef, dlogits, V, ld, scale, softcap);
+  else ce_bwd_kernel<false><<<T, NT, 0, ST(stream)>>>(logits, labels, lse, coef, dlogits, V, ld, scale, softcap);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_sumsq(const void* x, int is_fp32, int round_bf16, int64_t n, double* sumsq, void* stream) {
+  if (n <= 0) return 0;
+  const int g = grid_for(n, NT, 148 * 8);
+  if (is_fp32) {
+    if (round_bf16) sumsq_kernel<true, true><<<g, NT, 0, ST(stream)>>>(x, n, sumsq);
+    else sumsq_kernel<true, false><<<g, NT, 0, ST(stream)>>>(x, n, sumsq);
+  } else {
+    sumsq_kernel<false, false><<<g, NT, 0, ST(stream)>>>(x, n, sumsq);
+  }
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_cast_f32_bf16(const float* in, void* out, int64_t n, void* stream) {
+  if (n <= 0) return 0;
+  cast_f32_bf16_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(in, BFM(out), n);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}

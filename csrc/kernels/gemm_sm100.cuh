@@ -202,8 +202,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ epilogue (4 warps, one TMEM lane quadrant each)
     const int quad = warp & 3;
     int it = 0;
-    float sq_acc = 0.f;
-    int sq_batch = -1;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
       const int b = tile / per_batch;
       const int r = tile - b * per_batch;
@@ -226,17 +224,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
                           (((b * p.strideC) & 7) == 0);
 
-      if (EPI == EPI_SUMSQ && sq_batch != b) {
-        // flush the running sum when the batch entry changes
-        if (sq_batch >= 0) {
-          float w = sq_acc;
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
-          if (lane == 0) atomicAdd(&p.sumsq[sq_batch], (double)w);
-        }
-        sq_acc = 0.f;
-        sq_batch = b;
-      }
+      float sq_acc = 0.f;  // per-tile fp32 partial (256 squares per thread), flushed to fp64 below
 
       // LCE forward running statistics for this (row, column tile)
       float run_max = -INFINITY, run_sum = 0.f;
@@ -358,12 +346,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[buf]);
-    }
-    if (EPI == EPI_SUMSQ && sq_batch >= 0) {
-      float w = sq_acc;
+      if (EPI == EPI_SUMSQ) {
+        float w = sq_acc;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
-      if (lane == 0) atomicAdd(&p.sumsq[sq_batch], (double)w);
+        for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
+        if (lane == 0) atomicAdd(&p.sumsq[b], (double)w);
+      }
     }
   }
 

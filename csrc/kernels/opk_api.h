@@ -100,6 +100,8 @@ int opk_clip_scale(double* sumsq, float clip, int mode_auto, float gamma, int n_
                    float* scale_out, float* norm_out, int32_t* counters, int reset, void* stream);
 // acc[i] += float(bf16(float(g[i]) * scale)) with bf16 subnormals that rounded up flushed to zero.
 int opk_clip_accumulate(const void* g, const float* scale, float* acc, int64_t n, void* stream);
+// Same with overwrite != 0 meaning acc = bf16(g * scale) (first example of a step: no separate zeroing pass).
+int opk_clip_accumulate2(const void* g, const float* scale, float* acc, int64_t n, int overwrite, void* stream);
 // Gaussian noise from Philox4x32-10: out[i] (+)= sigma * N(0,1)_{key, stream, step, offset + i}.
 int opk_philox_normal(float* out, int64_t n, uint64_t seed, uint32_t stream_id, uint32_t step, uint64_t offset,
                       float sigma, int accumulate, void* stream);

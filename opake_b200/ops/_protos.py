@@ -1,4 +1,48 @@
 """ctypes prototypes of the non-GEMM entry points of libopake_kernels.so (see csrc/kernels/opk_api.h)."""
-from ctypes import c_double, c_float, c_int32, c_int64, c_uint64, c_void_p
+from ctypes import POINTER, Structure, c_float, c_int32, c_int64, c_uint32, c_uint64, c_void_p
 
-PROTOTYPES: dict = {}
+P, I, L, F = c_void_p, c_int32, c_int64, c_float
+
+
+class DpStepArgs(Structure):
+    _fields_ = [
+        ("grad_src", POINTER(c_void_p)), ("n_src", c_int32),
+        ("shard_begin", c_int64), ("shard_len", c_int64),
+        ("inv_batch", c_float), ("sigma", c_float),
+        ("seed", c_uint64), ("stream_id", c_uint32), ("step", c_uint32),
+        ("m", c_void_p), ("v", c_void_p), ("master", c_void_p),
+        ("param_dst", POINTER(c_void_p)), ("n_dst", c_int32), ("param_src", c_void_p),
+        ("lr", c_float), ("beta1", c_float), ("beta2", c_float), ("eps", c_float), ("weight_decay", c_float),
+        ("bc1", c_float), ("bc2", c_float), ("phi_hat", c_float), ("zero_grad", c_int32),
+        ("blt_state", c_void_p), ("blt_nbuf", c_int32), ("blt_decay", c_void_p), ("blt_scale", c_void_p),
+        ("sgd_mode", c_int32),
+    ]
+
+
+PROTOTYPES: dict = {
+    "opk_rmsnorm_fwd": (I, [P, P, P, P, I, I, F, F, P]),
+    "opk_add_rmsnorm_fwd": (I, [P, P, P, P, P, P, I, I, F, F, P]),
+    "opk_rmsnorm_bwd": (I, [P, P, P, P, P, P, P, I, I, F, P]),
+    "opk_layernorm_fwd": (I, [P, P, P, P, P, P, I, I, F, P]),
+    "opk_layernorm_bwd": (I, [P, P, P, P, P, P, P, P, P, I, I, P]),
+    "opk_rope": (I, [P, P, P, I, I, I, L, F, P]),
+    "opk_swiglu_fwd": (I, [P, P, I, I, P]),
+    "opk_swiglu_bwd": (I, [P, P, P, I, I, P]),
+    "opk_geglu_fwd": (I, [P, P, I, I, I, P]),
+    "opk_geglu_bwd": (I, [P, P, P, I, I, I, P]),
+    "opk_gelu_fwd": (I, [P, P, L, P]),
+    "opk_gelu_bwd": (I, [P, P, P, L, P]),
+    "opk_embedding_fwd": (I, [P, P, P, P, I, I, P]),
+    "opk_embedding_bwd_compact": (I, [P, P, P, P, P, P, I, I, P]),
+    "opk_embedding_accumulate": (I, [P, P, P, P, P, I, I, P]),
+    "opk_lce_finalize": (I, [P, P, P, P, P, P, I, I, P]),
+    "opk_cross_entropy_fwd": (I, [P, I, P, P, P, I, I, L, F, F, P]),
+    "opk_cross_entropy_bwd": (I, [P, I, P, P, P, P, I, I, L, F, F, P]),
+    "opk_sumsq": (I, [P, I, I, L, P, P]),
+    "opk_cast_f32_bf16": (I, [P, P, L, P]),
+    "opk_clip_scale": (I, [P, F, I, F, I, L, P, P, P, I, P]),
+    "opk_clip_accumulate": (I, [P, P, P, L, P]),
+    "opk_clip_accumulate2": (I, [P, P, P, L, I, P]),
+    "opk_philox_normal": (I, [P, L, c_uint64, c_uint32, c_uint32, c_uint64, F, I, P]),
+    "opk_dp_step": (I, [POINTER(DpStepArgs), P]),
+}

@@ -1,0 +1,254 @@
+"""Functional wrappers over the bandwidth-bound sm_100a kernels (csrc/kernels/elementwise.cu, dp_step.cu).
+
+They replace the reference's Triton kernels (packages/opake-patches/src/opake/api/patches/kernels/:
+rms_norm.py, fused_add_rms_norm.py, rope_embedding.py, swiglu.py, geglu.py, cross_entropy.py, _clip_sum.py)
+and the eager noise/optimizer math (opake-dpsgd noise/_gaussian.py, opake-optimizers _adam.py).
+Every function launches on the current CUDA stream and returns without synchronising.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._protos import DpStepArgs
+
+_bf16 = torch.bfloat16
+
+
+def _L():
+    return _lib.lib()
+
+
+def _s(t: torch.Tensor) -> int:
+    return _lib.stream_ptr(t.device)
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _chk(code: int, name: str) -> None:
+    if code != 0:
+        raise _lib.KernelLibraryError(f"{name} failed with code {code}: {_L().opk_last_error().decode()}")
+
+
+# ------------------------------------------------------------------------------------------------ norms
+def rmsnorm_fwd(x, w, eps: float = 1e-6, w_offset: float = 0.0, out=None):
+    T, D = x.shape
+    y = torch.empty_like(x) if out is None else out
+    rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+    _chk(_L().opk_rmsnorm_fwd(_p(x), _p(w), _p(y), _p(rstd), T, D, eps, w_offset, _s(x)), "rmsnorm_fwd")
+    return y, rstd
+
+
+def add_rmsnorm_fwd(x, r, w, eps: float = 1e-6, w_offset: float = 0.0):
+    T, D = x.shape
+    s, y = torch.empty_like(x), torch.empty_like(x)
+    rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+    _chk(_L().opk_add_rmsnorm_fwd(_p(x), _p(r), _p(w), _p(s), _p(y), _p(rstd), T, D, eps, w_offset, _s(x)),
+         "add_rmsnorm_fwd")
+    return s, y, rstd
+
+
+def rmsnorm_bwd(dy, x, w, rstd, dres=None, dw=None, w_offset: float = 0.0, out=None):
+    """Returns ``dx`` (plus ``dres`` when given); accumulates the weight gradient into fp32 ``dw`` when given."""
+    T, D = x.shape
+    dx = torch.empty_like(x) if out is None else out
+    _chk(_L().opk_rmsnorm_bwd(_p(dy), _p(x), _p(w), _p(rstd), _p(dres), _p(dx), _p(dw), T, D, w_offset, _s(x)),
+         "rmsnorm_bwd")
+    return dx
+
+
+def layernorm_fwd(x, w, b, eps: float = 1e-5):
+    T, D = x.shape
+    y = torch.empty_like(x)
+    mean = torch.empty(T, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+    _chk(_L().opk_layernorm_fwd(_p(x), _p(w), _p(b), _p(y), _p(mean), _p(rstd), T, D, eps, _s(x)), "layernorm_fwd")
+    return y, mean, rstd
+
+
+def layernorm_bwd(dy, x, w, mean, rstd, dres=None, dw=None, db=None, out=None):
+    T, D = x.shape
+    dx = torch.empty_like(x) if out is None else out
+    _chk(_L().opk_layernorm_bwd(_p(dy), _p(x), _p(w), _p(mean), _p(rstd), _p(dres), _p(dx), _p(dw), _p(db), T, D,
+                                _s(x)), "layernorm_bwd")
+    return dx
+
+
+# ------------------------------------------------------------------------------------------------ rope
+def rope_table(seq_len: int, head_dim: int, theta: float = 10000.0, device=None, scaling: dict | None = None):
+    """``[T, head_dim/2, 2]`` fp32 (cos, sin) table; ``scaling`` implements the Llama-3 frequency rescale."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float64) / head_dim))
+    if scaling and scaling.get("rope_type", scaling.get("type")) == "llama3":
+        factor = scaling["factor"]
+        lo, hi = scaling["low_freq_factor"], scaling["high_freq_factor"]
+        old = scaling["original_max_position_embeddings"]
+        wavelen = 2 * torch.pi / inv
+        smooth = ((old / wavelen) - lo) / (hi - lo)
+        scaled = torch.where(wavelen > old / lo, inv / factor, inv)
+        mid = (wavelen <= old / lo) & (wavelen >= old / hi)
+        inv = torch.where(mid, (1 - smooth) * inv / factor + smooth * inv, scaled)
+    ang = torch.arange(seq_len, dtype=torch.float64)[:, None] * inv[None, :]
+    return torch.stack([ang.cos(), ang.sin()], dim=-1).to(torch.float32).to(device).contiguous()
+
+
+def rope_(qk, table, n_heads: int, head_dim: int, pos=None, backward: bool = False):
+    """Rotate the first ``n_heads`` heads of every row of ``qk`` in place (rotate-half convention)."""
+    T = qk.shape[0]
+    _chk(_L().opk_rope(_p(qk), _p(table), _p(pos), T, n_heads, head_dim, qk.stride(0), -1.0 if backward else 1.0,
+                       _s(qk)), "rope")
+    return qk
+
+
+# ------------------------------------------------------------------------------------------------ activations
+def swiglu_fwd(gu):
+    T, F2 = gu.shape
+    act = torch.empty(T, F2 // 2, dtype=_bf16, device=gu.device)
+    _chk(_L().opk_swiglu_fwd(_p(gu), _p(act), T, F2 // 2, _s(gu)), "swiglu_fwd")
+    return act
+
+
+def swiglu_bwd(dact, gu, out=None):
+    T, F = dact.shape
+    dgu = torch.empty_like(gu) if out is None else out
+    _chk(_L().opk_swiglu_bwd(_p(dact), _p(gu), _p(dgu), T, F, _s(gu)), "swiglu_bwd")
+    return dgu
+
+
+def geglu_fwd(gu, approximate: bool = True):
+    T, F2 = gu.shape
+    act = torch.empty(T, F2 // 2, dtype=_bf16, device=gu.device)
+    _chk(_L().opk_geglu_fwd(_p(gu), _p(act), T, F2 // 2, int(approximate), _s(gu)), "geglu_fwd")
+    return act
+
+
+def geglu_bwd(dact, gu, approximate: bool = True):
+    T, F = dact.shape
+    dgu = torch.empty_like(gu)
+    _chk(_L().opk_geglu_bwd(_p(dact), _p(gu), _p(dgu), T, F, int(approximate), _s(gu)), "geglu_bwd")
+    return dgu
+
+
+def gelu_fwd(x):
+    y = torch.empty_like(x)
+    _chk(_L().opk_gelu_fwd(_p(x), _p(y), x.numel(), _s(x)), "gelu_fwd")
+    return y
+
+
+def gelu_bwd(dy, x):
+    dx = torch.empty_like(x)
+    _chk(_L().opk_gelu_bwd(_p(dy), _p(x), _p(dx), x.numel(), _s(x)), "gelu_bwd")
+    return dx
+
+
+# ------------------------------------------------------------------------------------------------ embedding
+def embedding_fwd(tok, table, pos_table=None):
+    T, D = tok.numel(), table.shape[1]
+    out = torch.empty(T, D, dtype=_bf16, device=table.device)
+    _chk(_L().opk_embedding_fwd(_p(tok), _p(table), _p(pos_table), _p(out), T, D, _s(table)), "embedding_fwd")
+    return out
+
+
+class EmbeddingGradWorkspace:
+    """Scratch for the per-example compact embedding gradient (first-occurrence table, fp32 rows)."""
+
+    def __init__(self, vocab: int, max_tokens: int, dim: int, device):
+        self.first_pos = torch.full((vocab,), 2**31 - 1, dtype=torch.int32, device=device)
+        self.rep = torch.empty(max_tokens, dtype=torch.int32, device=device)
+        self.gc = torch.empty(max_tokens, dim, dtype=torch.float32, device=device)
+
+
+def embedding_bwd_compact(tok, dx, ws: EmbeddingGradWorkspace, sumsq):
+    T, D = dx.shape
+    _chk(_L().opk_embedding_bwd_compact(_p(tok), _p(dx), _p(ws.first_pos), _p(ws.rep), _p(ws.gc), _p(sumsq), T, D,
+                                        _s(dx)), "embedding_bwd_compact")
+
+
+def embedding_accumulate(tok, ws: EmbeddingGradWorkspace, scale, acc, T: int):
+    D = acc.shape[1]
+    _chk(_L().opk_embedding_accumulate(_p(tok), _p(ws.rep), _p(ws.gc), _p(scale), _p(acc), T, D, _s(acc)),
+         "embedding_accumulate")
+
+
+# ------------------------------------------------------------------------------------------------ losses
+def lce_finalize(pmax, psum, tgt, labels):
+    T, tiles = pmax.shape
+    lse = torch.empty(T, dtype=torch.float32, device=pmax.device)
+    nll = torch.empty(T, dtype=torch.float32, device=pmax.device)
+    _chk(_L().opk_lce_finalize(_p(pmax), _p(psum), _p(tgt), _p(labels), _p(lse), _p(nll), T, tiles, _s(pmax)),
+         "lce_finalize")
+    return lse, nll
+
+
+def cross_entropy_fwd(logits, labels, scale: float = 1.0, softcap: float = 0.0):
+    T, V = logits.shape
+    nll = torch.empty(T, dtype=torch.float32, device=logits.device)
+    lse = torch.empty(T, dtype=torch.float32, device=logits.device)
+    _chk(_L().opk_cross_entropy_fwd(_p(logits), int(logits.dtype == torch.float32), _p(labels), _p(nll), _p(lse), T, V,
+                                    logits.stride(0), scale, softcap, _s(logits)), "cross_entropy_fwd")
+    return nll, lse
+
+
+def cross_entropy_bwd(logits, labels, lse, coef, scale: float = 1.0, softcap: float = 0.0):
+    T, V = logits.shape
+    d = torch.empty_like(logits)
+    _chk(_L().opk_cross_entropy_bwd(_p(logits), int(logits.dtype == torch.float32), _p(labels), _p(lse), _p(coef), _p(d),
+                                    T, V, logits.stride(0), scale, softcap, _s(logits)), "cross_entropy_bwd")
+    return d
+
+
+# ------------------------------------------------------------------------------------------------ DP primitives
+def sumsq_(x, out, round_bf16: bool = False):
+    """``out (float64 scalar) += sum(x**2)``."""
+    _chk(_L().opk_sumsq(_p(x), int(x.dtype == torch.float32), int(round_bf16), x.numel(), _p(out), _s(x)), "sumsq")
+
+
+def cast_f32_bf16(src, dst):
+    _chk(_L().opk_cast_f32_bf16(_p(src), _p(dst), src.numel(), _s(src)), "cast_f32_bf16")
+
+
+def clip_scale(sumsq, clip: float, *, scale_out, norm_out=None, counters=None, auto: bool = False, gamma: float = 0.01,
+               n_leaves: int = 1, widest_leaf: int = 1, reset: bool = True):
+    _chk(_L().opk_clip_scale(_p(sumsq), clip, int(auto), gamma, n_leaves, widest_leaf, _p(scale_out), _p(norm_out),
+                             _p(counters), int(reset), _s(sumsq)), "clip_scale")
+
+
+def clip_accumulate(g, scale, acc, overwrite: bool = False):
+    _chk(_L().opk_clip_accumulate2(_p(g), _p(scale), _p(acc), g.numel(), int(overwrite), _s(g)), "clip_accumulate")
+
+
+def philox_normal_(out, seed: int, step: int, *, stream_id: int = 0, offset: int = 0, sigma: float = 1.0,
+                   accumulate: bool = False):
+    _chk(_L().opk_philox_normal(_p(out), out.numel(), seed & (2**64 - 1), stream_id, step, offset, sigma,
+                                int(accumulate), _s(out)), "philox_normal")
+    return out
+
+
+def dp_step(*, grad_src: list[int], shard_begin: int, shard_len: int, inv_batch: float, sigma: float, seed: int,
+            step: int, m, v, master, param_dst: list[int], param_src, lr: float, beta1: float, beta2: float, eps: float,
+            weight_decay: float, bc1: float, bc2: float, phi_hat: float, stream_id: int = 0, zero_grad: bool = False,
+            blt_state=None, blt_decay=None, blt_scale=None, sgd_mode: bool = False, device=None):
+    """Launch the fused reduce-scatter + noise + DP-AdamW(-BC) + all-gather kernel for this rank's shard.
+
+    ``grad_src`` / ``param_dst`` are raw device addresses (this rank first, then its peers).
+    """
+    a = DpStepArgs()
+    gs = (ctypes.c_void_p * len(grad_src))(*grad_src)
+    pd = (ctypes.c_void_p * max(1, len(param_dst)))(*param_dst)
+    a.grad_src, a.n_src = gs, len(grad_src)
+    a.shard_begin, a.shard_len = shard_begin, shard_len
+    a.inv_batch, a.sigma = inv_batch, sigma
+    a.seed, a.stream_id, a.step = seed & (2**64 - 1), stream_id, step & 0xFFFFFFFF
+    a.m, a.v, a.master = _p(m), _p(v), _p(master)
+    a.param_dst, a.n_dst, a.param_src = pd, len(param_dst), _p(param_src)
+    a.lr, a.beta1, a.beta2, a.eps, a.weight_decay = lr, beta1, beta2, eps, weight_decay
+    a.bc1, a.bc2, a.phi_hat, a.zero_grad = bc1, bc2, phi_hat, int(zero_grad)
+    if blt_state is not None:
+        a.blt_state, a.blt_nbuf = _p(blt_state), blt_state.shape[0]
+        a.blt_decay, a.blt_scale = _p(blt_decay), _p(blt_scale)
+    a.sgd_mode = int(sgd_mode)
+    dev = device if device is not None else (m.device if m is not None else torch.device("cuda"))
+    _chk(_L().opk_dp_step(ctypes.byref(a), _lib.stream_ptr(dev)), "dp_step")
