@@ -545,6 +545,45 @@ __global__ void __launch_bounds__(NT) ce_bwd_kernel(const void* __restrict__ log
   }
 }
 
+// rows of an fp32 [R][D] matrix -> bf16 at dst_base + offsets[r]; sumsq += sum(bf16(v)^2)
+__global__ void __launch_bounds__(NT) scatter_rows_cast_sumsq_kernel(const float* __restrict__ src,
+                                                                     __nv_bfloat16* __restrict__ dst_base,
+                                                                     const long long* __restrict__ offsets, int D,
+                                                                     double* sumsq) {
+  __shared__ float sh[32];
+  const long long r = blockIdx.x;
+  const float* s = src + r * D;
+  __nv_bfloat16* d = dst_base + offsets[r];
+  float part = 0.f;
+  for (int i = threadIdx.x; i < D; i += NT) {
+    const __nv_bfloat16 b = __float2bfloat16(s[i]);
+    d[i] = b;
+    const float f = __bfloat162float(b);
+    part += f * f;
+  }
+  const float tot = block_sum<NT>(part, sh);
+  if (threadIdx.x == 0 && sumsq) atomicAdd(sumsq, (double)tot);
+}
+
+// out[n] (+)= sum_t dy[t][n]  (bias gradient)
+__global__ void colsum_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ out, int T, int N, long long ld) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  float a = 0.f;
+  for (int t = blockIdx.y; t < T; t += gridDim.y) a += __bfloat162float(dy[(long long)t * ld + n]);
+  atomicAdd(&out[n], a);
+}
+
+// tied embeddings: dense[tok[t]] += gc[t] for representative rows (no two representatives share a row)
+__global__ void emb_add_rows_kernel(const int* __restrict__ tok, const int* __restrict__ rep,
+                                    const float* __restrict__ gc, __nv_bfloat16* __restrict__ dense, int D) {
+  const long long t = blockIdx.x;
+  if (rep[t] != (int)t) return;
+  const float* src = gc + t * D;
+  __nv_bfloat16* dst = dense + (long long)tok[t] * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = __float2bfloat16(__bfloat162float(dst[d]) + src[d]);
+}
+
 inline int grid_for(long long n, int block, int cap_blocks = 148 * 16) {
   long long g = (n + block - 1) / block;
   if (g > cap_blocks) g = cap_blocks;
@@ -722,6 +761,28 @@ extern "C" int opk_sumsq(const void* x, int is_fp32, int round_bf16, int64_t n, 
 extern "C" int opk_cast_f32_bf16(const float* in, void* out, int64_t n, void* stream) {
   if (n <= 0) return 0;
   cast_f32_bf16_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(in, BFM(out), n);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int opk_scatter_rows_cast_sumsq(const float* src, void* dst_base, const int64_t* offsets, int R, int D,
+                                           double* sumsq, void* stream) {
+  if (R <= 0) return 0;
+  scatter_rows_cast_sumsq_kernel<<<R, NT, 0, ST(stream)>>>(src, BFM(dst_base), reinterpret_cast<const long long*>(offsets), D, sumsq);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_colsum(const void* dy, float* out, int T, int N, int64_t ld, void* stream) {
+  if (T <= 0 || N <= 0) return 0;
+  dim3 grid((N + 127) / 128, T < 32 ? T : 32);
+  colsum_kernel<<<grid, 128, 0, ST(stream)>>>(BF(dy), out, T, N, ld);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_embedding_add_rows(const int32_t* tok, const int32_t* rep, const float* gc, void* dense, int T, int D,
+                                      void* stream) {
+  if (T <= 0) return 0;
+  emb_add_rows_kernel<<<T, 256, 0, ST(stream)>>>(tok, rep, gc, BFM(dense), D);
   OPK_LAUNCH_CHECK();
   return 0;
 }

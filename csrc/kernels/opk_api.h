@@ -90,6 +90,14 @@ int opk_cross_entropy_bwd(const void* logits, int is_fp32, const int32_t* labels
                           void* dlogits, int T, int V, int64_t ld, float scale, float softcap, void* stream);
 // sum(x^2) of a bf16/fp32 vector (x rounded to bf16 first when round_bf16) added to *sumsq (double).
 int opk_sumsq(const void* x, int is_fp32, int round_bf16, int64_t n, double* sumsq, void* stream);
+// fp32 rows -> bf16 at dst_base + offsets[r] (device int64 array), with sum of squares of the stored values.
+int opk_scatter_rows_cast_sumsq(const float* src, void* dst_base, const int64_t* offsets, int R, int D, double* sumsq,
+                                void* stream);
+// out[n] += sum_t dy[t][n] (out fp32, zeroed by the caller)
+int opk_colsum(const void* dy, float* out, int T, int N, int64_t ld, void* stream);
+// Tied embeddings: dense[tok[t]] += gc[t] for first-occurrence rows (bf16 read-modify-write).
+int opk_embedding_add_rows(const int32_t* tok, const int32_t* rep, const float* gc, void* dense, int T, int D,
+                           void* stream);
 // out_bf16 = bf16(in_fp32)
 int opk_cast_f32_bf16(const float* in, void* out, int64_t n, void* stream);
 

@@ -1,0 +1,318 @@
+"""Native decoder runtime with an explicit backward that produces ONE example's gradient and its squared norm.
+
+The reference obtains per-example gradients with ``vmap(grad)`` and materialises ``[microbatch, *P]``
+(packages/opake-engine/src/opake/api/engine/clipping/_clipped_grad.py:278, _clipped_fun.py:805-850). For long
+sequences (one example = one sequence of thousands of tokens) the B200 design instead runs each example through
+ordinary tensor-core GEMMs with M = sequence length:
+
+* the weight-gradient GEMM of every Linear writes the example's gradient tile (bf16) into a single reusable
+  gradient buffer ``G`` and reduces ``sum(g^2)`` of the stored values in its epilogue, so the per-example norm costs
+  no extra pass and no ``[B, *P]`` tensor ever exists;
+* after the backward one tiny kernel turns the squared norm into the guarded clip factor and one bandwidth-bound
+  kernel adds ``bf16(G * factor)`` to the fp32 clipped-gradient sum.
+
+Shapes follow HuggingFace Llama / GPT-2 (fused QKV, interleaved gate/up rows); ``load_hf_state_dict`` converts names.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import attention as A
+from ..ops import gemm as G
+from ..ops import kernels as K
+from .config import DecoderConfig
+from .flat import Layout, build_layout
+
+_bf16 = torch.bfloat16
+
+
+@dataclass
+class ExampleStats:
+    loss: torch.Tensor       # device scalar fp32
+    n_tokens: torch.Tensor   # device scalar: number of supervised tokens
+
+
+class DecoderRuntime:
+    """Forward + per-example backward for dense decoders (Llama-style and GPT-2-style blocks)."""
+
+    def __init__(self, cfg: DecoderConfig, params: torch.Tensor, *, layout: Layout | None = None,
+                 attn_impl: str = "auto"):
+        if cfg.n_experts:
+            raise ValueError("use MoEDecoderRuntime for mixture-of-experts configs")
+        self.cfg = cfg
+        self.layout = layout or build_layout(cfg)
+        self.device = params.device
+        self.params = params
+        self.w = self.layout.views(params)
+        # per-example gradient of the dense region (the token embedding is handled row-wise unless tied)
+        self.G = torch.empty(self.layout.dense_total, dtype=_bf16, device=self.device)
+        self.g = self.layout.views(self.G, dense_only=True)
+        self.attn_impl = attn_impl
+        self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self.scale = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.norm = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.clip_count = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._ws: dict[int, dict] = {}
+        self._rope = None
+        # small-vector gradients (norm weights, biases) are produced in fp32 rows and scattered into G at the end
+        self._vec_names = [s.name for s in self.layout.slots
+                           if len(s.shape) == 1 and s.offset < self.layout.dense_total]
+        self._vec_row = {n: i for i, n in enumerate(self._vec_names)}
+        d = cfg.d_model
+        self._vec_width = max([d] + [self.layout.slot(n).numel for n in self._vec_names])
+        self._n_leaves = len(self.layout.slots)
+        self._widest = max(s.numel for s in self.layout.slots)
+
+    # ------------------------------------------------------------------ workspaces
+    def workspace(self, T: int) -> dict:
+        ws = self._ws.get(T)
+        if ws is not None:
+            return ws
+        cfg, dev = self.cfg, self.device
+        d, F, L = cfg.d_model, cfg.ffn, cfg.n_layers
+
+        def e(*shape, dtype=_bf16):
+            return torch.empty(*shape, dtype=dtype, device=dev)
+
+        layers = []
+        for _ in range(L):
+            a = {"x": e(T, d), "xn": e(T, d), "qkv": e(T, cfg.qkv_dim), "attn": e(T, cfg.n_heads * cfg.head_dim),
+                 "x_mid": e(T, d), "xn2": e(T, d)}
+            if cfg.act in ("swiglu", "geglu"):
+                a["gu"], a["act"] = e(T, 2 * F), e(T, F)
+            else:
+                a["fc"], a["act"] = e(T, F), e(T, F)
+            layers.append(a)
+        tiles = G.lce_tiles(cfg.vocab_size)
+        Vp = (cfg.vocab_size + 7) // 8 * 8
+        ws = {
+            "layers": layers, "x_last": e(T, d), "xf": e(T, d),
+            "pmax": e(T, tiles, dtype=torch.float32), "psum": e(T, tiles, dtype=torch.float32),
+            "tgt": e(T, dtype=torch.float32), "dlogits": e(T, Vp)[:, : cfg.vocab_size],
+            "dx": e(T, d), "dx2": e(T, d), "dact": e(T, F), "dqkv": e(T, cfg.qkv_dim),
+            "dwide": e(T, 2 * F if cfg.act in ("swiglu", "geglu") else F),
+            "dattn": e(T, cfg.n_heads * cfg.head_dim),
+            "vec": torch.zeros(len(self._vec_names), self._vec_width, dtype=torch.float32, device=dev),
+            "emb": K.EmbeddingGradWorkspace(cfg.vocab_size, T, d, dev),
+            "tok": torch.zeros(T, dtype=torch.int32, device=dev), "labels": torch.zeros(T, dtype=torch.int32, device=dev),
+            "loss": torch.zeros(1, dtype=torch.float32, device=dev), "ntok": torch.zeros(1, dtype=torch.float32, device=dev),
+        }
+        ws["vec_offsets"] = torch.tensor([self.layout.slot(n).offset for n in self._vec_names], dtype=torch.int64,
+                                         device=dev)
+        self._ws[T] = ws
+        return ws
+
+    def _rope_table(self, T: int):
+        cfg = self.cfg
+        if self._rope is None or self._rope.shape[0] < T:
+            self._rope = K.rope_table(max(T, cfg.max_seq), cfg.head_dim, cfg.rope_theta, device=self.device,
+                                      scaling=cfg.rope_scaling)
+        return self._rope
+
+    def _vec(self, ws, name: str) -> torch.Tensor:
+        n = self.layout.slot(name).numel
+        return ws["vec"][self._vec_row[name], :n]
+
+    # ------------------------------------------------------------------ norms
+    def _norm_fwd(self, x, prefix: str, out=None):
+        cfg, w = self.cfg, self.w
+        if cfg.norm == "rms":
+            y, rstd = K.rmsnorm_fwd(x, w[prefix + ".weight"], cfg.norm_eps, out=out)
+            return y, (rstd,)
+        y, mean, rstd = K.layernorm_fwd(x, w[prefix + ".weight"], w[prefix + ".bias"], cfg.norm_eps, out=out)
+        return y, (mean, rstd)
+
+    def _norm_bwd(self, ws, dy, x, prefix: str, stats, dres, out):
+        cfg, w = self.cfg, self.w
+        if cfg.norm == "rms":
+            return K.rmsnorm_bwd(dy, x, w[prefix + ".weight"], stats[0], dres=dres, dw=self._vec(ws, prefix + ".weight"),
+                                 out=out)
+        return K.layernorm_bwd(dy, x, w[prefix + ".weight"], stats[0], stats[1], dres=dres,
+                               dw=self._vec(ws, prefix + ".weight"), db=self._vec(ws, prefix + ".bias"), out=out)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, tok: torch.Tensor, labels: torch.Tensor | None, ws: dict | None = None):
+        """Runs the decoder on one sequence. Returns ``(per-token nll [T], lse, saved)``.
+
+        ``labels`` are already shifted (``labels[t]`` is the target of position ``t``; negative = ignored).
+        """
+        cfg, w = self.cfg, self.w
+        T = tok.numel()
+        ws = ws or self.workspace(T)
+        H, KV, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        x = K.embedding_fwd(tok, w["embed"], w.get("wpe") if cfg.pos == "learned" else None, out=ws["layers"][0]["x"])
+        saved = []
+        for li in range(cfg.n_layers):
+            a = ws["layers"][li]
+            p = f"layers.{li}."
+            xn, st1 = self._norm_fwd(x, p + "norm1", out=a["xn"])
+            G.gemm(xn, w[p + "wqkv"], out=a["qkv"], bias=w.get(p + "bqkv"))
+            if cfg.pos == "rope":
+                K.rope_(a["qkv"], self._rope_table(T), H + KV, hd)
+            _, actx = A.attention_fwd(a["qkv"], H, KV, hd, self.attn_impl, out=a["attn"])
+            # output projection with the residual add fused into the GEMM epilogue
+            G.gemm(a["attn"], w[p + "wo"], out=a["x_mid"], residual=x, bias=w.get(p + "bo"))
+            xn2, st2 = self._norm_fwd(a["x_mid"], p + "norm2", out=a["xn2"])
+            nxt = ws["layers"][li + 1]["x"] if li + 1 < cfg.n_layers else ws["x_last"]
+            if cfg.act == "swiglu":
+                G.gemm(xn2, w[p + "wgu"], out=a["gu"], epilogue=G.EPI_SWIGLU, act=a["act"])
+                G.gemm(a["act"], w[p + "wd"], out=nxt, residual=a["x_mid"])
+            elif cfg.act == "geglu":
+                G.gemm(xn2, w[p + "wgu"], out=a["gu"])
+                K.geglu_fwd(a["gu"], True, out=a["act"])
+                G.gemm(a["act"], w[p + "wd"], out=nxt, residual=a["x_mid"])
+            else:
+                G.gemm(xn2, w[p + "wfc"], out=a["fc"], bias=w.get(p + "bfc"))
+                K.gelu_fwd(a["fc"], out=a["act"])
+                G.gemm(a["act"], w[p + "wproj"], out=nxt, residual=a["x_mid"], bias=w.get(p + "bproj"))
+            saved.append((st1, st2, actx))
+            x = nxt
+        xf, stf = self._norm_fwd(x, "norm_f", out=ws["xf"])
+        head = w["embed"] if cfg.tie_embeddings else w["lm_head"]
+        nll = lse = None
+        if labels is not None:
+            G.gemm(xf, head, epilogue=G.EPI_LCE_FWD, labels=labels, pmax=ws["pmax"], psum=ws["psum"], tgt=ws["tgt"])
+            lse, nll = K.lce_finalize(ws["pmax"], ws["psum"], ws["tgt"], labels)
+        return nll, lse, (saved, stf)
+
+    def logits(self, tok: torch.Tensor) -> torch.Tensor:
+        """Full ``[T, V]`` logits (evaluation / generation path)."""
+        ws = self.workspace(tok.numel())
+        self.forward(tok, None, ws)
+        head = self.w["embed"] if self.cfg.tie_embeddings else self.w["lm_head"]
+        Vp = (self.cfg.vocab_size + 7) // 8 * 8
+        out = torch.empty(tok.numel(), Vp, dtype=_bf16, device=self.device)[:, : self.cfg.vocab_size]
+        return G.gemm(ws["xf"], head, out=out)
+
+    # ------------------------------------------------------------------ forward + backward of one example
+    def example_grad(self, tok: torch.Tensor, labels: torch.Tensor, *, loss_weight: torch.Tensor | None = None,
+                     ws: dict | None = None) -> ExampleStats:
+        """Computes this example's gradient into ``self.G`` (+ compact embedding rows) and ``self.sumsq``.
+
+        The example loss is the mean NLL over supervised tokens (per-example divisor, as
+        packages/opake-alignment/src/opake/api/alignment/sft/loss/_nll.py:43-88).
+        """
+        cfg, w, g = self.cfg, self.w, self.g
+        T = tok.numel()
+        ws = ws or self.workspace(T)
+        H, KV, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        nll, lse, (saved, stf) = self.forward(tok, labels, ws)
+        valid = (labels >= 0).to(torch.float32)
+        ntok = valid.sum().clamp_(min=1.0)
+        coef = valid / ntok
+        if loss_weight is not None:
+            coef = coef * loss_weight
+        loss = (nll * coef).sum()
+        ws["vec"].zero_()
+        self.sumsq.zero_()
+
+        head = w["embed"] if cfg.tie_embeddings else w["lm_head"]
+        ghead = g["embed"] if cfg.tie_embeddings else g["lm_head"]
+        dlog = G.gemm(ws["xf"], head, out=ws["dlogits"], epilogue=G.EPI_LCE_BWD, labels=labels, lse=lse, coef=coef)
+        dxf = G.gemm(dlog, head, b_mn=True, out=ws["dx2"])
+        if cfg.tie_embeddings:
+            G.linear_wgrad(dlog, ws["xf"], out=ghead)            # norm added after the embedding rows are merged
+        else:
+            G.linear_wgrad(dlog, ws["xf"], out=ghead, sumsq=self.sumsq)
+        x_last = ws["x_last"]
+        dx = self._norm_bwd(ws, dxf, x_last, "norm_f", stf, None, ws["dx"])
+
+        for li in reversed(range(cfg.n_layers)):
+            a = ws["layers"][li]
+            p = f"layers.{li}."
+            st1, st2, actx = saved[li]
+            # ---- MLP
+            if cfg.act in ("swiglu", "geglu"):
+                G.linear_wgrad(dx, a["act"], out=g[p + "wd"], sumsq=self.sumsq)
+                dact = G.gemm(dx, w[p + "wd"], b_mn=True, out=ws["dact"])
+                dgu = ws["dwide"]
+                if cfg.act == "swiglu":
+                    K.swiglu_bwd(dact, a["gu"], out=dgu)
+                else:
+                    K.geglu_bwd(dact, a["gu"], True, out=dgu)
+                G.linear_wgrad(dgu, a["xn2"], out=g[p + "wgu"], sumsq=self.sumsq)
+                dxn2 = G.gemm(dgu, w[p + "wgu"], b_mn=True, out=ws["dx2"])
+            else:
+                G.linear_wgrad(dx, a["act"], out=g[p + "wproj"], sumsq=self.sumsq)
+                if cfg.bias:
+                    K.colsum_(dx, self._vec(ws, p + "bproj"))
+                dact = G.gemm(dx, w[p + "wproj"], b_mn=True, out=ws["dact"])
+                dfc = K.gelu_bwd(dact, a["fc"], out=ws["dwide"])
+                G.linear_wgrad(dfc, a["xn2"], out=g[p + "wfc"], sumsq=self.sumsq)
+                if cfg.bias:
+                    K.colsum_(dfc, self._vec(ws, p + "bfc"))
+                dxn2 = G.gemm(dfc, w[p + "wfc"], b_mn=True, out=ws["dx2"])
+            dx_mid = self._norm_bwd(ws, dxn2, a["x_mid"], p + "norm2", st2, dx, ws["dx"])  # in place over dres
+            # ---- attention
+            G.linear_wgrad(dx_mid, a["attn"], out=g[p + "wo"], sumsq=self.sumsq)
+            if cfg.bias:
+                K.colsum_(dx_mid, self._vec(ws, p + "bo"))
+            dattn = G.gemm(dx_mid, w[p + "wo"], b_mn=True, out=ws["dattn"])
+            dqkv = ws["dqkv"]
+            A.attention_bwd(dattn, a["qkv"], a["attn"], actx, H, KV, hd, dqkv)
+            if cfg.pos == "rope":
+                K.rope_(dqkv, self._rope_table(T), H + KV, hd, backward=True)
+            G.linear_wgrad(dqkv, a["xn"], out=g[p + "wqkv"], sumsq=self.sumsq)
+            if cfg.bias:
+                K.colsum_(dqkv, self._vec(ws, p + "bqkv"))
+            dxn = G.gemm(dqkv, w[p + "wqkv"], b_mn=True, out=ws["dx2"])
+            dx = self._norm_bwd(ws, dxn, a["x"], p + "norm1", st1, dx_mid, ws["dx"])
+
+        # ---- embeddings
+        K.embedding_bwd_compact(tok, dx, ws["emb"], None if cfg.tie_embeddings else self.sumsq)
+        if cfg.pos == "learned":
+            gw = g["wpe"]
+            gw[:T].copy_(dx)
+            gw[T:].zero_()
+            K.sumsq_(gw[:T], self.sumsq)
+        if cfg.tie_embeddings:
+            K.embedding_add_rows(tok, ws["emb"], ghead, T)
+            K.sumsq_(ghead, self.sumsq)
+        # ---- vector parameters (norm weights, biases): fp32 rows -> bf16 slots of G, with their norm
+        if all(self.layout.slot(n).numel == self._vec_width for n in self._vec_names):
+            K.scatter_rows_cast_sumsq(ws["vec"], self.G, ws["vec_offsets"], self.sumsq)
+        else:
+            self._scatter_vec_rows(ws)
+        return ExampleStats(loss=loss, n_tokens=ntok)
+
+    def _scatter_vec_rows(self, ws) -> None:
+        for n in self._vec_names:
+            row = self._vec(ws, n)
+            dst = self.g[n]
+            K.cast_f32_bf16(row, dst)
+            K.sumsq_(dst, self.sumsq)
+
+    # ------------------------------------------------------------------ clip + accumulate
+    def clip_and_accumulate(self, acc: torch.Tensor, clip: float, ws: dict, tok: torch.Tensor, *, auto: bool = False,
+                            gamma: float = 0.01, overwrite: bool = False) -> None:
+        """``acc`` (fp32, full flat layout) ``+= clip_factor * G`` with the conservative storage rounding."""
+        K.clip_scale(self.sumsq, clip, scale_out=self.scale, norm_out=self.norm, counters=self.clip_count, auto=auto,
+                     gamma=gamma, n_leaves=self._n_leaves, widest_leaf=self._widest, reset=True)
+        K.clip_accumulate(self.G, self.scale, acc[: self.layout.dense_total], overwrite=overwrite)
+        if not self.cfg.tie_embeddings:
+            emb = self.layout.slot("embed")
+            acc_emb = acc[emb.offset : emb.offset + emb.numel].view(emb.shape)
+            K.embedding_accumulate(tok, ws["emb"], self.scale, acc_emb, tok.numel())
+
+
+def init_params_(cfg: DecoderConfig, params: torch.Tensor, layout: Layout, seed: int = 0, std: float = 0.02) -> None:
+    """Random-normal weights (std 0.02, output projections scaled by 1/sqrt(2L)), unit norm weights, zero biases."""
+    gen = torch.Generator(device=params.device).manual_seed(seed)
+    params.zero_()
+    for s in layout.slots:
+        v = params[s.offset : s.offset + s.numel]
+        if s.name.endswith("norm1.weight") or s.name.endswith("norm2.weight") or s.name == "norm_f.weight":
+            v.fill_(1.0)
+        elif len(s.shape) == 1:
+            v.zero_()
+        else:
+            scale = std
+            if s.name.endswith(("wo", "wd", "wproj", "experts.wd")):
+                scale = std / (2 * cfg.n_layers) ** 0.5
+            # chunked fill keeps the fp32 temporary small for multi-GB tensors
+            step = 1 << 26
+            for b in range(0, s.numel, step):
+                n = min(step, s.numel - b)
+                v[b : b + n].copy_(torch.randn(n, generator=gen, device=params.device, dtype=torch.float32) * scale)

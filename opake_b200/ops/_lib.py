@@ -63,7 +63,11 @@ def _declare_optional(L: ctypes.CDLL) -> None:
         fn.argtypes = argtypes
 
 
+LAUNCHES = [0]  # number of native kernel entry-point calls issued by this process
+
+
 def check(code: int, what: str) -> None:
+    LAUNCHES[0] += 1
     if code != 0:
         msg = lib().opk_last_error().decode("utf-8", "replace")
         raise KernelLibraryError(f"{what} failed (code {code}): {msg}")

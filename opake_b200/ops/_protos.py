@@ -39,6 +39,9 @@ PROTOTYPES: dict = {
     "opk_cross_entropy_fwd": (I, [P, I, P, P, P, I, I, L, F, F, P]),
     "opk_cross_entropy_bwd": (I, [P, I, P, P, P, P, I, I, L, F, F, P]),
     "opk_sumsq": (I, [P, I, I, L, P, P]),
+    "opk_scatter_rows_cast_sumsq": (I, [P, P, P, I, I, P, P]),
+    "opk_colsum": (I, [P, P, I, I, L, P]),
+    "opk_embedding_add_rows": (I, [P, P, P, P, I, I, P]),
     "opk_cast_f32_bf16": (I, [P, P, L, P]),
     "opk_clip_scale": (I, [P, F, I, F, I, L, P, P, P, I, P]),
     "opk_clip_accumulate": (I, [P, P, P, L, P]),

@@ -30,6 +30,7 @@ def _p(t):
 
 
 def _chk(code: int, name: str) -> None:
+    _lib.LAUNCHES[0] += 1
     if code != 0:
         raise _lib.KernelLibraryError(f"{name} failed with code {code}: {_L().opk_last_error().decode()}")
 
@@ -61,9 +62,9 @@ def rmsnorm_bwd(dy, x, w, rstd, dres=None, dw=None, w_offset: float = 0.0, out=N
     return dx
 
 
-def layernorm_fwd(x, w, b, eps: float = 1e-5):
+def layernorm_fwd(x, w, b, eps: float = 1e-5, out=None):
     T, D = x.shape
-    y = torch.empty_like(x)
+    y = torch.empty_like(x) if out is None else out
     mean = torch.empty(T, dtype=torch.float32, device=x.device)
     rstd = torch.empty(T, dtype=torch.float32, device=x.device)
     _chk(_L().opk_layernorm_fwd(_p(x), _p(w), _p(b), _p(y), _p(mean), _p(rstd), T, D, eps, _s(x)), "layernorm_fwd")
@@ -118,36 +119,37 @@ def swiglu_bwd(dact, gu, out=None):
     return dgu
 
 
-def geglu_fwd(gu, approximate: bool = True):
+def geglu_fwd(gu, approximate: bool = True, out=None):
     T, F2 = gu.shape
-    act = torch.empty(T, F2 // 2, dtype=_bf16, device=gu.device)
+    act = torch.empty(T, F2 // 2, dtype=_bf16, device=gu.device) if out is None else out
     _chk(_L().opk_geglu_fwd(_p(gu), _p(act), T, F2 // 2, int(approximate), _s(gu)), "geglu_fwd")
     return act
 
 
-def geglu_bwd(dact, gu, approximate: bool = True):
+def geglu_bwd(dact, gu, approximate: bool = True, out=None):
     T, F = dact.shape
-    dgu = torch.empty_like(gu)
+    dgu = torch.empty_like(gu) if out is None else out
     _chk(_L().opk_geglu_bwd(_p(dact), _p(gu), _p(dgu), T, F, int(approximate), _s(gu)), "geglu_bwd")
     return dgu
 
 
-def gelu_fwd(x):
-    y = torch.empty_like(x)
+def gelu_fwd(x, out=None):
+    y = torch.empty_like(x) if out is None else out
     _chk(_L().opk_gelu_fwd(_p(x), _p(y), x.numel(), _s(x)), "gelu_fwd")
     return y
 
 
-def gelu_bwd(dy, x):
-    dx = torch.empty_like(x)
+def gelu_bwd(dy, x, out=None):
+    dx = torch.empty_like(x) if out is None else out
     _chk(_L().opk_gelu_bwd(_p(dy), _p(x), _p(dx), x.numel(), _s(x)), "gelu_bwd")
     return dx
 
 
 # ------------------------------------------------------------------------------------------------ embedding
-def embedding_fwd(tok, table, pos_table=None):
+def embedding_fwd(tok, table, pos_table=None, out=None):
     T, D = tok.numel(), table.shape[1]
-    out = torch.empty(T, D, dtype=_bf16, device=table.device)
+    if out is None:
+        out = torch.empty(T, D, dtype=_bf16, device=table.device)
     _chk(_L().opk_embedding_fwd(_p(tok), _p(table), _p(pos_table), _p(out), T, D, _s(table)), "embedding_fwd")
     return out
 
@@ -204,6 +206,23 @@ def cross_entropy_bwd(logits, labels, lse, coef, scale: float = 1.0, softcap: fl
 def sumsq_(x, out, round_bf16: bool = False):
     """``out (float64 scalar) += sum(x**2)``."""
     _chk(_L().opk_sumsq(_p(x), int(x.dtype == torch.float32), int(round_bf16), x.numel(), _p(out), _s(x)), "sumsq")
+
+
+def scatter_rows_cast_sumsq(src, dst_base, offsets, sumsq):
+    """fp32 rows ``src[r]`` -> bf16 at ``dst_base + offsets[r]``; ``sumsq += sum(stored**2)``."""
+    R, D = src.shape
+    _chk(_L().opk_scatter_rows_cast_sumsq(_p(src), _p(dst_base), _p(offsets), R, D, _p(sumsq), _s(src)),
+         "scatter_rows_cast_sumsq")
+
+
+def colsum_(dy, out):
+    T, N = dy.shape
+    _chk(_L().opk_colsum(_p(dy), _p(out), T, N, dy.stride(0), _s(dy)), "colsum")
+
+
+def embedding_add_rows(tok, ws, dense, T: int):
+    _chk(_L().opk_embedding_add_rows(_p(tok), _p(ws.rep), _p(ws.gc), _p(dense), T, dense.shape[1], _s(dense)),
+         "embedding_add_rows")
 
 
 def cast_f32_bf16(src, dst):

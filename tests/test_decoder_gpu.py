@@ -1,0 +1,102 @@
+"""Native decoder runtime vs the autograd oracle: loss, per-example gradient, its norm, clip + accumulate."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(cfg, cuda, T, seed=0):
+    from opake_b200.models.decoder import DecoderRuntime, init_params_
+    from opake_b200.models.flat import build_layout
+
+    layout = build_layout(cfg)
+    params = torch.empty(layout.total, dtype=torch.bfloat16, device=cuda)
+    init_params_(cfg, params, layout, seed=seed, std=0.05)
+    # non-trivial norm weights / biases
+    g = torch.Generator(device=cuda).manual_seed(1)
+    for s in layout.slots:
+        if len(s.shape) == 1:
+            params[s.offset : s.offset + s.numel] += (torch.randn(s.numel, generator=g, device=cuda) * 0.1).bfloat16()
+    rt = DecoderRuntime(cfg, params, layout=layout, attn_impl="auto")
+    tok = torch.randint(0, min(cfg.vocab_size, 97), (T,), device=cuda, dtype=torch.int32)
+    labels = torch.roll(tok, -1)
+    labels[-1] = -100
+    labels[: T // 4] = -100
+    return layout, params, rt, tok, labels
+
+
+def _oracle(cfg, layout, params, tok, labels, rt):
+    from opake_b200.models.reference_torch import example_loss
+
+    w = {k: v.detach().float().requires_grad_() for k, v in layout.views(params).items()}
+    table = rt._rope_table(tok.numel()) if cfg.pos == "rope" else None
+    loss = example_loss(cfg, w, tok, labels, table)
+    loss.backward()
+    return loss.item(), {k: v.grad for k, v in w.items()}
+
+
+@pytest.mark.parametrize("name", ["tiny-llama", "tiny-llama-tied", "tiny-gpt2"])
+def test_example_grad_matches_autograd(cuda, name):
+    from opake_b200.models import config as C
+
+    if name == "tiny-llama":
+        cfg = C.tiny_llama()
+    elif name == "tiny-llama-tied":
+        cfg = C.tiny_llama(tie_embeddings=True)
+    else:
+        cfg = C.gpt2_small(n_layers=2, d_model=256, n_heads=4, n_kv_heads=4, head_dim=64, ffn=1024, vocab_size=1001,
+                           max_seq=128, name="tiny-gpt2")
+    T = 128
+    layout, params, rt, tok, labels = _setup(cfg, cuda, T)
+    st = rt.example_grad(tok, labels)
+    ref_loss, ref_g = _oracle(cfg, layout, params, tok, labels, rt)
+    assert abs(st.loss.item() - ref_loss) < 2e-2 * max(1.0, abs(ref_loss))
+    # gradients: every dense slot, compared by relative Frobenius error
+    total_sq = 0.0
+    for s in layout.slots:
+        if s.offset >= layout.dense_total:
+            continue
+        got = rt.g[s.name].float()
+        want = ref_g[s.name]
+        err = (got - want).norm().item() / (want.norm().item() + 1e-8)
+        assert err < 6e-2, f"{s.name}: rel err {err}"
+        total_sq += got.double().pow(2).sum().item()
+    ws = rt.workspace(T)
+    if not cfg.tie_embeddings:
+        dense = torch.zeros(cfg.vocab_size, cfg.d_model, device=cuda)
+        rows = ws["emb"].rep.long() == torch.arange(T, device=cuda)
+        dense[tok.long()[rows]] = ws["emb"].gc[rows]
+        err = (dense - ref_g["embed"]).norm().item() / ref_g["embed"].norm().item()
+        assert err < 6e-2
+        total_sq += dense.to(torch.bfloat16).double().pow(2).sum().item()
+    assert abs(rt.sumsq.item() - total_sq) / total_sq < 1e-3
+    # clip and accumulate twice: acc == 2 * clip_factor * g and the stored clipped norm respects the bound
+    acc = torch.zeros(layout.total, device=cuda)
+    true_norm = total_sq**0.5
+    C_ = 0.5 * true_norm
+    ss = rt.sumsq.clone()
+    rt.clip_and_accumulate(acc, C_, ws, tok)
+    rt.sumsq.copy_(ss)
+    rt.clip_and_accumulate(acc, C_, ws, tok)
+    assert abs(rt.norm.item() - true_norm) / true_norm < 1e-3
+    assert (acc.double() / 2).norm().item() <= C_ * (1 + 1e-6)
+    assert (acc.double() / 2).norm().item() > 0.98 * C_
+
+
+def test_cuda_graph_replay_is_identical(cuda):
+    from opake_b200.models import config as C
+    from opake_b200.parallel.engine import EngineConfig, ShardedDPEngine
+
+    cfg = C.tiny_llama()
+    T, B = 128, 3
+    tok = torch.randint(0, cfg.vocab_size, (B, T), dtype=torch.int32).pin_memory()
+    labels = torch.roll(tok, -1, 1).clone()
+    labels[:, -1] = -100
+    res = []
+    for graph in (False, True):
+        eng = ShardedDPEngine(cfg, EngineConfig(logical_batch=B, noise_multiplier=0.5, use_cuda_graph=graph, seed=3), cuda)
+        losses = [eng.step(tok, labels).item() for _ in range(2)]
+        res.append((losses, eng.params.clone()))
+    assert res[0][0] == pytest.approx(res[1][0], rel=1e-3)
+    assert (res[0][1].float() - res[1][1].float()).abs().max().item() < 1e-2
+    assert res[0][0][1] != res[0][0][0]
