@@ -13,6 +13,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace {
 
@@ -125,7 +126,9 @@ __global__ void __launch_bounds__(256) clip_accumulate_kernel(const bf16x8* __re
                                                               float4* __restrict__ acc, long long nvec, int overwrite) {
   const float s = *scale;
   for (long long i = blockIdx.x * 256ll + threadIdx.x; i < nvec; i += (long long)gridDim.x * 256) {
-    const bf16x8 v = g[i];
+    // streaming accesses: this kernel runs next to tensor-core GEMMs whose operand tiles live in L2
+    const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(g) + i);
+    const bf16x8 v = *reinterpret_cast<const bf16x8*>(&raw);
     float f[8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -138,13 +141,13 @@ __global__ void __launch_bounds__(256) clip_accumulate_kernel(const bf16x8* __re
       a0 = make_float4(0.f, 0.f, 0.f, 0.f);
       a1 = a0;
     } else {
-      a0 = acc[2 * i];
-      a1 = acc[2 * i + 1];
+      a0 = __ldcs(acc + 2 * i);
+      a1 = __ldcs(acc + 2 * i + 1);
     }
     a0.x += clip_store(f[0], s); a0.y += clip_store(f[1], s); a0.z += clip_store(f[2], s); a0.w += clip_store(f[3], s);
     a1.x += clip_store(f[4], s); a1.y += clip_store(f[5], s); a1.z += clip_store(f[6], s); a1.w += clip_store(f[7], s);
-    acc[2 * i] = a0;
-    acc[2 * i + 1] = a1;
+    __stcs(acc + 2 * i, a0);
+    __stcs(acc + 2 * i + 1, a1);
   }
 }
 __global__ void clip_accumulate_tail_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ scale,
@@ -276,8 +279,17 @@ extern "C" int opk_clip_accumulate2(const void* g, const float* scale, float* ac
   if (n <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(g) & 15) || (reinterpret_cast<uintptr_t>(acc) & 15)) return -1;
   const long long nvec = n >> 3;
+  static int cap_ctas = -1;
+  if (cap_ctas < 0) {
+    // Same shared-memory carve-out as the GEMM kernels, so that CTAs of this kernel can be co-resident with them
+    // on an SM (an SM does not mix carve-out configurations).
+    cudaFuncSetAttribute(clip_accumulate_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    const char* e = getenv("OPK_ACC_CTAS");
+    cap_ctas = e ? atoi(e) : 148 * 16;
+    if (cap_ctas <= 0) cap_ctas = 148 * 16;
+  }
   if (nvec > 0)
-    clip_accumulate_kernel<<<grid_for(nvec, 256, 148 * 16), 256, 0, ST(stream)>>>(
+    clip_accumulate_kernel<<<grid_for(nvec, 256, cap_ctas), 256, 0, ST(stream)>>>(
         reinterpret_cast<const bf16x8*>(g), scale, reinterpret_cast<float4*>(acc), nvec, overwrite);
   const long long tail = n - (nvec << 3);
   if (tail > 0)

@@ -102,76 +102,63 @@ __global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __
   }
 }
 
-// One CTA walks rows blockIdx.x, +gridDim.x, ...; column ownership is fixed per thread so the weight gradient
-// partial stays in registers until a single atomicAdd per column at the end.
-constexpr int MAX_COL_ITERS = 8;  // D <= 8 * 2048
-__global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
-                                                         const __nv_bfloat16* __restrict__ x,
-                                                         const __nv_bfloat16* __restrict__ w,
-                                                         const float* __restrict__ rstd,
-                                                         const __nv_bfloat16* __restrict__ dres,
-                                                         __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, int T,
-                                                         int D, float w_off) {
-  __shared__ float sh[32];
+// Backward: one warp per row (two passes over the L1-resident row, shuffle reductions only). The weight gradient
+// is accumulated per CTA in shared memory and flushed once with global atomics.
+constexpr int MAX_COL_ITERS = 8;  // layernorm backward: D <= 8 * 2048
+constexpr int RMS_BWD_WARPS = 8;
+__global__ void __launch_bounds__(RMS_BWD_WARPS * 32) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                                        const __nv_bfloat16* __restrict__ x,
+                                                                        const __nv_bfloat16* __restrict__ w,
+                                                                        const float* __restrict__ rstd,
+                                                                        const __nv_bfloat16* __restrict__ dres,
+                                                                        __nv_bfloat16* __restrict__ dx,
+                                                                        float* __restrict__ dw, int T, int D,
+                                                                        float w_off) {
+  extern __shared__ float sdw[];  // [D]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nv = D >> 3;
-  float dwp[MAX_COL_ITERS][8];
-#pragma unroll
-  for (int c = 0; c < MAX_COL_ITERS; ++c)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) dwp[c][j] = 0.f;
+  if (dw) {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) sdw[i] = 0.f;
+    __syncthreads();
+  }
   const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
-  for (long long row = blockIdx.x; row < T; row += gridDim.x) {
+  for (long long row = (long long)blockIdx.x * RMS_BWD_WARPS + warp; row < T; row += (long long)gridDim.x * RMS_BWD_WARPS) {
     const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + row * D);
     const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * D);
     const float rs = rstd[row];
     float dot = 0.f;
+    for (int i = lane; i < nv; i += 32) {
+      float g[8], xv[8], wv[8];
+      unpack8(dyr[i], g);
+      unpack8(xr[i], xv);
+      unpack8(wr[i], wv);
 #pragma unroll
-    for (int c = 0; c < MAX_COL_ITERS; ++c) {
-      const int i = threadIdx.x + c * NT;
-      if (i < nv) {
-        float g[8], xv[8], wv[8];
-        unpack8(dyr[i], g);
-        unpack8(xr[i], xv);
-        unpack8(wr[i], wv);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float xh = xv[j] * rs;
-          dwp[c][j] += g[j] * xh;
-          dot += g[j] * (wv[j] + w_off) * xh;
-        }
-      }
+      for (int j = 0; j < 8; ++j) dot += g[j] * (wv[j] + w_off) * xv[j];
     }
-    const float mean_dot = block_sum<NT>(dot, sh) / (float)D;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float mean_dot = dot * rs / (float)D;
     const bf16x8* drr = dres ? reinterpret_cast<const bf16x8*>(dres + row * D) : nullptr;
     bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + row * D);
+    for (int i = lane; i < nv; i += 32) {
+      float g[8], xv[8], wv[8], o[8];
+      unpack8(dyr[i], g);
+      unpack8(xr[i], xv);
+      unpack8(wr[i], wv);
+      if (drr) unpack8(drr[i], o);
 #pragma unroll
-    for (int c = 0; c < MAX_COL_ITERS; ++c) {
-      const int i = threadIdx.x + c * NT;
-      if (i < nv) {
-        float g[8], xv[8], wv[8], o[8];
-        unpack8(dyr[i], g);
-        unpack8(xr[i], xv);
-        unpack8(wr[i], wv);
-        if (drr) unpack8(drr[i], o);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float xh = xv[j] * rs;
-          const float d = rs * (g[j] * (wv[j] + w_off) - xh * mean_dot);
-          o[j] = drr ? o[j] + d : d;
-        }
-        dxr[i] = pack8(o);
+      for (int j = 0; j < 8; ++j) {
+        const float xh = xv[j] * rs;
+        const float d = rs * (g[j] * (wv[j] + w_off) - xh * mean_dot);
+        o[j] = drr ? o[j] + d : d;
+        if (dw) atomicAdd(&sdw[i * 8 + j], g[j] * xh);
       }
+      dxr[i] = pack8(o);
     }
   }
   if (dw) {
-#pragma unroll
-    for (int c = 0; c < MAX_COL_ITERS; ++c) {
-      const int i = threadIdx.x + c * NT;
-      if (i < nv) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) atomicAdd(&dw[i * 8 + j], dwp[c][j]);
-      }
-    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < D; i += blockDim.x) atomicAdd(&dw[i], sdw[i]);
   }
 }
 
@@ -616,9 +603,11 @@ extern "C" int opk_add_rmsnorm_fwd(const void* x, const void* r, const void* w, 
 extern "C" int opk_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
                                void* dx_out, float* dw, int T, int D, float w_offset, void* stream) {
   if (T <= 0) return 0;
-  if (D % 8 || D > MAX_COL_ITERS * NT * 8) return -1;
-  const int grid = T < 148 * 2 ? T : 148 * 2;
-  rmsnorm_bwd_kernel<<<grid, NT, 0, ST(stream)>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx_out), dw, T, D, w_offset);
+  if (D % 8 || D > 12288) return -1;
+  int grid = (T + RMS_BWD_WARPS - 1) / RMS_BWD_WARPS;
+  if (grid > 148 * 2) grid = 148 * 2;
+  rmsnorm_bwd_kernel<<<grid, RMS_BWD_WARPS * 32, sizeof(float) * D, ST(stream)>>>(BF(dy), BF(x), BF(w), rstd, BF(dres),
+                                                                                   BFM(dx_out), dw, T, D, w_offset);
   OPK_LAUNCH_CHECK();
   return 0;
 }

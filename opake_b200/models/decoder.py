@@ -38,7 +38,7 @@ class DecoderRuntime:
     """Forward + per-example backward for dense decoders (Llama-style and GPT-2-style blocks)."""
 
     def __init__(self, cfg: DecoderConfig, params: torch.Tensor, *, layout: Layout | None = None,
-                 attn_impl: str = "auto"):
+                 attn_impl: str = "auto", n_slots: int = 1):
         if cfg.n_experts:
             raise ValueError("use MoEDecoderRuntime for mixture-of-experts configs")
         self.cfg = cfg
@@ -47,12 +47,15 @@ class DecoderRuntime:
         self.params = params
         self.w = self.layout.views(params)
         # per-example gradient of the dense region (the token embedding is handled row-wise unless tied)
-        self.G = torch.empty(self.layout.dense_total, dtype=_bf16, device=self.device)
-        self.g = self.layout.views(self.G, dense_only=True)
+        # With two slots the clipped accumulation of example i can run on a side stream while example i+1 is
+        # being computed into the other slot.
+        self.n_slots = n_slots
+        self.Gs = [torch.empty(self.layout.dense_total, dtype=_bf16, device=self.device) for _ in range(n_slots)]
+        self.gs = [self.layout.views(G_, dense_only=True) for G_ in self.Gs]
         self.attn_impl = attn_impl
-        self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
-        self.scale = torch.zeros(1, dtype=torch.float32, device=self.device)
-        self.norm = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.sumsqs = [torch.zeros(1, dtype=torch.float64, device=self.device) for _ in range(n_slots)]
+        self.scales = [torch.zeros(1, dtype=torch.float32, device=self.device) for _ in range(n_slots)]
+        self.norms = [torch.zeros(1, dtype=torch.float32, device=self.device) for _ in range(n_slots)]
         self.clip_count = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._ws: dict[int, dict] = {}
         self._rope = None
@@ -64,6 +67,27 @@ class DecoderRuntime:
         self._vec_width = max([d] + [self.layout.slot(n).numel for n in self._vec_names])
         self._n_leaves = len(self.layout.slots)
         self._widest = max(s.numel for s in self.layout.slots)
+
+    # slot-0 aliases (single-buffer users and tests)
+    @property
+    def G(self):
+        return self.Gs[0]
+
+    @property
+    def g(self):
+        return self.gs[0]
+
+    @property
+    def sumsq(self):
+        return self.sumsqs[0]
+
+    @property
+    def scale(self):
+        return self.scales[0]
+
+    @property
+    def norm(self):
+        return self.norms[0]
 
     # ------------------------------------------------------------------ workspaces
     def workspace(self, T: int) -> dict:
@@ -95,12 +119,14 @@ class DecoderRuntime:
             "dwide": e(T, 2 * F if cfg.act in ("swiglu", "geglu") else F),
             "dattn": e(T, cfg.n_heads * cfg.head_dim),
             "vec": torch.zeros(len(self._vec_names), self._vec_width, dtype=torch.float32, device=dev),
-            "emb": K.EmbeddingGradWorkspace(cfg.vocab_size, T, d, dev),
-            "tok": torch.zeros(T, dtype=torch.int32, device=dev), "labels": torch.zeros(T, dtype=torch.int32, device=dev),
+            "embs": [K.EmbeddingGradWorkspace(cfg.vocab_size, T, d, dev) for _ in range(self.n_slots)],
+            "toks": [torch.zeros(T, dtype=torch.int32, device=dev) for _ in range(self.n_slots)],
+            "labels": torch.zeros(T, dtype=torch.int32, device=dev),
             "loss": torch.zeros(1, dtype=torch.float32, device=dev), "ntok": torch.zeros(1, dtype=torch.float32, device=dev),
         }
         ws["vec_offsets"] = torch.tensor([self.layout.slot(n).offset for n in self._vec_names], dtype=torch.int64,
                                          device=dev)
+        ws["emb"], ws["tok"] = ws["embs"][0], ws["toks"][0]
         self._ws[T] = ws
         return ws
 
@@ -188,15 +214,17 @@ class DecoderRuntime:
 
     # ------------------------------------------------------------------ forward + backward of one example
     def example_grad(self, tok: torch.Tensor, labels: torch.Tensor, *, loss_weight: torch.Tensor | None = None,
-                     ws: dict | None = None) -> ExampleStats:
-        """Computes this example's gradient into ``self.G`` (+ compact embedding rows) and ``self.sumsq``.
+                     ws: dict | None = None, slot: int = 0) -> ExampleStats:
+        """Computes this example's gradient into ``self.G`` (+ compact embedding rows) and ``sumsq``.
 
         The example loss is the mean NLL over supervised tokens (per-example divisor, as
         packages/opake-alignment/src/opake/api/alignment/sft/loss/_nll.py:43-88).
         """
-        cfg, w, g = self.cfg, self.w, self.g
+        cfg, w, g = self.cfg, self.w, self.gs[slot]
+        sumsq, emb_ws = self.sumsqs[slot], None
         T = tok.numel()
         ws = ws or self.workspace(T)
+        emb_ws = ws["embs"][slot]
         H, KV, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
         nll, lse, (saved, stf) = self.forward(tok, labels, ws)
         valid = (labels >= 0).to(torch.float32)
@@ -206,7 +234,7 @@ class DecoderRuntime:
             coef = coef * loss_weight
         loss = (nll * coef).sum()
         ws["vec"].zero_()
-        self.sumsq.zero_()
+        sumsq.zero_()
 
         head = w["embed"] if cfg.tie_embeddings else w["lm_head"]
         ghead = g["embed"] if cfg.tie_embeddings else g["lm_head"]
@@ -215,7 +243,7 @@ class DecoderRuntime:
         if cfg.tie_embeddings:
             G.linear_wgrad(dlog, ws["xf"], out=ghead)            # norm added after the embedding rows are merged
         else:
-            G.linear_wgrad(dlog, ws["xf"], out=ghead, sumsq=self.sumsq)
+            G.linear_wgrad(dlog, ws["xf"], out=ghead, sumsq=sumsq)
         x_last = ws["x_last"]
         dx = self._norm_bwd(ws, dxf, x_last, "norm_f", stf, None, ws["dx"])
 
@@ -225,28 +253,28 @@ class DecoderRuntime:
             st1, st2, actx = saved[li]
             # ---- MLP
             if cfg.act in ("swiglu", "geglu"):
-                G.linear_wgrad(dx, a["act"], out=g[p + "wd"], sumsq=self.sumsq)
+                G.linear_wgrad(dx, a["act"], out=g[p + "wd"], sumsq=sumsq)
                 dact = G.gemm(dx, w[p + "wd"], b_mn=True, out=ws["dact"])
                 dgu = ws["dwide"]
                 if cfg.act == "swiglu":
                     K.swiglu_bwd(dact, a["gu"], out=dgu)
                 else:
                     K.geglu_bwd(dact, a["gu"], True, out=dgu)
-                G.linear_wgrad(dgu, a["xn2"], out=g[p + "wgu"], sumsq=self.sumsq)
+                G.linear_wgrad(dgu, a["xn2"], out=g[p + "wgu"], sumsq=sumsq)
                 dxn2 = G.gemm(dgu, w[p + "wgu"], b_mn=True, out=ws["dx2"])
             else:
-                G.linear_wgrad(dx, a["act"], out=g[p + "wproj"], sumsq=self.sumsq)
+                G.linear_wgrad(dx, a["act"], out=g[p + "wproj"], sumsq=sumsq)
                 if cfg.bias:
                     K.colsum_(dx, self._vec(ws, p + "bproj"))
                 dact = G.gemm(dx, w[p + "wproj"], b_mn=True, out=ws["dact"])
                 dfc = K.gelu_bwd(dact, a["fc"], out=ws["dwide"])
-                G.linear_wgrad(dfc, a["xn2"], out=g[p + "wfc"], sumsq=self.sumsq)
+                G.linear_wgrad(dfc, a["xn2"], out=g[p + "wfc"], sumsq=sumsq)
                 if cfg.bias:
                     K.colsum_(dfc, self._vec(ws, p + "bfc"))
                 dxn2 = G.gemm(dfc, w[p + "wfc"], b_mn=True, out=ws["dx2"])
             dx_mid = self._norm_bwd(ws, dxn2, a["x_mid"], p + "norm2", st2, dx, ws["dx"])  # in place over dres
             # ---- attention
-            G.linear_wgrad(dx_mid, a["attn"], out=g[p + "wo"], sumsq=self.sumsq)
+            G.linear_wgrad(dx_mid, a["attn"], out=g[p + "wo"], sumsq=sumsq)
             if cfg.bias:
                 K.colsum_(dx_mid, self._vec(ws, p + "bo"))
             dattn = G.gemm(dx_mid, w[p + "wo"], b_mn=True, out=ws["dattn"])
@@ -254,47 +282,55 @@ class DecoderRuntime:
             A.attention_bwd(dattn, a["qkv"], a["attn"], actx, H, KV, hd, dqkv)
             if cfg.pos == "rope":
                 K.rope_(dqkv, self._rope_table(T), H + KV, hd, backward=True)
-            G.linear_wgrad(dqkv, a["xn"], out=g[p + "wqkv"], sumsq=self.sumsq)
+            G.linear_wgrad(dqkv, a["xn"], out=g[p + "wqkv"], sumsq=sumsq)
             if cfg.bias:
                 K.colsum_(dqkv, self._vec(ws, p + "bqkv"))
             dxn = G.gemm(dqkv, w[p + "wqkv"], b_mn=True, out=ws["dx2"])
             dx = self._norm_bwd(ws, dxn, a["x"], p + "norm1", st1, dx_mid, ws["dx"])
 
         # ---- embeddings
-        K.embedding_bwd_compact(tok, dx, ws["emb"], None if cfg.tie_embeddings else self.sumsq)
+        K.embedding_bwd_compact(tok, dx, emb_ws, None if cfg.tie_embeddings else sumsq)
         if cfg.pos == "learned":
             gw = g["wpe"]
             gw[:T].copy_(dx)
             gw[T:].zero_()
-            K.sumsq_(gw[:T], self.sumsq)
+            K.sumsq_(gw[:T], sumsq)
         if cfg.tie_embeddings:
-            K.embedding_add_rows(tok, ws["emb"], ghead, T)
-            K.sumsq_(ghead, self.sumsq)
+            K.embedding_add_rows(tok, emb_ws, ghead, T)
+            K.sumsq_(ghead, sumsq)
         # ---- vector parameters (norm weights, biases): fp32 rows -> bf16 slots of G, with their norm
         if all(self.layout.slot(n).numel == self._vec_width for n in self._vec_names):
-            K.scatter_rows_cast_sumsq(ws["vec"], self.G, ws["vec_offsets"], self.sumsq)
+            K.scatter_rows_cast_sumsq(ws["vec"], self.Gs[slot], ws["vec_offsets"], sumsq)
         else:
-            self._scatter_vec_rows(ws)
+            self._scatter_vec_rows(ws, slot)
         return ExampleStats(loss=loss, n_tokens=ntok)
 
-    def _scatter_vec_rows(self, ws) -> None:
+    def _scatter_vec_rows(self, ws, slot: int = 0) -> None:
         for n in self._vec_names:
             row = self._vec(ws, n)
-            dst = self.g[n]
+            dst = self.gs[slot][n]
             K.cast_f32_bf16(row, dst)
-            K.sumsq_(dst, self.sumsq)
+            K.sumsq_(dst, self.sumsqs[slot])
 
     # ------------------------------------------------------------------ clip + accumulate
-    def clip_and_accumulate(self, acc: torch.Tensor, clip: float, ws: dict, tok: torch.Tensor, *, auto: bool = False,
-                            gamma: float = 0.01, overwrite: bool = False) -> None:
-        """``acc`` (fp32, full flat layout) ``+= clip_factor * G`` with the conservative storage rounding."""
-        K.clip_scale(self.sumsq, clip, scale_out=self.scale, norm_out=self.norm, counters=self.clip_count, auto=auto,
-                     gamma=gamma, n_leaves=self._n_leaves, widest_leaf=self._widest, reset=True)
-        K.clip_accumulate(self.G, self.scale, acc[: self.layout.dense_total], overwrite=overwrite)
+    def clip_factor(self, clip: float, *, auto: bool = False, gamma: float = 0.01, slot: int = 0) -> None:
+        """Turns the slot's squared norm into the guarded clip factor (device scalar) and resets the accumulator."""
+        K.clip_scale(self.sumsqs[slot], clip, scale_out=self.scales[slot], norm_out=self.norms[slot],
+                     counters=self.clip_count, auto=auto, gamma=gamma, n_leaves=self._n_leaves,
+                     widest_leaf=self._widest, reset=True)
+
+    def accumulate(self, acc: torch.Tensor, ws: dict, tok: torch.Tensor, *, slot: int = 0, overwrite: bool = False) -> None:
+        """``acc`` (fp32, full flat layout) ``+= clip_factor * G[slot]`` with the conservative storage rounding."""
+        K.clip_accumulate(self.Gs[slot], self.scales[slot], acc[: self.layout.dense_total], overwrite=overwrite)
         if not self.cfg.tie_embeddings:
             emb = self.layout.slot("embed")
             acc_emb = acc[emb.offset : emb.offset + emb.numel].view(emb.shape)
-            K.embedding_accumulate(tok, ws["emb"], self.scale, acc_emb, tok.numel())
+            K.embedding_accumulate(tok, ws["embs"][slot], self.scales[slot], acc_emb, tok.numel())
+
+    def clip_and_accumulate(self, acc: torch.Tensor, clip: float, ws: dict, tok: torch.Tensor, *, auto: bool = False,
+                            gamma: float = 0.01, overwrite: bool = False, slot: int = 0) -> None:
+        self.clip_factor(clip, auto=auto, gamma=gamma, slot=slot)
+        self.accumulate(acc, ws, tok, slot=slot, overwrite=overwrite)
 
 
 def init_params_(cfg: DecoderConfig, params: torch.Tensor, layout: Layout, seed: int = 0, std: float = 0.02) -> None:

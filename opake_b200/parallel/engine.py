@@ -18,6 +18,7 @@ gradients.py:150-200) with CPU-generated noise (packages/opake-dpsgd/src/opake/a
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 
 import torch
@@ -81,7 +82,9 @@ class ShardedDPEngine:
             self.blt_state = torch.zeros(nb, self.shard_len, dtype=torch.float32, device=device)
             self.blt_decay = torch.tensor(cfg.blt_decay, dtype=torch.float32, device=device)
             self.blt_scale = torch.tensor(cfg.blt_scale, dtype=torch.float32, device=device)
-        self.runtime = DecoderRuntime(model_cfg, self.params, layout=self.layout, attn_impl=cfg.attn_impl)
+        self.runtime = DecoderRuntime(model_cfg, self.params, layout=self.layout, attn_impl=cfg.attn_impl, n_slots=2)
+        self._side = torch.cuda.Stream(device=device)
+        self._warm: dict[int, bool] = {}
         self.step_count = 0
         self.phi = 0.0
         from ..engine.random import fold_in, key
@@ -93,49 +96,62 @@ class ShardedDPEngine:
         self.graph_kernel_launches = 0   # native launches replayed through CUDA graphs (not seen by the ctypes counter)
 
     # ------------------------------------------------------------------ one example
-    def _example_body(self, ws) -> None:
-        rt = self.runtime
-        st = rt.example_grad(ws["tok"], ws["labels"], ws=ws)
-        ws["loss"].copy_(st.loss.reshape(1))
-        rt.clip_and_accumulate(self.acc, self.cfg.clip_norm, ws, ws["tok"], auto=self.cfg.auto_clip,
-                               gamma=self.cfg.auto_gamma)
-        ws["loss_sum"].add_(ws["loss"])
+    def _example_body(self, ws, slot: int, drain_prev: bool) -> None:
+        """Gradient of the example staged in slot ``slot``; meanwhile (side stream) the clipped accumulation of the
+        previous example, which sits in the other slot. HBM-bound accumulation and tensor-core-bound GEMMs share
+        the SMs, so the accumulation is hidden."""
+        rt, cfg = self.runtime, self.cfg
+        main = torch.cuda.current_stream(self.device)
+        mode = os.environ.get("OPK_ACC_MODE", "overlap")   # diagnostic switch: overlap | serial | off
+        if drain_prev and mode == "serial":
+            rt.accumulate(self.acc, ws, ws["toks"][slot ^ 1], slot=slot ^ 1)
+            drain_prev = False
+        elif mode == "off":
+            drain_prev = False
+        if drain_prev:
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                rt.accumulate(self.acc, ws, ws["toks"][slot ^ 1], slot=slot ^ 1)
+        st = rt.example_grad(ws["toks"][slot], ws["labels"], ws=ws, slot=slot)
+        rt.clip_factor(cfg.clip_norm, auto=cfg.auto_clip, gamma=cfg.auto_gamma, slot=slot)
+        ws["loss_sum"].add_(st.loss.reshape(1))
+        if drain_prev:
+            main.wait_stream(self._side)
 
-    def _run_example(self, tok_host: torch.Tensor, labels_host: torch.Tensor) -> None:
+    def _run_example(self, tok_host: torch.Tensor, labels_host: torch.Tensor, index: int) -> None:
         T = tok_host.numel()
         ws = self.runtime.workspace(T)
-        if "loss_sum" not in ws:
-            ws["loss_sum"] = torch.zeros(1, dtype=torch.float32, device=self.device)
-        ws["tok"].copy_(tok_host, non_blocking=True)
+        slot = index & 1
+        drain = index > 0
+        ws["toks"][slot].copy_(tok_host, non_blocking=True)
         ws["labels"].copy_(labels_host, non_blocking=True)
         if not self.cfg.use_cuda_graph:
-            self._example_body(ws)
+            self._example_body(ws, slot, drain)
             return
-        entry = self._graphs.get(T)
+        key = (T, slot, drain)
+        entry = self._graphs.get(key)
         if entry is None:
-            # warm up eagerly (lazy workspaces, autotuned library state), then capture once per sequence length
-            s = torch.cuda.Stream(device=self.device)
-            s.wait_stream(torch.cuda.current_stream(self.device))
-            with torch.cuda.stream(s):
-                for _ in range(2):
-                    self._example_body(ws)
-            torch.cuda.current_stream(self.device).wait_stream(s)
-            torch.cuda.synchronize(self.device)
-            ws["loss_sum"].zero_()
-            self.acc.zero_()
-            # replay the inputs for the real run after the warm-up consumed them
-            ws["tok"].copy_(tok_host, non_blocking=True)
-            ws["labels"].copy_(labels_host, non_blocking=True)
-            g = torch.cuda.CUDAGraph()
             from ..ops import _lib
 
+            if not self._warm.get(T):
+                # eager warm-up (lazy workspaces, library autotuning) on a side stream, state restored afterwards
+                saved = (ws["loss_sum"].clone(), self.acc.clone() if self.acc.numel() < (1 << 28) else None)
+                s = torch.cuda.Stream(device=self.device)
+                s.wait_stream(torch.cuda.current_stream(self.device))
+                with torch.cuda.stream(s):
+                    self._example_body(ws, slot, False)
+                torch.cuda.current_stream(self.device).wait_stream(s)
+                torch.cuda.synchronize(self.device)
+                ws["loss_sum"].copy_(saved[0])
+                self.runtime.clip_count.zero_()
+                self._warm[T] = True
+            g = torch.cuda.CUDAGraph()
             before = _lib.LAUNCHES[0]
             with torch.cuda.graph(g):
-                self._example_body(ws)
-            self._graphs[T] = (g, _lib.LAUNCHES[0] - before)
-            ws["loss_sum"].zero_()
-            self.acc.zero_()
-            entry = self._graphs[T]
+                self._example_body(ws, slot, drain)
+            entry = (g, _lib.LAUNCHES[0] - before)
+            self._graphs[key] = entry
+            # capture does not execute: fall through to the first replay
         entry[0].replay()
         self.graph_kernel_launches += entry[1]
 
@@ -156,7 +172,10 @@ class ShardedDPEngine:
             ws["loss_sum"] = torch.zeros(1, dtype=torch.float32, device=self.device)
         ws["loss_sum"].zero_()
         for i in range(B_local):
-            self._run_example(tokens[i], labels[i])
+            self._run_example(tokens[i], labels[i], i)
+        last = (B_local - 1) & 1
+        if B_local > 0:
+            self.runtime.accumulate(self.acc, ws, ws["toks"][last], slot=last)   # drain the final example
         loss_sum = ws["loss_sum"].clone()
         self.apply_update()
         return loss_sum
