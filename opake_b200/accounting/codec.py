@@ -22,6 +22,11 @@ def process_to_dict(p: DpProcess) -> dict[str, Any]:
     stack = [(p, root)]
     while stack:
         node, out = stack.pop()
+        custom = lookup_serializer(type(node))
+        if custom is not None and custom[0] is not _generic_save:
+            out.update(custom[0](node))      # classes with their own codec (e.g. strategy-carrying mechanisms)
+            out.setdefault("type", type(node).__name__)
+            continue
         out["type"] = type(node).__name__
         for f in dataclasses.fields(node):
             v = getattr(node, f.name)
