@@ -775,3 +775,54 @@ extern "C" int opk_embedding_add_rows(const int32_t* tok, const int32_t* rep, co
   OPK_LAUNCH_CHECK();
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Allocation-free variant of the compact embedding gradient (declared in opk_noalloc.h).
+// The scratch table is a file-scope device array; host code must not pass its name to a kernel (on the host the name
+// is only a stand-in), so the device address is resolved once per device with cudaGetSymbolAddress.
+#include "opk_noalloc.h"
+
+namespace {
+static __device__ __align__(256) int g_noalloc_first_pos[OPK_NOALLOC_MAX_VOCAB];
+
+__global__ void noalloc_fill_kernel(int* __restrict__ p, int n, int value) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) p[i] = value;
+}
+
+constexpr int kMaxDevices = 64;
+int* g_noalloc_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" int opk_embedding_bwd_compact_noalloc(const int32_t* tok, const void* dx, int32_t* rep, float* gc,
+                                                 double* sumsq, int T, int D, int vocab, void* stream) {
+  if (T < 0 || D <= 0 || vocab <= 0 || !tok || !dx || !rep || !gc) return -1;
+  if (vocab > OPK_NOALLOC_MAX_VOCAB) return -2;
+  if (T == 0) return 0;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return -1;
+  cudaStream_t st = ST(stream);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // one-time set-up for this device: resolve the device address and put every entry into the idle state
+    int* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_first_pos);
+    if (e != cudaSuccess) return (int)e;
+    noalloc_fill_kernel<<<256, 256, 0, st>>>(p, OPK_NOALLOC_MAX_VOCAB, INT_MAX);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_ptr[dev] = p;
+  }
+  int* first_pos = g_noalloc_ptr[dev];
+  e = cudaMemsetAsync(gc, 0, sizeof(float) * (size_t)T * D, st);
+  if (e != cudaSuccess) return (int)e;
+  // entries touched by this call are forced to the idle value first: the table keeps whatever the previous call
+  // (possibly one that was interrupted) left behind
+  emb_reset_kernel<<<(T + 255) / 256, 256, 0, st>>>(tok, first_pos, T);
+  emb_first_pos_kernel<<<(T + 255) / 256, 256, 0, st>>>(tok, first_pos, T);
+  emb_scatter_kernel<<<T, 256, 0, st>>>(tok, BF(dx), first_pos, rep, gc, D);
+  emb_reset_kernel<<<(T + 255) / 256, 256, 0, st>>>(tok, first_pos, T);
+  if (sumsq) sumsq_kernel<true, true><<<grid_for((long long)T * D, NT, 148 * 4), NT, 0, st>>>(gc, (long long)T * D, sumsq);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
