@@ -1,0 +1,35 @@
+"""1-rank vs 2-rank parity of the sharded DP engine (fused P2P reduce-scatter + noise + AdamW + all-gather)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(world: int, out: str, extra=()):
+    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
+    if world == 1:
+        cmd = [sys.executable, "-m", "opake_b200.parallel.selftest", "--out", out, *extra]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+               "--master-addr", "127.0.0.1", "--master-port", "29533", "-m", "opake_b200.parallel.selftest", "--out", out,
+               *extra]
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    return torch.load(out)
+
+
+@pytest.mark.parametrize("blt", [False, True])
+def test_two_ranks_match_one_rank(tmp_path, blt):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    extra = ("--blt",) if blt else ()
+    one = _run(1, str(tmp_path / "w1.pt"), extra)
+    two = _run(2, str(tmp_path / "w2.pt"), extra)
+    assert one["losses"] == pytest.approx(two["losses"], rel=2e-3)
+    diff = (one["params"] - two["params"]).abs().max().item()
+    assert diff <= 2e-2 * one["params"].abs().max().item(), diff
