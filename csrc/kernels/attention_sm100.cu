@@ -1,0 +1,101 @@
+// Host side of the tcgen05 flash-attention kernels: tensor maps over the fused projection buffer and launches.
+#include "attention_sm100.cuh"
+#include "opk_api.h"
+
+#include <cudaTypedefs.h>
+#include <mutex>
+
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encoder() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+  });
+  return fn;
+}
+
+// {cols, rows} bf16 map with a {64, box_rows} box and 128-byte swizzle
+bool map2d(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t ld, uint32_t box_rows) {
+  EncodeFn enc = encoder();
+  if (!enc || (reinterpret_cast<uintptr_t>(base) & 15) || (ld * 2) % 16) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t es[2] = {1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <class K>
+bool set_smem(K kern, int bytes) {
+  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" int opk_attn_fwd(const void* qkv, void* out, float* lse, int T, int H, int KV, int hd, int64_t ld, int64_t ldo,
+                            float scale, int32_t* err, void* stream) {
+  if (T <= 0 || H <= 0 || KV <= 0 || H % KV || (hd != 64 && hd != 128)) return -1;
+  if ((ldo % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) return -1;
+  CUtensorMap tm;
+  if (!map2d(&tm, qkv, (uint64_t)(H + 2 * KV) * hd, (uint64_t)T, (uint64_t)ld, 128)) return -2;
+  opk::AttnParams p{};
+  p.T = T; p.H = H; p.KV = KV; p.hd = hd; p.ld = ld; p.ldo = ldo; p.out = out; p.lse = lse; p.scale = scale; p.err = err;
+  const int grid = ((T + 127) / 128) * H;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (hd == 128) {
+    static bool once = set_smem(opk::attn_fwd_kernel<128>, opk::FwdSmem<128>::BYTES);
+    if (!once) return -3;
+    opk::attn_fwd_kernel<128><<<grid, 192, opk::FwdSmem<128>::BYTES, st>>>(tm, p);
+  } else {
+    static bool once = set_smem(opk::attn_fwd_kernel<64>, opk::FwdSmem<64>::BYTES);
+    if (!once) return -3;
+    opk::attn_fwd_kernel<64><<<grid, 192, opk::FwdSmem<64>::BYTES, st>>>(tm, p);
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int opk_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* dsum, void* dqkv,
+                            int T, int H, int KV, int hd, int64_t ld, int64_t ldo, float scale, int32_t* err,
+                            void* stream) {
+  if (T <= 0 || H <= 0 || KV <= 0 || H % KV || (hd != 64 && hd != 128)) return -1;
+  if ((ld % 8) || (ldo % 8) || (reinterpret_cast<uintptr_t>(dqkv) & 15)) return -1;
+  const uint64_t cols = (uint64_t)(H + 2 * KV) * hd;
+  CUtensorMap tm128, tm64, tmdo64, tmdo128;
+  if (!map2d(&tm128, qkv, cols, (uint64_t)T, (uint64_t)ld, 128)) return -2;
+  if (!map2d(&tm64, qkv, cols, (uint64_t)T, (uint64_t)ld, 64)) return -2;
+  if (!map2d(&tmdo64, dout, (uint64_t)H * hd, (uint64_t)T, (uint64_t)ldo, 64)) return -2;
+  if (!map2d(&tmdo128, dout, (uint64_t)H * hd, (uint64_t)T, (uint64_t)ldo, 128)) return -2;
+  opk::AttnParams p{};
+  p.T = T; p.H = H; p.KV = KV; p.hd = hd; p.ld = ld; p.ldo = ldo; p.lse = const_cast<float*>(lse); p.dsum = dsum;
+  p.dout = dout; p.dqkv = dqkv; p.scale = scale; p.err = err;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const long long warps = (long long)T * H;
+  opk::attn_dsum_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), dsum, T, H, hd, ldo);
+  const int n_kt = (T + 127) / 128;
+  if (hd == 128) {
+    static bool once = set_smem(opk::attn_dkv_kernel<128>, opk::DkvSmem<128>::BYTES) &&
+                       set_smem(opk::attn_dq_kernel<128>, opk::DqSmem<128>::BYTES);
+    if (!once) return -3;
+    opk::attn_dkv_kernel<128><<<n_kt * KV, 192, opk::DkvSmem<128>::BYTES, st>>>(tm128, tm64, tmdo64, p);
+    opk::attn_dq_kernel<128><<<n_kt * H, 192, opk::DqSmem<128>::BYTES, st>>>(tm128, tm64, tmdo128, p);
+  } else {
+    static bool once = set_smem(opk::attn_dkv_kernel<64>, opk::DkvSmem<64>::BYTES) &&
+                       set_smem(opk::attn_dq_kernel<64>, opk::DqSmem<64>::BYTES);
+    if (!once) return -3;
+    opk::attn_dkv_kernel<64><<<n_kt * KV, 192, opk::DkvSmem<64>::BYTES, st>>>(tm128, tm64, tmdo64, p);
+    opk::attn_dq_kernel<64><<<n_kt * H, 192, opk::DqSmem<64>::BYTES, st>>>(tm128, tm64, tmdo128, p);
+  }
+  return (int)cudaGetLastError();
+}

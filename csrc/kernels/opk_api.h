@@ -101,6 +101,14 @@ int opk_embedding_add_rows(const int32_t* tok, const int32_t* rep, const float* 
 // out_bf16 = bf16(in_fp32)
 int opk_cast_f32_bf16(const float* in, void* out, int64_t n, void* stream);
 
+// ---- causal GQA flash attention on the fused projection buffer (csrc/kernels/attention_sm100.cu) -------------
+// qkv bf16 [T][(H+2KV)*hd] (row pitch ld), out bf16 [T][H*hd] (row pitch ldo), lse fp32 [H][T]. hd in {64, 128}.
+int opk_attn_fwd(const void* qkv, void* out, float* lse, int T, int H, int KV, int hd, int64_t ld, int64_t ldo,
+                 float scale, int32_t* err, void* stream);
+// Backward: dqkv (same layout as qkv) receives dQ, dK, dV. dsum is an fp32 [H][T] work buffer (rowsum(dO * O)).
+int opk_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* dsum, void* dqkv, int T,
+                 int H, int KV, int hd, int64_t ld, int64_t ldo, float scale, int32_t* err, void* stream);
+
 // ---- DP clipping / noise / optimizer (csrc/kernels/dp_step.cu) ---------------------------------------------
 // scale = guarded min(1, C / sqrt(sumsq)) (fixed) or R / (sqrt(sumsq) + gamma) (auto); see dp_step.cu.
 // Also: norm_out[0] = sqrt(sumsq), counters[0] += (norm > C), and *sumsq is reset to 0 when reset != 0.

@@ -21,7 +21,8 @@ def _split(qkv: torch.Tensor, H: int, KV: int, hd: int):
 
 
 def have_flash() -> bool:
-    return hasattr(_lib.lib(), "opk_attn_fwd")
+    L = _lib.lib()
+    return hasattr(L, "opk_attn_fwd") and hasattr(L, "opk_attn_bwd")
 
 
 def attention_fwd(qkv: torch.Tensor, H: int, KV: int, hd: int, impl: str = "auto", out: torch.Tensor | None = None):
