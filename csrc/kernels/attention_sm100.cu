@@ -56,20 +56,22 @@ extern "C" int opk_attn_fwd(const void* qkv, void* out, float* lse, int T, int H
   if (hd == 128) {
     static bool once = set_smem(opk::attn_fwd_kernel<128>, opk::FwdSmem<128>::BYTES);
     if (!once) return -3;
-    opk::attn_fwd_kernel<128><<<grid, 192, opk::FwdSmem<128>::BYTES, st>>>(tm, p);
+    opk::attn_fwd_kernel<128><<<grid, opk::kAttnThreads, opk::FwdSmem<128>::BYTES, st>>>(tm, p);
   } else {
     static bool once = set_smem(opk::attn_fwd_kernel<64>, opk::FwdSmem<64>::BYTES);
     if (!once) return -3;
-    opk::attn_fwd_kernel<64><<<grid, 192, opk::FwdSmem<64>::BYTES, st>>>(tm, p);
+    opk::attn_fwd_kernel<64><<<grid, opk::kAttnThreads, opk::FwdSmem<64>::BYTES, st>>>(tm, p);
   }
   return (int)cudaGetLastError();
 }
 
 extern "C" int opk_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* dsum, void* dqkv,
-                            int T, int H, int KV, int hd, int64_t ld, int64_t ldo, float scale, int32_t* err,
+                            float* part, int T, int H, int KV, int hd, int64_t ld, int64_t ldo, float scale, int32_t* err,
                             void* stream) {
   if (T <= 0 || H <= 0 || KV <= 0 || H % KV || (hd != 64 && hd != 128)) return -1;
-  if ((ld % 8) || (ldo % 8) || (reinterpret_cast<uintptr_t>(dqkv) & 15)) return -1;
+  if ((ld % 8) || (ldo % 8) || (reinterpret_cast<uintptr_t>(dqkv) & 15) || (reinterpret_cast<uintptr_t>(dsum) & 15))
+    return -1;
+  const int T64 = (T + 63) / 64 * 64;
   const uint64_t cols = (uint64_t)(H + 2 * KV) * hd;
   CUtensorMap tm128, tm64, tmdo64, tmdo128;
   if (!map2d(&tm128, qkv, cols, (uint64_t)T, (uint64_t)ld, 128)) return -2;
@@ -78,24 +80,36 @@ extern "C" int opk_attn_bwd(const void* qkv, const void* out, const void* dout, 
   if (!map2d(&tmdo128, dout, (uint64_t)H * hd, (uint64_t)T, (uint64_t)ldo, 128)) return -2;
   opk::AttnParams p{};
   p.T = T; p.H = H; p.KV = KV; p.hd = hd; p.ld = ld; p.ldo = ldo; p.lse = const_cast<float*>(lse); p.dsum = dsum;
+  p.nlse2 = dsum + (long long)H * T64; p.T64 = T64;
+  if (part && (reinterpret_cast<uintptr_t>(part) & 15)) return -1;
+  p.part = (H > KV) ? part : nullptr;       // without grouping every CTA already owns its dK / dV tile
+  const int dkv_grid = ((T + 127) / 128) * (p.part ? H : KV);
   p.dout = dout; p.dqkv = dqkv; p.scale = scale; p.err = err;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const long long warps = (long long)T * H;
+  const long long warps = (long long)T64 * H;
   opk::attn_dsum_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(
-      reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), dsum, T, H, hd, ldo);
+      reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), lse, dsum,
+      dsum + (long long)H * T64, T, T64, H, hd, ldo);
   const int n_kt = (T + 127) / 128;
   if (hd == 128) {
     static bool once = set_smem(opk::attn_dkv_kernel<128>, opk::DkvSmem<128>::BYTES) &&
                        set_smem(opk::attn_dq_kernel<128>, opk::DqSmem<128>::BYTES);
     if (!once) return -3;
-    opk::attn_dkv_kernel<128><<<n_kt * KV, 192, opk::DkvSmem<128>::BYTES, st>>>(tm128, tm64, tmdo64, p);
-    opk::attn_dq_kernel<128><<<n_kt * H, 192, opk::DqSmem<128>::BYTES, st>>>(tm128, tm64, tmdo128, p);
+    opk::attn_dkv_kernel<128><<<dkv_grid, opk::kAttnThreads, opk::DkvSmem<128>::BYTES, st>>>(tm128, tm64, tmdo64, p);
+    opk::attn_dq_kernel<128><<<n_kt * H, opk::kAttnThreads, opk::DqSmem<128>::BYTES, st>>>(tm128, tm64, tmdo128, p);
   } else {
     static bool once = set_smem(opk::attn_dkv_kernel<64>, opk::DkvSmem<64>::BYTES) &&
                        set_smem(opk::attn_dq_kernel<64>, opk::DqSmem<64>::BYTES);
     if (!once) return -3;
-    opk::attn_dkv_kernel<64><<<n_kt * KV, 192, opk::DkvSmem<64>::BYTES, st>>>(tm128, tm64, tmdo64, p);
-    opk::attn_dq_kernel<64><<<n_kt * H, 192, opk::DqSmem<64>::BYTES, st>>>(tm128, tm64, tmdo128, p);
+    opk::attn_dkv_kernel<64><<<dkv_grid, opk::kAttnThreads, opk::DkvSmem<64>::BYTES, st>>>(tm128, tm64, tmdo64, p);
+    opk::attn_dq_kernel<64><<<n_kt * H, opk::kAttnThreads, opk::DqSmem<64>::BYTES, st>>>(tm128, tm64, tmdo128, p);
+  }
+  if (p.part) {
+    const int kvw = KV * hd;
+    const long long n4 = (long long)T * (kvw / 4) * 2;
+    const unsigned blocks = (unsigned)((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
+    opk::attn_dkv_reduce_kernel<<<blocks, 256, 0, st>>>(p.part, reinterpret_cast<__nv_bfloat16*>(dqkv), T, H / KV, kvw, ld,
+                                                         H * hd);
   }
   return (int)cudaGetLastError();
 }

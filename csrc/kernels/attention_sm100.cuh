@@ -23,7 +23,10 @@ struct AttnParams {
   void* out;               // fwd: bf16 [T][H*hd]
   float* lse;              // [H][T] natural-log-sum-exp of scaled scores
   const void* dout;        // bwd: bf16 [T][H*hd]
-  const float* dsum;       // bwd: [H][T] rowsum(dO * O)
+  const float* dsum;       // bwd: [H][T64] rowsum(dO * O), T64 = T rounded up to a multiple of 64
+  const float* nlse2;      // bwd: [H][T64] -lse * log2(e), -inf in the padding
+  int T64;
+  float* part;             // bwd, optional: fp32 [2][H/KV][T][KV*hd] partial dK / dV (one CTA per query head)
   void* dqkv;              // bwd: bf16, same layout as qkv
   float scale;             // 1/sqrt(hd)
   int* err;
@@ -59,27 +62,108 @@ __device__ __forceinline__ void issue_product(uint32_t d_tmem, uint32_t a_base, 
   }
 }
 
+// One warp-collective bounded wait: lane 0 polls (acquire), __syncwarp orders the other lanes' later memory reads
+// after it (a shuffle alone is no memory barrier: without the __syncwarp the compiler may hoist a shared-memory
+// load of lanes 1..31 above the wait), then the result is broadcast.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane) {
+  int w = 1;
+  if (lane == 0) w = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+  __syncwarp();
+  return __shfl_sync(0xffffffffu, w, 0) != 0;
+}
+
 // ------------------------------------------------------------------------------------------------ forward
 // CTA = (query tile of 128 rows, head). KV tiles of 128 keys, double-buffered K and V stages, S double-buffered in
-// TMEM, O partials double-buffered in TMEM and folded into register accumulators one iteration late so that the
-// P*V product of tile j overlaps the softmax of tile j+1.
+// TMEM. O accumulates in TMEM across KV tiles; the running maximum is updated lazily: rows are rescaled (TMEM
+// load-multiply-store by the softmax warps) only when their maximum grew by more than 2^8, otherwise the stale
+// maximum stays in use (probabilities may then exceed 1 by at most 2^8, harmless in bf16 / fp32). The softmax of a
+// tile is a single pass over registers: 128 fmax, 128 ffma + ex2.approx, 64 packs, 16 shared stores per thread.
+#ifdef OPK_ATTN_TRACE
+// Debug-only timeline of CTA 0 (clock64 stamps per role / tile / event); never compiled into the library.
+__device__ long long g_attn_trace[3 * 1024];
+#define OPK_TRACE(role, j, e) do { if (blockIdx.x == 0) g_attn_trace[(role) * 1024 + (j) * 8 + (e)] = clock64(); } while (0)
+#else
+#define OPK_TRACE(role, j, e) do { } while (0)
+#endif
+
+constexpr int kSoftmaxWarps = 8;                       // warps 2..9; warps 0 / 1 drive TMA / MMA
+constexpr int kAttnThreads = (2 + kSoftmaxWarps) * 32;
+
 template <int HD>
 struct FwdSmem {
   static constexpr int TILE = 128 * HD * 2;           // bytes of one [128][HD] tile
   static constexpr int Q_OFF = 0;
   static constexpr int K_OFF = TILE;                  // 2 stages
   static constexpr int V_OFF = K_OFF + 2 * TILE;      // 2 stages
-  static constexpr int P_OFF = V_OFF + 2 * TILE;      // [128][128] bf16 = 32 KB
-  static constexpr int BAR_OFF = P_OFF + 128 * 128 * 2;
-  static constexpr int BYTES = BAR_OFF + 256 + 1024;
+  static constexpr int P_OFF = V_OFF + 2 * TILE;      // 2 x [128][128] bf16 = 64 KB
+  static constexpr int P_BYTES = 128 * 128 * 2;
+  static constexpr int BAR_OFF = P_OFF + 2 * P_BYTES;      // 256 B of barriers, then 2 KB of row exchange space
+  static constexpr int USED = BAR_OFF + 256 + 2048;
+  // The tiles need a 1024-byte-aligned base. The launch asks for the per-CTA maximum, which leaves less than 1 KB
+  // of slack; the kernel checks that the alignment padding fits and reports an error otherwise.
+  static constexpr int BYTES = (USED + 1024 <= 232448) ? USED + 1024 : 232448;
 };
 
+// Maximum of 64 scores (columns col0 .. col0+63 of the tile) with four independent chains; MASKED drops columns > r.
+template <bool MASKED>
+__device__ __forceinline__ float row_max64(const uint32_t (&a)[32], const uint32_t (&b)[32], int col0, int r) {
+  float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    if (!MASKED || col0 + i <= r) m0 = fmaxf(m0, __uint_as_float(a[i]));
+    if (!MASKED || col0 + i + 1 <= r) m1 = fmaxf(m1, __uint_as_float(a[i + 1]));
+    if (!MASKED || col0 + 32 + i <= r) m2 = fmaxf(m2, __uint_as_float(b[i]));
+    if (!MASKED || col0 + 33 + i <= r) m3 = fmaxf(m3, __uint_as_float(b[i + 1]));
+  }
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+// Rendezvous of the two warps that share a TMEM lane quarter, on an mbarrier of count 2 (bounded like every wait
+// here; a named bar.sync would hang the partner if one side had given up). Shared-memory writes made before the
+// call are visible to the partner after it.
+__device__ __forceinline__ bool pair_sync(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+  return warp_wait(bar, parity, abort_flag, lane);
+}
+
+// exp2(x * c2 - mc) for 32 columns starting at col0, packed to bf16 and stored swizzled; returns the partial row sum.
+template <bool MASKED>
+__device__ __forceinline__ float softmax_chunk(const uint32_t (&x)[32], int col0, int r, float c2, float mc,
+                                               uint8_t* p_smem) {
+  float sum0 = 0.f, sum1 = 0.f;
+  uint32_t packed[16];
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    float e0 = ex2_approx(fmaf(__uint_as_float(x[i]), c2, -mc));
+    float e1 = ex2_approx(fmaf(__uint_as_float(x[i + 1]), c2, -mc));
+    if (MASKED) {
+      if (col0 + i > r) e0 = 0.f;
+      if (col0 + i + 1 > r) e1 = 0.f;
+    }
+    sum0 += e0;
+    sum1 += e1;
+    packed[i >> 1] = pack_bf16x2(e0, e1);
+  }
+  const float sum = sum0 + sum1;
+  uint8_t* chunk = p_smem + (col0 >> 6) * 16384;
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    *reinterpret_cast<uint4*>(chunk + swz_off(r, (col0 & 63) + q * 8)) =
+        make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+  return sum;
+}
+
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   using SM = FwdSmem<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if ((int)(smem - smem_raw) + SM::USED > SM::BYTES) {   // uniform over the CTA; nothing has been set up yet
+    if (threadIdx.x == 0 && p.err) atomicExch(p.err, 2);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
   uint64_t* q_full = bars + 0;
   uint64_t* k_full = bars + 1;    // [2]
@@ -88,11 +172,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   uint64_t* v_empty = bars + 7;   // [2]
   uint64_t* s_full = bars + 9;    // [2]
   uint64_t* s_free = bars + 11;   // [2]
-  uint64_t* p_full = bars + 13;
-  uint64_t* o_full = bars + 14;   // [2]
-  uint64_t* o_free = bars + 16;   // [2]
+  uint64_t* p_full = bars + 13;   // [2]
+  uint64_t* o_done = bars + 15;   // [2] P*V of a tile has completed (its P buffer is reusable, O is consistent)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint64_t* x_bar = bars + 20;    // [2 tiles][4 quads] pair rendezvous for the row maxima; [8..11]: final row sums
+  float* xchg = reinterpret_cast<float*>(bars + 32);   // [2 tiles][2 halves][128 rows] partial maxima (row sums at the end)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qt = (p.T + 127) / 128;
@@ -107,10 +192,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4);
-      mbar_init(&o_full[i], 1); mbar_init(&o_free[i], 4);
+      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], kSoftmaxWarps);
+      mbar_init(&p_full[i], kSoftmaxWarps); mbar_init(&o_done[i], 1);
     }
-    mbar_init(p_full, 4);
+    for (int i = 0; i < 12; ++i) mbar_init(&x_bar[i], 2);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -119,24 +204,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t S_COL = 0, O_COL = 256;   // S buffers at 0 / 128, O buffers at 256 / 256 + HD
+  const uint32_t S_COL = 0, O_COL = 256;   // S buffers at 0 / 128, O accumulator at 256
 
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tm);
       mbar_expect_tx(q_full, SM::TILE);
       for (int c = 0; c < HD / 64; ++c) tma_load_2d(smem + SM::Q_OFF + c * 16384, &tm, q_full, q_col + c * 64, qt * 128);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_empty[s], ph ^ 1u, abort_flag)) break;
-        mbar_expect_tx(&k_full[s], SM::TILE);
-        for (int c = 0; c < HD / 64; ++c)
-          tma_load_2d(smem + SM::K_OFF + s * SM::TILE + c * 16384, &tm, &k_full[s], k_col + c * 64, j * 128);
-        if (!mbar_wait(&v_empty[s], ph ^ 1u, abort_flag)) break;
-        mbar_expect_tx(&v_full[s], SM::TILE);
-        for (int c = 0; c < HD / 64; ++c)
-          tma_load_2d(smem + SM::V_OFF + s * SM::TILE + c * 16384, &tm, &v_full[s], v_col + c * 64, j * 128);
+      // K(j) is issued one tile ahead of V(j-1): the K stage frees when S(j-2) has completed, well before the V
+      // stage (which waits for P*V of tile j-3), so neither wait holds the other load back.
+      for (int j = 0; j <= n_kv; ++j) {
+        if (j < n_kv) {
+          const int s = j & 1;
+          const uint32_t ph = (j >> 1) & 1;
+          if (!mbar_wait(&k_empty[s], ph ^ 1u, abort_flag)) break;
+          OPK_TRACE(0, j, 0);
+          mbar_expect_tx(&k_full[s], SM::TILE);
+          for (int c = 0; c < HD / 64; ++c)
+            tma_load_2d(smem + SM::K_OFF + s * SM::TILE + c * 16384, &tm, &k_full[s], k_col + c * 64, j * 128);
+        }
+        if (j >= 1) {
+          const int jv = j - 1, s = jv & 1;
+          const uint32_t ph = (jv >> 1) & 1;
+          if (!mbar_wait(&v_empty[s], ph ^ 1u, abort_flag)) break;
+          OPK_TRACE(0, jv, 1);
+          mbar_expect_tx(&v_full[s], SM::TILE);
+          for (int c = 0; c < HD / 64; ++c)
+            tma_load_2d(smem + SM::V_OFF + s * SM::TILE + c * 16384, &tm, &v_full[s], v_col + c * 64, jv * 128);
+        }
       }
     }
     __syncwarp();
@@ -148,7 +243,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(&k_full[s], ph, abort_flag)) return false;
+        OPK_TRACE(1, j, 0);
         if (!mbar_wait(&s_free[s], ph ^ 1u, abort_flag)) return false;
+        OPK_TRACE(1, j, 1);
         tc_fence_after();
         issue_product<false, false>(tmem + S_COL + s * 128, q_s, 128, smem_u32(smem + SM::K_OFF + s * SM::TILE), 128, 128,
                                     HD, false);
@@ -162,146 +259,122 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
         if (!ok) break;
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
+        OPK_TRACE(1, j, 2);
         if (!mbar_wait(&v_full[s], ph, abort_flag)) break;
-        if (!mbar_wait(&o_free[s], ph ^ 1u, abort_flag)) break;
-        if (!mbar_wait(p_full, j & 1, abort_flag)) break;
+        OPK_TRACE(1, j, 3);
+        if (!mbar_wait(&p_full[s], ph, abort_flag)) break;
+        OPK_TRACE(1, j, 4);
         tc_fence_after();
-        // O_j[128 x HD] = P[128 x 128 keys] * V[keys x HD]: B is MN-major (rows = keys)
-        issue_product<false, true>(tmem + O_COL + s * HD, p_s, 128, smem_u32(smem + SM::V_OFF + s * SM::TILE), 128, HD,
-                                   128, false);
+        // O[128 x HD] += P[128 x 128 keys] * V[keys x HD]: B is MN-major (rows = keys)
+        issue_product<false, true>(tmem + O_COL, p_s + s * SM::P_BYTES, 128, smem_u32(smem + SM::V_OFF + s * SM::TILE), 128, HD, 128, j > 0);
         umma_commit(&v_empty[s]);
-        umma_commit(&o_full[s]);
+        umma_commit(&o_done[s]);
+        OPK_TRACE(1, j, 5);
       }
     }
     __syncwarp();
   } else {
+    // 8 softmax warps: warps with the same (warp & 3) share 32 TMEM lanes (rows); `half` selects 64 of the 128 keys.
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;            // row inside the query tile
     const int row = qt * 128 + r;
+    const int col0 = half * 64;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     const float c2 = p.scale * 1.4426950408889634f;
-    float acc[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) acc[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
-    uint8_t* p_smem = smem + SM::P_OFF;
+    float m_run = -INFINITY, l_run = 0.f;      // m_run: maximum in use (possibly stale); l_run: this half's row sum
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int s = j & 1;
       const uint32_t ph = (j >> 1) & 1;
-      int w = 1;
-      if (lane == 0) w = mbar_wait(&s_full[s], ph, abort_flag) ? 1 : 0;
-      w = __shfl_sync(0xffffffffu, w, 0);
-      if (!w) { ok = false; break; }
+      uint8_t* p_smem = smem + SM::P_OFF + s * SM::P_BYTES;
+      if (warp == 2 && lane == 0) OPK_TRACE(2, j, 0);
+      if (!warp_wait(&s_full[s], ph, abort_flag, lane)) { ok = false; break; }
+      if (warp == 2 && lane == 0) OPK_TRACE(2, j, 1);
       tc_fence_after();
-      const bool diag = (j == qt);
-      // pass 1: row maximum
-      float mx = m_run;
-      for (int c0 = 0; c0 < 128; c0 += 32) {
-        uint32_t raw[32];
-        __syncwarp();
-        tmem_ld32(tmem + lane_base + S_COL + s * 128 + c0, raw);
-        tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float v = __uint_as_float(raw[i]);
-          if (!diag || (c0 + i) <= r) mx = fmaxf(mx, v);
-        }
-      }
-      const float alpha = exp2f((m_run - mx) * c2);     // 0 on the first tile (m_run = -inf), 1 if unchanged
-      // P of the previous tile must have been consumed (its P*V finished) before the buffer is overwritten
-      if (j > 0) {
-        int w2 = 1;
-        if (lane == 0) w2 = mbar_wait(&o_full[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag) ? 1 : 0;
-        w2 = __shfl_sync(0xffffffffu, w2, 0);
-        if (!w2) { ok = false; break; }
-      }
-      // pass 2: probabilities -> shared memory (bf16, swizzled), row sum
-      float lsum = 0.f;
-      for (int c0 = 0; c0 < 128; c0 += 32) {
-        uint32_t raw[32];
-        __syncwarp();
-        tmem_ld32(tmem + lane_base + S_COL + s * 128 + c0, raw);
-        tc_wait_ld();
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float e0 = (!diag || (c0 + i) <= r) ? exp2f((__uint_as_float(raw[i]) - mx) * c2) : 0.f;
-          float e1 = (!diag || (c0 + i + 1) <= r) ? exp2f((__uint_as_float(raw[i + 1]) - mx) * c2) : 0.f;
-          // the row sum uses the rounded values that the P*V product will see
-          __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
-          float2 f = __bfloat1622float2(b);
-          lsum += f.x + f.y;
-          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&b);
-        }
-        uint8_t* chunk = p_smem + (c0 >> 6) * 16384;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int c = (c0 & 63) + q * 8;
-          *reinterpret_cast<uint4*>(chunk + swz_off(r, c)) =
-              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-        }
-      }
+      uint32_t x0[32], x1[32];
+      __syncwarp();
+      const uint32_t sa = tmem + lane_base + S_COL + s * 128 + col0;
+      tmem_ld32(sa, x0); tmem_ld32(sa + 32, x1);
+      tc_wait_ld();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[s]);
+      if (lane == 0) mbar_arrive(&s_free[s]);   // S lives in registers now
+      if (warp == 2 && lane == 0) OPK_TRACE(2, j, 2);
+      const bool diag = (j == qt);
+      float mx = diag ? row_max64<true>(x0, x1, col0, r) : row_max64<false>(x0, x1, col0, r);
+      // combine with the other half of the row (through shared memory, 64-thread named barrier)
+      float* xm = xchg + s * 256;
+      xm[half * 128 + r] = mx;
+      if (!pair_sync(&x_bar[s * 4 + quad], ph, abort_flag, lane)) { ok = false; break; }
+      mx = fmaxf(fmaxf(mx, xm[(half ^ 1) * 128 + r]), m_run);
+      if (warp == 2 && lane == 0) OPK_TRACE(2, j, 3);
+      // lazy rescale: adopt the new maximum only if it grew by more than 8 in the exponent domain
+      const bool grow = (mx - m_run) * c2 > 8.f;   // true on the first tile (m_run = -inf)
+      const unsigned any_grow = __ballot_sync(0xffffffffu, grow);
+      // P buffer s was last read by the P*V of tile j-2
+      if (j > 1 && !warp_wait(&o_done[s], ph ^ 1u, abort_flag, lane)) { ok = false; break; }
+      float alpha = 1.f;
+      if (grow) {
+        alpha = ex2_approx((m_run - mx) * c2);     // 0 when m_run = -inf
+        l_run *= alpha;
+        m_run = mx;
+      }
+      if (any_grow && j > 0) {
+        // O may only be touched once the P*V of tile j-1 has completed; the next one waits for this warp's P
+        if (!warp_wait(&o_done[s ^ 1], ((j - 1) >> 1) & 1, abort_flag, lane)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+          uint32_t o[32];
+          __syncwarp();
+          tmem_ld32(tmem + lane_base + O_COL + half * (HD / 2) + c0, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(tmem + lane_base + O_COL + half * (HD / 2) + c0, o);
+        }
+        tc_wait_st();
+      }
+      if (warp == 2 && lane == 0) OPK_TRACE(2, j, 4);
+      const float mc = m_run * c2;
+      if (diag) l_run += softmax_chunk<true>(x0, col0, r, c2, mc, p_smem) + softmax_chunk<true>(x1, col0 + 32, r, c2, mc, p_smem);
+      else l_run += softmax_chunk<false>(x0, col0, r, c2, mc, p_smem) + softmax_chunk<false>(x1, col0 + 32, r, c2, mc, p_smem);
+      if (warp == 2 && lane == 0) OPK_TRACE(2, j, 5);
+      tc_fence_before();
       fence_proxy_async();           // make the generic-proxy writes of P visible to the tensor core
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
-      l_run = l_run * alpha + lsum;
-      m_run = mx;
-      // fold in O of the previous tile (already waited for above): acc = acc * alpha_prev + O_{j-1}
-      if (j > 0) {
-        const int so = (j - 1) & 1;
-        tc_fence_after();
-#pragma unroll
-        for (int c0 = 0; c0 < HD; c0 += 32) {
-          uint32_t raw[32];
-          __syncwarp();
-          tmem_ld32(tmem + lane_base + O_COL + so * HD + c0, raw);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c0 + i] = acc[c0 + i] * alpha_prev + __uint_as_float(raw[i]);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&o_free[so]);
-      }
-      alpha_prev = alpha;
+      if (lane == 0) mbar_arrive(&p_full[s]);
+      if (warp == 2 && lane == 0) OPK_TRACE(2, j, 6);
     }
-    if (ok) {
-      const int so = (n_kv - 1) & 1;
-      int w = 1;
-      if (lane == 0) w = mbar_wait(&o_full[so], ((n_kv - 1) >> 1) & 1, abort_flag) ? 1 : 0;
-      w = __shfl_sync(0xffffffffu, w, 0);
-      if (w) {
-        tc_fence_after();
-        const float inv = 1.f / l_run;
-        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ldo + h * HD;
+    if (ok && warp_wait(&o_done[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort_flag, lane)) {
+      tc_fence_after();
+      // total row sum = both halves (same running maximum on both sides)
+      float* xl = xchg + (n_kv & 1) * 256;      // the buffer the last tile did not use
+      xl[half * 128 + r] = l_run;
+      const bool both = pair_sync(&x_bar[8 + quad], 0, abort_flag, lane);
+      const float l_tot = l_run + xl[(half ^ 1) * 128 + r];
+      const float inv = both ? 1.f / l_tot : 0.f;
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ldo + h * HD + half * (HD / 2);
 #pragma unroll
-        for (int c0 = 0; c0 < HD; c0 += 32) {
-          uint32_t raw[32];
-          __syncwarp();
-          tmem_ld32(tmem + lane_base + O_COL + so * HD + c0, raw);
-          tc_wait_ld();
-          if (row < p.T) {
+      for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+        uint32_t raw[32];
+        __syncwarp();
+        tmem_ld32(tmem + lane_base + O_COL + half * (HD / 2) + c0, raw);
+        tc_wait_ld();
+        if (row < p.T) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 o;
-              uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int i = q * 8 + e * 2;
-                const float a0 = (acc[c0 + i] * alpha_prev + __uint_as_float(raw[i])) * inv;
-                const float a1 = (acc[c0 + i + 1] * alpha_prev + __uint_as_float(raw[i + 1])) * inv;
-                ow[e] = pack_bf16x2(a0, a1);
-              }
-              *reinterpret_cast<uint4*>(orow + c0 + q * 8) = o;
-            }
+          for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(raw[8 * q + 0]) * inv, __uint_as_float(raw[8 * q + 1]) * inv);
+            o.y = pack_bf16x2(__uint_as_float(raw[8 * q + 2]) * inv, __uint_as_float(raw[8 * q + 3]) * inv);
+            o.z = pack_bf16x2(__uint_as_float(raw[8 * q + 4]) * inv, __uint_as_float(raw[8 * q + 5]) * inv);
+            o.w = pack_bf16x2(__uint_as_float(raw[8 * q + 6]) * inv, __uint_as_float(raw[8 * q + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c0 + q * 8) = o;
           }
         }
-        if (row < p.T) p.lse[(long long)h * p.T + row] = m_run * p.scale + logf(l_run);
       }
+      if (half == 0 && row < p.T) p.lse[(long long)h * p.T + row] = m_run * p.scale + logf(l_tot);
     }
   }
   tc_fence_before();
@@ -310,42 +383,47 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, 1);
 }
 
-
 // ------------------------------------------------------------------------------------------------ backward helpers
-// D[h][t] = sum_d dO[t][h*hd + d] * O[t][h*hd + d]
+// Backward preprocessing, one warp per (t, h) with t < T64 (T rounded up to a multiple of 64):
+//   dsum[h][t] = sum_d dO[t][h*hd + d] * O[t][h*hd + d]        nlse2[h][t] = -lse[h][t] * log2(e)
+// Rows t >= T get dsum = 0 and nlse2 = -inf, so that exp2(s * c + nlse2) is exactly 0 for padded queries.
 __global__ void attn_dsum_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
-                                 float* __restrict__ dsum, int T, int H, int hd, long long ldo) {
+                                 const float* __restrict__ lse, float* __restrict__ dsum, float* __restrict__ nlse2,
+                                 int T, int T64, int H, int hd, long long ldo) {
   const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (w >= T * H) return;
+  if (w >= T64 * H) return;
   const int t = w / H, h = w % H;
-  const __nv_bfloat16* a = o + (long long)t * ldo + h * hd;
-  const __nv_bfloat16* b = dout + (long long)t * ldo + h * hd;
+  if (t >= T) {
+    if (lane == 0) { dsum[(long long)h * T64 + t] = 0.f; nlse2[(long long)h * T64 + t] = -INFINITY; }
+    return;
+  }
+  const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(o + (long long)t * ldo + h * hd);
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(dout + (long long)t * ldo + h * hd);
   float s = 0.f;
-  for (int i = lane; i < hd; i += 32) s += __bfloat162float(a[i]) * __bfloat162float(b[i]);
+  for (int i = lane; i < hd / 2; i += 32) {
+    const float2 x = __bfloat1622float2(a[i]), y = __bfloat1622float2(b[i]);
+    s += x.x * y.x + x.y * y.y;
+  }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) dsum[(long long)h * T + t] = s;
+  if (lane == 0) {
+    dsum[(long long)h * T64 + t] = s;
+    nlse2[(long long)h * T64 + t] = -lse[(long long)h * T + t] * 1.4426950408889634f;
+  }
 }
 
-// One warp-collective bounded wait: lane 0 polls, the result is broadcast.
-__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane) {
-  int w = 1;
-  if (lane == 0) w = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
-  return __shfl_sync(0xffffffffu, w, 0) != 0;
-}
-
-// Write 64 packed bf16 values (32 words) of row r into a [128 rows][64 cols] swizzled chunk.
-__device__ __forceinline__ void store_row64(uint8_t* chunk, int r, const uint32_t (&w)[32]) {
+// Write 32 packed bf16 values (16 words) of row r, columns col0 .. col0+31, into a [128 rows][64 cols] swizzled chunk.
+__device__ __forceinline__ void store_row32(uint8_t* chunk, int r, int col0, const uint32_t (&w)[16]) {
 #pragma unroll
-  for (int q = 0; q < 8; ++q)
-    *reinterpret_cast<uint4*>(chunk + swz_off(r, q * 8)) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+  for (int q = 0; q < 4; ++q)
+    *reinterpret_cast<uint4*>(chunk + swz_off(r, col0 + q * 8)) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
 }
 
-// Store one TMEM accumulator row block (HD fp32 columns starting at tmem column `col`) as bf16.
-template <int HD>
-__device__ __forceinline__ void store_acc_rows(uint32_t tmem_addr, __nv_bfloat16* dst, bool valid) {
+// Store NCOLS fp32 accumulator columns of this thread's TMEM lane (starting at tmem_addr) as bf16 to dst.
+template <int NCOLS>
+__device__ __forceinline__ void store_acc_rows(uint32_t tmem_addr, __nv_bfloat16* dst, bool valid, float mul) {
 #pragma unroll
-  for (int c0 = 0; c0 < HD; c0 += 32) {
+  for (int c0 = 0; c0 < NCOLS; c0 += 32) {
     uint32_t raw[32];
     __syncwarp();
     tmem_ld32(tmem_addr + c0, raw);
@@ -354,13 +432,53 @@ __device__ __forceinline__ void store_acc_rows(uint32_t tmem_addr, __nv_bfloat16
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         uint4 o;
-        o.x = pack_bf16x2(__uint_as_float(raw[8 * q + 0]), __uint_as_float(raw[8 * q + 1]));
-        o.y = pack_bf16x2(__uint_as_float(raw[8 * q + 2]), __uint_as_float(raw[8 * q + 3]));
-        o.z = pack_bf16x2(__uint_as_float(raw[8 * q + 4]), __uint_as_float(raw[8 * q + 5]));
-        o.w = pack_bf16x2(__uint_as_float(raw[8 * q + 6]), __uint_as_float(raw[8 * q + 7]));
+        o.x = pack_bf16x2(__uint_as_float(raw[8 * q + 0]) * mul, __uint_as_float(raw[8 * q + 1]) * mul);
+        o.y = pack_bf16x2(__uint_as_float(raw[8 * q + 2]) * mul, __uint_as_float(raw[8 * q + 3]) * mul);
+        o.z = pack_bf16x2(__uint_as_float(raw[8 * q + 4]) * mul, __uint_as_float(raw[8 * q + 5]) * mul);
+        o.w = pack_bf16x2(__uint_as_float(raw[8 * q + 6]) * mul, __uint_as_float(raw[8 * q + 7]) * mul);
         *reinterpret_cast<uint4*>(dst + c0 + q * 8) = o;
       }
     }
+  }
+}
+
+// Same, keeping fp32 (partial results that a later kernel sums).
+template <int NCOLS>
+__device__ __forceinline__ void store_acc_rows_f32(uint32_t tmem_addr, float* dst, bool valid, float mul) {
+#pragma unroll
+  for (int c0 = 0; c0 < NCOLS; c0 += 32) {
+    uint32_t raw[32];
+    __syncwarp();
+    tmem_ld32(tmem_addr + c0, raw);
+    tc_wait_ld();
+    if (valid) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        *reinterpret_cast<float4*>(dst + c0 + q * 4) =
+            make_float4(__uint_as_float(raw[4 * q]) * mul, __uint_as_float(raw[4 * q + 1]) * mul,
+                        __uint_as_float(raw[4 * q + 2]) * mul, __uint_as_float(raw[4 * q + 3]) * mul);
+    }
+  }
+}
+
+// dqkv[t][K | V columns] = bf16(sum over the G partials), summed in index order (deterministic).
+__global__ void attn_dkv_reduce_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ dqkv, int T, int G,
+                                       int kvw, long long ld, int k_col0) {
+  const long long n4 = (long long)T * (kvw / 4) * 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const int which = (int)(i / ((long long)T * (kvw / 4)));          // 0 = dK, 1 = dV
+    const long long rem = i - (long long)which * T * (kvw / 4);
+    const int t = (int)(rem / (kvw / 4)), c = (int)(rem % (kvw / 4)) * 4;
+    const float* src = part + ((long long)which * G * T + t) * kvw + c;
+    float4 a = *reinterpret_cast<const float4*>(src);
+    for (int gq = 1; gq < G; ++gq) {
+      const float4 b = *reinterpret_cast<const float4*>(src + (long long)gq * T * kvw);
+      a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+    uint2 o;
+    o.x = pack_bf16x2(a.x, a.y);
+    o.y = pack_bf16x2(a.z, a.w);
+    *reinterpret_cast<uint2*>(dqkv + (long long)t * ld + k_col0 + (long long)which * kvw + c) = o;
   }
 }
 
@@ -380,12 +498,38 @@ struct DkvSmem {
   static constexpr int DO_OFF = Q_OFF + 2 * Q_TILE;       // 2 stages
   static constexpr int PT_OFF = DO_OFF + 2 * Q_TILE;      // [128][64] bf16
   static constexpr int DST_OFF = PT_OFF + 16384;
-  static constexpr int BAR_OFF = DST_OFF + 16384;
+  static constexpr int ROW_OFF = DST_OFF + 16384;         // 2 stages x (64 nlse2 + 64 dsum) floats
+  static constexpr int BAR_OFF = ROW_OFF + 2 * 512;
   static constexpr int BYTES = BAR_OFF + 256 + 1024;
 };
 
+// One 32-query chunk of the transposed backward softmax for a key row: Pt = exp2(St*c2 + nlse2[q]) and
+// dSt = Pt * (dPt - D[q]) (the softmax scale is applied when dK is stored). `kd` = key - first query of the chunk.
+template <bool MASKED>
+__device__ __forceinline__ void dkv_chunk(const uint32_t (&sraw)[32], const uint32_t (&draw)[32], const float4* nl4,
+                                          const float4* d4, float c2, int kd, uint32_t* pw, uint32_t* dw) {
+#pragma unroll
+  for (int e = 0; e < 32; e += 4) {
+    const float4 L = nl4[e >> 2], D = d4[e >> 2];
+    float p0 = ex2_approx(fmaf(__uint_as_float(sraw[e + 0]), c2, L.x));
+    float p1 = ex2_approx(fmaf(__uint_as_float(sraw[e + 1]), c2, L.y));
+    float p2 = ex2_approx(fmaf(__uint_as_float(sraw[e + 2]), c2, L.z));
+    float p3 = ex2_approx(fmaf(__uint_as_float(sraw[e + 3]), c2, L.w));
+    if (MASKED) {
+      if (e + 0 < kd) p0 = 0.f;
+      if (e + 1 < kd) p1 = 0.f;
+      if (e + 2 < kd) p2 = 0.f;
+      if (e + 3 < kd) p3 = 0.f;
+    }
+    pw[(e >> 1) + 0] = pack_bf16x2(p0, p1);
+    pw[(e >> 1) + 1] = pack_bf16x2(p2, p3);
+    dw[(e >> 1) + 0] = pack_bf16x2(p0 * (__uint_as_float(draw[e + 0]) - D.x), p1 * (__uint_as_float(draw[e + 1]) - D.y));
+    dw[(e >> 1) + 1] = pack_bf16x2(p2 * (__uint_as_float(draw[e + 2]) - D.z), p3 * (__uint_as_float(draw[e + 3]) - D.w));
+  }
+}
+
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kAttnThreads, 1)
 attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_q,
                 const __grid_constant__ CUtensorMap tm_do, const AttnParams p) {
   using SM = DkvSmem<HD>;
@@ -404,21 +548,27 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.H / p.KV;
-  const int g = blockIdx.x % p.KV;
-  const int kt = blockIdx.x / p.KV;                      // low key tiles (most work) first
+  // Two work splits: one CTA per (key tile, KV head) that loops over the G query heads of the group and stores
+  // bf16 results directly; or, with a partial buffer, one CTA per (key tile, query head) that stores fp32 partials
+  // which a second kernel sums in a fixed order (4x more CTAs: the causal triangle balances far better).
+  const bool split = p.part != nullptr;
+  const int per_kt = split ? p.H : p.KV;
+  const int kt = blockIdx.x / per_kt;                    // low key tiles (most work) first
+  const int g = split ? (int)(blockIdx.x % per_kt) / G : (int)(blockIdx.x % per_kt);
+  const int h_first = split ? (int)(blockIdx.x % per_kt) : g * G;
   const int n_q64 = (p.T + 63) / 64;
   const int q_first = 2 * kt;
   const int per_head = n_q64 - q_first;
-  const int n_it = per_head * G;
+  const int n_it = per_head * (split ? 1 : G);
   const int k_col = (p.H + g) * HD, v_col = (p.H + p.KV + g) * HD;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1);
-      mbar_init(&st_full[i], 1); mbar_init(&st_free[i], 4);
+      mbar_init(&st_full[i], 1); mbar_init(&st_free[i], kSoftmaxWarps);
     }
-    mbar_init(pd_full, 4);
+    mbar_init(pd_full, kSoftmaxWarps);
     mbar_init(pd_free, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -442,9 +592,11 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
       for (int i = 0; i < n_it; ++i) {
         const int s = i & 1;
         const uint32_t ph = (i >> 1) & 1;
-        const int h = g * G + i / per_head, q64 = q_first + i % per_head;
+        const int h = h_first + i / per_head, q64 = q_first + i % per_head;
         if (!mbar_wait(&q_empty[s], ph ^ 1u, abort_flag)) break;
-        mbar_expect_tx(&q_full[s], 2 * SM::Q_TILE);
+        mbar_expect_tx(&q_full[s], 2 * SM::Q_TILE + 512);
+        bulk_load_1d(smem + SM::ROW_OFF + s * 512, p.nlse2 + (long long)h * p.T64 + q64 * 64, 256, &q_full[s]);
+        bulk_load_1d(smem + SM::ROW_OFF + s * 512 + 256, p.dsum + (long long)h * p.T64 + q64 * 64, 256, &q_full[s]);
         for (int c = 0; c < HD / 64; ++c) {
           tma_load_2d(smem + SM::Q_OFF + s * SM::Q_TILE + c * 8192, &tm_q, &q_full[s], h * HD + c * 64, q64 * 64);
           tma_load_2d(smem + SM::DO_OFF + s * SM::Q_TILE + c * 8192, &tm_do, &q_full[s], h * HD + c * 64, q64 * 64);
@@ -486,60 +638,60 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
     }
     __syncwarp();
   } else {
+    // 8 softmax warps: (warp & 3) picks the 32 key rows (TMEM lanes), `half` 32 of the 64 queries of the sub-tile
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const int key = kt * 128 + r;
+    const int c0 = half * 32;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     const float c2 = p.scale * 1.4426950408889634f;
     bool ok = true;
     for (int i = 0; i < n_it && ok; ++i) {
       const int s = i & 1;
       const uint32_t ph = (i >> 1) & 1;
-      const int h = g * G + i / per_head, q64 = q_first + i % per_head;
+      const int q64 = q_first + i % per_head;
       if (!warp_wait(&st_full[s], ph, abort_flag, lane)) { ok = false; break; }
       tc_fence_after();
-      const float* lse_h = p.lse + (long long)h * p.T;
-      const float* ds_h = p.dsum + (long long)h * p.T;
-      uint32_t pw[32], dw[32];
-#pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 32) {
+      // the row vectors of this stage arrived with Q / dO; the phase has completed already (the scores needed it),
+      // the wait only orders this warp's shared-memory reads after the bulk copy
+      if (!warp_wait(&q_full[s], ph, abort_flag, lane)) { ok = false; break; }
+      const float4* nl4 = reinterpret_cast<const float4*>(smem + SM::ROW_OFF + s * 512) + (c0 >> 2);
+      const float4* d4 = nl4 + 16;
+      const bool masked = (q64 - q_first) < 2;
+      uint32_t pw[16], dw[16];
+      {
         uint32_t sraw[32], draw[32];
         __syncwarp();
         tmem_ld32(tmem + lane_base + ST_COL + s * 64 + c0, sraw);
         tmem_ld32(tmem + lane_base + DPT_COL + s * 64 + c0, draw);
         tc_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int q = q64 * 64 + c0 + e + u;
-            const bool live = (q < p.T) && (q >= key) && (key < p.T);
-            const float l = live ? __ldg(lse_h + q) : 0.f;
-            const float dd = live ? __ldg(ds_h + q) : 0.f;
-            const float pr = live ? exp2f(__uint_as_float(sraw[e + u]) * c2 - l * 1.4426950408889634f) : 0.f;
-            pv[u] = pr;
-            dv[u] = pr * (__uint_as_float(draw[e + u]) - dd) * p.scale;
-          }
-          pw[(c0 + e) >> 1] = pack_bf16x2(pv[0], pv[1]);
-          dw[(c0 + e) >> 1] = pack_bf16x2(dv[0], dv[1]);
-        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&st_free[s]);     // scores are in registers
+        if (masked) dkv_chunk<true>(sraw, draw, nl4, d4, c2, key - (q64 * 64 + c0), pw, dw);
+        else dkv_chunk<false>(sraw, draw, nl4, d4, c2, 0, pw, dw);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&st_free[s]);
       if (i > 0 && !warp_wait(pd_free, (i - 1) & 1, abort_flag, lane)) { ok = false; break; }
-      store_row64(smem + SM::PT_OFF, r, pw);
-      store_row64(smem + SM::DST_OFF, r, dw);
+      store_row32(smem + SM::PT_OFF, r, c0, pw);
+      store_row32(smem + SM::DST_OFF, r, c0, dw);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(pd_full);
     }
     if (ok && warp_wait(pd_free, (n_it - 1) & 1, abort_flag, lane)) {
       tc_fence_after();
-      __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.dqkv) + (long long)key * p.ld;
-      store_acc_rows<HD>(tmem + lane_base + DV_COL, base + v_col, key < p.T);
-      store_acc_rows<HD>(tmem + lane_base + DK_COL, base + k_col, key < p.T);
+      if (split) {
+        const long long kvw = (long long)p.KV * HD;
+        float* pk = p.part + ((long long)(h_first % G) * p.T + key) * kvw + g * HD + half * (HD / 2);
+        float* pv = pk + (long long)G * p.T * kvw;
+        store_acc_rows_f32<HD / 2>(tmem + lane_base + DK_COL + half * (HD / 2), pk, key < p.T, p.scale);
+        store_acc_rows_f32<HD / 2>(tmem + lane_base + DV_COL + half * (HD / 2), pv, key < p.T, 1.f);
+      } else {
+        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.dqkv) + (long long)key * p.ld + half * (HD / 2);
+        store_acc_rows<HD / 2>(tmem + lane_base + DV_COL + half * (HD / 2), base + v_col, key < p.T, 1.f);
+        store_acc_rows<HD / 2>(tmem + lane_base + DK_COL + half * (HD / 2), base + k_col, key < p.T, p.scale);
+      }
     }
   }
   tc_fence_before();
@@ -564,8 +716,25 @@ struct DqSmem {
   static constexpr int BYTES = BAR_OFF + 256 + 1024;
 };
 
+// One 32-key chunk of the backward softmax for a query row: dS = exp2(S*c2 + nlse2) * (dP - D); keys with local
+// index above `lim` are masked (causal diagonal).
+template <bool MASKED>
+__device__ __forceinline__ void dq_chunk(const uint32_t (&sraw)[32], const uint32_t (&draw)[32], float c2, float nl,
+                                         float d, int lim, uint32_t* dw) {
+#pragma unroll
+  for (int e = 0; e < 32; e += 2) {
+    float p0 = ex2_approx(fmaf(__uint_as_float(sraw[e]), c2, nl));
+    float p1 = ex2_approx(fmaf(__uint_as_float(sraw[e + 1]), c2, nl));
+    if (MASKED) {
+      if (e > lim) p0 = 0.f;
+      if (e + 1 > lim) p1 = 0.f;
+    }
+    dw[e >> 1] = pack_bf16x2(p0 * (__uint_as_float(draw[e]) - d), p1 * (__uint_as_float(draw[e + 1]) - d));
+  }
+}
+
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kAttnThreads, 1)
 attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                const __grid_constant__ CUtensorMap tm_do, const AttnParams p) {
   using SM = DqSmem<HD>;
@@ -594,9 +763,9 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4);
+      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], kSoftmaxWarps);
     }
-    mbar_init(ds_full, 4);
+    mbar_init(ds_full, kSoftmaxWarps);
     mbar_init(ds_free, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -661,54 +830,47 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
     __syncwarp();
   } else {
+    // 8 softmax warps: (warp & 3) picks the 32 query rows (TMEM lanes), `half` 32 of the 64 keys of the sub-tile
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const int qrow = qt * 128 + r;
+    const int c0 = half * 32;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     const float c2 = p.scale * 1.4426950408889634f;
     const bool qvalid = qrow < p.T;
-    const float lse_r = qvalid ? p.lse[(long long)h * p.T + qrow] * 1.4426950408889634f : 0.f;
-    const float d_r = qvalid ? p.dsum[(long long)h * p.T + qrow] : 0.f;
+    const float nl_r = qvalid ? p.nlse2[(long long)h * p.T64 + qrow] : -INFINITY;   // invalid rows give P = 0
+    const float d_r = qvalid ? p.dsum[(long long)h * p.T64 + qrow] : 0.f;
     bool ok = true;
     for (int i = 0; i < n_it && ok; ++i) {
       const int s = i & 1;
       const uint32_t ph = (i >> 1) & 1;
       if (!warp_wait(&s_full[s], ph, abort_flag, lane)) { ok = false; break; }
       tc_fence_after();
-      uint32_t dw[32];
-#pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 32) {
+      uint32_t dw[16];
+      const bool masked = i >= 2 * qt;          // the two sub-tiles on the causal diagonal
+      {
         uint32_t sraw[32], draw[32];
         __syncwarp();
         tmem_ld32(tmem + lane_base + S_COL + s * 64 + c0, sraw);
         tmem_ld32(tmem + lane_base + DP_COL + s * 64 + c0, draw);
         tc_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float dv[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int key = i * 64 + c0 + e + u;
-            const bool live = qvalid && key <= qrow;
-            const float pr = live ? exp2f(__uint_as_float(sraw[e + u]) * c2 - lse_r) : 0.f;
-            dv[u] = pr * (__uint_as_float(draw[e + u]) - d_r) * p.scale;
-          }
-          dw[(c0 + e) >> 1] = pack_bf16x2(dv[0], dv[1]);
-        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free[s]);      // scores are in registers
+        if (masked) dq_chunk<true>(sraw, draw, c2, nl_r, d_r, qrow - (i * 64 + c0), dw);
+        else dq_chunk<false>(sraw, draw, c2, nl_r, d_r, 0, dw);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[s]);
       if (i > 0 && !warp_wait(ds_free, (i - 1) & 1, abort_flag, lane)) { ok = false; break; }
-      store_row64(smem + SM::DS_OFF, r, dw);
+      store_row32(smem + SM::DS_OFF, r, c0, dw);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(ds_full);
     }
     if (ok && warp_wait(ds_free, (n_it - 1) & 1, abort_flag, lane)) {
       tc_fence_after();
-      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.dqkv) + (long long)qrow * p.ld + q_col;
-      store_acc_rows<HD>(tmem + lane_base + DQ_COL, dst, qvalid);
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.dqkv) + (long long)qrow * p.ld + q_col + half * (HD / 2);
+      store_acc_rows<HD / 2>(tmem + lane_base + DQ_COL + half * (HD / 2), dst, qvalid, p.scale);
     }
   }
   tc_fence_before();

@@ -102,63 +102,98 @@ __global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __
   }
 }
 
-// Backward: one warp per row (two passes over the L1-resident row, shuffle reductions only). The weight gradient
-// is accumulated per CTA in shared memory and flushed once with global atomics.
+// RMSNorm backward. A CTA of 512 threads walks rows with a grid stride; every thread owns the same columns for
+// all rows (ITERS vectors of 8), so the weight gradient accumulates in registers without atomics and is written once
+// per CTA to partial[blockIdx][D]. A second kernel adds the column sums of `partial` into dw.
 constexpr int MAX_COL_ITERS = 8;  // layernorm backward: D <= 8 * 2048
-constexpr int RMS_BWD_WARPS = 8;
-__global__ void __launch_bounds__(RMS_BWD_WARPS * 32) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
-                                                                        const __nv_bfloat16* __restrict__ x,
-                                                                        const __nv_bfloat16* __restrict__ w,
-                                                                        const float* __restrict__ rstd,
-                                                                        const __nv_bfloat16* __restrict__ dres,
-                                                                        __nv_bfloat16* __restrict__ dx,
-                                                                        float* __restrict__ dw, int T, int D,
-                                                                        float w_off) {
-  extern __shared__ float sdw[];  // [D]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+constexpr int RMS_BWD_NT = 512;
+template <int ITERS>
+__global__ void __launch_bounds__(RMS_BWD_NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                                 const __nv_bfloat16* __restrict__ x,
+                                                                 const __nv_bfloat16* __restrict__ w,
+                                                                 const float* __restrict__ rstd,
+                                                                 const __nv_bfloat16* __restrict__ dres,
+                                                                 __nv_bfloat16* __restrict__ dx,
+                                                                 float* __restrict__ partial, int T, int D,
+                                                                 float w_off) {
+  __shared__ float sh[32];
   const int nv = D >> 3;
-  if (dw) {
-    for (int i = threadIdx.x; i < D; i += blockDim.x) sdw[i] = 0.f;
-    __syncthreads();
+  float wv[ITERS][8], acc[ITERS][8];
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int v = threadIdx.x + it * RMS_BWD_NT;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { acc[it][j] = 0.f; wv[it][j] = 0.f; }
+    if (v < nv) {
+      unpack8(reinterpret_cast<const bf16x8*>(w)[v], wv[it]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) wv[it][j] += w_off;
+    }
   }
-  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
-  for (long long row = (long long)blockIdx.x * RMS_BWD_WARPS + warp; row < T; row += (long long)gridDim.x * RMS_BWD_WARPS) {
+  for (long long row = blockIdx.x; row < T; row += gridDim.x) {
     const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + row * D);
     const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * D);
     const float rs = rstd[row];
+    float g[ITERS][8], xv[ITERS][8];
     float dot = 0.f;
-    for (int i = lane; i < nv; i += 32) {
-      float g[8], xv[8], wv[8];
-      unpack8(dyr[i], g);
-      unpack8(xr[i], xv);
-      unpack8(wr[i], wv);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) dot += g[j] * (wv[j] + w_off) * xv[j];
+    for (int it = 0; it < ITERS; ++it) {
+      const int v = threadIdx.x + it * RMS_BWD_NT;
+      if (v < nv) {
+        unpack8(dyr[v], g[it]);
+        unpack8(xr[v], xv[it]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dot += g[it][j] * wv[it][j] * xv[it][j];
+      }
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    const float mean_dot = dot * rs / (float)D;
+    const float mean_dot = block_sum<RMS_BWD_NT>(dot, sh) * rs / (float)D;
     const bf16x8* drr = dres ? reinterpret_cast<const bf16x8*>(dres + row * D) : nullptr;
     bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + row * D);
-    for (int i = lane; i < nv; i += 32) {
-      float g[8], xv[8], wv[8], o[8];
-      unpack8(dyr[i], g);
-      unpack8(xr[i], xv);
-      unpack8(wr[i], wv);
-      if (drr) unpack8(drr[i], o);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float xh = xv[j] * rs;
-        const float d = rs * (g[j] * (wv[j] + w_off) - xh * mean_dot);
-        o[j] = drr ? o[j] + d : d;
-        if (dw) atomicAdd(&sdw[i * 8 + j], g[j] * xh);
+    for (int it = 0; it < ITERS; ++it) {
+      const int v = threadIdx.x + it * RMS_BWD_NT;
+      if (v < nv) {
+        float o[8];
+        if (drr) unpack8(drr[v], o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = xv[it][j] * rs;
+          const float d = rs * (g[it][j] * wv[it][j] - xh * mean_dot);
+          o[j] = drr ? o[j] + d : d;
+          acc[it][j] += g[it][j] * xh;
+        }
+        dxr[v] = pack8(o);
       }
-      dxr[i] = pack8(o);
     }
   }
-  if (dw) {
-    __syncthreads();
-    for (int i = threadIdx.x; i < D; i += blockDim.x) atomicAdd(&dw[i], sdw[i]);
+  if (partial) {
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int v = threadIdx.x + it * RMS_BWD_NT;
+      if (v < nv) {
+        float4* dst = reinterpret_cast<float4*>(partial + (long long)blockIdx.x * D + v * 8);
+        dst[0] = make_float4(acc[it][0], acc[it][1], acc[it][2], acc[it][3]);
+        dst[1] = make_float4(acc[it][4], acc[it][5], acc[it][6], acc[it][7]);
+      }
+    }
+  }
+}
+
+// dst[c] += sum_r partial[r][c]; CTA = 32 columns x 8 row groups.
+__global__ void __launch_bounds__(256) colsum_add_kernel(const float* __restrict__ partial, float* __restrict__ dst,
+                                                         int rows, int D) {
+  __shared__ float sh[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
+  float s = 0.f;
+  if (c < D)
+    for (int r = ry; r < rows; r += 8) s += partial[(long long)r * D + c];
+  sh[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && c < D) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k) s += sh[k][cx];
+    dst[c] += s;
   }
 }
 
@@ -601,14 +636,26 @@ extern "C" int opk_add_rmsnorm_fwd(const void* x, const void* r, const void* w, 
   return 0;
 }
 extern "C" int opk_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
-                               void* dx_out, float* dw, int T, int D, float w_offset, void* stream) {
+                               void* dx_out, float* dw, float* workspace, int ws_rows, int T, int D, float w_offset,
+                               void* stream) {
   if (T <= 0) return 0;
-  if (D % 8 || D > 12288) return -1;
-  int grid = (T + RMS_BWD_WARPS - 1) / RMS_BWD_WARPS;
-  if (grid > 148 * 2) grid = 148 * 2;
-  rmsnorm_bwd_kernel<<<grid, RMS_BWD_WARPS * 32, sizeof(float) * D, ST(stream)>>>(BF(dy), BF(x), BF(w), rstd, BF(dres),
-                                                                                   BFM(dx_out), dw, T, D, w_offset);
+  if (D % 8 || D > 3 * RMS_BWD_NT * 8) return -1;
+  if (dw && (!workspace || ws_rows < 1)) return -1;
+  int grid = T < 148 * 2 ? T : 148 * 2;
+  if (dw && grid > ws_rows) grid = ws_rows;
+  float* part = dw ? workspace : nullptr;
+  const int iters = (D / 8 + RMS_BWD_NT - 1) / RMS_BWD_NT;
+  if (iters == 1)
+    rmsnorm_bwd_kernel<1><<<grid, RMS_BWD_NT, 0, ST(stream)>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx_out), part, T, D, w_offset);
+  else if (iters == 2)
+    rmsnorm_bwd_kernel<2><<<grid, RMS_BWD_NT, 0, ST(stream)>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx_out), part, T, D, w_offset);
+  else
+    rmsnorm_bwd_kernel<3><<<grid, RMS_BWD_NT, 0, ST(stream)>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx_out), part, T, D, w_offset);
   OPK_LAUNCH_CHECK();
+  if (dw) {
+    colsum_add_kernel<<<(D + 31) / 32, 256, 0, ST(stream)>>>(part, dw, grid, D);
+    OPK_LAUNCH_CHECK();
+  }
   return 0;
 }
 extern "C" int opk_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int T,

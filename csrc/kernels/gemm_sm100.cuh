@@ -211,6 +211,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t tph = (it >> 1) & 1;
       int ok = 1;
       if (lane == 0) ok = mbar_wait(&tfull[buf], tph, abort_flag) ? 1 : 0;
+      __syncwarp();   // orders the other lanes' accesses after lane 0's acquire (a shuffle is no memory barrier)
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       tc_fence_after();

@@ -49,8 +49,10 @@ int opk_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, i
 int opk_add_rmsnorm_fwd(const void* x, const void* r, const void* w, void* sum_out, void* y, float* rstd, int T, int D,
                         float eps, float w_offset, void* stream);
 // dx_out = dres (optional) + d(rmsnorm)/dx ; dw[D] (fp32) += sum_t dy * xhat.  dw must be zeroed by the caller.
+// workspace: fp32 [ws_rows][D] scratch for per-CTA partial weight gradients (needed when dw is given; 296 rows
+// let the kernel use its full grid). Calls that share a workspace must be ordered on one stream.
 int opk_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx_out,
-                    float* dw, int T, int D, float w_offset, void* stream);
+                    float* dw, float* workspace, int ws_rows, int T, int D, float w_offset, void* stream);
 // LayerNorm (GPT-2): y = (x - mean) * rstd * w + b
 int opk_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int T, int D,
                       float eps, void* stream);
@@ -105,9 +107,13 @@ int opk_cast_f32_bf16(const float* in, void* out, int64_t n, void* stream);
 // qkv bf16 [T][(H+2KV)*hd] (row pitch ld), out bf16 [T][H*hd] (row pitch ldo), lse fp32 [H][T]. hd in {64, 128}.
 int opk_attn_fwd(const void* qkv, void* out, float* lse, int T, int H, int KV, int hd, int64_t ld, int64_t ldo,
                  float scale, int32_t* err, void* stream);
-// Backward: dqkv (same layout as qkv) receives dQ, dK, dV. dsum is an fp32 [H][T] work buffer (rowsum(dO * O)).
-int opk_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* dsum, void* dqkv, int T,
-                 int H, int KV, int hd, int64_t ld, int64_t ldo, float scale, int32_t* err, void* stream);
+// Backward: dqkv (same layout as qkv) receives dQ, dK, dV. dsum is a 16-byte-aligned fp32 work buffer of
+// 2 * H * T64 elements, T64 = T rounded up to a multiple of 64 (rowsum(dO * O), then -lse * log2 e).
+// part (optional, 16-byte aligned, 2 * (H/KV) * T * KV*hd floats): with grouped-query attention the dK / dV kernel
+// then runs one CTA per query head, writes fp32 partials there and a reduce kernel sums them in a fixed order.
+int opk_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* dsum, void* dqkv,
+                 float* part, int T, int H, int KV, int hd, int64_t ld, int64_t ldo, float scale, int32_t* err,
+                 void* stream);
 
 // ---- DP clipping / noise / optimizer (csrc/kernels/dp_step.cu) ---------------------------------------------
 // scale = guarded min(1, C / sqrt(sumsq)) (fixed) or R / (sqrt(sumsq) + gamma) (auto); see dp_step.cu.

@@ -22,7 +22,7 @@ class DpStepArgs(Structure):
 PROTOTYPES: dict = {
     "opk_rmsnorm_fwd": (I, [P, P, P, P, I, I, F, F, P]),
     "opk_add_rmsnorm_fwd": (I, [P, P, P, P, P, P, I, I, F, F, P]),
-    "opk_rmsnorm_bwd": (I, [P, P, P, P, P, P, P, I, I, F, P]),
+    "opk_rmsnorm_bwd": (I, [P, P, P, P, P, P, P, P, I, I, I, F, P]),
     "opk_layernorm_fwd": (I, [P, P, P, P, P, P, I, I, F, P]),
     "opk_layernorm_bwd": (I, [P, P, P, P, P, P, P, P, P, I, I, P]),
     "opk_rope": (I, [P, P, P, I, I, I, L, F, P]),

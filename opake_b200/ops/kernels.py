@@ -53,12 +53,28 @@ def add_rmsnorm_fwd(x, r, w, eps: float = 1e-6, w_offset: float = 0.0):
     return s, y, rstd
 
 
+_RMS_WS: dict = {}
+_RMS_WS_ROWS = 296
+
+
+def _rms_workspace(device, D: int) -> torch.Tensor:
+    """Per-device scratch for the per-CTA partial weight gradients of the norm backward kernel. Calls on one device
+    share it, so they must be ordered on one stream (the model runtimes issue every example on a single stream)."""
+    key = device.index
+    ws = _RMS_WS.get(key)
+    if ws is None or ws.numel() < _RMS_WS_ROWS * D:
+        ws = torch.empty(_RMS_WS_ROWS * D, dtype=torch.float32, device=device)
+        _RMS_WS[key] = ws
+    return ws
+
+
 def rmsnorm_bwd(dy, x, w, rstd, dres=None, dw=None, w_offset: float = 0.0, out=None):
     """Returns ``dx`` (plus ``dres`` when given); accumulates the weight gradient into fp32 ``dw`` when given."""
     T, D = x.shape
     dx = torch.empty_like(x) if out is None else out
-    _chk(_L().opk_rmsnorm_bwd(_p(dy), _p(x), _p(w), _p(rstd), _p(dres), _p(dx), _p(dw), T, D, w_offset, _s(x)),
-         "rmsnorm_bwd")
+    ws = _rms_workspace(x.device, D) if dw is not None else None
+    _chk(_L().opk_rmsnorm_bwd(_p(dy), _p(x), _p(w), _p(rstd), _p(dres), _p(dx), _p(dw), _p(ws), _RMS_WS_ROWS, T, D,
+                              w_offset, _s(x)), "rmsnorm_bwd")
     return dx
 
 

@@ -33,8 +33,9 @@ def test_flash_forward(cuda, T, H, KV, hd):
     assert (out.float() - o_ref).abs().max().item() < 3e-2 * o_ref.abs().max().item() + 1e-3
 
 
+@pytest.mark.parametrize("split", [True, False])
 @pytest.mark.parametrize("T,H,KV,hd", [(128, 2, 1, 128), (384, 4, 2, 128), (300, 4, 4, 64), (1024, 8, 2, 128)])
-def test_flash_backward(cuda, T, H, KV, hd):
+def test_flash_backward(cuda, T, H, KV, hd, split):
     from opake_b200.ops import attention as A
     from opake_b200.ops._lib import raise_if_device_error
 
@@ -47,7 +48,7 @@ def test_flash_backward(cuda, T, H, KV, hd):
     dout = (torch.randn(T, H * hd, device=cuda) * 0.5).to(torch.bfloat16)
     out, lse = flash_fwd(qkv, H, KV, hd)
     dqkv = torch.full_like(qkv, float("nan"))
-    flash_bwd(dout, qkv, out, lse, H, KV, hd, dqkv)
+    flash_bwd(dout, qkv, out, lse, H, KV, hd, dqkv, split_heads=split)
     raise_if_device_error(cuda)
     x, o_ref, _ = _ref(qkv, H, KV, hd)
     o_ref.backward(dout.float())
