@@ -115,6 +115,17 @@ int opk_attn_bwd(const void* qkv, const void* out, const void* dout, const float
                  float* part, int T, int H, int KV, int hd, int64_t ld, int64_t ldo, float scale, int32_t* err,
                  void* stream);
 
+// ---- multi-tensor clip-and-sum of materialised per-example gradients (csrc/kernels/clip_sum.cu) -----------------
+// `tiles`: device array of n_tiles descriptors {const void* base; float* out; int64 n; int64 off; int32 is_bf16; int32 pad}
+// (opk_clip_sum_desc_bytes() bytes each), one per opk_clip_sum_tile() elements of one example of one leaf.
+int opk_clip_sum_tile(void);
+int opk_clip_sum_desc_bytes(void);
+// partial[b][tile] = sum of squares (fp32 squares, fp64 sum) of that tile of example b.
+int opk_clip_sumsq_partial(const void* tiles, int n_tiles, int B, double* partial, void* stream);
+// out[i] = sum_b stored(g_b[i] * f[b]) per leaf; post_partial (optional) [b][tile] = squared norm after clipping.
+int opk_clip_apply_sum(const void* tiles, int n_tiles, int B, const float* f_bf16, const float* f_fp32,
+                       double* post_partial, void* stream);
+
 // ---- DP clipping / noise / optimizer (csrc/kernels/dp_step.cu) ---------------------------------------------
 // scale = guarded min(1, C / sqrt(sumsq)) (fixed) or R / (sqrt(sumsq) + gamma) (auto); see dp_step.cu.
 // Also: norm_out[0] = sqrt(sumsq), counters[0] += (norm > C), and *sumsq is reset to 0 when reset != 0.

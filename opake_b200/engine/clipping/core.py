@@ -168,6 +168,12 @@ def clipped_fun(fun: Callable, has_aux: bool = False, *, batch_argnums=0, clippi
             norms = torch.sqrt(sum(v * v for v in group_norms.values()))
             mask = masks
         else:
+            fused = get_fused_clip_backend()
+            if (fused is not None and _scale_fn is None and builtin.kind != "auto" and not second_moment
+                    and compute_dtype is None and not isinstance(norm_value, torch.Tensor) and fused.supported(leaves)):
+                # CUDA: two multi-tensor kernels replace the per-leaf square / scale / sum passes
+                sums, norms, mask, cn = fused.fused_clip_sum(leaves, float(norm_value), with_postsq=return_aux)
+                return td, sums, None, norms, mask, cn, None
             sq = sum(N.per_example_sq(l, sqd) for l in leaves)
             if _scale_fn is not None:
                 norms = torch.sqrt(sq)

@@ -39,6 +39,10 @@ PROTOTYPES: dict = {
     "opk_cross_entropy_fwd": (I, [P, I, P, P, P, I, I, L, F, F, P]),
     "opk_cross_entropy_bwd": (I, [P, I, P, P, P, P, I, I, L, F, F, P]),
     "opk_sumsq": (I, [P, I, I, L, P, P]),
+    "opk_clip_sum_tile": (I, []),
+    "opk_clip_sum_desc_bytes": (I, []),
+    "opk_clip_sumsq_partial": (I, [P, I, I, P, P]),
+    "opk_clip_apply_sum": (I, [P, I, I, P, P, P, P]),
     "opk_scatter_rows_cast_sumsq": (I, [P, P, P, I, I, P, P]),
     "opk_colsum": (I, [P, P, I, I, L, P]),
     "opk_embedding_add_rows": (I, [P, P, P, P, I, I, P]),

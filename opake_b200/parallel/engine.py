@@ -204,6 +204,33 @@ class ShardedDPEngine:
         self.acc.zero_()
         self.step_count += 1
 
+    # ------------------------------------------------------------------ checkpointing
+    def state_dict(self) -> dict:
+        """This rank's shard of the training state (parameters are replicated, so rank 0's copy suffices for them)."""
+        out = {"step_count": self.step_count, "phi": float(self.phi), "shard_begin": self.shard_begin,
+               "shard_len": self.shard_len, "world": self.world, "m": self.m.cpu(), "v": self.v.cpu(),
+               "master": None if self.master is None else self.master.cpu(),
+               "blt_state": None if self.blt_state is None else self.blt_state.cpu(),
+               "noise_key": {"seed": self._noise_key.seed, "impl": self._noise_key.impl}}
+        if self.rank == 0:
+            out["params"] = self.params.cpu()
+        return out
+
+    def load_state_dict(self, sd: dict, params: torch.Tensor | None = None) -> None:
+        if sd["world"] != self.world or sd["shard_len"] != self.shard_len:
+            raise ValueError(f"engine checkpoint was written with world size {sd['world']} (shard {sd['shard_len']}); "
+                             f"this run has world size {self.world} (shard {self.shard_len})")
+        self.step_count, self.phi = int(sd["step_count"]), float(sd["phi"])
+        self.m.copy_(sd["m"])
+        self.v.copy_(sd["v"])
+        if self.master is not None and sd.get("master") is not None:
+            self.master.copy_(sd["master"])
+        if self.blt_state is not None and sd.get("blt_state") is not None:
+            self.blt_state.copy_(sd["blt_state"])
+        p = sd.get("params") if params is None else params
+        if p is not None:
+            self.params.copy_(p)
+
     def _rotate(self, ptrs: list[int]) -> list[int]:
         """This rank's buffer first, then the peers starting at rank+1 (spreads NVLink traffic across peers)."""
         r = self.rank

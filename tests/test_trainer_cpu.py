@@ -1,0 +1,211 @@
+"""DPTrainer / SFTTrainer / DPOTrainer, TrainingArguments, checkpoints and patches on CPU."""
+import os
+
+import pytest
+import torch
+from torch import nn
+
+
+class _Net(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.l1, self.l2 = nn.Linear(8, 16), nn.Linear(16, 3)
+
+    def forward(self, x, labels=None):
+        return {"logits": self.l2(torch.tanh(self.l1(x)))}
+
+
+class _DS(torch.utils.data.Dataset):
+    def __init__(self, n, seed=0):
+        g = torch.Generator().manual_seed(seed)
+        self.x = torch.randn(n, 8, generator=g)
+        self.y = (self.x[:, 0] > 0).long() + (self.x[:, 1] > 0).long()
+
+    def __len__(self):
+        return len(self.x)
+
+    def __getitem__(self, i):
+        return {"x": self.x[i], "labels": self.y[i]}
+
+
+def _args(out, **kw):
+    from opake_b200.transformers import TrainingArguments
+    base = dict(output_dir=str(out), per_device_train_batch_size=32, max_steps=8, learning_rate=0.05, optim="adamw-bc",
+                privacy_target_epsilon=6.0, logging_steps=4, save_steps=4, eval_strategy="steps", eval_steps=4, use_cpu=True,
+                lr_scheduler="cosine", warmup_steps=2, save_total_limit=2, use_compat_patches=False)
+    base.update(kw)
+    return TrainingArguments(**base)
+
+
+def test_training_arguments_validation_and_hf_conversion():
+    from opake_b200.base.exceptions import ConfigurationError
+    from opake_b200.transformers import TrainingArguments
+    a = TrainingArguments(privacy_noise_mechanism="mf_band")
+    assert a.resolved_sampling_mode == "cyclic_poisson" and a.resolved_mechanism_kwargs == {"bands": 16} and a.is_dpftrl
+    assert TrainingArguments().target_delta(10_000) == pytest.approx(10_000 ** -1.1)
+    with pytest.raises(ConfigurationError):
+        TrainingArguments(privacy_noise_mechanism="mf_blt", sampling_mode="poisson")
+    with pytest.raises(ConfigurationError):
+        TrainingArguments(privacy_target_epsilon=1.0, privacy_noise_multiplier=1.0)
+    with pytest.raises(ConfigurationError):
+        TrainingArguments(torch_compile=True)
+    b = TrainingArguments.from_hf({"per_device_train_batch_size": 4, "gradient_accumulation_steps": 8, "max_grad_norm": 0.5,
+                                   "optim": "adamw_torch_fused", "lr_scheduler_type": "cosine", "warmup_ratio": 0.1},
+                                  privacy_target_epsilon=8.0)
+    assert (b.per_device_train_batch_size, b.microbatch_size, b.clipping_norm, b.optim, b.lr_scheduler) == (32, 4, 0.5, "adamw", "cosine")
+    with pytest.raises(ConfigurationError):
+        TrainingArguments.from_hf({"deepspeed": "ds.json"})
+    assert TrainingArguments.from_dict(b.to_dict()).to_dict() == b.to_dict()
+
+
+def test_dp_trainer_trains_checkpoints_and_resumes_bit_exactly(tmp_path):
+    from opake_b200.transformers import DPTrainer
+    from opake_b200.transformers.checkpoint import load_runtime
+    torch.manual_seed(0)
+    tr = DPTrainer(_Net(), _args(tmp_path), train_dataset=_DS(600), eval_dataset=_DS(100, 1))
+    out = tr.train()
+    assert out.global_step == 8 and out.metrics["privacy_epsilon"] == pytest.approx(6.0, abs=1e-3)
+    names = sorted(os.listdir(tmp_path))
+    assert names == ["checkpoint-4", "checkpoint-8"]
+    files = set(os.listdir(tmp_path / "checkpoint-8"))
+    assert {"accountant.json", "dp_optimizer.pt", "dp_state.pt", "rng_state.pth", "trainer_state.json", "training_args.bin"} <= files
+    rt = load_runtime(str(tmp_path / "checkpoint-8" / "dp_state.pt"))
+    assert rt.version == 8 and rt.mechanism_kind == "gaussian" and rt.total_steps == 8 and rt.sampler_state
+    final = {k: v.clone() for k, v in tr.model.state_dict().items()}
+    torch.manual_seed(0)
+    tr2 = DPTrainer(_Net(), _args(tmp_path), train_dataset=_DS(600), eval_dataset=_DS(100, 1))
+    out2 = tr2.train(resume_from_checkpoint=str(tmp_path / "checkpoint-4"))
+    assert out2.global_step == 8
+    for k, v in tr2.model.state_dict().items():
+        assert torch.equal(v, final[k]), k           # sampler replay + noise counter + optimizer state all restored
+    assert tr2.privacy_spent() == pytest.approx(tr.privacy_spent(), rel=1e-9)
+    pred = tr.predict(_DS(40, 2))
+    assert pred.predictions.shape == (40, 3) and "test_loss" in pred.metrics
+
+
+def test_resume_refuses_privacy_relevant_drift_for_horizon_runs(tmp_path):
+    from opake_b200.base.exceptions import CheckpointError
+    from opake_b200.transformers import DPTrainer
+    kw = dict(privacy_noise_mechanism="mf_band", privacy_noise_mechanism_kwargs={"bands": 2}, privacy_target_epsilon=None,
+              privacy_noise_multiplier=1.0, eval_strategy="no", per_device_train_batch_size=16)
+    tr = DPTrainer(_Net(), _args(tmp_path, **kw), train_dataset=_DS(400))
+    tr.train()
+    kw2 = dict(kw, privacy_noise_multiplier=2.0)
+    tr2 = DPTrainer(_Net(), _args(tmp_path, **kw2), train_dataset=_DS(400))
+    with pytest.raises(CheckpointError):
+        tr2.train(resume_from_checkpoint=str(tmp_path / "checkpoint-4"))
+
+
+def test_callbacks_and_early_stop(tmp_path):
+    from opake_b200.transformers import DPTrainer, TrainerCallback
+    seen = []
+
+    class Stop(TrainerCallback):
+        def on_step_end(self, args, state, control, **kw):
+            seen.append(state.global_step)
+            if state.global_step == 3:
+                control.should_training_stop = True
+            return control
+
+    tr = DPTrainer(_Net(), _args(tmp_path, save_strategy="no", eval_strategy="no"), train_dataset=_DS(300), callbacks=[Stop()])
+    assert tr.train().global_step == 3 and seen == [1, 2, 3]
+
+
+def test_sft_and_dpo_trainers_on_native_model(tmp_path):
+    from opake_b200.models.config import tiny_llama
+    from opake_b200.models.native import NativeCausalLM
+    from opake_b200.transformers import DPOConfig, DPOTrainer, SFTConfig, SFTTrainer
+    cfg = tiny_llama(n_layers=1, d_model=64, n_heads=2, n_kv_heads=1, head_dim=32, ffn=128, vocab_size=128)
+
+    class LM(torch.utils.data.Dataset):
+        def __len__(self):
+            return 64
+
+        def __getitem__(self, i):
+            g = torch.Generator().manual_seed(i)
+            n = int(torch.randint(6, 14, (1,), generator=g))
+            return {"input_ids": torch.randint(0, 128, (n,), generator=g).tolist(), "completion_mask": [0] * 3 + [1] * (n - 3)}
+
+    common = dict(output_dir=str(tmp_path), per_device_train_batch_size=8, max_steps=2, privacy_noise_multiplier=1.0, use_cpu=True,
+                  save_strategy="no", max_length=16, use_compat_patches=False, logging_steps=1)
+    m = NativeCausalLM(cfg)
+    before = m.flat.detach().clone()
+    out = SFTTrainer(m, SFTConfig(completion_only_loss=True, **common), train_dataset=LM()).train()
+    assert out.global_step == 2 and not torch.equal(m.flat.detach(), before) and out.metrics["privacy_epsilon"] > 0
+
+    class Pref(torch.utils.data.Dataset):
+        def __len__(self):
+            return 48
+
+        def __getitem__(self, i):
+            g = torch.Generator().manual_seed(i)
+            p, c, r = (torch.randint(0, 128, (k,), generator=g).tolist() for k in (4, 3, 5))
+            return {"chosen_input_ids": p + c, "rejected_input_ids": p + r, "chosen_completion_mask": [0] * 4 + [1] * 3,
+                    "rejected_completion_mask": [0] * 4 + [1] * 5}
+
+    t = DPOTrainer(NativeCausalLM(cfg), None, DPOConfig(loss_type=["sigmoid", "sft"], loss_weights=[1.0, 0.1], **common),
+                   train_dataset=Pref(), eval_dataset=Pref())
+    assert "ref_chosen_logps" in t.train_dataset[0]
+    assert t.train().global_step == 2 and "eval_loss" in t.evaluate()
+
+
+def test_hf_weight_mapping_and_patches_roundtrip():
+    transformers = pytest.importorskip("transformers")
+    from opake_b200 import patches
+    from opake_b200.models.native import NativeCausalLM
+    torch.manual_seed(0)
+    hf = transformers.LlamaForCausalLM(transformers.LlamaConfig(vocab_size=96, hidden_size=32, intermediate_size=64,
+                                                                 num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                                                                 max_position_embeddings=32)).eval()
+    ids = torch.randint(0, 96, (2, 11))
+    with torch.no_grad():
+        want = hf(ids).logits
+    native = NativeCausalLM.from_hf(hf)
+    with torch.no_grad():
+        assert (native(ids)["logits"] - want).abs().max() < 1e-5
+    hf2 = transformers.LlamaForCausalLM(hf.config)
+    hf2.load_state_dict(native.to_hf_state_dict(), strict=False)
+    with torch.no_grad():
+        assert (hf2(ids).logits - want).abs().max() < 1e-5
+    rep = patches.apply_model_patches(hf)
+    assert rep["family"] == "llama" and rep["norms"] == 5 and rep["mlps"] == 2 and patches.is_runtime_patched()
+    with torch.no_grad():
+        assert (hf(ids).logits - want).abs().max() < 1e-5
+    assert len(patches.FAMILIES) >= 27 and patches.FAMILIES["olmoe"].moe
+
+
+def test_lora_functions_vmap_and_ghost_norms():
+    from opake_b200.patches.kernels.lora import lora_grad_sq_norms, lora_linear
+    from opake_b200.patches.peft import apply_peft_model_patches, inject_lora
+    torch.manual_seed(0)
+    W, A, B = torch.randn(20, 16), torch.randn(4, 16), torch.randn(20, 4)
+    xb = torch.randn(5, 7, 16)
+    loss = lambda A, B, x: lora_linear(x, W, A, B, 0.5).pow(2).sum()
+    ref = lambda A, B, x: (x @ W.t() + 0.5 * (x @ A.t()) @ B.t()).pow(2).sum()
+    gA, gB = torch.func.vmap(torch.func.grad(loss, argnums=(0, 1)), in_dims=(None, None, 0))(A, B, xb)
+    rA, rB = torch.func.vmap(torch.func.grad(ref, argnums=(0, 1)), in_dims=(None, None, 0))(A, B, xb)
+    assert torch.allclose(gA, rA, atol=1e-4) and torch.allclose(gB, rB, atol=1e-4)
+    dy = 2 * (xb @ W.t() + 0.5 * (xb @ A.t()) @ B.t())
+    na, nb = lora_grad_sq_norms(xb, dy, A, B, 0.5)
+    assert torch.allclose(na, rA.pow(2).sum((1, 2)), rtol=1e-4) and torch.allclose(nb, rB.pow(2).sum((1, 2)), rtol=1e-4)
+    net = nn.Sequential()
+    net.q_proj, net.other = nn.Linear(16, 16), nn.Linear(16, 16)
+    assert inject_lora(net, ("q_proj",)) == 1 and apply_peft_model_patches(net) == 1
+    assert [n for n, p in net.named_parameters() if p.requires_grad] == ["q_proj.lora_A.default.weight", "q_proj.lora_B.default.weight"]
+
+
+def test_moe_routes_agree_and_checkpoint_segment():
+    from opake_b200.patches.kernels.moe import dense_moe, grouped_moe, moe_dispatch_plan
+    from opake_b200.patches.torch_checkpoint import checkpoint_under_vmap
+    torch.manual_seed(0)
+    T, d, I, E, k = 37, 16, 24, 6, 2
+    x, gu, dn = torch.randn(T, d), torch.randn(E, 2 * I, d) * 0.2, torch.randn(E, d, I) * 0.2
+    w, idx = torch.topk(torch.randn(T, E).softmax(-1), k)
+    assert torch.allclose(dense_moe(x, gu, dn, idx, w), grouped_moe(x, gu, dn, idx, w), atol=1e-5)
+    assert moe_dispatch_plan(4096, 2048, 1024, 64, 8) == "grouped"
+    wt = torch.randn(3)
+    seg = lambda w_, x_: torch.tanh(x_ * w_).sum()
+    f = lambda w_, x_: checkpoint_under_vmap(seg, w_, x_)
+    g1 = torch.func.vmap(torch.func.grad(f), in_dims=(None, 0))(wt, torch.ones(4, 3))
+    g2 = torch.func.vmap(torch.func.grad(seg), in_dims=(None, 0))(wt, torch.ones(4, 3))
+    assert torch.allclose(g1, g2)
