@@ -37,6 +37,28 @@ __device__ __forceinline__ float load_elem(const TileDesc& t, long long idx) {
                    : reinterpret_cast<const float*>(t.base)[idx];
 }
 
+// Eight consecutive elements starting at idx (`valid` of them exist). Vector loads when the address allows it.
+__device__ __forceinline__ void load8(const TileDesc& t, long long idx, long long valid, bool vec, float (&x)[8]) {
+  if (vec && valid >= 8) {
+    if (t.is_bf16) {
+      const uint4 v = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(t.base) + idx));
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); x[2 * j] = f.x; x[2 * j + 1] = f.y; }
+    } else {
+      const float4 a = __ldcs(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(t.base) + idx));
+      const float4 b = __ldcs(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(t.base) + idx + 4));
+      x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = j < valid ? load_elem(t, idx + j) : 0.f;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    if (!isfinite(x[j])) x[j] = 0.f;           // NaN / Inf are sanitised to zero before clipping
+}
+
 __device__ __forceinline__ double block_sum_f64(double v, double* sh) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -57,14 +79,17 @@ __global__ void __launch_bounds__(CS_THREADS) sumsq_partial_kernel(const TileDes
   const int b = blockIdx.y;
   const long long base = (long long)b * t.n + t.off;
   const long long lim = t.n - t.off;
+  // vector loads need 16-byte aligned rows: the leaf base is, so the example stride must be a multiple of 8 elements
+  const bool vec = (t.n & 7) == 0 && (reinterpret_cast<uintptr_t>(t.base) & 15) == 0;
   double acc = 0.0;
-#pragma unroll 4
-  for (int k = 0; k < CS_PER_THREAD; ++k) {
-    const long long i = (long long)k * CS_THREADS + threadIdx.x;
+#pragma unroll
+  for (int k = 0; k < CS_PER_THREAD / 8; ++k) {
+    const long long i = ((long long)k * CS_THREADS + threadIdx.x) * 8;
     if (i < lim) {
-      float x = load_elem(t, base + i);
-      if (!isfinite(x)) x = 0.f;             // NaN / Inf are sanitised to zero before clipping
-      acc += (double)(x * x);
+      float x[8];
+      load8(t, base + i, lim - i, vec, x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc += (double)(x[j] * x[j]);
     }
   }
   const double s = block_sum_f64(acc, sh);
@@ -87,6 +112,7 @@ __global__ void __launch_bounds__(CS_THREADS) apply_sum_kernel(const TileDesc* _
   const TileDesc t = tiles[blockIdx.x];
   const long long lim = t.n - t.off;
   const float* fac = t.is_bf16 ? f_bf16 : f_fp32;
+  const bool vec = (t.n & 7) == 0 && (reinterpret_cast<uintptr_t>(t.base) & 15) == 0;
   float acc[CS_PER_THREAD];
 #pragma unroll
   for (int k = 0; k < CS_PER_THREAD; ++k) acc[k] = 0.f;
@@ -95,14 +121,17 @@ __global__ void __launch_bounds__(CS_THREADS) apply_sum_kernel(const TileDesc* _
     const long long base = (long long)b * t.n + t.off;
     double post = 0.0;
 #pragma unroll
-    for (int k = 0; k < CS_PER_THREAD; ++k) {
-      const long long i = (long long)k * CS_THREADS + threadIdx.x;
+    for (int k = 0; k < CS_PER_THREAD / 8; ++k) {
+      const long long i = ((long long)k * CS_THREADS + threadIdx.x) * 8;
       if (i < lim) {
-        float x = load_elem(t, base + i);
-        if (!isfinite(x)) x = 0.f;
-        const float st = store_round(x * f, t.is_bf16);
-        acc[k] += st;
-        if (POSTSQ) post += (double)(st * st);
+        float x[8];
+        load8(t, base + i, lim - i, vec, x);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float st = store_round(x[j] * f, t.is_bf16);
+          acc[k * 8 + j] += st;
+          if (POSTSQ) post += (double)(st * st);
+        }
       }
     }
     if (POSTSQ) {
@@ -111,9 +140,11 @@ __global__ void __launch_bounds__(CS_THREADS) apply_sum_kernel(const TileDesc* _
     }
   }
 #pragma unroll
-  for (int k = 0; k < CS_PER_THREAD; ++k) {
-    const long long i = (long long)k * CS_THREADS + threadIdx.x;
-    if (i < lim) t.out[t.off + i] = acc[k];
+  for (int k = 0; k < CS_PER_THREAD / 8; ++k) {
+    const long long i = ((long long)k * CS_THREADS + threadIdx.x) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (i + j < lim) t.out[t.off + i + j] = acc[k * 8 + j];
   }
 }
 

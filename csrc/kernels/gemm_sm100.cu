@@ -104,13 +104,16 @@ extern "C" int opk_gemm(const OpkGemmArgs* a, void* stream) {
   const int bn = pick_bn(a->N, a->epilogue);
   CUtensorMap ta, tb;
   // A: K-major -> {K, M, batch} box {64, 128}; MN-major -> {M, K, batch} box {64, 64}
+  if (a->tile_group && (a->batch != 1 || a->n_groups <= 0)) { set_err("opk_gemm: tile_group needs batch == 1 and n_groups"); return -1; }
+  if (a->tile_group && a->group_k) { set_err("opk_gemm: tile_group and group_k are exclusive"); return -1; }
+  const int abatch = a->group_k ? 1 : a->batch;
   if (a->a_mn) {
-    if (!make_map(&ta, a->A, a->M, a->K, a->batch, a->lda, a->strideA, 64)) return -2;
+    if (!make_map(&ta, a->A, a->M, a->K, abatch, a->lda, a->strideA, 64)) return -2;
   } else {
-    if (!make_map(&ta, a->A, a->K, a->M, a->batch, a->lda, a->strideA, 128)) return -2;
+    if (!make_map(&ta, a->A, a->K, a->M, abatch, a->lda, a->strideA, 128)) return -2;
   }
   const int bdiv = a->b_batch_div > 0 ? a->b_batch_div : 1;
-  const int bbatch = (a->batch + bdiv - 1) / bdiv;
+  const int bbatch = a->tile_group ? a->n_groups : (a->group_k ? 1 : (a->batch + bdiv - 1) / bdiv);
   if (a->b_mn) {
     if (!make_map(&tb, a->B, a->N, a->K, bbatch, a->ldb, a->strideB, 64)) return -2;
   } else {
@@ -123,6 +126,7 @@ extern "C" int opk_gemm(const OpkGemmArgs* a, void* stream) {
   p.alpha = a->alpha; p.sumsq = a->sumsq; p.act = a->act; p.ld_act = a->ld_act; p.labels = a->labels;
   p.pmax = a->pmax; p.psum = a->psum; p.tgt = a->tgt; p.lse = a->lse; p.coef = a->coef; p.softcap = a->softcap;
   p.err = a->err;
+  p.tile_group = a->tile_group; p.group_k = a->group_k; p.sumsq_stride = a->sumsq_shared ? 0 : 1;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int key = (a->a_mn ? 1 : 0) | (a->b_mn ? 2 : 0);
   const int mc = a->max_ctas;

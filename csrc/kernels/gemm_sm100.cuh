@@ -46,6 +46,15 @@ struct GemmParams {
   const float* coef;     // EPI_LCE_BWD: [M] per-row scale (mask / divisor * upstream grad)
   float softcap;         // EPI_LCE_*: 0 = off, else z = cap * tanh(z / cap)
   int* err;              // set to 1 when a bounded wait expired
+  // Grouped modes (mixture-of-experts), both driven by small device-side tables so that data-dependent group sizes
+  // need no host synchronisation and the launch stays capturable in a CUDA graph:
+  //  * tile_group[m_tile] (forward / dgrad): A and C are ONE row-grouped matrix, every 128-row tile belongs to one
+  //    group; B is batched and the tile uses B[tile_group[m_tile]]; tiles marked -1 are skipped.
+  //  * group_k[2*b] / group_k[2*b+1] (wgrad): first reduction element and number of 64-element blocks of batch entry
+  //    b inside the un-batched operands, i.e. C[b] = A[:, k0:k0+len]^T-style reduction over that group's rows.
+  const int* tile_group;
+  const int* group_k;
+  int sumsq_stride;      // EPI_SUMSQ accumulator index = b * sumsq_stride (0: all batch entries share sumsq[0])
 };
 
 template <int BN>
@@ -141,17 +150,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int r = tile - b * per_batch;
         const int tn = r / tiles_m;
         const int tm = r - tn * tiles_m;
-        const int bb = b / p.b_batch_div;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        int bb = b / p.b_batch_div, ba = b;
+        int kb0 = 0, nkb = kblocks;
+        if (p.tile_group) {
+          bb = p.tile_group[tm];
+          if (bb < 0) continue;
+        }
+        if (p.group_k) { kb0 = p.group_k[2 * b] / BK; nkb = p.group_k[2 * b + 1]; ba = 0; bb = 0; }
+        for (int kq = 0; kq < nkb; ++kq) {
+          const int kb = kb0 + kq;
           if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
           mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
           if (A_MN) {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_3d(sa + j * (BK * 128), &tmA, &full[s], tm * BM + j * 64, kb * BK, b);
+            for (int j = 0; j < BM / 64; ++j) tma_load_3d(sa + j * (BK * 128), &tmA, &full[s], tm * BM + j * 64, kb * BK, ba);
           } else {
-            tma_load_3d(sa, &tmA, &full[s], kb * BK, tm * BM, b);
+            tma_load_3d(sa, &tmA, &full[s], kb * BK, tm * BM, ba);
           }
           if (B_MN) {
 #pragma unroll
@@ -172,13 +188,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t ph = 0;
       bool ok = true;
       int it = 0;
-      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++it) {
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+        int nkb = kblocks;
+        if (p.tile_group || p.group_k) {
+          const int b = tile / per_batch;
+          const int r = tile - b * per_batch;
+          const int tm = r - (r / tiles_m) * tiles_m;
+          if (p.tile_group && p.tile_group[tm] < 0) continue;
+          if (p.group_k) nkb = p.group_k[2 * b + 1];
+        }
         const int buf = it & 1;
         const uint32_t tph = (it >> 1) & 1;
+        ++it;
         if (!mbar_wait(&tempty[buf], tph ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
@@ -202,13 +227,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ epilogue (4 warps, one TMEM lane quadrant each)
     const int quad = warp & 3;
     int it = 0;
-    for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
       const int b = tile / per_batch;
       const int r = tile - b * per_batch;
       const int tn = r / tiles_m;
       const int tm = r - tn * tiles_m;
+      if (p.tile_group && p.tile_group[tm] < 0) continue;
       const int buf = it & 1;
       const uint32_t tph = (it >> 1) & 1;
+      ++it;
       int ok = 1;
       if (lane == 0) ok = mbar_wait(&tfull[buf], tph, abort_flag) ? 1 : 0;
       __syncwarp();   // orders the other lanes' accesses after lane 0's acquire (a shuffle is no memory barrier)
@@ -351,7 +378,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         float w = sq_acc;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
-        if (lane == 0) atomicAdd(&p.sumsq[b], (double)w);
+        if (lane == 0) atomicAdd(&p.sumsq[b * p.sumsq_stride], (double)w);
       }
     }
   }

@@ -34,6 +34,11 @@ typedef struct OpkGemmArgs {
   const float* coef;
   int32_t* err;        // device int, set to 1 if a bounded wait expired
   int32_t max_ctas;    // 0 = one per SM
+  // grouped modes (see GemmParams in gemm_sm100.cuh); all optional
+  const int32_t* tile_group;  // device [ceil(M/128)]: group of every 128-row tile of A / C, -1 = skip; B has n_groups batches
+  int32_t n_groups;
+  const int32_t* group_k;     // device [batch][2]: {first reduction element, number of 64-element blocks} per batch entry
+  int32_t sumsq_shared;       // epilogue 1: every batch entry adds into sumsq[0]
 } OpkGemmArgs;
 
 int opk_gemm(const OpkGemmArgs* args, void* stream);
@@ -125,6 +130,27 @@ int opk_clip_sumsq_partial(const void* tiles, int n_tiles, int B, double* partia
 // out[i] = sum_b stored(g_b[i] * f[b]) per leaf; post_partial (optional) [b][tile] = squared norm after clipping.
 int opk_clip_apply_sum(const void* tiles, int n_tiles, int B, const float* f_bf16, const float* f_fp32,
                        double* post_partial, void* stream);
+
+// ---- mixture-of-experts routing / permutation (csrc/kernels/moe.cu) -------------------------------------------
+// probs = softmax(logits[T][E] bf16); idx / wts [T][k]: the k largest (ties: lowest expert), renormalised if norm_topk.
+int opk_moe_route(const void* logits, int64_t ld, int T, int E, int k, int norm_topk, int32_t* idx, float* wts, float* probs,
+                  void* stream);
+int opk_moe_route_bwd(const float* probs, const int32_t* idx, const float* dwts, int T, int E, int k, int norm_topk,
+                      void* dlogits, int64_t ld, void* stream);
+// Worst-case number of rows of the expert-sorted buffers for n_entries = T*k routed entries.
+int opk_moe_rows_capacity(int n_entries, int E);
+// Stable sort of the entries by expert into 128-row aligned segments. dest[n] = row of entry n; src_entry[row] = entry
+// or -1 (padding); tile_group[r_cap/128] and group_k[E][2] are the tables of the grouped GEMM modes; counts[E] optional.
+int opk_moe_plan(const int32_t* idx, int n_entries, int E, int r_cap, int32_t* dest, int32_t* src_entry, int32_t* tile_group,
+                 int32_t* group_k, int32_t* counts, void* stream);
+// out[row] = entry_scale[n] * x[n / k] for n = src_entry[row] (zeros when n < 0); bf16 rows of D elements.
+int opk_moe_gather(const void* x, int64_t ldx, const int32_t* src_entry, int k, const float* entry_scale, int R, int D, void* out,
+                   void* stream);
+// out[t] = residual[t] + sum_s wts[t][s] * y[dest[t][s]] (wts == NULL: plain sum).
+int opk_moe_combine(const void* y, const int32_t* dest, const float* wts, int k, const void* residual, int T, int D, void* out,
+                    void* stream);
+// dwts[n] = <dy[n / k], y[dest[n]]>.
+int opk_moe_combine_bwd(const void* dy, const void* y, const int32_t* dest, int n_entries, int k, int D, float* dwts, void* stream);
 
 // ---- DP clipping / noise / optimizer (csrc/kernels/dp_step.cu) ---------------------------------------------
 // scale = guarded min(1, C / sqrt(sumsq)) (fixed) or R / (sqrt(sumsq) + gamma) (auto); see dp_step.cu.

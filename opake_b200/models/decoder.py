@@ -39,8 +39,8 @@ class DecoderRuntime:
 
     def __init__(self, cfg: DecoderConfig, params: torch.Tensor, *, layout: Layout | None = None,
                  attn_impl: str = "auto", n_slots: int = 1):
-        if cfg.n_experts:
-            raise ValueError("use MoEDecoderRuntime for mixture-of-experts configs")
+        if cfg.n_experts and (cfg.act != "swiglu" or cfg.n_experts > 256 or cfg.top_k > 32 or cfg.d_model % 8):
+            raise ValueError("mixture-of-experts layers need SwiGLU experts, at most 256 experts and top_k <= 32")
         self.cfg = cfg
         self.layout = layout or build_layout(cfg)
         self.device = params.device
@@ -104,7 +104,15 @@ class DecoderRuntime:
         for _ in range(L):
             a = {"x": e(T, d), "xn": e(T, d), "qkv": e(T, cfg.qkv_dim), "attn": e(T, cfg.n_heads * cfg.head_dim),
                  "x_mid": e(T, d), "xn2": e(T, d)}
-            if cfg.act in ("swiglu", "geglu"):
+            if cfg.n_experts:
+                plan = K.MoePlan(T, cfg.n_experts, cfg.top_k, dev)
+                I = cfg.expert_ffn
+                a.update(plan=plan, rlogits=e(T, cfg.n_experts), xs=e(plan.R, d), gu=e(plan.R, 2 * I), act=e(plan.R, I),
+                         ye=e(plan.R, d))
+                # rows past the used segments are never written by the grouped GEMMs; keep them finite
+                for name in ("gu", "act", "ye"):
+                    a[name].zero_()
+            elif cfg.act in ("swiglu", "geglu"):
                 a["gu"], a["act"] = e(T, 2 * F), e(T, F)
             else:
                 a["fc"], a["act"] = e(T, F), e(T, F)
@@ -115,8 +123,8 @@ class DecoderRuntime:
             "layers": layers, "x_last": e(T, d), "xf": e(T, d),
             "pmax": e(T, tiles, dtype=torch.float32), "psum": e(T, tiles, dtype=torch.float32),
             "tgt": e(T, dtype=torch.float32), "dlogits": e(T, Vp)[:, : cfg.vocab_size],
-            "dx": e(T, d), "dx2": e(T, d), "dact": e(T, F), "dqkv": e(T, cfg.qkv_dim),
-            "dwide": e(T, 2 * F if cfg.act in ("swiglu", "geglu") else F),
+            "dx": e(T, d), "dx2": e(T, d), "dact": e(T, max(F, 8)), "dqkv": e(T, cfg.qkv_dim),
+            "dwide": e(T, max(2 * F if cfg.act in ("swiglu", "geglu") else F, 8)),
             "dattn": e(T, cfg.n_heads * cfg.head_dim),
             "vec": torch.zeros(len(self._vec_names), self._vec_width, dtype=torch.float32, device=dev),
             "embs": [K.EmbeddingGradWorkspace(cfg.vocab_size, T, d, dev) for _ in range(self.n_slots)],
@@ -127,6 +135,10 @@ class DecoderRuntime:
         ws["vec_offsets"] = torch.tensor([self.layout.slot(n).offset for n in self._vec_names], dtype=torch.int64,
                                          device=dev)
         ws["emb"], ws["tok"] = ws["embs"][0], ws["toks"][0]
+        if cfg.n_experts:
+            R, I = layers[0]["plan"].R, cfg.expert_ffn
+            ws.update(dye=e(R, d), dh=e(R, I).zero_(), dgu=e(R, 2 * I), dxs=e(R, d).zero_(),
+                      dwts=e(T, cfg.top_k, dtype=torch.float32), drl=e(T, cfg.n_experts))
         self._ws[T] = ws
         return ws
 
@@ -182,7 +194,15 @@ class DecoderRuntime:
             G.gemm(a["attn"], w[p + "wo"], out=a["x_mid"], residual=x, bias=w.get(p + "bo"))
             xn2, st2 = self._norm_fwd(a["x_mid"], p + "norm2", out=a["xn2"])
             nxt = ws["layers"][li + 1]["x"] if li + 1 < cfg.n_layers else ws["x_last"]
-            if cfg.act == "swiglu":
+            if cfg.n_experts:
+                plan = a["plan"]
+                G.gemm(xn2, w[p + "router"], out=a["rlogits"])
+                K.moe_route(a["rlogits"], plan, cfg.norm_topk_prob)
+                K.moe_gather(xn2, plan, a["xs"])
+                G.gemm(a["xs"], w[p + "experts.wgu"], out=a["gu"], epilogue=G.EPI_SWIGLU, act=a["act"], tile_group=plan.tile_group)
+                G.gemm(a["act"], w[p + "experts.wd"], out=a["ye"], tile_group=plan.tile_group)
+                K.moe_combine(a["ye"], plan, nxt, wts=plan.wts, residual=a["x_mid"])
+            elif cfg.act == "swiglu":
                 G.gemm(xn2, w[p + "wgu"], out=a["gu"], epilogue=G.EPI_SWIGLU, act=a["act"])
                 G.gemm(a["act"], w[p + "wd"], out=nxt, residual=a["x_mid"])
             elif cfg.act == "geglu":
@@ -252,7 +272,24 @@ class DecoderRuntime:
             p = f"layers.{li}."
             st1, st2, actx = saved[li]
             # ---- MLP
-            if cfg.act in ("swiglu", "geglu"):
+            if cfg.n_experts:
+                plan = a["plan"]
+                K.moe_combine_bwd(dx, a["ye"], plan, ws["dwts"])
+                K.moe_gather(dx, plan, ws["dye"], entry_scale=plan.wts)
+                # expert weight gradients: one grouped GEMM per matrix, reduction range of expert e = its row segment
+                G.gemm(ws["dye"], a["act"], a_mn=True, b_mn=True, out=g[p + "experts.wd"], epilogue=G.EPI_SUMSQ, sumsq=sumsq,
+                       group_k=plan.group_k, sumsq_shared=True)
+                G.gemm(ws["dye"], w[p + "experts.wd"], b_mn=True, out=ws["dh"], tile_group=plan.tile_group)
+                K.swiglu_bwd(ws["dh"], a["gu"], out=ws["dgu"])
+                G.gemm(ws["dgu"], a["xs"], a_mn=True, b_mn=True, out=g[p + "experts.wgu"], epilogue=G.EPI_SUMSQ, sumsq=sumsq,
+                       group_k=plan.group_k, sumsq_shared=True)
+                G.gemm(ws["dgu"], w[p + "experts.wgu"], b_mn=True, out=ws["dxs"], tile_group=plan.tile_group)
+                dxn2 = K.moe_combine(ws["dxs"], plan, ws["dx2"])
+                # router: d weights -> d logits -> router weight gradient and the second path into dxn2
+                K.moe_route_bwd(plan, ws["dwts"], ws["drl"], cfg.norm_topk_prob)
+                G.linear_wgrad(ws["drl"], a["xn2"], out=g[p + "router"], sumsq=sumsq)
+                G.gemm(ws["drl"], w[p + "router"], b_mn=True, out=dxn2, residual=dxn2)
+            elif cfg.act in ("swiglu", "geglu"):
                 G.linear_wgrad(dx, a["act"], out=g[p + "wd"], sumsq=sumsq)
                 dact = G.gemm(dx, w[p + "wd"], b_mn=True, out=ws["dact"])
                 dgu = ws["dwide"]

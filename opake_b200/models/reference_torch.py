@@ -23,8 +23,10 @@ def _norm(cfg: DecoderConfig, w: dict, prefix: str, x: torch.Tensor) -> torch.Te
     return F.layer_norm(x, (x.shape[-1],), w[prefix + ".weight"], w[prefix + ".bias"], cfg.norm_eps)
 
 
-def decoder_hidden(cfg: DecoderConfig, w: dict[str, torch.Tensor], tok: torch.Tensor, rope_table=None) -> torch.Tensor:
-    """Final-norm hidden states ``[T, d]`` for one sequence. ``w`` maps slot names to (float) tensors."""
+def decoder_hidden(cfg: DecoderConfig, w: dict[str, torch.Tensor], tok: torch.Tensor, rope_table=None, routing=None) -> torch.Tensor:
+    """Final-norm hidden states ``[T, d]`` for one sequence. ``w`` maps slot names to (float) tensors. ``routing``
+    (optional, list of ``[T, top_k]`` index tensors per layer) fixes the expert choice of MoE layers, which makes the
+    function comparable with a lower-precision run whose near-tied router scores resolve differently."""
     T = tok.numel()
     H, KV, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
     x = w["embed"][tok.long()]
@@ -52,7 +54,21 @@ def decoder_hidden(cfg: DecoderConfig, w: dict[str, torch.Tensor], tok: torch.Te
             o = o + w[p + "bo"]
         x = x + o
         xn2 = _norm(cfg, w, p + "norm2", x)
-        if cfg.act in ("swiglu", "geglu"):
+        if cfg.n_experts:
+            probs = (xn2 @ w[p + "router"].T).float().softmax(-1)
+            if routing is not None:
+                topi = routing[li].long()
+                topw = probs.gather(1, topi)
+            else:
+                topw, topi = torch.topk(probs, cfg.top_k, dim=-1)
+            if cfg.norm_topk_prob:
+                topw = topw / topw.sum(-1, keepdim=True)
+            gate = torch.zeros_like(probs).scatter(1, topi, topw).to(x.dtype)          # [T, E], zero off the top-k
+            gu = torch.einsum("td,efd->tef", xn2, w[p + "experts.wgu"])
+            h = F.silu(gu[..., 0::2]) * gu[..., 1::2]
+            y = torch.einsum("tei,edi->ted", h, w[p + "experts.wd"])
+            x = x + (y * gate.unsqueeze(-1)).sum(1)
+        elif cfg.act in ("swiglu", "geglu"):
             gu = xn2 @ w[p + "wgu"].T
             g, u = gu[:, 0::2], gu[:, 1::2]
             a = (F.silu(g) if cfg.act == "swiglu" else F.gelu(g, approximate="tanh")) * u
@@ -69,9 +85,9 @@ def decoder_hidden(cfg: DecoderConfig, w: dict[str, torch.Tensor], tok: torch.Te
 
 
 def example_loss(cfg: DecoderConfig, w: dict[str, torch.Tensor], tok: torch.Tensor, labels: torch.Tensor,
-                 rope_table=None) -> torch.Tensor:
+                 rope_table=None, routing=None) -> torch.Tensor:
     """Mean NLL over the supervised positions of one sequence (labels already shifted; negative = ignored)."""
-    h = decoder_hidden(cfg, w, tok, rope_table)
+    h = decoder_hidden(cfg, w, tok, rope_table, routing)
     head = w["embed"] if cfg.tie_embeddings else w["lm_head"]
     logits = h @ head.T
     nll = F.cross_entropy(logits, labels.long().clamp(min=0), reduction="none")

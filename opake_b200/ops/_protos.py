@@ -39,6 +39,13 @@ PROTOTYPES: dict = {
     "opk_cross_entropy_fwd": (I, [P, I, P, P, P, I, I, L, F, F, P]),
     "opk_cross_entropy_bwd": (I, [P, I, P, P, P, P, I, I, L, F, F, P]),
     "opk_sumsq": (I, [P, I, I, L, P, P]),
+    "opk_moe_route": (I, [P, L, I, I, I, I, P, P, P, P]),
+    "opk_moe_route_bwd": (I, [P, P, P, I, I, I, I, P, L, P]),
+    "opk_moe_rows_capacity": (I, [I, I]),
+    "opk_moe_plan": (I, [P, I, I, I, P, P, P, P, P, P]),
+    "opk_moe_gather": (I, [P, L, P, I, P, I, I, P, P]),
+    "opk_moe_combine": (I, [P, P, P, I, P, I, I, P, P]),
+    "opk_moe_combine_bwd": (I, [P, P, P, I, I, I, P, P]),
     "opk_clip_sum_tile": (I, []),
     "opk_clip_sum_desc_bytes": (I, []),
     "opk_clip_sumsq_partial": (I, [P, I, I, P, P]),

@@ -44,6 +44,9 @@ def gemm(
     softcap: float = 0.0,
     b_batch_div: int = 1,
     max_ctas: int = 0,
+    tile_group: torch.Tensor | None = None,
+    group_k: torch.Tensor | None = None,
+    sumsq_shared: bool = False,
 ) -> torch.Tensor | None:
     """General entry: ``out[b] = alpha * op(a[b]) @ op(b[b // b_batch_div])^T`` with an epilogue.
 
@@ -64,9 +67,11 @@ def gemm(
         N, Kb = b.shape[-2], b.shape[-1]
     if K != Kb:
         raise ValueError(f"reduction sizes differ: {K} vs {Kb}")
+    if group_k is not None:
+        batch = group_k.shape[0]          # one output per group; operands stay un-batched
     need_out = epilogue != EPI_LCE_FWD
     if out is None and need_out:
-        shape = (batch, M, N) if batched else (M, N)
+        shape = (batch, M, N) if (batched or group_k is not None) else (M, N)
         out = torch.empty(shape, dtype=torch.bfloat16, device=a.device)
     args = _lib.GemmArgs()
     args.A, args.B = a.data_ptr(), b.data_ptr()
@@ -74,7 +79,7 @@ def gemm(
     if out is not None:
         _check2d(out, "out")
         args.ldc = out.stride(-2)
-        args.strideC = out.stride(0) if batched else 0
+        args.strideC = out.stride(0) if (batched or group_k is not None) else 0
     if residual is not None:
         if residual.shape != out.shape or residual.stride() != out.stride():
             raise ValueError("residual must have the layout of out")
@@ -93,6 +98,12 @@ def gemm(
     args.lse, args.coef = _lib.ptr(lse), _lib.ptr(coef)
     args.err = _lib.err_word(a.device).data_ptr()
     args.max_ctas = max_ctas
+    if tile_group is not None:      # row-grouped A / C, B batched per group (mixture of experts forward / dgrad)
+        args.tile_group, args.n_groups = tile_group.data_ptr(), b.shape[0]
+        args.strideB = b.stride(0)
+    if group_k is not None:         # per-batch reduction ranges over un-batched operands (mixture of experts wgrad)
+        args.group_k = group_k.data_ptr()
+    args.sumsq_shared = int(sumsq_shared)
     _lib.check(_lib.lib().opk_gemm(args, _lib.stream_ptr(a.device)), "opk_gemm")
     return out
 

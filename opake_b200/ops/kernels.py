@@ -287,3 +287,53 @@ def dp_step(*, grad_src: list[int], shard_begin: int, shard_len: int, inv_batch:
     a.sgd_mode = int(sgd_mode)
     dev = device if device is not None else (m.device if m is not None else torch.device("cuda"))
     _chk(_L().opk_dp_step(ctypes.byref(a), _lib.stream_ptr(dev)), "dp_step")
+
+
+# ------------------------------------------------------------------------------------------------ mixture of experts
+class MoePlan:
+    """Device-side routing state of one MoE layer invocation (buffers are reused across examples)."""
+
+    def __init__(self, T: int, E: int, k: int, device):
+        self.T, self.E, self.k = T, E, k
+        self.n = T * k
+        self.R = _L().opk_moe_rows_capacity(self.n, E)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.idx = torch.empty(T, k, **i32)
+        self.wts = torch.empty(T, k, dtype=torch.float32, device=device)
+        self.probs = torch.empty(T, E, dtype=torch.float32, device=device)
+        self.dest = torch.empty(T, k, **i32)
+        self.src_entry = torch.empty(self.R, **i32)
+        self.tile_group = torch.empty(self.R // 128, **i32)
+        self.group_k = torch.empty(E, 2, **i32)
+        self.counts = torch.empty(E, **i32)
+
+
+def moe_route(logits, plan: MoePlan, norm_topk: bool = False):
+    T, E = logits.shape
+    _chk(_L().opk_moe_route(_p(logits), logits.stride(0), T, E, plan.k, int(norm_topk), _p(plan.idx), _p(plan.wts), _p(plan.probs),
+                            _s(logits)), "moe_route")
+    _chk(_L().opk_moe_plan(_p(plan.idx), plan.n, E, plan.R, _p(plan.dest), _p(plan.src_entry), _p(plan.tile_group), _p(plan.group_k),
+                           _p(plan.counts), _s(logits)), "moe_plan")
+    return plan
+
+
+def moe_route_bwd(plan: MoePlan, dwts, dlogits, norm_topk: bool = False):
+    _chk(_L().opk_moe_route_bwd(_p(plan.probs), _p(plan.idx), _p(dwts), plan.T, plan.E, plan.k, int(norm_topk), _p(dlogits),
+                                dlogits.stride(0), _s(dlogits)), "moe_route_bwd")
+    return dlogits
+
+
+def moe_gather(x, plan: MoePlan, out, entry_scale=None):
+    _chk(_L().opk_moe_gather(_p(x), x.stride(0), _p(plan.src_entry), plan.k, _p(entry_scale), plan.R, x.shape[1], _p(out), _s(x)),
+         "moe_gather")
+    return out
+
+
+def moe_combine(y, plan: MoePlan, out, wts=None, residual=None):
+    _chk(_L().opk_moe_combine(_p(y), _p(plan.dest), _p(wts), plan.k, _p(residual), plan.T, y.shape[1], _p(out), _s(y)), "moe_combine")
+    return out
+
+
+def moe_combine_bwd(dy, y, plan: MoePlan, dwts):
+    _chk(_L().opk_moe_combine_bwd(_p(dy), _p(y), _p(plan.dest), plan.n, plan.k, y.shape[1], _p(dwts), _s(y)), "moe_combine_bwd")
+    return dwts

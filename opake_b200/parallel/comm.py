@@ -50,6 +50,19 @@ class PeerBuffer:
         if self.handle is not None:
             self.handle.barrier()
 
+    def peer_view(self, rank: int, shape, dtype: torch.dtype | None = None, offset: int = 0) -> torch.Tensor:
+        """A tensor aliasing rank ``rank``'s copy of the buffer (``offset`` in elements). Reads and writes through it
+        are NVLink loads / stores; only this package's own kernels may be given such a tensor."""
+        dtype = dtype or self.local.dtype
+        if self.handle is None:
+            if rank != 0:
+                raise ValueError("single-rank buffer has no peers")
+            n = 1
+            for d in shape:
+                n *= d
+            return self.local.view(dtype)[offset:offset + n].view(*shape)
+        return self.handle.get_buffer(rank, tuple(shape), dtype, offset)
+
 
 def alloc_peer_buffer(numel: int, dtype: torch.dtype, device: torch.device, group=None) -> PeerBuffer:
     """Allocates ``numel`` elements that every rank of ``group`` can address.

@@ -30,12 +30,15 @@ def _oracle(cfg, layout, params, tok, labels, rt):
 
     w = {k: v.detach().float().requires_grad_() for k, v in layout.views(params).items()}
     table = rt._rope_table(tok.numel()) if cfg.pos == "rope" else None
-    loss = example_loss(cfg, w, tok, labels, table)
+    routing = None
+    if cfg.n_experts:      # compare at the runtime's expert choice (bf16 router scores have near-ties)
+        routing = [a["plan"].idx.clone() for a in rt.workspace(tok.numel())["layers"]]
+    loss = example_loss(cfg, w, tok, labels, table, routing)
     loss.backward()
     return loss.item(), {k: v.grad for k, v in w.items()}
 
 
-@pytest.mark.parametrize("name", ["tiny-llama", "tiny-llama-tied", "tiny-gpt2"])
+@pytest.mark.parametrize("name", ["tiny-llama", "tiny-llama-tied", "tiny-gpt2", "tiny-moe", "tiny-moe-norm"])
 def test_example_grad_matches_autograd(cuda, name):
     from opake_b200.models import config as C
 
@@ -43,6 +46,8 @@ def test_example_grad_matches_autograd(cuda, name):
         cfg = C.tiny_llama()
     elif name == "tiny-llama-tied":
         cfg = C.tiny_llama(tie_embeddings=True)
+    elif name.startswith("tiny-moe"):
+        cfg = C.tiny_llama(n_experts=8, top_k=2, expert_ffn=128, ffn=0, norm_topk_prob=name.endswith("norm"), name=name)
     else:
         cfg = C.gpt2_small(n_layers=2, d_model=256, n_heads=4, n_kv_heads=4, head_dim=64, ffn=1024, vocab_size=1001,
                            max_seq=128, name="tiny-gpt2")

@@ -33,3 +33,10 @@ def test_two_ranks_match_one_rank(tmp_path, blt):
     assert one["losses"] == pytest.approx(two["losses"], rel=2e-3)
     diff = (one["params"] - two["params"]).abs().max().item()
     assert diff <= 2e-2 * one["params"].abs().max().item(), diff
+
+
+def test_sharded_linear_reads_peer_shards(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _run(2, str(tmp_path / "sl.pt"), ("--sharded-linear",))
+    assert res["world"] == 2 and res["fwd_err"] < 2e-2 and res["dgrad_err"] < 2e-2
