@@ -90,6 +90,46 @@ def run_reference(args) -> None:
     }))
 
 
+def run_config_a(args) -> None:
+    """CPU plumbing configuration: fp32 DP-SGD on an MLP 784-512-10, 60000 synthetic samples, Poisson q = 256/60000,
+    C = 1.0, sigma = 1.1, SGD lr 0.1, 200 steps, PLD accountant at delta = 1e-5 (functional API, no GPU)."""
+    import torch
+    from torch import nn
+
+    from opake_b200 import accounting as acc
+    from opake_b200.dpsgd import PoissonSampler, clipped_grad, gaussian_noise
+    from opake_b200.dpsgd import accounting as sgd_acc
+    from opake_b200.engine.functional import make_functional
+    from opake_b200.engine.random import fold_in, key
+    from opake_b200.optimizers import apply_updates, sgd
+
+    steps, n, q, sigma, delta = 200, 60000, 256 / 60000, 1.1, 1e-5
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(n, 784, generator=g)
+    y = torch.randint(0, 10, (n,), generator=g)
+    model = nn.Sequential(nn.Linear(784, 512), nn.ReLU(), nn.Linear(512, 10))
+    fmodel, params, _ = make_functional(model, disable_autograd_tracking=True, partition_trainable=True)
+    loss_fn = lambda p, xe, ye: nn.functional.cross_entropy(fmodel(p, xe[None]), ye[None])
+    grad_fn, cs = clipped_grad(loss_fn, clipping_norm=1.0, normalize_by=256.0, batch_argnums=(1, 2))
+    noise_fn, ns = gaussian_noise(noise_multiplier=sigma, key=fold_in(key(0), "noise"))
+    opt = sgd(0.1)
+    os_ = opt.init(params)
+    ledger = acc.Accountant()
+    sampler = PoissonSampler(torch.utils.data.TensorDataset(x, y), q, n_steps=steps, key=fold_in(key(0), "sampler"))
+    t0, seen = time.perf_counter(), 0
+    for idx in sampler:
+        clipped, cs = grad_fn(params, x[idx], y[idx], state=cs)
+        noised, ns = noise_fn(clipped, ns)
+        upd, os_ = opt.update(noised, os_, params=params)
+        params = apply_updates(params, upd)
+        seen += len(idx)
+    dt = time.perf_counter() - t0
+    ledger = ledger | sgd_acc.poisson(sgd_acc.gaussian(sigma), q) * steps
+    print(json.dumps({"metric": "config a: CPU fp32 DP-SGD MLP 784-512-10, functional API", "value": seen / dt, "unit": "samples/s",
+                      "n_gpus": 0, "steps": steps, "higher_is_better": True, "epsilon_at_1e-5": ledger.epsilon_at(delta),
+                      "seconds": dt, "dtype": "fp32", "data": "synthetic, seed 0"}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -102,10 +142,23 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (invalidates the number)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--attn", default="auto")
+    ap.add_argument("--sigma", type=float, default=0.9)
+    ap.add_argument("--blt-buffers", type=int, default=0, help="DP-FTRL: buffered-linear-Toeplitz correlated noise buffers")
+    ap.add_argument("--config", default="d", choices=["a", "b", "c", "d", "e"],
+                    help="benchmark configuration: d = headline (Llama-3-8B DP-SGD); a = CPU MLP plumbing; b = GPT-2-small "
+                         "DP-SGD; c = Llama-3.2-1B DP-FTRL (BLT); e = OLMoE-1B-7B")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
         return
+    if args.config == "a":
+        run_config_a(args)
+        return
+    preset = {"b": dict(model="gpt2-small", seq=1024, batch=1024, sigma=0.8), "c": dict(model="llama3.2-1b", seq=2048, batch=512,
+              sigma=1.0, blt_buffers=4), "e": dict(model="olmoe-1b-7b", seq=2048, batch=512, sigma=1.0)}.get(args.config, {})
+    for k, v in preset.items():
+        if getattr(args, k) == ap.get_default(k):
+            setattr(args, k, v)
     if args.warmup < 3:
         args.warmup = 3
 
@@ -128,9 +181,14 @@ def main() -> None:
     if args.batch % world:
         raise SystemExit("logical batch must divide evenly over the ranks")
     b_local = args.batch // world
-    ecfg = EngineConfig(clip_norm=1.0, noise_multiplier=0.9, logical_batch=args.batch, lr=3e-4, weight_decay=0.01,
+    blt = {}
+    if args.blt_buffers:
+        k = args.blt_buffers
+        blt = dict(blt_decay=tuple(1.0 - 0.5 ** (i + 1) * 0.9 for i in range(k)), blt_scale=tuple(0.5 / k for _ in range(k)),
+                   noise_stream_tag="opake.dpftrl.mf_gaussian")
+    ecfg = EngineConfig(clip_norm=1.0, noise_multiplier=args.sigma, logical_batch=args.batch, lr=3e-4, weight_decay=0.01,
                         noise_bias_correction=True, master_weights=False, use_cuda_graph=not args.no_graph,
-                        attn_impl=args.attn, seed=1234)
+                        attn_impl=args.attn, seed=1234, **blt)
     eng = ShardedDPEngine(mcfg, ecfg, dev)
 
     tok = _zipf_tokens(b_local, args.seq, mcfg.vocab_size, seed=1000 + rank)
@@ -180,14 +238,16 @@ def main() -> None:
     e2e_value = tokens / (e2e_ms / 1e3)
     if rank == 0:
         print(json.dumps({
-            "metric": "DP tokens/sec/box (max over ranks), Llama-3-8B FSDP DP-SGD",
+            "metric": "DP tokens/sec/box (max over ranks), Llama-3-8B FSDP DP-SGD" if args.config == "d" else
+                      f"DP tokens/sec/box (max over ranks), config {args.config}: {mcfg.name}",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic Zipf(1.1) tokens, random-init weights", "impl": "ours",
             "config": {"model": mcfg.name, "layers": mcfg.n_layers, "global_batch": args.batch, "seq_len": args.seq,
                        "parallelism": f"fsdp{world} (sharded fp32 AdamW-BC state, fused P2P reduce-scatter/all-gather step; "
                                       f"bf16 parameter replica cached across the {b_local} accumulation micro-steps)",
-                       "clip_norm": 1.0, "noise_multiplier": 0.9, "optimizer": "adamw-bc", "sft_mask": "first 25%",
+                       "clip_norm": 1.0, "noise_multiplier": args.sigma, "optimizer": "adamw-bc", "sft_mask": "first 25%",
+                       "mechanism": f"dp-ftrl blt x{args.blt_buffers}" if args.blt_buffers else "dp-sgd gaussian",
                        "per_example_microbatch": 1, "cuda_graph": not args.no_graph,
                        "l2_policy": "inputs larger than L2: every step streams the 16 GB bf16 weights and 32 GB fp32 sums",
                        "final_loss_per_example": last_loss / b_local},

@@ -168,35 +168,103 @@ struct PeerTable {
   __nv_bfloat16* param[MAX_PEERS];
 };
 
+// One parameter update given the averaged, noised gradient. Returns the new parameter value.
+__device__ __forceinline__ float dp_update(const OpkDpStepArgs& a, float grad, float p_old, float& m, float& v) {
+  float upd;
+  if (a.sgd_mode) {
+    upd = grad + a.weight_decay * p_old;
+  } else {
+    m = a.beta1 * m + (1.f - a.beta1) * grad;
+    v = a.beta2 * v + (1.f - a.beta2) * grad * grad;
+    const float mh = m / a.bc1, vh = v / a.bc2;
+    const float d = vh - a.phi_hat;            // noise bias correction: subtract the noise's share of v-hat
+    const float den = sqrtf(d > 0.f ? d : vh) + a.eps;
+    upd = mh / den + a.weight_decay * p_old;
+  }
+  return p_old - a.lr * upd;
+}
+
 __global__ void __launch_bounds__(256) dp_step_kernel(const OpkDpStepArgs a, const PeerTable pt) {
-  // Each thread owns aligned quads of the shard; shard_begin is a multiple of 4 (checked on the host).
+  // Each thread owns aligned quads of the shard; shard_begin and shard_len are multiples of 4 except for a possible
+  // ragged last quad, which takes the scalar path. Everything is touched exactly once: streaming loads and stores.
   const long long nq = (a.shard_len + 3) >> 2;
+  const bool adam = !a.sgd_mode;
   for (long long q = blockIdx.x * 256ll + threadIdx.x; q < nq; q += (long long)gridDim.x * 256) {
     const long long i0 = q << 2;
     const long long e0 = a.shard_begin + i0;
     const int cnt = (int)((a.shard_len - i0) < 4 ? (a.shard_len - i0) : 4);
-    float g[4] = {0.f, 0.f, 0.f, 0.f};
-    if (cnt == 4) {
-      // reduce-scatter: sum the owned quad over every rank's buffer (peer reads travel over NVLink)
-#pragma unroll 4
-      for (int r = 0; r < a.n_src; ++r) {
-        const float4 v = *reinterpret_cast<const float4*>(pt.grad[r] + e0);
-        g[0] += v.x; g[1] += v.y; g[2] += v.z; g[3] += v.w;
-      }
-    } else {
-      for (int r = 0; r < a.n_src; ++r)
-        for (int j = 0; j < cnt; ++j) g[j] += pt.grad[r][e0 + j];
-    }
     float z[4] = {0.f, 0.f, 0.f, 0.f};
     if (a.sigma != 0.f) normal4((uint64_t)e0 >> 2, a.seed, a.stream_id, a.step, z);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (j >= cnt) break;
-      const long long i = i0 + j;
-      float noise = z[j];
+    if (cnt == 4) {
+      // reduce-scatter: sum the owned quad over every rank's buffer (peer reads travel over NVLink)
+      float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+      for (int r = 0; r < a.n_src; ++r) {
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(pt.grad[r] + e0));
+        g.x += v.x; g.y += v.y; g.z += v.z; g.w += v.w;
+      }
+      float gr[4] = {g.x, g.y, g.z, g.w};
       if (a.blt_nbuf > 0) {
         // streaming multiply by C^{-1} of a buffered linear Toeplitz factor: xhat = z - <scale, state>;
         // state_k = decay_k * state_k + xhat
+        float rd[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int k = 0; k < a.blt_nbuf; ++k) {
+          const float4 st = *reinterpret_cast<const float4*>(a.blt_state + (long long)k * a.shard_len + i0);
+          const float sc = a.blt_scale[k];
+          rd[0] += sc * st.x; rd[1] += sc * st.y; rd[2] += sc * st.z; rd[3] += sc * st.w;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) z[j] -= rd[j];
+        for (int k = 0; k < a.blt_nbuf; ++k) {
+          float4* sp = reinterpret_cast<float4*>(a.blt_state + (long long)k * a.shard_len + i0);
+          float4 st = *sp;
+          const float dc = a.blt_decay[k];
+          st.x = dc * st.x + z[0]; st.y = dc * st.y + z[1]; st.z = dc * st.z + z[2]; st.w = dc * st.w + z[3];
+          *sp = st;
+        }
+      }
+      float po[4];
+      if (a.master) {
+        const float4 mw = __ldcs(reinterpret_cast<const float4*>(a.master + i0));
+        po[0] = mw.x; po[1] = mw.y; po[2] = mw.z; po[3] = mw.w;
+      } else {
+        const uint2 pw = __ldcs(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.param_src) + e0));
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pw.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pw.y));
+        po[0] = lo.x; po[1] = lo.y; po[2] = hi.x; po[3] = hi.y;
+      }
+      float mm[4] = {0.f, 0.f, 0.f, 0.f}, vv[4] = {0.f, 0.f, 0.f, 0.f};
+      if (adam) {
+        const float4 m4 = __ldcs(reinterpret_cast<const float4*>(a.m + i0));
+        const float4 v4 = __ldcs(reinterpret_cast<const float4*>(a.v + i0));
+        mm[0] = m4.x; mm[1] = m4.y; mm[2] = m4.z; mm[3] = m4.w;
+        vv[0] = v4.x; vv[1] = v4.y; vv[2] = v4.z; vv[3] = v4.w;
+      }
+      float pn[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pn[j] = dp_update(a, gr[j] * a.inv_batch + a.sigma * z[j], po[j], mm[j], vv[j]);
+      if (adam) {
+        __stcs(reinterpret_cast<float4*>(a.m + i0), make_float4(mm[0], mm[1], mm[2], mm[3]));
+        __stcs(reinterpret_cast<float4*>(a.v + i0), make_float4(vv[0], vv[1], vv[2], vv[3]));
+      }
+      if (a.master) __stcs(reinterpret_cast<float4*>(a.master + i0), make_float4(pn[0], pn[1], pn[2], pn[3]));
+      // all-gather: write the updated bf16 quad into every rank's parameter buffer
+      uint2 o;
+      __nv_bfloat162 lo = __floats2bfloat162_rn(pn[0], pn[1]), hi = __floats2bfloat162_rn(pn[2], pn[3]);
+      o.x = *reinterpret_cast<uint32_t*>(&lo);
+      o.y = *reinterpret_cast<uint32_t*>(&hi);
+#pragma unroll 4
+      for (int r = 0; r < a.n_dst; ++r) *reinterpret_cast<uint2*>(pt.param[r] + e0) = o;
+      if (a.zero_grad) *reinterpret_cast<float4*>(const_cast<float*>(pt.grad[0]) + e0) = make_float4(0.f, 0.f, 0.f, 0.f);
+      continue;
+    }
+    // ragged tail (fewer than 4 elements)
+    for (int j = 0; j < cnt; ++j) {
+      const long long i = i0 + j;
+      float g = 0.f;
+      for (int r = 0; r < a.n_src; ++r) g += pt.grad[r][e0 + j];
+      float noise = z[j];
+      if (a.blt_nbuf > 0) {
         float rd = 0.f;
         for (int k = 0; k < a.blt_nbuf; ++k) rd += a.blt_scale[k] * a.blt_state[(long long)k * a.shard_len + i];
         noise = z[j] - rd;
@@ -205,42 +273,13 @@ __global__ void __launch_bounds__(256) dp_step_kernel(const OpkDpStepArgs a, con
           *sp = a.blt_decay[k] * (*sp) + noise;
         }
       }
-      const float grad = g[j] * a.inv_batch + a.sigma * noise;
-      float p_old;
-      if (a.master) p_old = a.master[i];
-      else p_old = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.param_src)[e0 + j]);
-      float upd;
-      if (a.sgd_mode) {
-        upd = grad + a.weight_decay * p_old;
-      } else {
-        const float m = a.beta1 * a.m[i] + (1.f - a.beta1) * grad;
-        const float v = a.beta2 * a.v[i] + (1.f - a.beta2) * grad * grad;
-        a.m[i] = m;
-        a.v[i] = v;
-        const float mh = m / a.bc1, vh = v / a.bc2;
-        const float d = vh - a.phi_hat;
-        const float den = sqrtf(d > 0.f ? d : vh) + a.eps;
-        upd = mh / den + a.weight_decay * p_old;
-      }
-      const float p_new = p_old - a.lr * upd;
+      const float p_old = a.master ? a.master[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.param_src)[e0 + j]);
+      float m = adam ? a.m[i] : 0.f, v = adam ? a.v[i] : 0.f;
+      const float p_new = dp_update(a, g * a.inv_batch + a.sigma * noise, p_old, m, v);
+      if (adam) { a.m[i] = m; a.v[i] = v; }
       if (a.master) a.master[i] = p_new;
-      g[j] = p_new;
-    }
-    // all-gather: write the updated bf16 quad into every rank's parameter buffer
-    if (cnt == 4) {
-      uint2 o;
-      __nv_bfloat162 lo = __floats2bfloat162_rn(g[0], g[1]), hi = __floats2bfloat162_rn(g[2], g[3]);
-      o.x = *reinterpret_cast<uint32_t*>(&lo);
-      o.y = *reinterpret_cast<uint32_t*>(&hi);
-#pragma unroll 4
-      for (int r = 0; r < a.n_dst; ++r) *reinterpret_cast<uint2*>(pt.param[r] + e0) = o;
-    } else {
-      for (int r = 0; r < a.n_dst; ++r)
-        for (int j = 0; j < cnt; ++j) pt.param[r][e0 + j] = __float2bfloat16(g[j]);
-    }
-    if (a.zero_grad) {
-      if (cnt == 4) *reinterpret_cast<float4*>(const_cast<float*>(pt.grad[0]) + e0) = make_float4(0.f, 0.f, 0.f, 0.f);
-      else for (int j = 0; j < cnt; ++j) const_cast<float*>(pt.grad[0])[e0 + j] = 0.f;
+      for (int r = 0; r < a.n_dst; ++r) pt.param[r][e0 + j] = __float2bfloat16(p_new);
+      if (a.zero_grad) const_cast<float*>(pt.grad[0])[e0 + j] = 0.f;
     }
   }
 }

@@ -30,7 +30,7 @@ __all__ = ["ExpertParallelLayer", "route"]
 
 
 def route(x: torch.Tensor, router_w: torch.Tensor, top_k: int, norm_topk: bool):
-    probs = (x @ router_w.t()).float().softmax(-1)
+    probs = (x @ router_w.t()).to(torch.promote_types(x.dtype, torch.float32)).softmax(-1)
     w, idx = torch.topk(probs, top_k, dim=-1)
     if norm_topk:
         w = w / w.sum(-1, keepdim=True)
@@ -120,7 +120,7 @@ class ExpertParallelLayer:
         k, W = self.top_k, self.world
         I = self.wd.shape[-1]
         # through the weighted combination
-        dw = (dy.unsqueeze(1) * c.y_rows.view(T, k, d)).sum(-1).float()                      # [T, k]
+        dw = (dy.unsqueeze(1) * c.y_rows.view(T, k, d)).sum(-1).to(c.probs.dtype)            # [T, k]
         d_rows = (dy.unsqueeze(1) * c.w.to(dy.dtype).unsqueeze(-1)).reshape(T * k, d)       # entry order
         send = d_rows[c.order]
         dy_rows = _a2a(send, c.send_counts, c.recv_counts, self.group) if W > 1 else send

@@ -6,7 +6,7 @@ producer pulls weight tiles straight from the remote GPU's memory over NVLink in
 while the tensor cores work on the previous stages. No gathered copy of the weight ever exists, no collective is
 called, and transfer overlaps math tile by tile inside the kernel's normal pipeline. Shards are visited starting with
 the local one and continuing with rank+1, rank+2, ... so that at any moment the ranks read from different peers.
-The loads are ordinary (non-multicast) TMA tile loads.
+The loads are ordinary TMA tile loads that each CTA issues for itself.
 
 The weight gradient of a row-sharded weight is local (``dW_s = dy[:, rows_s].T @ x`` is needed only by the owner
 when the ranks work on the same ``x``; under data parallelism it is followed by the reduce-scatter of the optimizer
