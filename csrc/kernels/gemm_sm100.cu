@@ -161,3 +161,36 @@ extern "C" int opk_gemm(const OpkGemmArgs* a, void* stream) {
   set_err("opk_gemm: unsupported (layout, epilogue) combination");
   return -3;
 }
+
+// ------------------------------------------------------------------------------------------------ wait self-test
+// One CTA waits on an mbarrier that nothing ever completes, with a short cycle budget. The wait gives up, the abort
+// flag is raised and the error word is set: the same unwinding path every pipeline role of the real kernels takes
+// when a producer or peer never shows up. The kernel returns normally and the context stays usable.
+namespace {
+__global__ void wait_selftest_kernel(int* err, long long budget_cycles, long long* waited_cycles) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    opk::mbar_init(&bar, 1);
+    abort_flag = 0;
+    opk::fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const long long t0 = clock64();
+    const bool ok = opk::mbar_wait(&bar, 0, &abort_flag, budget_cycles);
+    if (waited_cycles) *waited_cycles = clock64() - t0;
+    if (!ok && err) atomicExch(err, 1);
+  }
+  __syncthreads();
+  // every other thread sees the flag the waiting role raised
+  if (threadIdx.x == 1 && abort_flag && err) atomicOr(err, 2);
+}
+}  // namespace
+
+extern "C" int opk_wait_selftest(int32_t* err, int64_t budget_cycles, int64_t* waited_cycles, void* stream) {
+  if (budget_cycles <= 0 || budget_cycles > 4000000000LL) return -1;
+  wait_selftest_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(err, budget_cycles,
+                                                                           reinterpret_cast<long long*>(waited_cycles));
+  return (int)cudaGetLastError();
+}

@@ -44,6 +44,8 @@ typedef struct OpkGemmArgs {
 int opk_gemm(const OpkGemmArgs* args, void* stream);
 int opk_gemm_tiles_n(int N, int epilogue);  // number of column tiles the kernel uses (LCE partial buffers)
 int opk_num_sms(void);
+// Bounded-wait self-test: one CTA waits `budget_cycles` on a barrier nobody completes, then sets *err = 3 and returns.
+int opk_wait_selftest(int32_t* err, int64_t budget_cycles, int64_t* waited_cycles, void* stream);
 const char* opk_last_error(void);
 
 // ---- normalisation / rotary / activation / embedding (csrc/kernels/elementwise.cu) -------------------------
@@ -161,6 +163,9 @@ int opk_clip_scale(double* sumsq, float clip, int mode_auto, float gamma, int n_
 int opk_clip_accumulate(const void* g, const float* scale, float* acc, int64_t n, void* stream);
 // Same with overwrite != 0 meaning acc = bf16(g * scale) (first example of a step: no separate zeroing pass).
 int opk_clip_accumulate2(const void* g, const float* scale, float* acc, int64_t n, int overwrite, void* stream);
+// Two examples at once: acc (+)= stored(g0 * scale0) + stored(g1 * scale1) in one pass over acc.
+int opk_clip_accumulate_pair(const void* g0, const float* scale0, const void* g1, const float* scale1, float* acc, int64_t n,
+                             int overwrite, void* stream);
 // Gaussian noise from Philox4x32-10: out[i] (+)= sigma * N(0,1)_{key, stream, step, offset + i}.
 int opk_philox_normal(float* out, int64_t n, uint64_t seed, uint32_t stream_id, uint32_t step, uint64_t offset,
                       float sigma, int accumulate, void* stream);

@@ -46,6 +46,7 @@ PROTOTYPES: dict = {
     "opk_moe_gather": (I, [P, L, P, I, P, I, I, P, P]),
     "opk_moe_combine": (I, [P, P, P, I, P, I, I, P, P]),
     "opk_moe_combine_bwd": (I, [P, P, P, I, I, I, P, P]),
+    "opk_wait_selftest": (I, [P, L, P, P]),
     "opk_clip_sum_tile": (I, []),
     "opk_clip_sum_desc_bytes": (I, []),
     "opk_clip_sumsq_partial": (I, [P, I, I, P, P]),
@@ -57,6 +58,7 @@ PROTOTYPES: dict = {
     "opk_clip_scale": (I, [P, F, I, F, I, L, P, P, P, I, P]),
     "opk_clip_accumulate": (I, [P, P, P, L, P]),
     "opk_clip_accumulate2": (I, [P, P, P, L, I, P]),
+    "opk_clip_accumulate_pair": (I, [P, P, P, P, P, L, I, P]),
     "opk_philox_normal": (I, [P, L, c_uint64, c_uint32, c_uint32, c_uint64, F, I, P]),
     "opk_dp_step": (I, [POINTER(DpStepArgs), P]),
 }

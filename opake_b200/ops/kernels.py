@@ -255,6 +255,12 @@ def clip_accumulate(g, scale, acc, overwrite: bool = False):
     _chk(_L().opk_clip_accumulate2(_p(g), _p(scale), _p(acc), g.numel(), int(overwrite), _s(g)), "clip_accumulate")
 
 
+def clip_accumulate_pair(g0, scale0, g1, scale1, acc, overwrite: bool = False):
+    """``acc (+)= stored(g0 * scale0) + stored(g1 * scale1)``: two examples in one pass over the fp32 sums."""
+    _chk(_L().opk_clip_accumulate_pair(_p(g0), _p(scale0), _p(g1), _p(scale1), _p(acc), g0.numel(), int(overwrite), _s(acc)),
+         "clip_accumulate_pair")
+
+
 def philox_normal_(out, seed: int, step: int, *, stream_id: int = 0, offset: int = 0, sigma: float = 1.0,
                    accumulate: bool = False):
     _chk(_L().opk_philox_normal(_p(out), out.numel(), seed & (2**64 - 1), stream_id, step, offset, sigma,

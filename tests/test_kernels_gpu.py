@@ -213,3 +213,18 @@ def test_dp_step_single_rank_matches_reference_math(cuda):
     assert stable.float().mean().item() > 0.9
     assert diff.max().item() <= 2 * 2**-8 * p_ref.float().abs().max().item()
     assert acc.abs().max().item() == 0.0
+
+
+def test_bounded_wait_expires_and_reports(cuda):
+    """A pipeline wait on a barrier that nothing completes gives up after its cycle budget, raises the CTA abort flag and
+    sets the error word; the kernel returns and the context keeps working."""
+    from opake_b200.ops import _lib
+    L = _lib.lib()
+    err = torch.zeros(1, dtype=torch.int32, device=cuda)
+    waited = torch.zeros(1, dtype=torch.int64, device=cuda)
+    budget = 200_000_000      # about 0.1 s
+    assert L.opk_wait_selftest(err.data_ptr(), budget, waited.data_ptr(), _lib.stream_ptr(cuda)) == 0
+    torch.cuda.synchronize()
+    assert err.item() == 3 and budget <= waited.item() < 20 * budget
+    x = torch.ones(1024, device=cuda)
+    assert x.sum().item() == 1024.0          # context still usable
