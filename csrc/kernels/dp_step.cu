@@ -48,14 +48,15 @@ __device__ __forceinline__ void normal4(uint64_t q, uint64_t seed, uint32_t stre
   const float k = 2.3283064365386963e-10f;  // 2^-32
   const float u1 = ((float)r.x + 1.0f) * k, u2 = (float)r.y * k;
   const float u3 = ((float)r.z + 1.0f) * k, u4 = (float)r.w * k;
-  const float ra = sqrtf(-2.0f * logf(fminf(u1, 1.0f))), rb = sqrtf(-2.0f * logf(fminf(u3, 1.0f)));
-  float s, co;
-  sincospif(2.0f * u2, &s, &co);
-  z[0] = ra * co;
-  z[1] = ra * s;
-  sincospif(2.0f * u4, &s, &co);
-  z[2] = rb * co;
-  z[3] = rb * s;
+  // hardware lg2 / sin / cos (absolute error about 1e-6 here); the angle is taken in [-pi, pi), where the fast
+  // sine and cosine are most accurate, and the half-turn is undone by the sign: sin(t + pi) = -sin t, cos likewise
+  const float ra = sqrtf(-2.0f * __logf(fminf(u1, 1.0f))), rb = sqrtf(-2.0f * __logf(fminf(u3, 1.0f)));
+  const float two_pi = 6.283185307179586f;
+  const float ta = two_pi * (u2 - 0.5f), tb = two_pi * (u4 - 0.5f);
+  z[0] = -ra * __cosf(ta);
+  z[1] = -ra * __sinf(ta);
+  z[2] = -rb * __cosf(tb);
+  z[3] = -rb * __sinf(tb);
 }
 
 __global__ void philox_normal_kernel(float* __restrict__ out, long long n, uint64_t seed, uint32_t stream_id,
@@ -198,17 +199,18 @@ struct PeerTable {
 };
 
 // One parameter update given the averaged, noised gradient. Returns the new parameter value.
-__device__ __forceinline__ float dp_update(const OpkDpStepArgs& a, float grad, float p_old, float& m, float& v) {
+__device__ __forceinline__ float dp_update(const OpkDpStepArgs& a, float inv_bc1, float inv_bc2, float grad, float p_old,
+                                           float& m, float& v) {
   float upd;
   if (a.sgd_mode) {
     upd = grad + a.weight_decay * p_old;
   } else {
     m = a.beta1 * m + (1.f - a.beta1) * grad;
     v = a.beta2 * v + (1.f - a.beta2) * grad * grad;
-    const float mh = m / a.bc1, vh = v / a.bc2;
+    const float mh = m * inv_bc1, vh = v * inv_bc2;
     const float d = vh - a.phi_hat;            // noise bias correction: subtract the noise's share of v-hat
     const float den = sqrtf(d > 0.f ? d : vh) + a.eps;
-    upd = mh / den + a.weight_decay * p_old;
+    upd = __fdividef(mh, den) + a.weight_decay * p_old;
   }
   return p_old - a.lr * upd;
 }
@@ -218,6 +220,7 @@ __global__ void __launch_bounds__(256) dp_step_kernel(const OpkDpStepArgs a, con
   // ragged last quad, which takes the scalar path. Everything is touched exactly once: streaming loads and stores.
   const long long nq = (a.shard_len + 3) >> 2;
   const bool adam = !a.sgd_mode;
+  const float inv_bc1 = 1.f / a.bc1, inv_bc2 = 1.f / a.bc2;
   for (long long q = blockIdx.x * 256ll + threadIdx.x; q < nq; q += (long long)gridDim.x * 256) {
     const long long i0 = q << 2;
     const long long e0 = a.shard_begin + i0;
@@ -271,7 +274,7 @@ __global__ void __launch_bounds__(256) dp_step_kernel(const OpkDpStepArgs a, con
       }
       float pn[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) pn[j] = dp_update(a, gr[j] * a.inv_batch + a.sigma * z[j], po[j], mm[j], vv[j]);
+      for (int j = 0; j < 4; ++j) pn[j] = dp_update(a, inv_bc1, inv_bc2, gr[j] * a.inv_batch + a.sigma * z[j], po[j], mm[j], vv[j]);
       if (adam) {
         __stcs(reinterpret_cast<float4*>(a.m + i0), make_float4(mm[0], mm[1], mm[2], mm[3]));
         __stcs(reinterpret_cast<float4*>(a.v + i0), make_float4(vv[0], vv[1], vv[2], vv[3]));
@@ -304,7 +307,7 @@ __global__ void __launch_bounds__(256) dp_step_kernel(const OpkDpStepArgs a, con
       }
       const float p_old = a.master ? a.master[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.param_src)[e0 + j]);
       float m = adam ? a.m[i] : 0.f, v = adam ? a.v[i] : 0.f;
-      const float p_new = dp_update(a, g * a.inv_batch + a.sigma * noise, p_old, m, v);
+      const float p_new = dp_update(a, inv_bc1, inv_bc2, g * a.inv_batch + a.sigma * noise, p_old, m, v);
       if (adam) { a.m[i] = m; a.v[i] = v; }
       if (a.master) a.master[i] = p_new;
       for (int r = 0; r < a.n_dst; ++r) pt.param[r][e0 + j] = __float2bfloat16(p_new);
