@@ -442,6 +442,54 @@ class DPTrainer:
                 self._step_down_microbatch()
                 resume = resume if self.state.global_step == 0 else (ckpt.latest_checkpoint(self.args.output_dir) or resume)
 
+    def _install_sigterm_handler(self):
+        """``enable_jit_checkpoint``: SIGTERM (preemption notice) asks the loop to save a checkpoint after the step in
+        flight and stop; nothing is written from inside the signal handler."""
+        import signal
+        self._sigterm = False
+        if not self.args.enable_jit_checkpoint:
+            return None
+        try:
+            previous = signal.getsignal(signal.SIGTERM)
+
+            def handler(signum, frame):
+                self._sigterm = True
+
+            signal.signal(signal.SIGTERM, handler)
+            return previous
+        except ValueError:          # not the main thread: signals cannot be installed here
+            return None
+
+    def log_metrics(self, split: str, metrics: dict) -> None:
+        if not self.ddp.is_main:
+            return
+        width = max((len(k) for k in metrics), default=0)
+        print(f"***** {split} metrics *****")
+        for k in sorted(metrics):
+            v = metrics[k]
+            print(f"  {k:<{width}} = {v:.6g}" if isinstance(v, float) else f"  {k:<{width}} = {v}")
+
+    def save_metrics(self, split: str, metrics: dict, combined: bool = True) -> None:
+        if not self.ddp.is_main:
+            return
+        os.makedirs(self.args.output_dir, exist_ok=True)
+        with open(os.path.join(self.args.output_dir, f"{split}_results.json"), "w", encoding="utf-8") as f:
+            json.dump(metrics, f, indent=2, sort_keys=True, default=float)
+        if combined:
+            path = os.path.join(self.args.output_dir, "all_results.json")
+            allm = {}
+            if os.path.exists(path):
+                with open(path, encoding="utf-8") as f:
+                    allm = json.load(f)
+            allm.update(metrics)
+            with open(path, "w", encoding="utf-8") as f:
+                json.dump(allm, f, indent=2, sort_keys=True, default=float)
+
+    def save_state(self) -> None:
+        if self.ddp.is_main:
+            os.makedirs(self.args.output_dir, exist_ok=True)
+            self.state.save_to_json(os.path.join(self.args.output_dir, ckpt.FILES.TRAINER_STATE))
+
     def _cluster_needs_step_down(self, local: bool) -> bool:
         return bool(D.reduce_scalar(int(local), op="max")) if self.ddp.is_distributed else local
 
@@ -475,6 +523,7 @@ class DPTrainer:
                 raise CheckpointError(f"no checkpoint to resume from ({resume!r})")
             self._load_checkpoint(path)
         self.control = self.callback_handler.call_event("on_train_begin", a, st, self.control)
+        previous_sigterm = self._install_sigterm_handler()
         if a.eval_on_start and self.eval_dataset is not None:
             self.evaluate()
         t0 = time.time()
@@ -510,8 +559,14 @@ class DPTrainer:
             self._maybe_log_save_evaluate(t0)
             if a.torch_empty_cache_steps and st.global_step % a.torch_empty_cache_steps == 0 and torch.cuda.is_available():
                 torch.cuda.empty_cache()
+            if self._sigterm_agreed():
+                self._save_checkpoint()
+                self.control.should_training_stop = True
             if self.control.should_training_stop:
                 break
+        if previous_sigterm is not None:
+            import signal
+            signal.signal(signal.SIGTERM, previous_sigterm)
         if self.accountant is not None and rt["step_process"] is not None and not rt["per_step_process"]:
             self.accountant = self.accountant | rt["step_process"]      # horizon mechanism: one process for the whole run
         if epoch_seen >= 0:
@@ -529,6 +584,13 @@ class DPTrainer:
             self._load_model_weights(st.best_model_checkpoint)
         self.control = self.callback_handler.call_event("on_train_end", a, st, self.control)
         return TrainOutput(st.global_step, metrics["train_loss"], metrics)
+
+    def _sigterm_agreed(self) -> bool:
+        """True on every rank as soon as any rank has received SIGTERM (they must checkpoint together)."""
+        if not self.args.enable_jit_checkpoint:
+            return False
+        flag = bool(getattr(self, "_sigterm", False))
+        return bool(D.reduce_scalar(int(flag), op="max", device=self.device)) if self.ddp.is_distributed else flag
 
     def privacy_spent(self) -> float | None:
         """epsilon at the run's delta for everything released so far (``None`` without accounting)."""

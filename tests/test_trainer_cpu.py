@@ -209,3 +209,64 @@ def test_moe_routes_agree_and_checkpoint_segment():
     g1 = torch.func.vmap(torch.func.grad(f), in_dims=(None, 0))(wt, torch.ones(4, 3))
     g2 = torch.func.vmap(torch.func.grad(seg), in_dims=(None, 0))(wt, torch.ones(4, 3))
     assert torch.allclose(g1, g2)
+
+
+def test_oom_step_down_halves_microbatch_and_retries(tmp_path):
+    """A simulated out-of-memory error in the gradient computation halves the micro-batch and training restarts."""
+    from opake_b200.transformers import DPTrainer
+
+    class Flaky(DPTrainer):
+        calls = 0
+
+        def training_step(self, batch):
+            if (self._microbatch or 10**9) > 4:
+                Flaky.calls += 1
+                raise RuntimeError("CUDA out of memory. Tried to allocate 1.00 GiB (simulated)")
+            return super().training_step(batch)
+
+    args = _args(tmp_path, save_strategy="no", eval_strategy="no", max_steps=3, microbatch_size=16, auto_find_microbatch_size=True)
+    tr = Flaky(_Net(), args, train_dataset=_DS(300))
+    with pytest.warns(UserWarning, match="out of memory"):
+        out = tr.train()
+    assert out.global_step == 3 and tr._microbatch == 4 and Flaky.calls == 2
+    # without auto_find_microbatch_size the error propagates
+    Flaky.calls = 0
+    tr2 = Flaky(_Net(), _args(tmp_path, save_strategy="no", eval_strategy="no", microbatch_size=16), train_dataset=_DS(300))
+    with pytest.raises(RuntimeError, match="out of memory"):
+        tr2.train()
+
+
+def test_sigterm_triggers_checkpoint_and_clean_stop(tmp_path):
+    import signal
+
+    from opake_b200.transformers import DPTrainer, TrainerCallback
+
+    class Preempt(TrainerCallback):
+        def on_step_end(self, args, state, control, **kw):
+            if state.global_step == 2:
+                os.kill(os.getpid(), signal.SIGTERM)
+
+    args = _args(tmp_path, save_strategy="no", eval_strategy="no", max_steps=8, enable_jit_checkpoint=True)
+    tr = DPTrainer(_Net(), args, train_dataset=_DS(300), callbacks=[Preempt()])
+    out = tr.train()
+    assert out.global_step == 2 and (tmp_path / "checkpoint-2" / "dp_state.pt").exists()
+    tr.save_metrics("train", out.metrics)
+    tr.save_state()
+    assert (tmp_path / "train_results.json").exists() and (tmp_path / "trainer_state.json").exists()
+
+
+def test_accountant_engine_under_address_and_ub_sanitizers(tmp_path):
+    """Builds the stand-alone exercise of the C++ privacy-loss-distribution engine with ASAN + UBSAN and runs it."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("no C++ compiler")
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc", "accounting")
+    exe = str(tmp_path / "acc_selftest")
+    build = subprocess.run(["g++", "-std=c++17", "-O1", "-g", "-fsanitize=address,undefined", "-fno-omit-frame-pointer",
+                            "-pthread", os.path.join(root, "selftest.cpp"), "-o", exe], capture_output=True, text=True)
+    if build.returncode != 0 and "sanitize" in build.stderr:
+        pytest.skip("sanitizer runtime not installed")
+    assert build.returncode == 0, build.stderr[-2000:]
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0 and "all checks passed" in run.stdout, run.stdout[-2000:] + run.stderr[-2000:]
