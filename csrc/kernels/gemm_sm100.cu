@@ -1,10 +1,11 @@
 // Host side of the tcgen05 GEMM: builds the TMA tensor maps and launches the persistent kernel.
-#include "gemm_sm100.cuh"
+#include "gemm2_sm100.cuh"
 #include "opk_api.h"
 
 #include <cudaTypedefs.h>
 #include <mutex>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 namespace {
@@ -85,6 +86,37 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const opk::GemmParams& 
   return 0;
 }
 
+// Pair mode: eligible products (256-wide column tiles, no grouped tables, at least 256 rows) run on the two-CTA
+// kernel. -1 = not decided yet (environment variable OPK_GEMM_PAIR, default on).
+int g_pair_mode = -1;
+bool pair_mode() {
+  if (g_pair_mode < 0) {
+    const char* e = getenv("OPK_GEMM_PAIR");
+    g_pair_mode = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pair_mode == 1;
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const opk::GemmParams& p, int max_ctas, cudaStream_t st) {
+  using Cfg = opk::Gemm2Cfg;
+  auto kern = opk::gemm2_bf16_kernel<A_MN, B_MN, EPI>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) { set_err(cudaGetErrorString(e)); return (int)e; }
+    attr_done = true;
+  }
+  const int tiles = ((p.M + 255) / 256) * ((p.N + Cfg::BN - 1) / Cfg::BN) * p.batch;
+  int grid = (max_ctas > 0 ? max_ctas : num_sms()) & ~1;   // whole CTA pairs
+  if (grid < 2) grid = 2;
+  if (grid > 2 * tiles) grid = 2 * tiles;
+  kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(ta, tb, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_err(cudaGetErrorString(e)); return (int)e; }
+  return 0;
+}
+
 int pick_bn(int N, int epilogue) {
   if (epilogue == opk::EPI_LCE_FWD || epilogue == opk::EPI_LCE_BWD || epilogue == opk::EPI_SWIGLU) return 256;
   return N <= 128 ? 128 : 256;
@@ -94,6 +126,8 @@ int pick_bn(int N, int epilogue) {
 
 extern "C" const char* opk_last_error(void) { return g_err; }
 extern "C" int opk_num_sms(void) { return num_sms(); }
+extern "C" void opk_gemm_set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }
+extern "C" int opk_gemm_get_pair_mode(void) { return pair_mode() ? 1 : 0; }
 extern "C" int opk_gemm_tiles_n(int N, int epilogue) {
   const int bn = pick_bn(N, epilogue);
   return (N + bn - 1) / bn;
@@ -102,6 +136,7 @@ extern "C" int opk_gemm_tiles_n(int N, int epilogue) {
 extern "C" int opk_gemm(const OpkGemmArgs* a, void* stream) {
   if (!a || a->M <= 0 || a->N <= 0 || a->K <= 0 || a->batch <= 0) { set_err("opk_gemm: bad sizes"); return -1; }
   const int bn = pick_bn(a->N, a->epilogue);
+  const bool pair = bn == 256 && !a->tile_group && !a->group_k && a->M >= 256 && pair_mode();
   CUtensorMap ta, tb;
   // A: K-major -> {K, M, batch} box {64, 128}; MN-major -> {M, K, batch} box {64, 64}
   if (a->tile_group && (a->batch != 1 || a->n_groups <= 0)) { set_err("opk_gemm: tile_group needs batch == 1 and n_groups"); return -1; }
@@ -117,7 +152,7 @@ extern "C" int opk_gemm(const OpkGemmArgs* a, void* stream) {
   if (a->b_mn) {
     if (!make_map(&tb, a->B, a->N, a->K, bbatch, a->ldb, a->strideB, 64)) return -2;
   } else {
-    if (!make_map(&tb, a->B, a->K, a->N, bbatch, a->ldb, a->strideB, bn)) return -2;
+    if (!make_map(&tb, a->B, a->K, a->N, bbatch, a->ldb, a->strideB, pair ? 128 : bn)) return -2;
   }
   opk::GemmParams p;
   memset(&p, 0, sizeof(p));
@@ -130,6 +165,34 @@ extern "C" int opk_gemm(const OpkGemmArgs* a, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int key = (a->a_mn ? 1 : 0) | (a->b_mn ? 2 : 0);
   const int mc = a->max_ctas;
+  if (pair) {
+    switch (a->epilogue) {
+      case opk::EPI_STORE:
+        if (key == 0) return launch2<false, false, opk::EPI_STORE>(ta, tb, p, mc, st);
+        if (key == 2) return launch2<false, true, opk::EPI_STORE>(ta, tb, p, mc, st);
+        if (key == 3) return launch2<true, true, opk::EPI_STORE>(ta, tb, p, mc, st);
+        break;
+      case opk::EPI_SUMSQ:
+        if (!a->sumsq) { set_err("opk_gemm: sumsq pointer required"); return -1; }
+        if (key == 3) return launch2<true, true, opk::EPI_SUMSQ>(ta, tb, p, mc, st);
+        break;
+      case opk::EPI_SWIGLU:
+        if (!a->act || (a->N & 1)) { set_err("opk_gemm: swiglu needs act and even N"); return -1; }
+        if (key == 0) return launch2<false, false, opk::EPI_SWIGLU>(ta, tb, p, mc, st);
+        break;
+      case opk::EPI_LCE_FWD:
+        if (!a->labels || !a->pmax || !a->psum || !a->tgt) { set_err("opk_gemm: lce fwd buffers required"); return -1; }
+        if (key == 0) return launch2<false, false, opk::EPI_LCE_FWD>(ta, tb, p, mc, st);
+        break;
+      case opk::EPI_LCE_BWD:
+        if (!a->labels || !a->lse || !a->coef) { set_err("opk_gemm: lce bwd buffers required"); return -1; }
+        if (key == 0) return launch2<false, false, opk::EPI_LCE_BWD>(ta, tb, p, mc, st);
+        break;
+      default: break;
+    }
+    set_err("opk_gemm: unsupported (layout, epilogue) combination");
+    return -3;
+  }
   switch (a->epilogue) {
     case opk::EPI_STORE:
       if (key == 0) return bn == 256 ? launch<false, false, 256, opk::EPI_STORE>(ta, tb, p, mc, st)

@@ -90,6 +90,140 @@ __device__ __forceinline__ void store_row_chunk(__nv_bfloat16* dst, const float 
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
 
+// Epilogue of one accumulator tile for one thread's row: reads BN fp32 columns from TMEM (tmem_tile = lane-adjusted
+// address of the tile) and applies the epilogue EPI. Returns the thread's partial sum of squares (EPI_SUMSQ).
+template <int BN, int EPI>
+__device__ __forceinline__ float epilogue_tile(const GemmParams& p, uint32_t tmem_tile, int row, int tn, int tiles_n, int b) {
+  const bool row_ok = row < p.M;
+  const int n0 = tn * BN;
+  __nv_bfloat16* Crow = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.strideC + (long long)row * p.ldc;
+  const __nv_bfloat16* Rrow =
+      p.R ? reinterpret_cast<const __nv_bfloat16*>(p.R) + b * p.strideC + (long long)row * p.ldc : nullptr;
+  const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                      (((b * p.strideC) & 7) == 0);
+
+  float sq_acc = 0.f;  // per-tile fp32 partial (256 squares per thread), flushed to fp64 below
+
+  // LCE forward running statistics for this (row, column tile)
+  float run_max = -INFINITY, run_sum = 0.f;
+  int label = -1;
+  float lse_row = 0.f, coef_row = 0.f;
+  if (EPI == EPI_LCE_FWD || EPI == EPI_LCE_BWD) {
+    if (row_ok) label = p.labels[row];
+    if (EPI == EPI_LCE_BWD && row_ok) { lse_row = p.lse[row]; coef_row = p.coef[row]; }
+  }
+
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 32) {
+    uint32_t raw[32];
+    __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the predicated body below
+    tmem_ld32(tmem_tile + c0, raw);
+    tc_wait_ld();
+    const int col0 = n0 + c0;
+    const int ncols = min(32, p.N - col0);
+    if (row_ok && ncols > 0) {
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]) * p.alpha;
+
+    if (EPI == EPI_STORE || EPI == EPI_SUMSQ || EPI == EPI_SWIGLU) {
+      if (p.bias) {
+        const __nv_bfloat16* bs = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (j < ncols) v[j] += __bfloat162float(bs[j]);
+      }
+      if (Rrow) {
+        if (ncols >= 32 && vec_ok) {
+          const uint4* r4 = reinterpret_cast<const uint4*>(Rrow + col0);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 rr = r4[q];
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float2 f = __bfloat1622float2(h[e]);
+              v[8 * q + 2 * e] += f.x;
+              v[8 * q + 2 * e + 1] += f.y;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (j < ncols) v[j] += __bfloat162float(Rrow[col0 + j]);
+        }
+      }
+      if (EPI == EPI_SUMSQ) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (j < ncols) { float q = bf16_round(v[j]); sq_acc += q * q; }
+      }
+      store_row_chunk(Crow + col0, v, ncols, vec_ok);
+      if (EPI == EPI_SWIGLU) {
+        __nv_bfloat16* arow = reinterpret_cast<__nv_bfloat16*>(p.act) + (long long)row * p.ld_act + (col0 >> 1);
+        float a[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          // match the stored (bf16-rounded) pre-activations so backward recomputes the same values
+          const float g = bf16_round(v[2 * j]), u = bf16_round(v[2 * j + 1]);
+          a[j] = g / (1.f + __expf(-g)) * u;
+        }
+        const int na = ncols >> 1;
+        if (na == 16 && ((p.ld_act & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.act) & 15) == 0)) {
+          uint4* d4 = reinterpret_cast<uint4*>(arow);
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            uint4 o;
+            o.x = pack_bf16x2(a[8 * q + 0], a[8 * q + 1]);
+            o.y = pack_bf16x2(a[8 * q + 2], a[8 * q + 3]);
+            o.z = pack_bf16x2(a[8 * q + 4], a[8 * q + 5]);
+            o.w = pack_bf16x2(a[8 * q + 6], a[8 * q + 7]);
+            d4[q] = o;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) if (j < na) arow[j] = __float2bfloat16(a[j]);
+        }
+      }
+    } else {
+      if (p.softcap > 0.f) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = p.softcap * tanhf(v[j] / p.softcap);
+      }
+      if (EPI == EPI_LCE_FWD) {
+        float cmax = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (j < ncols) cmax = fmaxf(cmax, v[j]);
+        const float nmax = fmaxf(run_max, cmax);
+        float add = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (j < ncols) add += __expf(v[j] - nmax);
+        run_sum = run_sum * __expf(run_max - nmax) + add;
+        run_max = nmax;
+        if (label >= col0 && label < col0 + ncols) {
+          float t = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (col0 + j == label) t = v[j];
+          p.tgt[row] = t;
+        }
+      } else {  // EPI_LCE_BWD
+        float d[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float pr = __expf(v[j] - lse_row);
+          float g = (pr - ((col0 + j == label) ? 1.f : 0.f)) * coef_row;
+          if (p.softcap > 0.f) { const float th = v[j] / p.softcap; g *= (1.f - th * th); }
+          d[j] = g;
+        }
+        store_row_chunk(Crow + col0, d, ncols, vec_ok);
+      }
+    }
+    }  // row_ok && ncols > 0
+  }
+  if (EPI == EPI_LCE_FWD && row_ok) {
+    p.pmax[(long long)row * tiles_n + tn] = run_max;
+    p.psum[(long long)row * tiles_n + tn] = run_sum;
+  }
+  return sq_acc;
+}
+
 template <bool A_MN, bool B_MN, int BN, int EPI>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -244,133 +378,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
 
       const int row = tm * BM + quad * 32 + lane;
-      const bool row_ok = row < p.M;
-      const int n0 = tn * BN;
-      __nv_bfloat16* Crow = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.strideC + (long long)row * p.ldc;
-      const __nv_bfloat16* Rrow =
-          p.R ? reinterpret_cast<const __nv_bfloat16*>(p.R) + b * p.strideC + (long long)row * p.ldc : nullptr;
-      const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
-                          (((b * p.strideC) & 7) == 0);
-
-      float sq_acc = 0.f;  // per-tile fp32 partial (256 squares per thread), flushed to fp64 below
-
-      // LCE forward running statistics for this (row, column tile)
-      float run_max = -INFINITY, run_sum = 0.f;
-      int label = -1;
-      float lse_row = 0.f, coef_row = 0.f;
-      if (EPI == EPI_LCE_FWD || EPI == EPI_LCE_BWD) {
-        if (row_ok) label = p.labels[row];
-        if (EPI == EPI_LCE_BWD && row_ok) { lse_row = p.lse[row]; coef_row = p.coef[row]; }
-      }
-
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t raw[32];
-        __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the predicated body below
-        tmem_ld32(tmem_base + (uint32_t(quad * 32) << 16) + buf * BN + c0, raw);
-        tc_wait_ld();
-        const int col0 = n0 + c0;
-        const int ncols = min(32, p.N - col0);
-        if (row_ok && ncols > 0) {
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]) * p.alpha;
-
-        if (EPI == EPI_STORE || EPI == EPI_SUMSQ || EPI == EPI_SWIGLU) {
-          if (p.bias) {
-            const __nv_bfloat16* bs = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) if (j < ncols) v[j] += __bfloat162float(bs[j]);
-          }
-          if (Rrow) {
-            if (ncols >= 32 && vec_ok) {
-              const uint4* r4 = reinterpret_cast<const uint4*>(Rrow + col0);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint4 rr = r4[q];
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&rr);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  float2 f = __bfloat1622float2(h[e]);
-                  v[8 * q + 2 * e] += f.x;
-                  v[8 * q + 2 * e + 1] += f.y;
-                }
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (j < ncols) v[j] += __bfloat162float(Rrow[col0 + j]);
-            }
-          }
-          if (EPI == EPI_SUMSQ) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) if (j < ncols) { float q = bf16_round(v[j]); sq_acc += q * q; }
-          }
-          store_row_chunk(Crow + col0, v, ncols, vec_ok);
-          if (EPI == EPI_SWIGLU) {
-            __nv_bfloat16* arow = reinterpret_cast<__nv_bfloat16*>(p.act) + (long long)row * p.ld_act + (col0 >> 1);
-            float a[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              // match the stored (bf16-rounded) pre-activations so backward recomputes the same values
-              const float g = bf16_round(v[2 * j]), u = bf16_round(v[2 * j + 1]);
-              a[j] = g / (1.f + __expf(-g)) * u;
-            }
-            const int na = ncols >> 1;
-            if (na == 16 && ((p.ld_act & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.act) & 15) == 0)) {
-              uint4* d4 = reinterpret_cast<uint4*>(arow);
-#pragma unroll
-              for (int q = 0; q < 2; ++q) {
-                uint4 o;
-                o.x = pack_bf16x2(a[8 * q + 0], a[8 * q + 1]);
-                o.y = pack_bf16x2(a[8 * q + 2], a[8 * q + 3]);
-                o.z = pack_bf16x2(a[8 * q + 4], a[8 * q + 5]);
-                o.w = pack_bf16x2(a[8 * q + 6], a[8 * q + 7]);
-                d4[q] = o;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) if (j < na) arow[j] = __float2bfloat16(a[j]);
-            }
-          }
-        } else {
-          if (p.softcap > 0.f) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = p.softcap * tanhf(v[j] / p.softcap);
-          }
-          if (EPI == EPI_LCE_FWD) {
-            float cmax = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) if (j < ncols) cmax = fmaxf(cmax, v[j]);
-            const float nmax = fmaxf(run_max, cmax);
-            float add = 0.f;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) if (j < ncols) add += __expf(v[j] - nmax);
-            run_sum = run_sum * __expf(run_max - nmax) + add;
-            run_max = nmax;
-            if (label >= col0 && label < col0 + ncols) {
-              float t = 0.f;
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (col0 + j == label) t = v[j];
-              p.tgt[row] = t;
-            }
-          } else {  // EPI_LCE_BWD
-            float d[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float pr = __expf(v[j] - lse_row);
-              float g = (pr - ((col0 + j == label) ? 1.f : 0.f)) * coef_row;
-              if (p.softcap > 0.f) { const float th = v[j] / p.softcap; g *= (1.f - th * th); }
-              d[j] = g;
-            }
-            store_row_chunk(Crow + col0, d, ncols, vec_ok);
-          }
-        }
-        }  // row_ok && ncols > 0
-      }
-      if (EPI == EPI_LCE_FWD && row_ok) {
-        p.pmax[(long long)row * tiles_n + tn] = run_max;
-        p.psum[(long long)row * tiles_n + tn] = run_sum;
-      }
+      const float sq_acc = epilogue_tile<BN, EPI>(p, tmem_base + (uint32_t(quad * 32) << 16) + buf * BN, row, tn, tiles_n, b);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[buf]);

@@ -44,6 +44,9 @@ typedef struct OpkGemmArgs {
 int opk_gemm(const OpkGemmArgs* args, void* stream);
 int opk_gemm_tiles_n(int N, int epilogue);  // number of column tiles the kernel uses (LCE partial buffers)
 int opk_num_sms(void);
+// Two-CTA (cta_group::2) kernel for eligible products: on by default, OPK_GEMM_PAIR=0 or set_pair_mode(0) turns it off.
+void opk_gemm_set_pair_mode(int on);
+int opk_gemm_get_pair_mode(void);
 // Bounded-wait self-test: one CTA waits `budget_cycles` on a barrier nobody completes, then sets *err = 3 and returns.
 int opk_wait_selftest(int32_t* err, int64_t budget_cycles, int64_t* waited_cycles, void* stream);
 const char* opk_last_error(void);

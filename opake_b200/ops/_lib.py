@@ -48,6 +48,9 @@ def lib() -> ctypes.CDLL:
     L.opk_gemm_tiles_n.argtypes = [c_int32, c_int32]
     L.opk_gemm_tiles_n.restype = c_int32
     L.opk_num_sms.restype = c_int32
+    L.opk_gemm_set_pair_mode.argtypes = [c_int32]
+    L.opk_gemm_set_pair_mode.restype = None
+    L.opk_gemm_get_pair_mode.restype = c_int32
     _declare_optional(L)
     return L
 

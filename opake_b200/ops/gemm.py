@@ -130,3 +130,14 @@ def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, *, out=None, sumsq: torch.Te
 
 def lce_tiles(n_vocab: int) -> int:
     return _lib.lib().opk_gemm_tiles_n(n_vocab, EPI_LCE_FWD)
+
+
+def set_pair_mode(on: bool) -> None:
+    """Route eligible products (256-wide column tiles, at least 256 rows, no grouped tables) to the two-CTA
+    (``cta_group::2``) kernel, or keep everything on the single-CTA kernel. Process-wide; the default is on
+    (environment variable ``OPK_GEMM_PAIR=0`` turns it off)."""
+    _lib.lib().opk_gemm_set_pair_mode(1 if on else 0)
+
+
+def pair_mode() -> bool:
+    return bool(_lib.lib().opk_gemm_get_pair_mode())

@@ -5,6 +5,17 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["pair", "single"])
+def _kernel_variant(request):
+    """Every case runs on the two-CTA kernel (where the shape is eligible) and on the single-CTA kernel."""
+    from opake_b200.ops import gemm as G
+
+    before = G.pair_mode()
+    G.set_pair_mode(request.param == "pair")
+    yield
+    G.set_pair_mode(before)
+
+
 def _rand(shape, dev, scale=1.0):
     return (torch.randn(shape, device=dev, dtype=torch.float32) * scale).to(torch.bfloat16)
 
