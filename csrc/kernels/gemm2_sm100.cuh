@@ -77,7 +77,7 @@ struct Gemm2Cfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = (BN / 2) * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;          // 32 KB
-  static constexpr int STAGES = 6;
+  static constexpr int STAGES = 7;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = 2 * BN;                        // two accumulator buffers
 };
@@ -142,8 +142,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       for (int tile = cluster_id; tile < total && ok; tile += n_clusters) {
         const int b = tile / per_batch;
         const int r = tile - b * per_batch;
-        const int tn = r / tiles_m;
-        const int tm = r - tn * tiles_m;
+        int tm, tn;
+        tile_coords(r, tiles_m, tiles_n, tm, tn);
         const int bb = b / p.b_batch_div;
         const int row0 = tm * 2 * BM + (int)rank * BM;          // this CTA's rows of A
         const int col0 = tn * BN + (int)rank * (BN / 2);        // this CTA's columns of B
@@ -209,8 +209,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     for (int tile = cluster_id; tile < total; tile += n_clusters, ++it) {
       const int b = tile / per_batch;
       const int r = tile - b * per_batch;
-      const int tn = r / tiles_m;
-      const int tm = r - tn * tiles_m;
+      int tm, tn;
+      tile_coords(r, tiles_m, tiles_n, tm, tn);
       const int buf = it & 1;
       const uint32_t tph = (it >> 1) & 1;
       int ok = 1;

@@ -224,6 +224,20 @@ __device__ __forceinline__ float epilogue_tile(const GemmParams& p, uint32_t tme
   return sq_acc;
 }
 
+// Tile order of the persistent schedule. Column tiles are walked in bands of kRasterBand; inside a band the column
+// index runs fastest, then the row index. The CTAs that run at the same time therefore cover a roughly square patch
+// of the output (8 column tiles x as many row tiles as there are CTAs / 8): the band's B tiles and the patch's A tiles
+// stay in L2 and each operand is fetched from DRAM about once per band instead of once per column tile.
+constexpr int kRasterBand = 8;
+__device__ __forceinline__ void tile_coords(int r, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int band_tiles = kRasterBand * tiles_m;
+  const int band = r / band_tiles;
+  const int rr = r - band * band_tiles;
+  const int w = min(kRasterBand, tiles_n - band * kRasterBand);
+  tm = rr / w;
+  tn = band * kRasterBand + (rr - tm * w);
+}
+
 template <bool A_MN, bool B_MN, int BN, int EPI>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -282,8 +296,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
         const int b = tile / per_batch;
         const int r = tile - b * per_batch;
-        const int tn = r / tiles_m;
-        const int tm = r - tn * tiles_m;
+        int tm, tn;
+        tile_coords(r, tiles_m, tiles_n, tm, tn);
         int bb = b / p.b_batch_div, ba = b;
         int kb0 = 0, nkb = kblocks;
         if (p.tile_group) {
@@ -327,7 +341,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (p.tile_group || p.group_k) {
           const int b = tile / per_batch;
           const int r = tile - b * per_batch;
-          const int tm = r - (r / tiles_m) * tiles_m;
+          int tm, tn;
+          tile_coords(r, tiles_m, tiles_n, tm, tn);
           if (p.tile_group && p.tile_group[tm] < 0) continue;
           if (p.group_k) nkb = p.group_k[2 * b + 1];
         }
@@ -364,8 +379,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
       const int b = tile / per_batch;
       const int r = tile - b * per_batch;
-      const int tn = r / tiles_m;
-      const int tm = r - tn * tiles_m;
+      int tm, tn;
+      tile_coords(r, tiles_m, tiles_n, tm, tn);
       if (p.tile_group && p.tile_group[tm] < 0) continue;
       const int buf = it & 1;
       const uint32_t tph = (it >> 1) & 1;
