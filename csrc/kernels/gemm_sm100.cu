@@ -118,7 +118,9 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const opk::GemmParams&
 }
 
 int pick_bn(int N, int epilogue) {
-  if (epilogue == opk::EPI_LCE_FWD || epilogue == opk::EPI_LCE_BWD || epilogue == opk::EPI_SWIGLU) return 256;
+  if (epilogue == opk::EPI_LCE_FWD || epilogue == opk::EPI_LCE_BWD || epilogue == opk::EPI_SWIGLU ||
+      epilogue == opk::EPI_SWIGLU_BWD)
+    return 256;
   return N <= 128 ? 128 : 256;
 }
 
@@ -180,6 +182,10 @@ extern "C" int opk_gemm(const OpkGemmArgs* a, void* stream) {
         if (!a->act || (a->N & 1)) { set_err("opk_gemm: swiglu needs act and even N"); return -1; }
         if (key == 0) return launch2<false, false, opk::EPI_SWIGLU>(ta, tb, p, mc, st);
         break;
+      case opk::EPI_SWIGLU_BWD:
+        if (!a->act || a->R || a->bias) { set_err("opk_gemm: swiglu backward needs the saved pre-activations and takes no bias / residual"); return -1; }
+        if (key == 2) return launch2<false, true, opk::EPI_SWIGLU_BWD>(ta, tb, p, mc, st);
+        break;
       case opk::EPI_LCE_FWD:
         if (!a->labels || !a->pmax || !a->psum || !a->tgt) { set_err("opk_gemm: lce fwd buffers required"); return -1; }
         if (key == 0) return launch2<false, false, opk::EPI_LCE_FWD>(ta, tb, p, mc, st);
@@ -210,6 +216,10 @@ extern "C" int opk_gemm(const OpkGemmArgs* a, void* stream) {
     case opk::EPI_SWIGLU:
       if (!a->act || (a->N & 1)) { set_err("opk_gemm: swiglu needs act and even N"); return -1; }
       if (key == 0) return launch<false, false, 256, opk::EPI_SWIGLU>(ta, tb, p, mc, st);
+      break;
+    case opk::EPI_SWIGLU_BWD:
+      if (!a->act || a->R || a->bias) { set_err("opk_gemm: swiglu backward needs the saved pre-activations and takes no bias / residual"); return -1; }
+      if (key == 2) return launch<false, true, 256, opk::EPI_SWIGLU_BWD>(ta, tb, p, mc, st);
       break;
     case opk::EPI_LCE_FWD:
       if (!a->labels || !a->pmax || !a->psum || !a->tgt) { set_err("opk_gemm: lce fwd buffers required"); return -1; }

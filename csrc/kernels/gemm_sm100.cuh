@@ -24,6 +24,7 @@ enum GemmEpilogue : int {
   EPI_SWIGLU = 2,   // columns interleaved (gate, up): C = raw, act[m][n/2] = silu(gate)*up
   EPI_LCE_FWD = 3,  // per-(row, column-tile) max / sum-exp partials and the target logit; no logits stored
   EPI_LCE_BWD = 4,  // C = (exp(z - lse[m]) - [n == label[m]]) * coef[m]
+  EPI_SWIGLU_BWD = 5,  // acc = d(act); act = saved (gate, up) pairs [M][2N]; C[m][2n], C[m][2n+1] = d(gate), d(up)
 };
 
 struct GemmParams {
@@ -36,7 +37,7 @@ struct GemmParams {
   const void* bias;      // optional bf16 [N]
   float alpha;
   double* sumsq;         // EPI_SUMSQ: one accumulator per batch entry (sumsq[b])
-  void* act;             // EPI_SWIGLU: bf16 [M][ld_act]
+  void* act;             // EPI_SWIGLU: bf16 [M][ld_act] (written); EPI_SWIGLU_BWD: saved pre-activations (read)
   long long ld_act;
   const int* labels;     // EPI_LCE_*: [M], negative = ignored
   float* pmax;           // EPI_LCE_FWD: [M][tiles_n]
@@ -181,6 +182,39 @@ __device__ __forceinline__ float epilogue_tile(const GemmParams& p, uint32_t tme
 #pragma unroll
           for (int j = 0; j < 16; ++j) if (j < na) arow[j] = __float2bfloat16(a[j]);
         }
+      }
+    } else if (EPI == EPI_SWIGLU_BWD) {
+      // 32 accumulator columns = 32 (gate, up) pairs = 64 stored columns, read and written as 8 x 16 bytes
+      const __nv_bfloat16* grow = reinterpret_cast<const __nv_bfloat16*>(p.act) + (long long)row * p.ld_act + 2 * col0;
+      __nv_bfloat16* drow = Crow + 2 * col0;
+      const bool v2 = ncols >= 32 && vec_ok && ((p.ld_act & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.act) & 15) == 0);
+      if (v2) {
+        const uint4* g4 = reinterpret_cast<const uint4*>(grow);
+        uint4* d4 = reinterpret_cast<uint4*>(drow);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const uint4 in = g4[q];
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&in);
+          uint32_t o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 gu = __bfloat1622float2(h[e]);
+            const float d = bf16_round(v[4 * q + e]);
+            const float sg = 1.f / (1.f + __expf(-gu.x));
+            o[e] = pack_bf16x2(d * gu.y * (sg * (1.f + gu.x * (1.f - sg))), d * (gu.x * sg));
+          }
+          d4[q] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncols) {
+            const float g = __bfloat162float(grow[2 * j]), u = __bfloat162float(grow[2 * j + 1]);
+            const float d = bf16_round(v[j]);
+            const float sg = 1.f / (1.f + __expf(-g));
+            drow[2 * j] = __float2bfloat16(d * u * (sg * (1.f + g * (1.f - sg))));
+            drow[2 * j + 1] = __float2bfloat16(d * (g * sg));
+          }
       }
     } else {
       if (p.softcap > 0.f) {

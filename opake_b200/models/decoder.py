@@ -137,7 +137,7 @@ class DecoderRuntime:
         ws["emb"], ws["tok"] = ws["embs"][0], ws["toks"][0]
         if cfg.n_experts:
             R, I = layers[0]["plan"].R, cfg.expert_ffn
-            ws.update(dye=e(R, d), dh=e(R, I).zero_(), dgu=e(R, 2 * I), dxs=e(R, d).zero_(),
+            ws.update(dye=e(R, d), dgu=e(R, 2 * I).zero_(), dxs=e(R, d).zero_(),
                       dwts=e(T, cfg.top_k, dtype=torch.float32), drl=e(T, cfg.n_experts))
         self._ws[T] = ws
         return ws
@@ -279,8 +279,7 @@ class DecoderRuntime:
                 # expert weight gradients: one grouped GEMM per matrix, reduction range of expert e = its row segment
                 G.gemm(ws["dye"], a["act"], a_mn=True, b_mn=True, out=g[p + "experts.wd"], epilogue=G.EPI_SUMSQ, sumsq=sumsq,
                        group_k=plan.group_k, sumsq_shared=True)
-                G.gemm(ws["dye"], w[p + "experts.wd"], b_mn=True, out=ws["dh"], tile_group=plan.tile_group)
-                K.swiglu_bwd(ws["dh"], a["gu"], out=ws["dgu"])
+                G.swiglu_dgrad(ws["dye"], w[p + "experts.wd"], a["gu"], out=ws["dgu"], tile_group=plan.tile_group)
                 G.gemm(ws["dgu"], a["xs"], a_mn=True, b_mn=True, out=g[p + "experts.wgu"], epilogue=G.EPI_SUMSQ, sumsq=sumsq,
                        group_k=plan.group_k, sumsq_shared=True)
                 G.gemm(ws["dgu"], w[p + "experts.wgu"], b_mn=True, out=ws["dxs"], tile_group=plan.tile_group)
@@ -291,11 +290,11 @@ class DecoderRuntime:
                 G.gemm(ws["drl"], w[p + "router"], b_mn=True, out=dxn2, residual=dxn2)
             elif cfg.act in ("swiglu", "geglu"):
                 G.linear_wgrad(dx, a["act"], out=g[p + "wd"], sumsq=sumsq)
-                dact = G.gemm(dx, w[p + "wd"], b_mn=True, out=ws["dact"])
                 dgu = ws["dwide"]
-                if cfg.act == "swiglu":
-                    K.swiglu_bwd(dact, a["gu"], out=dgu)
+                if cfg.act == "swiglu":       # d(act) stays in the accumulator: SwiGLU backward runs in the dgrad epilogue
+                    G.swiglu_dgrad(dx, w[p + "wd"], a["gu"], out=dgu)
                 else:
+                    dact = G.gemm(dx, w[p + "wd"], b_mn=True, out=ws["dact"])
                     K.geglu_bwd(dact, a["gu"], True, out=dgu)
                 G.linear_wgrad(dgu, a["xn2"], out=g[p + "wgu"], sumsq=sumsq)
                 dxn2 = G.gemm(dgu, w[p + "wgu"], b_mn=True, out=ws["dx2"])

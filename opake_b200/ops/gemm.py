@@ -10,7 +10,7 @@ import torch
 
 from . import _lib
 
-EPI_STORE, EPI_SUMSQ, EPI_SWIGLU, EPI_LCE_FWD, EPI_LCE_BWD = range(5)
+EPI_STORE, EPI_SUMSQ, EPI_SWIGLU, EPI_LCE_FWD, EPI_LCE_BWD, EPI_SWIGLU_BWD = range(6)
 
 
 def _check2d(t: torch.Tensor, name: str) -> None:
@@ -70,6 +70,8 @@ def gemm(
     if group_k is not None:
         batch = group_k.shape[0]          # one output per group; operands stay un-batched
     need_out = epilogue != EPI_LCE_FWD
+    if epilogue == EPI_SWIGLU_BWD and (out is None or act is None or out.shape != act.shape or act.shape[-1] != 2 * N):
+        raise ValueError("swiglu backward epilogue: act (saved gate/up pairs) and out must both be [M, 2N]")
     if out is None and need_out:
         shape = (batch, M, N) if (batched or group_k is not None) else (M, N)
         out = torch.empty(shape, dtype=torch.bfloat16, device=a.device)
@@ -116,6 +118,13 @@ def linear_fwd(x: torch.Tensor, w: torch.Tensor, *, bias=None, residual=None, ou
 def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, *, out=None, residual=None) -> torch.Tensor:
     """``dx = dy @ w`` with ``dy [T, N]``, ``w [N, K]`` (weight consumed in place, no transposed copy)."""
     return gemm(dy, w, b_mn=True, out=out, residual=residual)
+
+
+def swiglu_dgrad(dy: torch.Tensor, w_down: torch.Tensor, gu: torch.Tensor, *, out: torch.Tensor, tile_group=None) -> torch.Tensor:
+    """Backward through ``act = silu(gate) * up`` fused into the down projection's data gradient: the accumulator
+    ``d_act = dy @ w_down`` (``dy [T, d]``, ``w_down [d, F]``) never reaches memory; the epilogue reads the saved
+    interleaved pre-activations ``gu [T, 2F]`` and writes ``out [T, 2F]`` = interleaved ``(d_gate, d_up)``."""
+    return gemm(dy, w_down, b_mn=True, out=out, epilogue=EPI_SWIGLU_BWD, act=gu, tile_group=tile_group)
 
 
 def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, *, out=None, sumsq: torch.Tensor | None = None) -> torch.Tensor:

@@ -100,6 +100,24 @@ def test_gemm_swiglu(cuda):
     _close(act, torch.nn.functional.silu(g) * u)
 
 
+@pytest.mark.parametrize("T,F,D", [(256, 512, 128), (300, 200, 72), (2048, 1024, 256)])
+def test_gemm_swiglu_backward_epilogue(cuda, T, F, D):
+    """d(act) = dy @ w_down stays in the accumulator; the epilogue emits interleaved (d_gate, d_up)."""
+    from opake_b200.ops import gemm as G
+    from opake_b200.ops._lib import raise_if_device_error
+
+    dy, wd = _rand((T, D), cuda), _rand((D, F), cuda, 0.1)
+    gu = _rand((T, 2 * F), cuda)
+    out = torch.empty_like(gu)
+    G.swiglu_dgrad(dy, wd, gu, out=out)
+    raise_if_device_error(cuda)
+    g, u = gu.float()[:, 0::2], gu.float()[:, 1::2]
+    dact = (dy.float() @ wd.float())
+    sg = torch.sigmoid(g)
+    ref = torch.stack([dact * u * sg * (1 + g * (1 - sg)), dact * g * sg], dim=-1).reshape(T, 2 * F)
+    _close(out, ref)
+
+
 def test_gemm_lce(cuda):
     from opake_b200.ops import gemm as G
 
