@@ -490,17 +490,25 @@ __global__ void attn_dkv_reduce_kernel(const float* __restrict__ part, __nv_bflo
 //   dV += Pt dO        dK += dSt Q
 template <int HD>
 struct DkvSmem {
+  // The Q / dO ring is deeper than the two score buffers in TMEM: a stage stays occupied from the score products of
+  // its sub-tile until the dK product of the same sub-tile has completed (about two iterations), and the refill needs
+  // a full TMA round trip on top, so two stages leave that round trip exposed in every iteration.
+  static constexpr int NS = 4;
   static constexpr int KV_TILE = 128 * HD * 2;
   static constexpr int Q_TILE = 64 * HD * 2;
   static constexpr int K_OFF = 0;
   static constexpr int V_OFF = KV_TILE;
-  static constexpr int Q_OFF = 2 * KV_TILE;               // 2 stages
-  static constexpr int DO_OFF = Q_OFF + 2 * Q_TILE;       // 2 stages
-  static constexpr int PT_OFF = DO_OFF + 2 * Q_TILE;      // [128][64] bf16
+  static constexpr int Q_OFF = 2 * KV_TILE;               // NS stages
+  static constexpr int DO_OFF = Q_OFF + NS * Q_TILE;      // NS stages
+  static constexpr int PT_OFF = DO_OFF + NS * Q_TILE;     // [128][64] bf16
   static constexpr int DST_OFF = PT_OFF + 16384;
-  static constexpr int ROW_OFF = DST_OFF + 16384;         // 2 stages x (64 nlse2 + 64 dsum) floats
-  static constexpr int BAR_OFF = ROW_OFF + 2 * 512;
-  static constexpr int BYTES = BAR_OFF + 256 + 1024;
+  static constexpr int ROW_OFF = DST_OFF + 16384;         // NS stages x (64 nlse2 + 64 dsum) floats
+  static constexpr int BAR_OFF = ROW_OFF + NS * 512;
+  static constexpr int USED = BAR_OFF + 256;
+  // up to 1 KB of alignment padding in front; at HD = 128 the layout only fits when the padding is below 768 bytes,
+  // which the kernel checks before it touches anything
+  static constexpr int BYTES = (USED + 1024 <= 232448) ? USED + 1024 : 232448;
+  static_assert(USED <= 232448, "dK/dV shared-memory layout does not fit");
 };
 
 // One 32-query chunk of the transposed backward softmax for a key row: Pt = exp2(St*c2 + nlse2[q]) and
@@ -535,15 +543,20 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
   using SM = DkvSmem<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if ((int)(smem - smem_raw) + SM::USED > SM::BYTES) {   // uniform over the CTA; nothing has been set up yet
+    if (threadIdx.x == 0 && p.err) atomicExch(p.err, 2);
+    return;
+  }
+  constexpr int NS = SM::NS;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
   uint64_t* kv_full = bars + 0;
-  uint64_t* q_full = bars + 1;    // [2]
-  uint64_t* q_empty = bars + 3;   // [2]
-  uint64_t* st_full = bars + 5;   // [2]
-  uint64_t* st_free = bars + 7;   // [2]
-  uint64_t* pd_full = bars + 9;
-  uint64_t* pd_free = bars + 10;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* q_full = bars + 1;             // [NS]
+  uint64_t* q_empty = q_full + NS;         // [NS]
+  uint64_t* st_full = q_empty + NS;        // [2]
+  uint64_t* st_free = st_full + 2;         // [2]
+  uint64_t* pd_full = st_free + 2;
+  uint64_t* pd_free = pd_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pd_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -564,10 +577,8 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1);
-      mbar_init(&st_full[i], 1); mbar_init(&st_free[i], kSoftmaxWarps);
-    }
+    for (int i = 0; i < NS; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_free[i], kSoftmaxWarps); }
     mbar_init(pd_full, kSoftmaxWarps);
     mbar_init(pd_free, 1);
     *abort_flag = 0;
@@ -590,8 +601,8 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
         tma_load_2d(smem + SM::V_OFF + c * 16384, &tm_kv, kv_full, v_col + c * 64, kt * 128);
       }
       for (int i = 0; i < n_it; ++i) {
-        const int s = i & 1;
-        const uint32_t ph = (i >> 1) & 1;
+        const int s = i % NS;
+        const uint32_t ph = (i / NS) & 1;
         const int h = h_first + i / per_head, q64 = q_first + i % per_head;
         if (!mbar_wait(&q_empty[s], ph ^ 1u, abort_flag)) break;
         mbar_expect_tx(&q_full[s], 2 * SM::Q_TILE + 512);
@@ -610,12 +621,12 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
       const uint32_t pt_s = smem_u32(smem + SM::PT_OFF), dst_s = smem_u32(smem + SM::DST_OFF);
       bool ok = mbar_wait(kv_full, 0, abort_flag);
       auto scores = [&](int i) -> bool {
-        const int s = i & 1;
+        const int s = i & 1, sq = i % NS;
         const uint32_t ph = (i >> 1) & 1;
-        if (!mbar_wait(&q_full[s], ph, abort_flag)) return false;
+        if (!mbar_wait(&q_full[sq], (i / NS) & 1, abort_flag)) return false;
         if (!mbar_wait(&st_free[s], ph ^ 1u, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t q_s = smem_u32(smem + SM::Q_OFF + s * SM::Q_TILE), do_s = smem_u32(smem + SM::DO_OFF + s * SM::Q_TILE);
+        const uint32_t q_s = smem_u32(smem + SM::Q_OFF + sq * SM::Q_TILE), do_s = smem_u32(smem + SM::DO_OFF + sq * SM::Q_TILE);
         issue_product<false, false>(tmem + ST_COL + s * 64, k_s, 128, q_s, 64, 64, HD, false);
         issue_product<false, false>(tmem + DPT_COL + s * 64, v_s, 128, do_s, 64, 64, HD, false);
         umma_commit(&st_full[s]);
@@ -625,14 +636,14 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
       for (int i = 0; i < n_it && ok; ++i) {
         if (i + 1 < n_it) ok = scores(i + 1);
         if (!ok) break;
-        const int s = i & 1;
+        const int sq = i % NS;
         if (!mbar_wait(pd_full, i & 1, abort_flag)) break;
         tc_fence_after();
-        const uint32_t q_s = smem_u32(smem + SM::Q_OFF + s * SM::Q_TILE), do_s = smem_u32(smem + SM::DO_OFF + s * SM::Q_TILE);
+        const uint32_t q_s = smem_u32(smem + SM::Q_OFF + sq * SM::Q_TILE), do_s = smem_u32(smem + SM::DO_OFF + sq * SM::Q_TILE);
         // dV[keys x HD] += Pt[keys x 64 q] * dO[64 q x HD]   (B rows = queries: MN-major)
         issue_product<false, true>(tmem + DV_COL, pt_s, 128, do_s, 64, HD, 64, i > 0);
         issue_product<false, true>(tmem + DK_COL, dst_s, 128, q_s, 64, HD, 64, i > 0);
-        umma_commit(&q_empty[s]);
+        umma_commit(&q_empty[sq]);
         umma_commit(pd_free);
       }
     }
@@ -648,15 +659,15 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
     const float c2 = p.scale * 1.4426950408889634f;
     bool ok = true;
     for (int i = 0; i < n_it && ok; ++i) {
-      const int s = i & 1;
+      const int s = i & 1, sq = i % NS;
       const uint32_t ph = (i >> 1) & 1;
       const int q64 = q_first + i % per_head;
       if (!warp_wait(&st_full[s], ph, abort_flag, lane)) { ok = false; break; }
       tc_fence_after();
       // the row vectors of this stage arrived with Q / dO; the phase has completed already (the scores needed it),
       // the wait only orders this warp's shared-memory reads after the bulk copy
-      if (!warp_wait(&q_full[s], ph, abort_flag, lane)) { ok = false; break; }
-      const float4* nl4 = reinterpret_cast<const float4*>(smem + SM::ROW_OFF + s * 512) + (c0 >> 2);
+      if (!warp_wait(&q_full[sq], (i / NS) & 1, abort_flag, lane)) { ok = false; break; }
+      const float4* nl4 = reinterpret_cast<const float4*>(smem + SM::ROW_OFF + sq * 512) + (c0 >> 2);
       const float4* d4 = nl4 + 16;
       const bool masked = (q64 - q_first) < 2;
       uint32_t pw[16], dw[16];
@@ -705,15 +716,17 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
 //   S = Q K^T [q x 64 keys]   dP = dO V^T [q x 64 keys]   dS = P * (dP - D) * scale   dQ += dS K
 template <int HD>
 struct DqSmem {
+  static constexpr int NS = 4;                            // K / V ring depth (see DkvSmem)
   static constexpr int Q_TILE = 128 * HD * 2;
   static constexpr int KV_TILE = 64 * HD * 2;
   static constexpr int Q_OFF = 0;
   static constexpr int DO_OFF = Q_TILE;
-  static constexpr int K_OFF = 2 * Q_TILE;                // 2 stages
-  static constexpr int V_OFF = K_OFF + 2 * KV_TILE;       // 2 stages
-  static constexpr int DS_OFF = V_OFF + 2 * KV_TILE;      // [128][64] bf16
+  static constexpr int K_OFF = 2 * Q_TILE;                // NS stages
+  static constexpr int V_OFF = K_OFF + NS * KV_TILE;      // NS stages
+  static constexpr int DS_OFF = V_OFF + NS * KV_TILE;     // [128][64] bf16
   static constexpr int BAR_OFF = DS_OFF + 16384;
   static constexpr int BYTES = BAR_OFF + 256 + 1024;
+  static_assert(BYTES <= 232448, "dQ shared-memory layout does not fit");
 };
 
 // One 32-key chunk of the backward softmax for a query row: dS = exp2(S*c2 + nlse2) * (dP - D); keys with local
@@ -741,14 +754,15 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
+  constexpr int NS = SM::NS;
   uint64_t* q_full = bars + 0;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;    // [2]
-  uint64_t* s_free = bars + 7;    // [2]
-  uint64_t* ds_full = bars + 9;
-  uint64_t* ds_free = bars + 10;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* kv_full = bars + 1;            // [NS]
+  uint64_t* kv_empty = kv_full + NS;       // [NS]
+  uint64_t* s_full = kv_empty + NS;        // [2]
+  uint64_t* s_free = s_full + 2;           // [2]
+  uint64_t* ds_full = s_free + 2;
+  uint64_t* ds_free = ds_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ds_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -761,10 +775,8 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], kSoftmaxWarps);
-    }
+    for (int i = 0; i < NS; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], kSoftmaxWarps); }
     mbar_init(ds_full, kSoftmaxWarps);
     mbar_init(ds_free, 1);
     *abort_flag = 0;
@@ -786,8 +798,8 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tma_load_2d(smem + SM::DO_OFF + c * 16384, &tm_do, q_full, q_col + c * 64, qt * 128);
       }
       for (int i = 0; i < n_it; ++i) {
-        const int s = i & 1;
-        const uint32_t ph = (i >> 1) & 1;
+        const int s = i % NS;
+        const uint32_t ph = (i / NS) & 1;
         if (!mbar_wait(&kv_empty[s], ph ^ 1u, abort_flag)) break;
         mbar_expect_tx(&kv_full[s], 2 * SM::KV_TILE);
         for (int c = 0; c < HD / 64; ++c) {
@@ -803,12 +815,12 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const uint32_t ds_s = smem_u32(smem + SM::DS_OFF);
       bool ok = mbar_wait(q_full, 0, abort_flag);
       auto scores = [&](int i) -> bool {
-        const int s = i & 1;
+        const int s = i & 1, sk = i % NS;
         const uint32_t ph = (i >> 1) & 1;
-        if (!mbar_wait(&kv_full[s], ph, abort_flag)) return false;
+        if (!mbar_wait(&kv_full[sk], (i / NS) & 1, abort_flag)) return false;
         if (!mbar_wait(&s_free[s], ph ^ 1u, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t k_s = smem_u32(smem + SM::K_OFF + s * SM::KV_TILE), v_s = smem_u32(smem + SM::V_OFF + s * SM::KV_TILE);
+        const uint32_t k_s = smem_u32(smem + SM::K_OFF + sk * SM::KV_TILE), v_s = smem_u32(smem + SM::V_OFF + sk * SM::KV_TILE);
         issue_product<false, false>(tmem + S_COL + s * 64, q_s, 128, k_s, 64, 64, HD, false);
         issue_product<false, false>(tmem + DP_COL + s * 64, do_s, 128, v_s, 64, 64, HD, false);
         umma_commit(&s_full[s]);
@@ -818,13 +830,13 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       for (int i = 0; i < n_it && ok; ++i) {
         if (i + 1 < n_it) ok = scores(i + 1);
         if (!ok) break;
-        const int s = i & 1;
+        const int sk = i % NS;
         if (!mbar_wait(ds_full, i & 1, abort_flag)) break;
         tc_fence_after();
-        const uint32_t k_s = smem_u32(smem + SM::K_OFF + s * SM::KV_TILE);
+        const uint32_t k_s = smem_u32(smem + SM::K_OFF + sk * SM::KV_TILE);
         // dQ[q x HD] += dS[q x 64 keys] * K[64 keys x HD]   (B rows = keys: MN-major)
         issue_product<false, true>(tmem + DQ_COL, ds_s, 128, k_s, 64, HD, 64, i > 0);
-        umma_commit(&kv_empty[s]);
+        umma_commit(&kv_empty[sk]);
         umma_commit(ds_free);
       }
     }
