@@ -20,7 +20,7 @@ namespace opk {
 
 enum GemmEpilogue : int {
   EPI_STORE = 0,    // C = alpha*acc (+bias[n]) (+R[m][n])
-  EPI_SUMSQ = 1,    // C = bf16(alpha*acc); *sumsq += sum(C^2)
+  EPI_SUMSQ = 1,    // C = bf16(alpha*acc); *sumsq += sum(C^2); with C == nullptr only the sum is produced
   EPI_SWIGLU = 2,   // columns interleaved (gate, up): C = raw, act[m][n/2] = silu(gate)*up
   EPI_LCE_FWD = 3,  // per-(row, column-tile) max / sum-exp partials and the target logit; no logits stored
   EPI_LCE_BWD = 4,  // C = (exp(z - lse[m]) - [n == label[m]]) * coef[m]
@@ -156,7 +156,7 @@ __device__ __forceinline__ float epilogue_tile(const GemmParams& p, uint32_t tme
 #pragma unroll
         for (int j = 0; j < 32; ++j) if (j < ncols) { float q = bf16_round(v[j]); sq_acc += q * q; }
       }
-      store_row_chunk(Crow + col0, v, ncols, vec_ok);
+      if (EPI != EPI_SUMSQ || p.C) store_row_chunk(Crow + col0, v, ncols, vec_ok);   // EPI_SUMSQ without C: norm only
       if (EPI == EPI_SWIGLU) {
         __nv_bfloat16* arow = reinterpret_cast<__nv_bfloat16*>(p.act) + (long long)row * p.ld_act + (col0 >> 1);
         float a[16];

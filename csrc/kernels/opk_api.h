@@ -136,6 +136,43 @@ int opk_clip_sumsq_partial(const void* tiles, int n_tiles, int B, double* partia
 int opk_clip_apply_sum(const void* tiles, int n_tiles, int B, const float* f_bf16, const float* f_fp32,
                        double* post_partial, void* stream);
 
+// ---- expert-parallel dispatch / combine over peer memory (csrc/kernels/ep.cu) ------------------------------------
+#define OPK_EP_MAX_RANKS 8
+#define OPK_EP_PHASES 6
+#define OPK_EP_PHASE_COUNTS 0   // routing histograms have been stored into the peers' control blocks
+#define OPK_EP_PHASE_ROWS 1     // forward rows have been stored into the owners' receive buffers
+#define OPK_EP_PHASE_OUT 2      // expert outputs are complete in the owner's buffer
+#define OPK_EP_PHASE_DROWS 3    // backward: upstream-gradient rows have been stored
+#define OPK_EP_PHASE_DOUT 4     // backward: input-gradient rows are complete in the owner's buffer
+#define OPK_EP_PHASE_BARRIER 5  // plain group barrier (buffer reuse)
+typedef struct {
+  int32_t world, rank, n_experts;
+  int32_t r_cap;                      // rows of every rank's row buffers (multiple of 128)
+  void* ctrl[OPK_EP_MAX_RANKS];       // device address of every rank's control block (opk_ep_ctrl_ints int32, zeroed once)
+} OpkEpGroup;
+typedef struct { void* p[OPK_EP_MAX_RANKS]; } OpkEpPeers;   // the same row buffer on every rank
+int opk_ep_ctrl_ints(int world, int n_experts);
+int opk_ep_rows_capacity(int world, int n_entries, int n_experts);
+// entry_rank[n] = stable rank of entry n among this rank's entries of the same expert; histogram pushed to all peers.
+int opk_ep_count(const OpkEpGroup* g, const int32_t* idx, int n_entries, int32_t* entry_rank, int epoch, void* stream);
+// Stores row (n / k) of x (times entry_scale[n]) into its slot on the owner. replay = 0: slots derived from the
+// histograms (entry_pos written: owner << 26 | row); replay = 1: slots read from entry_pos (backward pass).
+int opk_ep_dispatch(const OpkEpGroup* g, const OpkEpPeers* rows, const void* x, int64_t ldx, int k, const float* entry_scale,
+                    const int32_t* idx, const int32_t* entry_rank, int32_t* entry_pos, int replay, int n_entries, int D,
+                    int wait_phase, int signal_phase, int epoch, int32_t* err, void* stream);
+// Owner side: tile -> local expert table [r_cap / 128], reduction ranges per local expert [E_local][2] and per
+// (local expert, source) [E_local * world][2], row -> source table [r_cap] (-1 = padding), number of rows in use.
+int opk_ep_prepare(const OpkEpGroup* g, int wait_phase, int epoch, int32_t* tile_group, int32_t* group_k_expert,
+                   int32_t* group_k_src, int32_t* row_src, int32_t* rows_total, int32_t* err, void* stream);
+int opk_ep_zero_pad(void* rows, const int32_t* row_src, const int32_t* rows_total, int r_cap, int D, void* stream);
+int opk_ep_scale_rows(const void* rows, const int32_t* row_src, const float* scale, int r_cap, int D, void* out, void* stream);
+int opk_ep_signal(const OpkEpGroup* g, int phase, int epoch, void* stream);
+int opk_ep_wait(const OpkEpGroup* g, int phase, int epoch, int32_t* err, void* stream);
+int opk_ep_combine(const OpkEpGroup* g, const OpkEpPeers* y, const int32_t* entry_pos, const float* wts, int k,
+                   const void* residual, int T, int D, void* out, int wait_phase, int epoch, int32_t* err, void* stream);
+int opk_ep_combine_bwd(const OpkEpPeers* y, const void* dy, const int32_t* entry_pos, int n_entries, int k, int D, float* dwts,
+                       void* stream);
+
 // ---- mixture-of-experts routing / permutation (csrc/kernels/moe.cu) -------------------------------------------
 // probs = softmax(logits[T][E] bf16); idx / wts [T][k]: the k largest (ties: lowest expert), renormalised if norm_topk.
 int opk_moe_route(const void* logits, int64_t ld, int T, int E, int k, int norm_topk, int32_t* idx, float* wts, float* probs,

@@ -19,7 +19,28 @@ class DpStepArgs(Structure):
     ]
 
 
+class EpGroup(Structure):
+    _fields_ = [("world", c_int32), ("rank", c_int32), ("n_experts", c_int32), ("r_cap", c_int32), ("ctrl", c_void_p * 8)]
+
+
+class EpPeers(Structure):
+    _fields_ = [("p", c_void_p * 8)]
+
+
+_G, _PE = POINTER(EpGroup), POINTER(EpPeers)
+
 PROTOTYPES: dict = {
+    "opk_ep_ctrl_ints": (I, [I, I]),
+    "opk_ep_rows_capacity": (I, [I, I, I]),
+    "opk_ep_count": (I, [_G, P, I, P, I, P]),
+    "opk_ep_dispatch": (I, [_G, _PE, P, L, I, P, P, P, P, I, I, I, I, I, I, P, P]),
+    "opk_ep_prepare": (I, [_G, I, I, P, P, P, P, P, P, P]),
+    "opk_ep_zero_pad": (I, [P, P, P, I, I, P]),
+    "opk_ep_scale_rows": (I, [P, P, P, I, I, P, P]),
+    "opk_ep_signal": (I, [_G, I, I, P]),
+    "opk_ep_wait": (I, [_G, I, I, P, P]),
+    "opk_ep_combine": (I, [_G, _PE, P, P, I, P, I, I, P, I, I, P, P]),
+    "opk_ep_combine_bwd": (I, [_PE, P, P, I, I, I, P, P]),
     "opk_rmsnorm_fwd": (I, [P, P, P, P, I, I, F, F, P]),
     "opk_add_rmsnorm_fwd": (I, [P, P, P, P, P, P, I, I, F, F, P]),
     "opk_rmsnorm_bwd": (I, [P, P, P, P, P, P, P, P, I, I, I, F, P]),

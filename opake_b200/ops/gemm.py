@@ -47,6 +47,7 @@ def gemm(
     tile_group: torch.Tensor | None = None,
     group_k: torch.Tensor | None = None,
     sumsq_shared: bool = False,
+    norm_only: bool = False,
 ) -> torch.Tensor | None:
     """General entry: ``out[b] = alpha * op(a[b]) @ op(b[b // b_batch_div])^T`` with an epilogue.
 
@@ -69,7 +70,9 @@ def gemm(
         raise ValueError(f"reduction sizes differ: {K} vs {Kb}")
     if group_k is not None:
         batch = group_k.shape[0]          # one output per group; operands stay un-batched
-    need_out = epilogue != EPI_LCE_FWD
+    if norm_only and (epilogue != EPI_SUMSQ or out is not None or residual is not None):
+        raise ValueError("norm_only: EPI_SUMSQ without an output or residual (only sum(C^2) is produced)")
+    need_out = epilogue != EPI_LCE_FWD and not norm_only
     if epilogue == EPI_SWIGLU_BWD and (out is None or act is None or out.shape != act.shape or act.shape[-1] != 2 * N):
         raise ValueError("swiglu backward epilogue: act (saved gate/up pairs) and out must both be [M, 2N]")
     if out is None and need_out:

@@ -23,11 +23,20 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--blt", action="store_true")
     ap.add_argument("--sharded-linear", action="store_true", help="check the sharded-weight GEMMs instead of the engine")
+    ap.add_argument("--ep-fused", action="store_true", help="check the expert-parallel dispatch / combine kernels")
     a = ap.parse_args()
     rank, world, local = comm.init_distributed()
     dev = torch.device("cuda", local)
     if a.sharded_linear:
         _sharded_linear_check(rank, world, dev, a.out)
+        return
+    if a.ep_fused:
+        res = ep_fused_check(rank, world, dev)
+        if rank == 0:
+            torch.save(res, a.out)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
         return
     cfg = tiny_llama()
     ecfg = EngineConfig(logical_batch=a.batch, noise_multiplier=0.7, lr=1e-2, seed=5, use_cuda_graph=False,
@@ -83,3 +92,75 @@ def _sharded_linear_check(rank: int, world: int, dev: torch.device, out: str) ->
 
 if __name__ == "__main__":
     main()
+
+
+def ep_fused_check(rank: int, world: int, dev: torch.device, T: int = 256, d: int = 128, I: int = 64, E: int = 8, k: int = 2,
+                   calls: int = 2) -> dict:
+    """Runs the fused expert-parallel layer (forward, backward with per-source norms, clipped accumulation) and
+    compares every result with a dense fp32 autograd computation that uses the layer's own routing decisions.
+    Every rank generates all ranks' inputs, so the oracle needs no communication beyond gathering the routing."""
+    import torch.nn.functional as F
+
+    from ..ops._lib import raise_if_device_error
+    from .ep_fused import EpContext, FusedExpertParallelLayer
+
+    gen = torch.Generator().manual_seed(11)
+    bf = lambda t: t.to(torch.bfloat16).to(dev)
+    router = bf(torch.randn(E, d, generator=gen) * 0.5)
+    wgu = bf(torch.randn(E, 2 * I, d, generator=gen) * 0.1)      # gate / up rows interleaved
+    wd = bf(torch.randn(E, d, I, generator=gen) * 0.1)
+    El = E // world
+    mine = slice(rank * El, (rank + 1) * El)
+    ctx = EpContext(E, T * k, dev)
+    layer = FusedExpertParallelLayer(ctx, router, wgu[mine].contiguous(), wd[mine].contiguous(), T, k)
+    worst = {"out": 0.0, "dx": 0.0, "d_router": 0.0, "norms": 0.0, "acc_wgu": 0.0, "acc_wd": 0.0}
+
+    def rel(a, b):
+        return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-12)).item()
+
+    for _ in range(calls):                                       # the second call reuses every buffer and flag
+        xs = bf(torch.randn(world, T, d, generator=gen))
+        dys = bf(torch.randn(world, T, d, generator=gen))
+        scales = torch.tensor([0.5, 0.25, 1.0, 0.125, 0.75, 0.3, 0.9, 0.6][:world], device=dev)
+        x, dy = xs[rank].contiguous(), dys[rank].contiguous()
+        out = layer.forward(x, residual=x)
+        dx, d_router, norms = layer.backward(dy)
+        acc_wgu = torch.zeros(El, 2 * I, d, dtype=torch.float32, device=dev)
+        acc_wd = torch.zeros(El, d, I, dtype=torch.float32, device=dev)
+        layer.accumulate_clipped(scales, acc_wgu, acc_wd)
+        raise_if_device_error(dev)
+        idx_all = [torch.empty_like(layer.idx) for _ in range(world)]
+        if world > 1:
+            dist.all_gather(idx_all, layer.idx)
+        else:
+            idx_all = [layer.idx]
+        ref_norms = torch.zeros(world, dtype=torch.float64, device=dev)
+        ref_wgu, ref_wd = torch.zeros_like(acc_wgu), torch.zeros_like(acc_wd)
+        for s in range(world):
+            xf = xs[s].float().requires_grad_(True)
+            rw, wguf, wdf = (t.float().requires_grad_(True) for t in (router, wgu, wd))
+            idx = idx_all[s].long()
+            w = (xf @ rw.t()).softmax(-1).gather(1, idx)
+            y = xf.clone()
+            for slot in range(k):
+                for e in range(E):
+                    rows = (idx[:, slot] == e).nonzero().squeeze(1)
+                    if rows.numel():
+                        gu = xf[rows] @ wguf[e].t()
+                        h = F.silu(gu[:, 0::2]) * gu[:, 1::2]
+                        y = y.index_add(0, rows, (h @ wdf[e].t()) * w[rows, slot].unsqueeze(1))
+            gx, gr, gwgu, gwd = torch.autograd.grad((y * dys[s].float()).sum(), (xf, rw, wguf, wdf))
+            ref_norms[s] = gwgu[mine].double().pow(2).sum() + gwd[mine].double().pow(2).sum()
+            ref_wgu += scales[s] * gwgu[mine]
+            ref_wd += scales[s] * gwd[mine]
+            if s == rank:
+                worst["out"] = max(worst["out"], rel(out, y.detach()))
+                worst["dx"] = max(worst["dx"], rel(dx.float() + dy.float(), gx))   # oracle includes the residual path
+                worst["d_router"] = max(worst["d_router"], rel(d_router, gr))
+        worst["norms"] = max(worst["norms"], ((norms - ref_norms).abs() / (ref_norms + 1e-12)).max().item())
+        worst["acc_wgu"] = max(worst["acc_wgu"], rel(acc_wgu, ref_wgu))
+        worst["acc_wd"] = max(worst["acc_wd"], rel(acc_wd, ref_wd))
+    errs = torch.tensor(list(worst.values()), device=dev)
+    if world > 1:
+        dist.all_reduce(errs, op=dist.ReduceOp.MAX)
+    return {"world": world, **{name: v for name, v in zip(worst, errs.tolist())}}

@@ -92,3 +92,13 @@ def test_grouped_gemm_modes(cuda):
     assert abs(ss.item() - dW.double().pow(2).sum().item()) < 1e-3 * ss.item()
     from opake_b200.ops._lib import raise_if_device_error
     raise_if_device_error(cuda)
+
+
+def test_expert_parallel_fused_single_rank(cuda):
+    """The expert-parallel kernels with a group of one rank (every peer pointer is the rank's own buffer): dispatch,
+    grouped GEMMs, combine, per-source norms and clipped accumulation against a dense fp32 oracle."""
+    from opake_b200.parallel.selftest import ep_fused_check
+
+    res = ep_fused_check(0, 1, cuda)
+    for name in ("out", "dx", "d_router", "acc_wgu", "acc_wd", "norms"):
+        assert res[name] < 3e-2, (name, res)

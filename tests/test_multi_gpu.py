@@ -40,3 +40,14 @@ def test_sharded_linear_reads_peer_shards(tmp_path):
         pytest.skip("needs 2 GPUs")
     res = _run(2, str(tmp_path / "sl.pt"), ("--sharded-linear",))
     assert res["world"] == 2 and res["fwd_err"] < 2e-2 and res["dgrad_err"] < 2e-2
+
+
+def test_expert_parallel_fused_two_ranks(tmp_path):
+    """Dispatch / combine kernels over peer memory, grouped GEMMs and per-source norms against a dense fp32 oracle."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _run(2, str(tmp_path / "ep.pt"), ("--ep-fused",))
+    assert res["world"] == 2
+    for name in ("out", "dx", "d_router", "acc_wgu", "acc_wd"):
+        assert res[name] < 3e-2, (name, res)
+    assert res["norms"] < 3e-2, res
