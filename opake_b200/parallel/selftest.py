@@ -90,9 +90,6 @@ def _sharded_linear_check(rank: int, world: int, dev: torch.device, out: str) ->
         dist.destroy_process_group()
 
 
-if __name__ == "__main__":
-    main()
-
 
 def ep_fused_check(rank: int, world: int, dev: torch.device, T: int = 256, d: int = 128, I: int = 64, E: int = 8, k: int = 2,
                    calls: int = 2) -> dict:
@@ -164,3 +161,6 @@ def ep_fused_check(rank: int, world: int, dev: torch.device, T: int = 256, d: in
     if world > 1:
         dist.all_reduce(errs, op=dist.ReduceOp.MAX)
     return {"world": world, **{name: v for name, v in zip(worst, errs.tolist())}}
+
+if __name__ == "__main__":
+    main()
