@@ -63,10 +63,10 @@ __global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __
                                                          const __nv_bfloat16* __restrict__ w,
                                                          __nv_bfloat16* __restrict__ sum_out,
                                                          __nv_bfloat16* __restrict__ y, float* __restrict__ rstd,
-                                                         int D, float eps, float w_off) {
+                                                         int D, float eps, float w_off, long long ldx, long long ldy) {
   __shared__ float sh[32];
   const long long row = blockIdx.x;
-  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * D);
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * ldx);
   const bf16x8* rr = ADD ? reinterpret_cast<const bf16x8*>(r + row * D) : nullptr;
   bf16x8* sr = ADD ? reinterpret_cast<bf16x8*>(sum_out + row * D) : nullptr;
   const int nv = D >> 3;
@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __
   if (threadIdx.x == 0 && rstd) rstd[row] = rs;
   const bf16x8* src = ADD ? reinterpret_cast<const bf16x8*>(sum_out + row * D) : xr;
   const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
-  bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * D);
+  bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * ldy);
   for (int i = threadIdx.x; i < nv; i += NT) {
     float f[8], g[8];
     unpack8(src[i], f);
@@ -115,7 +115,8 @@ __global__ void __launch_bounds__(RMS_BWD_NT) rmsnorm_bwd_kernel(const __nv_bflo
                                                                  const __nv_bfloat16* __restrict__ dres,
                                                                  __nv_bfloat16* __restrict__ dx,
                                                                  float* __restrict__ partial, int T, int D,
-                                                                 float w_off) {
+                                                                 float w_off, long long ld_dy, long long ldx,
+                                                                 long long ld_dx) {
   __shared__ float sh[32];
   const int nv = D >> 3;
   float wv[ITERS][8], acc[ITERS][8];
@@ -131,8 +132,8 @@ __global__ void __launch_bounds__(RMS_BWD_NT) rmsnorm_bwd_kernel(const __nv_bflo
     }
   }
   for (long long row = blockIdx.x; row < T; row += gridDim.x) {
-    const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + row * D);
-    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * D);
+    const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + row * ld_dy);
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * ldx);
     const float rs = rstd[row];
     float g[ITERS][8], xv[ITERS][8];
     float dot = 0.f;
@@ -147,8 +148,8 @@ __global__ void __launch_bounds__(RMS_BWD_NT) rmsnorm_bwd_kernel(const __nv_bflo
       }
     }
     const float mean_dot = block_sum<RMS_BWD_NT>(dot, sh) * rs / (float)D;
-    const bf16x8* drr = dres ? reinterpret_cast<const bf16x8*>(dres + row * D) : nullptr;
-    bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + row * D);
+    const bf16x8* drr = dres ? reinterpret_cast<const bf16x8*>(dres + row * ld_dx) : nullptr;
+    bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + row * ld_dx);
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
       const int v = threadIdx.x + it * RMS_BWD_NT;
@@ -619,44 +620,54 @@ inline int grid_for(long long n, int block, int cap_blocks = 148 * 16) {
 #define BF(p) reinterpret_cast<const __nv_bfloat16*>(p)
 #define BFM(p) reinterpret_cast<__nv_bfloat16*>(p)
 
-extern "C" int opk_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int D, float eps,
-                               float w_offset, void* stream) {
+extern "C" int opk_rmsnorm_fwd_ld(const void* x, int64_t ldx, const void* w, void* y, int64_t ldy, float* rstd, int T, int D,
+                                  float eps, float w_offset, void* stream) {
   if (T <= 0) return 0;
-  if (D % 8) return -1;
-  rmsnorm_fwd_kernel<false><<<T, NT, 0, ST(stream)>>>(BF(x), nullptr, BF(w), nullptr, BFM(y), rstd, D, eps, w_offset);
+  if (D % 8 || ldx % 8 || ldy % 8 || ldx < D || ldy < D) return -1;
+  rmsnorm_fwd_kernel<false><<<T, NT, 0, ST(stream)>>>(BF(x), nullptr, BF(w), nullptr, BFM(y), rstd, D, eps, w_offset, ldx, ldy);
   OPK_LAUNCH_CHECK();
   return 0;
+}
+extern "C" int opk_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int D, float eps,
+                               float w_offset, void* stream) {
+  return opk_rmsnorm_fwd_ld(x, D, w, y, D, rstd, T, D, eps, w_offset, stream);
 }
 extern "C" int opk_add_rmsnorm_fwd(const void* x, const void* r, const void* w, void* sum_out, void* y, float* rstd,
                                    int T, int D, float eps, float w_offset, void* stream) {
   if (T <= 0) return 0;
   if (D % 8) return -1;
-  rmsnorm_fwd_kernel<true><<<T, NT, 0, ST(stream)>>>(BF(x), BF(r), BF(w), BFM(sum_out), BFM(y), rstd, D, eps, w_offset);
+  rmsnorm_fwd_kernel<true><<<T, NT, 0, ST(stream)>>>(BF(x), BF(r), BF(w), BFM(sum_out), BFM(y), rstd, D, eps, w_offset, D, D);
   OPK_LAUNCH_CHECK();
   return 0;
 }
-extern "C" int opk_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
-                               void* dx_out, float* dw, float* workspace, int ws_rows, int T, int D, float w_offset,
-                               void* stream) {
+extern "C" int opk_rmsnorm_bwd_ld(const void* dy, int64_t ld_dy, const void* x, int64_t ldx, const void* w, const float* rstd,
+                                  const void* dres, void* dx_out, int64_t ld_dx, float* dw, float* workspace, int ws_rows,
+                                  int T, int D, float w_offset, void* stream) {
   if (T <= 0) return 0;
   if (D % 8 || D > 3 * RMS_BWD_NT * 8) return -1;
+  if (ld_dy % 8 || ldx % 8 || ld_dx % 8 || ld_dy < D || ldx < D || ld_dx < D) return -1;
   if (dw && (!workspace || ws_rows < 1)) return -1;
   int grid = T < 148 * 2 ? T : 148 * 2;
   if (dw && grid > ws_rows) grid = ws_rows;
   float* part = dw ? workspace : nullptr;
   const int iters = (D / 8 + RMS_BWD_NT - 1) / RMS_BWD_NT;
   if (iters == 1)
-    rmsnorm_bwd_kernel<1><<<grid, RMS_BWD_NT, 0, ST(stream)>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx_out), part, T, D, w_offset);
+    rmsnorm_bwd_kernel<1><<<grid, RMS_BWD_NT, 0, ST(stream)>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx_out), part, T, D, w_offset, ld_dy, ldx, ld_dx);
   else if (iters == 2)
-    rmsnorm_bwd_kernel<2><<<grid, RMS_BWD_NT, 0, ST(stream)>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx_out), part, T, D, w_offset);
+    rmsnorm_bwd_kernel<2><<<grid, RMS_BWD_NT, 0, ST(stream)>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx_out), part, T, D, w_offset, ld_dy, ldx, ld_dx);
   else
-    rmsnorm_bwd_kernel<3><<<grid, RMS_BWD_NT, 0, ST(stream)>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx_out), part, T, D, w_offset);
+    rmsnorm_bwd_kernel<3><<<grid, RMS_BWD_NT, 0, ST(stream)>>>(BF(dy), BF(x), BF(w), rstd, BF(dres), BFM(dx_out), part, T, D, w_offset, ld_dy, ldx, ld_dx);
   OPK_LAUNCH_CHECK();
   if (dw) {
     colsum_add_kernel<<<(D + 31) / 32, 256, 0, ST(stream)>>>(part, dw, grid, D);
     OPK_LAUNCH_CHECK();
   }
   return 0;
+}
+extern "C" int opk_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
+                               void* dx_out, float* dw, float* workspace, int ws_rows, int T, int D, float w_offset,
+                               void* stream) {
+  return opk_rmsnorm_bwd_ld(dy, D, x, D, w, rstd, dres, dx_out, D, dw, workspace, ws_rows, T, D, w_offset, stream);
 }
 extern "C" int opk_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int T,
                                  int D, float eps, void* stream) {

@@ -55,6 +55,13 @@ const char* opk_last_error(void);
 // y = x * rsqrt(mean(x^2) + eps) * (w + offset); rstd[T] saved for backward. x, y, w bf16.
 int opk_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int D, float eps, float w_offset,
                     void* stream);
+// The same with row pitches (elements): normalises a column slice of a wider matrix, e.g. the query part of a fused
+// QKV activation. x and y may alias.
+int opk_rmsnorm_fwd_ld(const void* x, int64_t ldx, const void* w, void* y, int64_t ldy, float* rstd, int T, int D, float eps,
+                       float w_offset, void* stream);
+int opk_rmsnorm_bwd_ld(const void* dy, int64_t ld_dy, const void* x, int64_t ldx, const void* w, const float* rstd,
+                       const void* dres, void* dx_out, int64_t ld_dx, float* dw, float* workspace, int ws_rows, int T, int D,
+                       float w_offset, void* stream);
 // s = x + r (stored to sum_out), then RMSNorm of s.
 int opk_add_rmsnorm_fwd(const void* x, const void* r, const void* w, void* sum_out, void* y, float* rstd, int T, int D,
                         float eps, float w_offset, void* stream);

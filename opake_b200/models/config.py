@@ -28,6 +28,8 @@ class DecoderConfig:
     top_k: int = 0
     expert_ffn: int = 0
     norm_topk_prob: bool = False
+    # RMSNorm over the whole query / key projection before RoPE (OLMoE: `self_attn.q_norm`, `self_attn.k_norm`)
+    qk_norm: bool = False
     family: str = "llama"
 
     @property
@@ -55,7 +57,7 @@ def gpt2_small(**kw) -> DecoderConfig:
 
 def olmoe_1b_7b(**kw) -> DecoderConfig:
     return replace(DecoderConfig("olmoe-1b-7b", 50304, 2048, 16, 16, 16, 128, 0, 2048, rope_theta=10000.0, n_experts=64,
-                                 top_k=8, expert_ffn=1024, family="olmoe"), **kw)
+                                 top_k=8, expert_ffn=1024, qk_norm=True, family="olmoe"), **kw)
 
 
 def tiny_llama(**kw) -> DecoderConfig:

@@ -104,6 +104,8 @@ class DecoderRuntime:
         for _ in range(L):
             a = {"x": e(T, d), "xn": e(T, d), "qkv": e(T, cfg.qkv_dim), "attn": e(T, cfg.n_heads * cfg.head_dim),
                  "x_mid": e(T, d), "xn2": e(T, d)}
+            if cfg.qk_norm:      # pre-normalisation queries and keys, needed by the norm's backward
+                a["qk_raw"] = e(T, (cfg.n_heads + cfg.n_kv_heads) * cfg.head_dim)
             if cfg.n_experts:
                 plan = K.MoePlan(T, cfg.n_experts, cfg.top_k, dev)
                 I = cfg.expert_ffn
@@ -187,6 +189,13 @@ class DecoderRuntime:
             p = f"layers.{li}."
             xn, st1 = self._norm_fwd(x, p + "norm1", out=a["xn"])
             G.gemm(xn, w[p + "wqkv"], out=a["qkv"], bias=w.get(p + "bqkv"))
+            stq = None
+            if cfg.qk_norm:
+                nq, nk = H * hd, KV * hd
+                a["qk_raw"].copy_(a["qkv"][:, : nq + nk])
+                _, rq = K.rmsnorm_fwd(a["qk_raw"][:, :nq], w[p + "q_norm.weight"], cfg.norm_eps, out=a["qkv"][:, :nq])
+                _, rk = K.rmsnorm_fwd(a["qk_raw"][:, nq:], w[p + "k_norm.weight"], cfg.norm_eps, out=a["qkv"][:, nq : nq + nk])
+                stq = (rq, rk)
             if cfg.pos == "rope":
                 K.rope_(a["qkv"], self._rope_table(T), H + KV, hd)
             _, actx = A.attention_fwd(a["qkv"], H, KV, hd, self.attn_impl, out=a["attn"])
@@ -213,7 +222,7 @@ class DecoderRuntime:
                 G.gemm(xn2, w[p + "wfc"], out=a["fc"], bias=w.get(p + "bfc"))
                 K.gelu_fwd(a["fc"], out=a["act"])
                 G.gemm(a["act"], w[p + "wproj"], out=nxt, residual=a["x_mid"], bias=w.get(p + "bproj"))
-            saved.append((st1, st2, actx))
+            saved.append((st1, st2, actx, stq))
             x = nxt
         xf, stf = self._norm_fwd(x, "norm_f", out=ws["xf"])
         head = w["embed"] if cfg.tie_embeddings else w["lm_head"]
@@ -270,7 +279,7 @@ class DecoderRuntime:
         for li in reversed(range(cfg.n_layers)):
             a = ws["layers"][li]
             p = f"layers.{li}."
-            st1, st2, actx = saved[li]
+            st1, st2, actx, stq = saved[li]
             # ---- MLP
             if cfg.n_experts:
                 plan = a["plan"]
@@ -318,6 +327,12 @@ class DecoderRuntime:
             A.attention_bwd(dattn, a["qkv"], a["attn"], actx, H, KV, hd, dqkv)
             if cfg.pos == "rope":
                 K.rope_(dqkv, self._rope_table(T), H + KV, hd, backward=True)
+            if cfg.qk_norm:      # in place on the query and key columns of dqkv
+                nq, nk = H * hd, KV * hd
+                K.rmsnorm_bwd(dqkv[:, :nq], a["qk_raw"][:, :nq], w[p + "q_norm.weight"], stq[0],
+                              dw=self._vec(ws, p + "q_norm.weight"), out=dqkv[:, :nq])
+                K.rmsnorm_bwd(dqkv[:, nq : nq + nk], a["qk_raw"][:, nq:], w[p + "k_norm.weight"], stq[1],
+                              dw=self._vec(ws, p + "k_norm.weight"), out=dqkv[:, nq : nq + nk])
             G.linear_wgrad(dqkv, a["xn"], out=g[p + "wqkv"], sumsq=sumsq)
             if cfg.bias:
                 K.colsum_(dqkv, self._vec(ws, p + "bqkv"))
@@ -385,7 +400,7 @@ def init_params_(cfg: DecoderConfig, params: torch.Tensor, layout: Layout, seed:
     params.zero_()
     for s in layout.slots:
         v = params[s.offset : s.offset + s.numel]
-        if s.name.endswith("norm1.weight") or s.name.endswith("norm2.weight") or s.name == "norm_f.weight":
+        if s.name.endswith(("norm1.weight", "norm2.weight", "q_norm.weight", "k_norm.weight")) or s.name == "norm_f.weight":
             v.fill_(1.0)
         elif len(s.shape) == 1:
             v.zero_()

@@ -80,6 +80,9 @@ def build_layout(cfg: DecoderConfig, shard_multiple: int = 1) -> Layout:
         add(p + "wqkv", cfg.qkv_dim, d)
         if cfg.bias:
             add(p + "bqkv", cfg.qkv_dim)
+        if cfg.qk_norm:
+            add(p + "q_norm.weight", cfg.n_heads * cfg.head_dim)
+            add(p + "k_norm.weight", cfg.n_kv_heads * cfg.head_dim)
         add(p + "wo", d, cfg.n_heads * cfg.head_dim)
         if cfg.bias:
             add(p + "bo", d)

@@ -144,7 +144,7 @@ def config_from_hf(conf: Any) -> DecoderConfig:
         rope_scaling=get("rope_scaling"), tie_embeddings=bool(get("tie_word_embeddings", False)), bias=False,
         n_experts=int(get("num_local_experts", get("num_experts", 0)) or 0), top_k=int(get("num_experts_per_tok", 0) or 0),
         expert_ffn=int(get("moe_intermediate_size", get("intermediate_size", 0)) or 0) if get("num_local_experts", get("num_experts", 0)) else 0,
-        norm_topk_prob=bool(get("norm_topk_prob", False)), family=mt)
+        norm_topk_prob=bool(get("norm_topk_prob", False)), qk_norm=(mt == "olmoe"), family=mt)
 
 
 def _interleave(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -181,6 +181,9 @@ def hf_to_flat_views(cfg: DecoderConfig, sd: Mapping[str, torch.Tensor], w: dict
         put(p + "wqkv", torch.cat([sd[s + "self_attn.q_proj.weight"], sd[s + "self_attn.k_proj.weight"],
                                    sd[s + "self_attn.v_proj.weight"]], dim=0))
         put(p + "wo", sd[s + "self_attn.o_proj.weight"])
+        if cfg.qk_norm:
+            put(p + "q_norm.weight", sd[s + "self_attn.q_norm.weight"])
+            put(p + "k_norm.weight", sd[s + "self_attn.k_norm.weight"])
         if cfg.n_experts:
             put(p + "router", sd[s + "mlp.gate.weight"] if s + "mlp.gate.weight" in sd else sd[s + "block_sparse_moe.gate.weight"])
             for e in range(cfg.n_experts):
@@ -222,6 +225,9 @@ def flat_views_to_hf(cfg: DecoderConfig, w: Mapping[str, torch.Tensor]) -> dict[
         out[s + "self_attn.k_proj.weight"] = qkv[H * hd:(H + KV) * hd]
         out[s + "self_attn.v_proj.weight"] = qkv[(H + KV) * hd:]
         out[s + "self_attn.o_proj.weight"] = w[p + "wo"]
+        if cfg.qk_norm:
+            out[s + "self_attn.q_norm.weight"] = w[p + "q_norm.weight"]
+            out[s + "self_attn.k_norm.weight"] = w[p + "k_norm.weight"]
         if cfg.n_experts:
             out[s + "mlp.gate.weight"] = w[p + "router"]
             for e in range(cfg.n_experts):

@@ -38,8 +38,12 @@ def decoder_hidden(cfg: DecoderConfig, w: dict[str, torch.Tensor], tok: torch.Te
         qkv = xn @ w[p + "wqkv"].T
         if cfg.bias:
             qkv = qkv + w[p + "bqkv"]
-        q = qkv[:, : H * hd].view(T, H, hd)
-        k = qkv[:, H * hd : (H + KV) * hd].view(T, KV, hd)
+        qf, kf = qkv[:, : H * hd], qkv[:, H * hd : (H + KV) * hd]
+        if cfg.qk_norm:
+            qf = qf * torch.rsqrt(qf.pow(2).mean(-1, keepdim=True) + cfg.norm_eps) * w[p + "q_norm.weight"]
+            kf = kf * torch.rsqrt(kf.pow(2).mean(-1, keepdim=True) + cfg.norm_eps) * w[p + "k_norm.weight"]
+        q = qf.reshape(T, H, hd)
+        k = kf.reshape(T, KV, hd)
         v = qkv[:, (H + KV) * hd :].view(T, KV, hd)
         if cfg.pos == "rope":
             q, k = _rope(q, rope_table[:T]), _rope(k, rope_table[:T])

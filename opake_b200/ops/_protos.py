@@ -42,6 +42,8 @@ PROTOTYPES: dict = {
     "opk_ep_combine": (I, [_G, _PE, P, P, I, P, I, I, P, I, I, P, P]),
     "opk_ep_combine_bwd": (I, [_PE, P, P, I, I, I, P, P]),
     "opk_rmsnorm_fwd": (I, [P, P, P, P, I, I, F, F, P]),
+    "opk_rmsnorm_fwd_ld": (I, [P, L, P, P, L, P, I, I, F, F, P]),
+    "opk_rmsnorm_bwd_ld": (I, [P, L, P, L, P, P, P, P, L, P, P, I, I, I, F, P]),
     "opk_add_rmsnorm_fwd": (I, [P, P, P, P, P, P, I, I, F, F, P]),
     "opk_rmsnorm_bwd": (I, [P, P, P, P, P, P, P, P, I, I, I, F, P]),
     "opk_layernorm_fwd": (I, [P, P, P, P, P, P, I, I, F, P]),

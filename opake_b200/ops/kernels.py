@@ -37,10 +37,12 @@ def _chk(code: int, name: str) -> None:
 
 # ------------------------------------------------------------------------------------------------ norms
 def rmsnorm_fwd(x, w, eps: float = 1e-6, w_offset: float = 0.0, out=None):
+    """``x`` and ``out`` may be column slices of wider row-major matrices (row pitch = ``stride(0)``)."""
     T, D = x.shape
     y = torch.empty_like(x) if out is None else out
     rstd = torch.empty(T, dtype=torch.float32, device=x.device)
-    _chk(_L().opk_rmsnorm_fwd(_p(x), _p(w), _p(y), _p(rstd), T, D, eps, w_offset, _s(x)), "rmsnorm_fwd")
+    _chk(_L().opk_rmsnorm_fwd_ld(_p(x), x.stride(0), _p(w), _p(y), y.stride(0), _p(rstd), T, D, eps, w_offset, _s(x)),
+         "rmsnorm_fwd")
     return y, rstd
 
 
@@ -73,8 +75,10 @@ def rmsnorm_bwd(dy, x, w, rstd, dres=None, dw=None, w_offset: float = 0.0, out=N
     T, D = x.shape
     dx = torch.empty_like(x) if out is None else out
     ws = _rms_workspace(x.device, D) if dw is not None else None
-    _chk(_L().opk_rmsnorm_bwd(_p(dy), _p(x), _p(w), _p(rstd), _p(dres), _p(dx), _p(dw), _p(ws), _RMS_WS_ROWS, T, D,
-                              w_offset, _s(x)), "rmsnorm_bwd")
+    if dres is not None and dres.stride(0) != dx.stride(0):
+        raise ValueError("dres must have the row pitch of the output")
+    _chk(_L().opk_rmsnorm_bwd_ld(_p(dy), dy.stride(0), _p(x), x.stride(0), _p(w), _p(rstd), _p(dres), _p(dx), dx.stride(0),
+                                 _p(dw), _p(ws), _RMS_WS_ROWS, T, D, w_offset, _s(x)), "rmsnorm_bwd")
     return dx
 
 
