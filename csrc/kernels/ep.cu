@@ -80,23 +80,45 @@ __device__ void signal_all(const OpkEpGroup& g, int phase, int epoch) {
 }
 
 // ------------------------------------------------------------------------------------------------ count
+// One CTA, one pass over the entries. Warp w owns the contiguous chunk w of the entry list: (1) per-warp histograms
+// in shared memory, (2) per expert an exclusive prefix over the warps, which is the rank of the warp's first entry of
+// that expert, (3) every warp walks its chunk in order, 32 entries at a time; lanes with the same expert find each
+// other with match.any, their rank is the warp's running count plus the number of lower lanes in the match group.
 __global__ void __launch_bounds__(1024) ep_count_kernel(const OpkEpGroup g, const int* __restrict__ idx, int n_entries,
                                                         int* __restrict__ entry_rank, int epoch) {
+  __shared__ int hist[32][MAX_E];     // [warp][expert]; becomes the running rank base of the warp
   __shared__ int counts[MAX_E];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int E = g.n_experts;
-  for (int e = warp; e < E; e += nwarps) {
-    int rank = 0;
-    for (int base = 0; base < n_entries; base += 32) {
-      const int n = base + lane;
-      const bool hit = n < n_entries && idx[n] == e;
-      const unsigned m = __ballot_sync(0xffffffffu, hit);
-      if (hit) entry_rank[n] = rank + __popc(m & ((1u << lane) - 1u));
-      rank += __popc(m);
+  for (int i = threadIdx.x; i < 32 * MAX_E; i += blockDim.x) (&hist[0][0])[i] = 0;
+  __syncthreads();
+  const int chunk = ((n_entries + 31) / 32 + 31) / 32 * 32;   // entries per warp, a multiple of 32
+  const int c0 = warp * chunk, c1 = min(c0 + chunk, n_entries);
+  for (int n = c0 + lane; n < c1; n += 32) atomicAdd(&hist[warp][idx[n]], 1);
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int c = hist[w][e];
+      hist[w][e] = run;
+      run += c;
     }
-    if (lane == 0) counts[e] = rank;
+    counts[e] = run;
   }
   __syncthreads();
+  for (int base = c0; base < c1; base += 32) {
+    const int n = base + lane;
+    const bool valid = n < c1;
+    const int e = valid ? idx[n] : -1 - lane;                 // invalid lanes match nobody
+    const unsigned m = __match_any_sync(0xffffffffu, e);
+    if (valid) {
+      const int before = __popc(m & ((1u << lane) - 1u));
+      entry_rank[n] = hist[warp][e] + before;
+    }
+    __syncwarp();
+    if (valid && (m >> lane) == 1u) hist[warp][e] += __popc(m);   // highest lane of each match group
+    __syncwarp();
+  }
   for (int i = threadIdx.x; i < E * g.world; i += blockDim.x) {
     const int r = i / E, e = i - r * E;
     ctrl_counts(g.ctrl[r])[g.rank * E + e] = counts[e];
@@ -319,14 +341,28 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const OpkEpGroup g, con
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     }
-    for (int s = 0; s < k; ++s) {
-      const int pos = entry_pos[(long long)t * k + s];
-      const float w = wts ? wts[(long long)t * k + s] : 1.f;
-      const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(y.p[pos >> 26]) + (long long)(pos & 0x3FFFFFF) * D + c * 8;
-      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src));
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    // the remote loads of four slots are issued together, then summed in slot order (deterministic)
+    for (int s0 = 0; s0 < k; s0 += 4) {
+      uint4 v[4];
+      float w[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); acc[2 * j] += w * f.x; acc[2 * j + 1] += w * f.y; }
+      for (int q = 0; q < 4; ++q) {
+        v[q] = make_uint4(0, 0, 0, 0);
+        w[q] = 0.f;
+        if (s0 + q < k) {
+          const int pos = entry_pos[(long long)t * k + s0 + q];
+          w[q] = wts ? wts[(long long)t * k + s0 + q] : 1.f;
+          const __nv_bfloat16* src =
+              reinterpret_cast<const __nv_bfloat16*>(y.p[pos >> 26]) + (long long)(pos & 0x3FFFFFF) * D + c * 8;
+          v[q] = __ldcg(reinterpret_cast<const uint4*>(src));
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[q]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); acc[2 * j] += w[q] * f.x; acc[2 * j + 1] += w[q] * f.y; }
+      }
     }
     uint4 o;
     __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);

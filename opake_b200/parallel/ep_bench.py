@@ -49,6 +49,7 @@ def main() -> None:
     ap.add_argument("--top-k", type=int, default=8)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--phases", action="store_true", help="also report the device time of every kernel of the fused arm")
     a = ap.parse_args()
     rank, world, local = comm.init_distributed()
     dev = torch.device("cuda", local)
@@ -71,23 +72,46 @@ def main() -> None:
     row_src, rows_total = torch.zeros(ctx.r_cap, **i32), torch.zeros(1, **i32)
     out = torch.empty(T, d, dtype=torch.bfloat16, device=dev)
 
+    marks: list = []
+
+    def mark(name):
+        if a.phases:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            marks.append((name, e))
+
     def fused():
+        mark("start")
         ctx.barrier()
+        mark("barrier")
         ctx.epoch += 1
         ep = ctx.epoch
         _lib.check(L.opk_ep_count(ctx.g, _p(idx), n, _p(entry_rank), ep, s), "ep_count")
+        mark("count")
         _lib.check(L.opk_ep_dispatch(ctx.g, recv_peers, _p(x), x.stride(0), k, None, _p(idx), _p(entry_rank), _p(entry_pos), 0, n,
                                      d, PHASE_COUNTS, PHASE_ROWS, ep, err, s), "ep_dispatch")
+        mark("dispatch")
         _lib.check(L.opk_ep_prepare(ctx.g, PHASE_ROWS, ep, _p(tile_group), _p(gk_e), _p(gk_s), _p(row_src), _p(rows_total), err, s),
                    "ep_prepare")
+        mark("prepare")
         _lib.check(L.opk_ep_zero_pad(_p(recv), _p(row_src), _p(rows_total), ctx.r_cap, d, s), "ep_zero_pad")
         # (expert GEMMs would run here on `recv`; the exchange is timed with the received rows as the outputs)
+        mark("zero_pad")
         _lib.check(L.opk_ep_signal(ctx.g, PHASE_OUT, ep, s), "ep_signal")
         _lib.check(L.opk_ep_combine(ctx.g, recv_peers, _p(entry_pos), _p(wts), k, None, T, d, _p(out), PHASE_OUT, ep, err, s),
                    "ep_combine")
+        mark("signal+combine")
 
     t_fused = _time(fused, a.iters, a.warmup, dev)
     _lib.raise_if_device_error(dev)
+    phases = {}
+    if a.phases:      # per-kernel device time of the timed iterations (this rank), microseconds
+        per = len(marks) // (a.iters + a.warmup)
+        for it in range(a.warmup, a.warmup + a.iters):
+            row = marks[it * per:(it + 1) * per]
+            for (_, e0), (name, e1) in zip(row[:-1], row[1:]):
+                phases[name] = phases.get(name, 0.0) + e0.elapsed_time(e1) * 1e3 / a.iters
+        phases = {k_: round(v, 1) for k_, v in phases.items()}
     ref_fused = out.float().clone()
 
     # ---------------------------------------------------------------- library arm
@@ -136,7 +160,7 @@ def main() -> None:
                           "fused_us": round(t_fused, 1), "all_to_all_us": round(t_lib, 1),
                           "speedup": round(t_lib / t_fused, 2), "nvlink_roofline_us": round(roof, 1),
                           "fused_frac_of_roofline": round(roof / t_fused, 3) if world > 1 else None,
-                          "arms_mismatch": mismatch}))
+                          "arms_mismatch": mismatch, **({"phases_us": phases} if a.phases else {})}))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
