@@ -180,6 +180,46 @@ __global__ void __launch_bounds__(256) clip_accumulate_pair_kernel(const bf16x8*
     __stcs(acc + 2 * i + 1, a1);
   }
 }
+// N examples in one pass over the fp32 sums: acc += sum_j stored(g_j * s_j). Per example this moves 2 + 8 / N bytes per
+// parameter; N is bounded by how many whole-model gradient buffers fit next to the optimizer state.
+struct AccGroup {
+  const bf16x8* g[OPK_ACC_GROUP_MAX];
+  const float* scale[OPK_ACC_GROUP_MAX];
+};
+template <int N>
+__global__ void __launch_bounds__(256) clip_accumulate_group_kernel(const AccGroup grp, float4* __restrict__ acc, long long nvec,
+                                                                    int overwrite) {
+  float s[N];
+#pragma unroll
+  for (int j = 0; j < N; ++j) s[j] = *grp.scale[j];
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < nvec; i += (long long)gridDim.x * 256) {
+    uint4 r[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) r[j] = __ldcs(reinterpret_cast<const uint4*>(grp.g[j]) + i);
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+    if (!overwrite) {
+      a0 = __ldcs(acc + 2 * i);
+      a1 = __ldcs(acc + 2 * i + 1);
+    }
+    float f[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) f[q] = 0.f;
+#pragma unroll
+    for (int j = 0; j < N; ++j) {       // examples in slot order: the sum does not depend on the launch shape
+      const bf16x8 v = *reinterpret_cast<const bf16x8*>(&r[j]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 t = __bfloat1622float2(v.h[q]);
+        f[2 * q] += clip_store(t.x, s[j]);
+        f[2 * q + 1] += clip_store(t.y, s[j]);
+      }
+    }
+    a0.x += f[0]; a0.y += f[1]; a0.z += f[2]; a0.w += f[3];
+    a1.x += f[4]; a1.y += f[5]; a1.z += f[6]; a1.w += f[7];
+    __stcs(acc + 2 * i, a0);
+    __stcs(acc + 2 * i + 1, a1);
+  }
+}
 __global__ void clip_accumulate_tail_kernel(const __nv_bfloat16* __restrict__ g, const float* __restrict__ scale,
                                             float* __restrict__ acc, long long begin, long long n, int overwrite) {
   const float s = *scale;
@@ -323,6 +363,21 @@ inline int grid_for(long long n, int block, int cap_blocks) {
   return (int)g;
 }
 
+// ragged tail (fewer than 8 elements) of the group pass, same association as the vector body
+__global__ void clip_accumulate_group_tail_kernel(const AccGroup grp, int n_group, float* __restrict__ acc, long long begin,
+                                                  long long n, int overwrite) {
+  const long long i = begin + threadIdx.x;
+  if (i >= n) return;
+  float f = 0.f;
+  for (int j = 0; j < n_group; ++j)
+    f += clip_store(__bfloat162float(reinterpret_cast<const __nv_bfloat16*>(grp.g[j])[i]), *grp.scale[j]);
+  acc[i] = (overwrite ? 0.f : acc[i]) + f;
+}
+template <int N>
+void launch_acc_group(const AccGroup& grp, float* acc, long long nvec, int overwrite, cudaStream_t st) {
+  clip_accumulate_group_kernel<N><<<grid_for(nvec, 256, 148 * 16), 256, 0, st>>>(grp, reinterpret_cast<float4*>(acc), nvec, overwrite);
+}
+
 }  // namespace
 
 #define ST(s) reinterpret_cast<cudaStream_t>(s)
@@ -384,6 +439,35 @@ extern "C" int opk_clip_accumulate_pair(const void* g0, const float* scale0, con
     clip_accumulate_tail_kernel<<<1, 32, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(g0), scale0, acc, nvec << 3, n, overwrite);
     clip_accumulate_tail_kernel<<<1, 32, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(g1), scale1, acc, nvec << 3, n, 0);
   }
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_clip_accumulate_group(const void* const* g, const float* const* scale, int n_group, float* acc, int64_t n,
+                                         int overwrite, void* stream) {
+  if (n <= 0 || n_group <= 0) return 0;
+  if (n_group > OPK_ACC_GROUP_MAX || (reinterpret_cast<uintptr_t>(acc) & 15)) return -1;
+  AccGroup grp;
+  for (int j = 0; j < OPK_ACC_GROUP_MAX; ++j) {
+    grp.g[j] = j < n_group ? reinterpret_cast<const bf16x8*>(g[j]) : nullptr;
+    grp.scale[j] = j < n_group ? scale[j] : nullptr;
+    if (j < n_group && (reinterpret_cast<uintptr_t>(g[j]) & 15)) return -1;
+  }
+  const long long nvec = n >> 3;
+  cudaStream_t st = ST(stream);
+  if (nvec > 0) {
+    switch (n_group) {
+      case 1: launch_acc_group<1>(grp, acc, nvec, overwrite, st); break;
+      case 2: launch_acc_group<2>(grp, acc, nvec, overwrite, st); break;
+      case 3: launch_acc_group<3>(grp, acc, nvec, overwrite, st); break;
+      case 4: launch_acc_group<4>(grp, acc, nvec, overwrite, st); break;
+      case 5: launch_acc_group<5>(grp, acc, nvec, overwrite, st); break;
+      case 6: launch_acc_group<6>(grp, acc, nvec, overwrite, st); break;
+      case 7: launch_acc_group<7>(grp, acc, nvec, overwrite, st); break;
+      default: launch_acc_group<8>(grp, acc, nvec, overwrite, st); break;
+    }
+  }
+  const long long tail = n - (nvec << 3);
+  if (tail > 0) clip_accumulate_group_tail_kernel<<<1, 32, 0, st>>>(grp, n_group, acc, nvec << 3, n, overwrite);
   OPK_LAUNCH_CHECK();
   return 0;
 }

@@ -213,6 +213,11 @@ int opk_clip_accumulate2(const void* g, const float* scale, float* acc, int64_t 
 // Two examples at once: acc (+)= stored(g0 * scale0) + stored(g1 * scale1) in one pass over acc.
 int opk_clip_accumulate_pair(const void* g0, const float* scale0, const void* g1, const float* scale1, float* acc, int64_t n,
                              int overwrite, void* stream);
+// The same for a group of up to OPK_ACC_GROUP_MAX examples: acc += sum_j stored(g[j] * *scale[j]) in one pass over acc.
+// g and scale are HOST arrays of device pointers.
+#define OPK_ACC_GROUP_MAX 8
+int opk_clip_accumulate_group(const void* const* g, const float* const* scale, int n_group, float* acc, int64_t n, int overwrite,
+                              void* stream);
 // Gaussian noise from Philox4x32-10: out[i] (+)= sigma * N(0,1)_{key, stream, step, offset + i}.
 int opk_philox_normal(float* out, int64_t n, uint64_t seed, uint32_t stream_id, uint32_t step, uint64_t offset,
                       float sigma, int accumulate, void* stream);

@@ -388,6 +388,17 @@ class DecoderRuntime:
             K.embedding_accumulate(tok0, ws["embs"][0], self.scales[0], acc_emb, tok0.numel())
             K.embedding_accumulate(tok1, ws["embs"][1], self.scales[1], acc_emb, tok1.numel())
 
+    def accumulate_group(self, acc: torch.Tensor, ws: dict, n: int, *, overwrite: bool = False) -> None:
+        """Adds the clipped gradients of the examples held in slots ``0 .. n-1`` in one pass over ``acc``: the fp32
+        sums are read and written once for the whole group."""
+        K.clip_accumulate_group(self.Gs[:n], self.scales[:n], acc[: self.layout.dense_total], overwrite=overwrite)
+        if not self.cfg.tie_embeddings:
+            emb = self.layout.slot("embed")
+            acc_emb = acc[emb.offset : emb.offset + emb.numel].view(emb.shape)
+            for j in range(n):
+                tok = ws["toks"][j]
+                K.embedding_accumulate(tok, ws["embs"][j], self.scales[j], acc_emb, tok.numel())
+
     def clip_and_accumulate(self, acc: torch.Tensor, clip: float, ws: dict, tok: torch.Tensor, *, auto: bool = False,
                             gamma: float = 0.01, overwrite: bool = False, slot: int = 0) -> None:
         self.clip_factor(clip, auto=auto, gamma=gamma, slot=slot)

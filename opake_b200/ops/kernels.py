@@ -265,6 +265,18 @@ def clip_accumulate_pair(g0, scale0, g1, scale1, acc, overwrite: bool = False):
          "clip_accumulate_pair")
 
 
+def clip_accumulate_group(gs, scales, acc, overwrite: bool = False):
+    """``acc (+)= sum_j stored(gs[j] * scales[j])`` for up to 8 examples in one pass over the fp32 sums."""
+    import ctypes
+
+    n = len(gs)
+    if not 1 <= n <= 8 or len(scales) != n:
+        raise ValueError("a group holds 1 to 8 gradient buffers with one scale each")
+    gp = (ctypes.c_void_p * n)(*[g.data_ptr() for g in gs])
+    sp = (ctypes.c_void_p * n)(*[t.data_ptr() for t in scales])
+    _chk(_L().opk_clip_accumulate_group(gp, sp, n, _p(acc), gs[0].numel(), int(overwrite), _s(acc)), "clip_accumulate_group")
+
+
 def philox_normal_(out, seed: int, step: int, *, stream_id: int = 0, offset: int = 0, sigma: float = 1.0,
                    accumulate: bool = False):
     _chk(_L().opk_philox_normal(_p(out), out.numel(), seed & (2**64 - 1), stream_id, step, offset, sigma,

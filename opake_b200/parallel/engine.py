@@ -82,10 +82,12 @@ class ShardedDPEngine:
             self.blt_state = torch.zeros(nb, self.shard_len, dtype=torch.float32, device=device)
             self.blt_decay = torch.tensor(cfg.blt_decay, dtype=torch.float32, device=device)
             self.blt_scale = torch.tensor(cfg.blt_scale, dtype=torch.float32, device=device)
-        self.runtime = DecoderRuntime(model_cfg, self.params, layout=self.layout, attn_impl=cfg.attn_impl, n_slots=2)
-        self._side = torch.cuda.Stream(device=device)
-        # how clipped gradients reach the fp32 sums: "pair" (default), or the diagnostic modes overlap | serial | off
+        # how clipped gradients reach the fp32 sums: "pair" (default: groups of examples share one pass over the
+        # sums), or the diagnostic modes overlap | serial | off
         self._acc_mode = os.environ.get("OPK_ACC_MODE", "pair")
+        self.group = self._pick_group_size() if self._acc_mode == "pair" else 2
+        self.runtime = DecoderRuntime(model_cfg, self.params, layout=self.layout, attn_impl=cfg.attn_impl, n_slots=self.group)
+        self._side = torch.cuda.Stream(device=device)
         self._warm: dict[int, bool] = {}
         self.step_count = 0
         self.phi = 0.0
@@ -97,6 +99,20 @@ class ShardedDPEngine:
         self._losses = None
         self.graph_kernel_launches = 0   # native launches replayed through CUDA graphs (not seen by the ctypes counter)
 
+    def _pick_group_size(self) -> int:
+        """How many whole-model bf16 gradient buffers to keep: the clipped accumulation reads and writes the fp32
+        sums once per GROUP of examples (2 + 8 / group bytes per parameter and example), so more buffers mean less HBM
+        traffic. Sharding the optimizer state over more ranks frees the memory for them. ``OPK_ACC_GROUP`` overrides."""
+        forced = os.environ.get("OPK_ACC_GROUP")
+        if forced:
+            return max(2, min(8, int(forced)))
+        if self.device.type != "cuda":
+            return 2
+        free, _ = torch.cuda.mem_get_info(self.device)
+        g_bytes = 2 * self.layout.dense_total
+        reserve = 24 << 30 if g_bytes > (4 << 30) else 4 * g_bytes + (2 << 30)   # activations, workspaces, allocator slack
+        return int(max(2, min(8, (free - reserve) // max(g_bytes, 1))))
+
     # ------------------------------------------------------------------ one example
     def _example_body(self, ws, slot: int, drain_prev: bool) -> None:
         """Gradient of the example staged in slot ``slot``; meanwhile (side stream) the clipped accumulation of the
@@ -106,13 +122,14 @@ class ShardedDPEngine:
         main = torch.cuda.current_stream(self.device)
         mode = self._acc_mode
         if mode == "pair":
-            # examples alternate between the two gradient buffers; after every second one both are clipped and added
-            # in a single pass over the fp32 sums (6 instead of 10 bytes of HBM traffic per parameter and example)
+            # examples cycle through the gradient buffers; when the last buffer of the group is full, all of them are
+            # clipped and added in a single pass over the fp32 sums (2 + 8 / group bytes of HBM traffic per parameter
+            # and example instead of 10)
             st = rt.example_grad(ws["toks"][slot], ws["labels"], ws=ws, slot=slot)
             rt.clip_factor(cfg.clip_norm, auto=cfg.auto_clip, gamma=cfg.auto_gamma, slot=slot)
             ws["loss_sum"].add_(st.loss.reshape(1))
-            if slot == 1:
-                rt.accumulate_pair(self.acc, ws, ws["toks"][0], ws["toks"][1])
+            if slot == self.group - 1:
+                rt.accumulate_group(self.acc, ws, self.group)
             return
         if drain_prev and mode == "serial":
             rt.accumulate(self.acc, ws, ws["toks"][slot ^ 1], slot=slot ^ 1)
@@ -132,7 +149,7 @@ class ShardedDPEngine:
     def _run_example(self, tok_host: torch.Tensor, labels_host: torch.Tensor, index: int) -> None:
         T = tok_host.numel()
         ws = self.runtime.workspace(T)
-        slot = index & 1
+        slot = index % self.group if self._acc_mode == "pair" else index & 1
         drain = index > 0
         ws["toks"][slot].copy_(tok_host, non_blocking=True)
         ws["labels"].copy_(labels_host, non_blocking=True)
@@ -186,8 +203,8 @@ class ShardedDPEngine:
             self._run_example(tokens[i], labels[i], i)
         last = (B_local - 1) & 1
         if self._acc_mode == "pair":
-            if B_local & 1:
-                self.runtime.accumulate(self.acc, ws, ws["toks"][0], slot=0)     # odd count: the last example is alone
+            if B_local % self.group:                                             # incomplete last group
+                self.runtime.accumulate_group(self.acc, ws, B_local % self.group)
         elif B_local > 0:
             self.runtime.accumulate(self.acc, ws, ws["toks"][last], slot=last)   # drain the final example
         loss_sum = ws["loss_sum"].clone()

@@ -184,6 +184,28 @@ def test_clip_scale_and_accumulate(cuda):
     assert scale.item() == 1.0 and cnt.item() == 1
 
 
+@pytest.mark.parametrize("group", [1, 2, 3, 5, 8])
+def test_clip_accumulate_group_equals_one_by_one(cuda, group):
+    """One pass over the sums for a whole group of examples gives the sum of the individually stored clipped gradients."""
+    from opake_b200.ops import kernels as K
+
+    n = 100003 * 8 + 5                     # vector body plus a ragged tail
+    gs = [_rand((n,), cuda) for _ in range(group)]
+    scales = [torch.full((1,), 0.1 + 0.07 * j, device=cuda) for j in range(group)]
+    acc = torch.randn(n, device=cuda)
+    want = acc.clone()
+    f = torch.zeros(n, device=cuda)
+    for g, s in zip(gs, scales):
+        ref = torch.zeros(n, device=cuda)
+        K.clip_accumulate(g, s, ref, overwrite=True)     # stored(g * s) exactly as the single-example kernel rounds it
+        f += ref
+    want += f
+    K.clip_accumulate_group(gs, scales, acc)
+    assert torch.equal(acc, want)
+    K.clip_accumulate_group(gs, scales, acc, overwrite=True)
+    assert torch.equal(acc, f)
+
+
 def test_dp_step_single_rank_matches_reference_math(cuda):
     from opake_b200.ops import kernels as K
     from opake_b200.ops.philox_ref import normal
