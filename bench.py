@@ -249,6 +249,7 @@ def main() -> None:
                        "clip_norm": 1.0, "noise_multiplier": args.sigma, "optimizer": "adamw-bc", "sft_mask": "first 25%",
                        "mechanism": f"dp-ftrl blt x{args.blt_buffers}" if args.blt_buffers else "dp-sgd gaussian",
                        "per_example_microbatch": 1, "cuda_graph": not args.no_graph,
+                       "accumulate_group": getattr(eng, "group", None),
                        "l2_policy": "inputs larger than L2: every step streams the 16 GB bf16 weights and 32 GB fp32 sums",
                        "final_loss_per_example": last_loss / b_local},
             "clocks": clocks,
