@@ -5,8 +5,8 @@
 // its own TMEM. Per tensor-core cycle this halves the shared-memory and TMA traffic of the B operand, which is what
 // limits the single-CTA kernel.
 //
-// Roles per CTA (192 threads): warp 0 = TMA producer (both CTAs; every load reports its bytes to the EVEN CTA's
-// `full` barrier), warp 1 = TMEM allocation (both) and MMA issue (even CTA only), warps 2-5 = epilogue (both; they
+// Roles per CTA: warp 0 = TMA producer (both CTAs; every load reports its bytes to the EVEN CTA's `full`
+// barrier), warp 1 = TMEM allocation (both) and MMA issue (even CTA only), warps 2.. = epilogue (both; they
 // release the accumulator buffer by arriving on the even CTA's `tempty` barrier). tcgen05.commit with a CTA mask
 // signals the barriers at the same offset in both CTAs. All mbarrier waits are bounded as in the single-CTA kernel;
 // the loads are ordinary tile loads that each CTA issues for its own shared memory.
@@ -83,7 +83,7 @@ struct Gemm2Cfg {
 };
 
 template <bool A_MN, bool B_MN, int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * gemm_epi_warps(EPI), 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   using Cfg = Gemm2Cfg;
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, STAGES = Cfg::STAGES;
@@ -107,7 +107,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
-      mbar_init(&tempty[b], 8);    // 4 epilogue warps of each CTA
+      mbar_init(&tempty[b], 2 * gemm_epi_warps(EPI));    // the epilogue warps of both CTAs
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -205,6 +205,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows each)
     const int quad = warp & 3;
+    constexpr int CSPLIT = gemm_epi_warps(EPI) / 4;
+    const int c_begin = ((warp - 2) >> 2) * (BN / CSPLIT), c_end = c_begin + BN / CSPLIT;
     int it = 0;
     for (int tile = cluster_id; tile < total; tile += n_clusters, ++it) {
       const int b = tile / per_batch;
@@ -213,6 +215,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tile_coords(r, tiles_m, tiles_n, tm, tn);
       const int buf = it & 1;
       const uint32_t tph = (it >> 1) & 1;
+      if (EPI == EPI_SWIGLU_BWD) prefetch_swiglu_row<BN>(p, tm * 2 * BM + (int)rank * BM + quad * 32 + lane, tn);
       int ok = 1;
       if (lane == 0) ok = mbar_wait(&tfull[buf], tph, abort_flag) ? 1 : 0;
       __syncwarp();
@@ -220,7 +223,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (!ok) break;
       tc_fence_after();
       const int row = tm * 2 * BM + (int)rank * BM + quad * 32 + lane;
-      const float sq_acc = epilogue_tile<BN, EPI>(p, tmem_base + (uint32_t(quad * 32) << 16) + buf * BN, row, tn, tiles_n, b);
+      const float sq_acc = epilogue_tile<BN, EPI>(p, tmem_base + (uint32_t(quad * 32) << 16) + buf * BN, row, tn, tiles_n, b,
+                                                  c_begin, c_end);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[buf]), 0));

@@ -58,6 +58,12 @@ struct GemmParams {
   int sumsq_stride;      // EPI_SUMSQ accumulator index = b * sumsq_stride (0: all batch entries share sumsq[0])
 };
 
+// Epilogue warps per CTA: four (one per TMEM lane quadrant) for the epilogues that only store; eight (two per
+// quadrant, each taking half of the tile's columns) for the SwiGLU-backward epilogue, which reads and writes four
+// times the bytes of a plain store per accumulator column and needs the extra loads in flight to stay hidden under
+// the next tile's main loop. (With eight warps the store-only kernels measured 3-5 % slower.)
+__host__ __device__ constexpr int gemm_epi_warps(int epi) { return epi == EPI_SWIGLU_BWD ? 8 : 4; }
+
 template <int BN>
 struct GemmCfg {
   static constexpr int BM = 128;
@@ -91,10 +97,27 @@ __device__ __forceinline__ void store_row_chunk(__nv_bfloat16* dst, const float 
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
 
+// L2 prefetch of the 2 * BN saved pre-activation values (gate / up pairs) that the SwiGLU-backward epilogue of this
+// thread's row will read: issued before the wait for the accumulator, so the loads later hit L2 instead of DRAM.
+template <int BN>
+__device__ __forceinline__ void prefetch_swiglu_row(const GemmParams& p, int row, int tn) {
+  if (row < p.M) {
+    const char* g = reinterpret_cast<const char*>(reinterpret_cast<const __nv_bfloat16*>(p.act) + (long long)row * p.ld_act +
+                                                  2LL * tn * BN);
+    const int cols = min(2 * BN, 2 * (p.N - tn * BN));
+#pragma unroll
+    for (int b = 0; b < 2 * BN * 2; b += 128)
+      if (b < cols * 2) asm volatile("prefetch.global.L2 [%0];" ::"l"(g + b));
+  }
+}
+
 // Epilogue of one accumulator tile for one thread's row: reads BN fp32 columns from TMEM (tmem_tile = lane-adjusted
 // address of the tile) and applies the epilogue EPI. Returns the thread's partial sum of squares (EPI_SUMSQ).
+// The tile's columns [c_begin, c_end) are handled by the calling warp (the column range is split over the epilogue
+// warps that share a TMEM lane quadrant).
 template <int BN, int EPI>
-__device__ __forceinline__ float epilogue_tile(const GemmParams& p, uint32_t tmem_tile, int row, int tn, int tiles_n, int b) {
+__device__ __forceinline__ float epilogue_tile(const GemmParams& p, uint32_t tmem_tile, int row, int tn, int tiles_n, int b,
+                                               int c_begin = 0, int c_end = BN) {
   const bool row_ok = row < p.M;
   const int n0 = tn * BN;
   __nv_bfloat16* Crow = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.strideC + (long long)row * p.ldc;
@@ -115,7 +138,7 @@ __device__ __forceinline__ float epilogue_tile(const GemmParams& p, uint32_t tme
   }
 
 #pragma unroll 1
-  for (int c0 = 0; c0 < BN; c0 += 32) {
+  for (int c0 = c_begin; c0 < c_end; c0 += 32) {
     uint32_t raw[32];
     __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the predicated body below
     tmem_ld32(tmem_tile + c0, raw);
@@ -191,9 +214,12 @@ __device__ __forceinline__ float epilogue_tile(const GemmParams& p, uint32_t tme
       if (v2) {
         const uint4* g4 = reinterpret_cast<const uint4*>(grow);
         uint4* d4 = reinterpret_cast<uint4*>(drow);
+        uint4 gin[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) gin[q] = g4[q];       // all eight loads in flight before the first use
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-          const uint4 in = g4[q];
+          const uint4 in = gin[q];
           const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&in);
           uint32_t o[4];
 #pragma unroll
@@ -273,7 +299,7 @@ __device__ __forceinline__ void tile_coords(int r, int tiles_m, int tiles_n, int
 }
 
 template <bool A_MN, bool B_MN, int BN, int EPI>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(64 + 32 * gemm_epi_warps(EPI), 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmParams p) {
   using Cfg = GemmCfg<BN>;
@@ -297,7 +323,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
-      mbar_init(&tempty[b], 4);
+      mbar_init(&tempty[b], gemm_epi_warps(EPI));
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -407,8 +433,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------ epilogue (4 warps, one TMEM lane quadrant each)
+    // ------------------------------------------------------------ epilogue (one TMEM lane quadrant per warp & 3)
     const int quad = warp & 3;
+    constexpr int CSPLIT = gemm_epi_warps(EPI) / 4;
+    const int c_begin = ((warp - 2) >> 2) * (BN / CSPLIT), c_end = c_begin + BN / CSPLIT;
     int it = 0;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
       const int b = tile / per_batch;
@@ -419,6 +447,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int buf = it & 1;
       const uint32_t tph = (it >> 1) & 1;
       ++it;
+      if (EPI == EPI_SWIGLU_BWD) prefetch_swiglu_row<BN>(p, tm * BM + quad * 32 + lane, tn);
       int ok = 1;
       if (lane == 0) ok = mbar_wait(&tfull[buf], tph, abort_flag) ? 1 : 0;
       __syncwarp();   // orders the other lanes' accesses after lane 0's acquire (a shuffle is no memory barrier)
@@ -427,7 +456,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
 
       const int row = tm * BM + quad * 32 + lane;
-      const float sq_acc = epilogue_tile<BN, EPI>(p, tmem_base + (uint32_t(quad * 32) << 16) + buf * BN, row, tn, tiles_n, b);
+      const float sq_acc = epilogue_tile<BN, EPI>(p, tmem_base + (uint32_t(quad * 32) << 16) + buf * BN, row, tn, tiles_n, b,
+                                                  c_begin, c_end);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[buf]);

@@ -88,6 +88,20 @@ def case_gemm(t: _Timer, a) -> None:
     ss = torch.zeros(1, dtype=torch.float64, device=dev)
     us = t.run(lambda: G.linear_wgrad(dy, x, out=dw, sumsq=ss), a.iters)
     _emit("gemm", {"kind": "wgrad_gate_up_sumsq", "M": 2 * f, "N": d, "K": T}, us, flops=2.0 * T * d * 2 * f)
+    # down projection's input gradient: plain product + separate SwiGLU backward against the fused epilogue
+    from . import kernels as K
+    dyd, wd = torch.randn(T, d, device=dev, dtype=bf), torch.randn(d, f, device=dev, dtype=bf) * 0.05
+    gu, dgu = torch.randn(T, 2 * f, device=dev, dtype=bf), torch.empty(T, 2 * f, device=dev, dtype=bf)
+    dact = torch.empty(T, f, device=dev, dtype=bf)
+
+    def unfused():
+        G.gemm(dyd, wd, b_mn=True, out=dact)
+        K.swiglu_bwd(dact, gu, out=dgu)
+
+    us = t.run(unfused, a.iters)
+    _emit("gemm", {"kind": "dgrad_down_then_swiglu_bwd", "M": T, "N": f, "K": d}, us, flops=2.0 * T * d * f)
+    us = t.run(lambda: G.swiglu_dgrad(dyd, wd, gu, out=dgu), a.iters)
+    _emit("gemm", {"kind": "dgrad_down_swiglu_bwd_epilogue", "M": T, "N": f, "K": d}, us, flops=2.0 * T * d * f)
 
 
 def case_attention(t: _Timer, a) -> None:
