@@ -338,6 +338,40 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ qk, const float* __restr
   }
 }
 
+// Vector form: a thread rotates 8 consecutive pairs (x[i..i+7], x[i+half..i+half+7]) with 16-byte accesses.
+__global__ void __launch_bounds__(256) rope_vec8_kernel(__nv_bfloat16* __restrict__ qk, const float* __restrict__ cs,
+                                                        const int* __restrict__ pos, int T, int n_heads, int hd, long long ld,
+                                                        float sign) {
+  const int half = hd >> 1, hv = half >> 3;
+  const long long total = (long long)T * n_heads * hv;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int iv = (int)(idx % hv);
+    const long long th = idx / hv;
+    const int h = (int)(th % n_heads);
+    const long long t = th / n_heads;
+    const long long p = pos ? pos[t] : t;
+    const float4* c4 = reinterpret_cast<const float4*>(cs + (p * half + iv * 8) * 2);
+    bf16x8* lo = reinterpret_cast<bf16x8*>(qk + t * ld + (long long)h * hd + iv * 8);
+    bf16x8* hi = reinterpret_cast<bf16x8*>(qk + t * ld + (long long)h * hd + half + iv * 8);
+    float a[8], b[8];
+    unpack8(*lo, a);
+    unpack8(*hi, b);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float4 v = c4[q];            // (cos, sin) of pairs 2q and 2q + 1
+      const float s0 = v.y * sign, s1 = v.w * sign;
+      const float x1 = a[2 * q], x2 = b[2 * q], y1 = a[2 * q + 1], y2 = b[2 * q + 1];
+      a[2 * q] = x1 * v.x - x2 * s0;
+      b[2 * q] = x2 * v.x + x1 * s0;
+      a[2 * q + 1] = y1 * v.z - y2 * s1;
+      b[2 * q + 1] = y2 * v.z + y1 * s1;
+    }
+    *lo = pack8(a);
+    *hi = pack8(b);
+  }
+}
+
 // ------------------------------------------------------------------------------------------- gated activations
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
 __device__ __forceinline__ float gelu_tanh(float x) {
@@ -690,7 +724,11 @@ extern "C" int opk_rope(void* qk, const float* cs, const int32_t* pos, int T, in
                         float sign, void* stream) {
   const long long n = (long long)T * n_rot_heads * (head_dim / 2);
   if (n <= 0) return 0;
-  rope_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(BFM(qk), cs, pos, T, n_rot_heads, head_dim, ld, sign);
+  if ((head_dim % 16) == 0 && (ld % 8) == 0 && (reinterpret_cast<uintptr_t>(qk) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(cs) & 15) == 0)
+    rope_vec8_kernel<<<grid_for(n / 8, 256), 256, 0, ST(stream)>>>(BFM(qk), cs, pos, T, n_rot_heads, head_dim, ld, sign);
+  else
+    rope_kernel<<<grid_for(n, 256), 256, 0, ST(stream)>>>(BFM(qk), cs, pos, T, n_rot_heads, head_dim, ld, sign);
   OPK_LAUNCH_CHECK();
   return 0;
 }
