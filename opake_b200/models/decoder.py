@@ -59,6 +59,14 @@ class DecoderRuntime:
         self.clip_count = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._ws: dict[int, dict] = {}
         self._rope = None
+        # Weight-gradient GEMMs run on a second stream next to the input-gradient GEMMs of the same layer: both are
+        # persistent kernels that want every SM, so the second one's CTAs fill the SMs that the first one's last
+        # (partial) wave of tiles leaves idle, and launch gaps disappear. OPK_WGRAD_OVERLAP=0 keeps one stream.
+        import os
+
+        self._wstream = None
+        if self.device.type == "cuda" and os.environ.get("OPK_WGRAD_OVERLAP", "1") != "0":
+            self._wstream = torch.cuda.Stream(device=self.device)
         # small-vector gradients (norm weights, biases) are produced in fp32 rows and scattered into G at the end
         self._vec_names = [s.name for s in self.layout.slots
                            if len(s.shape) == 1 and s.offset < self.layout.dense_total]
@@ -154,6 +162,22 @@ class DecoderRuntime:
     def _vec(self, ws, name: str) -> torch.Tensor:
         n = self.layout.slot(name).numel
         return ws["vec"][self._vec_row[name], :n]
+
+    # ------------------------------------------------------------------ second stream for weight gradients
+    def _wgrad(self, dy, x, out, sumsq=None) -> None:
+        """``out = dy^T x`` (+ squared norm) ordered after everything issued so far, on the weight-gradient stream."""
+        side = self._wstream
+        if side is None:
+            G.linear_wgrad(dy, x, out=out, sumsq=sumsq)
+            return
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            G.linear_wgrad(dy, x, out=out, sumsq=sumsq)
+
+    def _wgrad_join(self) -> None:
+        """Later work on the main stream (which may overwrite the operands) waits for the weight gradients issued so far."""
+        if self._wstream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self._wstream)
 
     # ------------------------------------------------------------------ norms
     def _norm_fwd(self, x, prefix: str, out=None):
@@ -268,11 +292,11 @@ class DecoderRuntime:
         head = w["embed"] if cfg.tie_embeddings else w["lm_head"]
         ghead = g["embed"] if cfg.tie_embeddings else g["lm_head"]
         dlog = G.gemm(ws["xf"], head, out=ws["dlogits"], epilogue=G.EPI_LCE_BWD, labels=labels, lse=lse, coef=coef)
-        dxf = G.gemm(dlog, head, b_mn=True, out=ws["dx2"])
         if cfg.tie_embeddings:
-            G.linear_wgrad(dlog, ws["xf"], out=ghead)            # norm added after the embedding rows are merged
+            self._wgrad(dlog, ws["xf"], ghead)                   # norm added after the embedding rows are merged
         else:
-            G.linear_wgrad(dlog, ws["xf"], out=ghead, sumsq=sumsq)
+            self._wgrad(dlog, ws["xf"], ghead, sumsq)
+        dxf = G.gemm(dlog, head, b_mn=True, out=ws["dx2"])
         x_last = ws["x_last"]
         dx = self._norm_bwd(ws, dxf, x_last, "norm_f", stf, None, ws["dx"])
 
@@ -298,15 +322,16 @@ class DecoderRuntime:
                 G.linear_wgrad(ws["drl"], a["xn2"], out=g[p + "router"], sumsq=sumsq)
                 G.gemm(ws["drl"], w[p + "router"], b_mn=True, out=dxn2, residual=dxn2)
             elif cfg.act in ("swiglu", "geglu"):
-                G.linear_wgrad(dx, a["act"], out=g[p + "wd"], sumsq=sumsq)
+                self._wgrad(dx, a["act"], g[p + "wd"], sumsq)
                 dgu = ws["dwide"]
                 if cfg.act == "swiglu":       # d(act) stays in the accumulator: SwiGLU backward runs in the dgrad epilogue
                     G.swiglu_dgrad(dx, w[p + "wd"], a["gu"], out=dgu)
                 else:
                     dact = G.gemm(dx, w[p + "wd"], b_mn=True, out=ws["dact"])
                     K.geglu_bwd(dact, a["gu"], True, out=dgu)
-                G.linear_wgrad(dgu, a["xn2"], out=g[p + "wgu"], sumsq=sumsq)
+                self._wgrad(dgu, a["xn2"], g[p + "wgu"], sumsq)
                 dxn2 = G.gemm(dgu, w[p + "wgu"], b_mn=True, out=ws["dx2"])
+                self._wgrad_join()            # the norm backward below overwrites dx in place
             else:
                 G.linear_wgrad(dx, a["act"], out=g[p + "wproj"], sumsq=sumsq)
                 if cfg.bias:
@@ -319,7 +344,7 @@ class DecoderRuntime:
                 dxn2 = G.gemm(dfc, w[p + "wfc"], b_mn=True, out=ws["dx2"])
             dx_mid = self._norm_bwd(ws, dxn2, a["x_mid"], p + "norm2", st2, dx, ws["dx"])  # in place over dres
             # ---- attention
-            G.linear_wgrad(dx_mid, a["attn"], out=g[p + "wo"], sumsq=sumsq)
+            self._wgrad(dx_mid, a["attn"], g[p + "wo"], sumsq)
             if cfg.bias:
                 K.colsum_(dx_mid, self._vec(ws, p + "bo"))
             dattn = G.gemm(dx_mid, w[p + "wo"], b_mn=True, out=ws["dattn"])
@@ -333,12 +358,14 @@ class DecoderRuntime:
                               dw=self._vec(ws, p + "q_norm.weight"), out=dqkv[:, :nq])
                 K.rmsnorm_bwd(dqkv[:, nq : nq + nk], a["qk_raw"][:, nq:], w[p + "k_norm.weight"], stq[1],
                               dw=self._vec(ws, p + "k_norm.weight"), out=dqkv[:, nq : nq + nk])
-            G.linear_wgrad(dqkv, a["xn"], out=g[p + "wqkv"], sumsq=sumsq)
+            self._wgrad(dqkv, a["xn"], g[p + "wqkv"], sumsq)
             if cfg.bias:
                 K.colsum_(dqkv, self._vec(ws, p + "bqkv"))
             dxn = G.gemm(dqkv, w[p + "wqkv"], b_mn=True, out=ws["dx2"])
+            self._wgrad_join()                # dx_mid (read by the wo gradient) is overwritten in place below
             dx = self._norm_bwd(ws, dxn, a["x"], p + "norm1", st1, dx_mid, ws["dx"])
 
+        self._wgrad_join()
         # ---- embeddings
         K.embedding_bwd_compact(tok, dx, emb_ws, None if cfg.tie_embeddings else sumsq)
         if cfg.pos == "learned":
