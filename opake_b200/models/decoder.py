@@ -267,8 +267,11 @@ class DecoderRuntime:
 
     # ------------------------------------------------------------------ forward + backward of one example
     def example_grad(self, tok: torch.Tensor, labels: torch.Tensor, *, loss_weight: torch.Tensor | None = None,
-                     ws: dict | None = None, slot: int = 0) -> ExampleStats:
+                     ws: dict | None = None, slot: int = 0, before_wgrad=None) -> ExampleStats:
         """Computes this example's gradient into ``self.G`` (+ compact embedding rows) and ``sumsq``.
+
+        ``before_wgrad`` (optional callable) runs once, after the forward pass and right before the first kernel that
+        writes the slot's gradient buffer: the place to wait for a consumer of the buffer's previous contents.
 
         The example loss is the mean NLL over supervised tokens (per-example divisor, as
         packages/opake-alignment/src/opake/api/alignment/sft/loss/_nll.py:43-88).
@@ -292,6 +295,8 @@ class DecoderRuntime:
         head = w["embed"] if cfg.tie_embeddings else w["lm_head"]
         ghead = g["embed"] if cfg.tie_embeddings else g["lm_head"]
         dlog = G.gemm(ws["xf"], head, out=ws["dlogits"], epilogue=G.EPI_LCE_BWD, labels=labels, lse=lse, coef=coef)
+        if before_wgrad is not None:
+            before_wgrad()
         if cfg.tie_embeddings:
             self._wgrad(dlog, ws["xf"], ghead)                   # norm added after the embedding rows are merged
         else:
@@ -415,15 +420,16 @@ class DecoderRuntime:
             K.embedding_accumulate(tok0, ws["embs"][0], self.scales[0], acc_emb, tok0.numel())
             K.embedding_accumulate(tok1, ws["embs"][1], self.scales[1], acc_emb, tok1.numel())
 
-    def accumulate_group(self, acc: torch.Tensor, ws: dict, n: int, *, overwrite: bool = False) -> None:
+    def accumulate_group(self, acc: torch.Tensor, ws: dict, n: int, *, overwrite: bool = False, toks=None) -> None:
         """Adds the clipped gradients of the examples held in slots ``0 .. n-1`` in one pass over ``acc``: the fp32
-        sums are read and written once for the whole group."""
+        sums are read and written once for the whole group. ``toks``: the token tensors of the slots when they are not
+        ``ws["toks"]`` any more (a slot's token buffer is refilled before a deferred accumulation runs)."""
         K.clip_accumulate_group(self.Gs[:n], self.scales[:n], acc[: self.layout.dense_total], overwrite=overwrite)
         if not self.cfg.tie_embeddings:
             emb = self.layout.slot("embed")
             acc_emb = acc[emb.offset : emb.offset + emb.numel].view(emb.shape)
             for j in range(n):
-                tok = ws["toks"][j]
+                tok = ws["toks"][j] if toks is None else toks[j]
                 K.embedding_accumulate(tok, ws["embs"][j], self.scales[j], acc_emb, tok.numel())
 
     def clip_and_accumulate(self, acc: torch.Tensor, clip: float, ws: dict, tok: torch.Tensor, *, auto: bool = False,

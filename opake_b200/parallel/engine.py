@@ -110,7 +110,7 @@ class ShardedDPEngine:
             return 2
         free, _ = torch.cuda.mem_get_info(self.device)
         g_bytes = 2 * self.layout.dense_total
-        reserve = 24 << 30 if g_bytes > (4 << 30) else 4 * g_bytes + (2 << 30)   # activations, workspaces, allocator slack
+        reserve = 32 << 30 if g_bytes > (4 << 30) else 4 * g_bytes + (2 << 30)   # activations, workspaces, allocator slack
         return int(max(2, min(8, (free - reserve) // max(g_bytes, 1))))
 
     # ------------------------------------------------------------------ one example
@@ -125,11 +125,20 @@ class ShardedDPEngine:
             # examples cycle through the gradient buffers; when the last buffer of the group is full, all of them are
             # clipped and added in a single pass over the fp32 sums (2 + 8 / group bytes of HBM traffic per parameter
             # and example instead of 10)
-            st = rt.example_grad(ws["toks"][slot], ws["labels"], ws=ws, slot=slot)
+            # The pass itself is deferred to the start of the NEXT group's first example and runs on the side stream
+            # under that example's forward GEMMs (HBM-bound next to tensor-core-bound work); the example waits for it
+            # right before its first weight-gradient GEMM, the first kernel that overwrites a gradient buffer.
+            hook = None
+            if drain_prev and slot == 0:
+                self._side.wait_stream(main)
+                with torch.cuda.stream(self._side):
+                    rt.accumulate_group(self.acc, ws, self.group, toks=self._group_toks(ws, self.group))
+                hook = lambda: main.wait_stream(self._side)
+            st = rt.example_grad(ws["toks"][slot], ws["labels"], ws=ws, slot=slot, before_wgrad=hook)
             rt.clip_factor(cfg.clip_norm, auto=cfg.auto_clip, gamma=cfg.auto_gamma, slot=slot)
             ws["loss_sum"].add_(st.loss.reshape(1))
-            if slot == self.group - 1:
-                rt.accumulate_group(self.acc, ws, self.group)
+            if slot == 0:
+                ws["tok_keep"].copy_(ws["toks"][0])      # slot 0's tokens are replaced before its deferred pass runs
             return
         if drain_prev and mode == "serial":
             rt.accumulate(self.acc, ws, ws["toks"][slot ^ 1], slot=slot ^ 1)
@@ -145,6 +154,10 @@ class ShardedDPEngine:
         ws["loss_sum"].add_(st.loss.reshape(1))
         if drain_prev:
             main.wait_stream(self._side)
+
+    @staticmethod
+    def _group_toks(ws, n: int):
+        return [ws["tok_keep"], *ws["toks"][1:n]]
 
     def _run_example(self, tok_host: torch.Tensor, labels_host: torch.Tensor, index: int) -> None:
         T = tok_host.numel()
@@ -198,13 +211,18 @@ class ShardedDPEngine:
         ws = self.runtime.workspace(tokens.shape[1])
         if "loss_sum" not in ws:
             ws["loss_sum"] = torch.zeros(1, dtype=torch.float32, device=self.device)
+        if "tok_keep" not in ws:
+            ws["tok_keep"] = torch.zeros_like(ws["toks"][0])
         ws["loss_sum"].zero_()
         for i in range(B_local):
             self._run_example(tokens[i], labels[i], i)
         last = (B_local - 1) & 1
         if self._acc_mode == "pair":
-            if B_local % self.group:                                             # incomplete last group
-                self.runtime.accumulate_group(self.acc, ws, B_local % self.group)
+            # the last group (complete or not) has not been added yet: every earlier one was added at the start of
+            # the example that followed it
+            n_last = B_local % self.group or min(self.group, B_local)
+            if n_last:
+                self.runtime.accumulate_group(self.acc, ws, n_last, toks=self._group_toks(ws, n_last))
         elif B_local > 0:
             self.runtime.accumulate(self.acc, ws, ws["toks"][last], slot=last)   # drain the final example
         loss_sum = ws["loss_sum"].clone()
