@@ -80,7 +80,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const opk::GemmParams& 
   const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN) * p.batch;
   int grid = max_ctas > 0 ? max_ctas : num_sms();
   if (grid > tiles) grid = tiles;
-  kern<<<grid, 64 + 32 * opk::gemm_epi_warps(EPI), Cfg::SMEM_BYTES, st>>>(ta, tb, p);
+  kern<<<grid, 64 + 32 * opk::gemm1_epi_warps(EPI), Cfg::SMEM_BYTES, st>>>(ta, tb, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_err(cudaGetErrorString(e)); return (int)e; }
   return 0;

@@ -63,6 +63,9 @@ struct GemmParams {
 // times the bytes of a plain store per accumulator column and needs the extra loads in flight to stay hidden under
 // the next tile's main loop. (With eight warps the store-only kernels measured 3-5 % slower.)
 __host__ __device__ constexpr int gemm_epi_warps(int epi) { return epi == EPI_SWIGLU_BWD ? 8 : 4; }
+// The single-CTA kernel serves the grouped (mixture-of-experts) modes, whose per-expert reductions are only a few
+// k-blocks long while every tile is still written in full: there the epilogue, not the main loop, sets the pace.
+__host__ __device__ constexpr int gemm1_epi_warps(int epi) { return epi == EPI_LCE_FWD ? 4 : 8; }
 
 template <int BN>
 struct GemmCfg {
@@ -299,7 +302,7 @@ __device__ __forceinline__ void tile_coords(int r, int tiles_m, int tiles_n, int
 }
 
 template <bool A_MN, bool B_MN, int BN, int EPI>
-__global__ void __launch_bounds__(64 + 32 * gemm_epi_warps(EPI), 1)
+__global__ void __launch_bounds__(64 + 32 * gemm1_epi_warps(EPI), 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmParams p) {
   using Cfg = GemmCfg<BN>;
@@ -323,7 +326,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
-      mbar_init(&tempty[b], gemm_epi_warps(EPI));
+      mbar_init(&tempty[b], gemm1_epi_warps(EPI));
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -435,7 +438,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     // ------------------------------------------------------------ epilogue (one TMEM lane quadrant per warp & 3)
     const int quad = warp & 3;
-    constexpr int CSPLIT = gemm_epi_warps(EPI) / 4;
+    constexpr int CSPLIT = gemm1_epi_warps(EPI) / 4;
     const int c_begin = ((warp - 2) >> 2) * (BN / CSPLIT), c_end = c_begin + BN / CSPLIT;
     int it = 0;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {

@@ -126,24 +126,34 @@ __global__ void __launch_bounds__(256) moe_route_bwd_kernel(const float* __restr
 }
 
 // ------------------------------------------------------------------------------------------------ plan
-// Single CTA. Stable counting sort by expert: entry n = t*k + slot goes to row off[e] + (number of earlier entries
-// with the same expert). Segments are padded to multiples of 128 rows and are at least 128 rows long (an expert
+// Single CTA, one pass over the entries. Stable counting sort by expert: entry n = t*k + slot goes to row off[e] +
+// (number of earlier entries with the same expert). Warp w owns the contiguous chunk w of the entry list: per-warp
+// histograms in shared memory, per expert an exclusive prefix over the warps (the rank of the warp's first entry of
+// that expert), then every warp walks its chunk in order, 32 entries at a time, lanes with the same expert finding
+// each other with match.any. Segments are padded to multiples of 128 rows and are at least 128 rows long (an expert
 // without tokens still owns one all-zero tile, so its weight gradient is produced as exact zeros by the GEMM).
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ idx, int n_entries, int E, int r_cap,
                                                         int* __restrict__ dest, int* __restrict__ src_entry,
                                                         int* __restrict__ tile_group, int* __restrict__ group_k,
                                                         int* __restrict__ counts_out) {
+  __shared__ int hist[32][MAX_E];     // [warp][expert]; becomes the next free row of (warp, expert)
   __shared__ int counts[MAX_E];
   __shared__ int offs[MAX_E + 1];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  for (int e = warp; e < E; e += nwarps) {
-    int c = 0;
-    for (int base = 0; base < n_entries; base += 32) {
-      const int n = base + lane;
-      const bool hit = n < n_entries && idx[n] == e;
-      c += __popc(__ballot_sync(0xffffffffu, hit));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < 32 * MAX_E; i += blockDim.x) (&hist[0][0])[i] = 0;
+  __syncthreads();
+  const int chunk = ((n_entries + 31) / 32 + 31) / 32 * 32;   // entries per warp, a multiple of 32
+  const int c0 = warp * chunk, c1 = min(c0 + chunk, n_entries);
+  for (int n = c0 + lane; n < c1; n += 32) atomicAdd(&hist[warp][idx[n]], 1);
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int c = hist[w][e];
+      hist[w][e] = run;
+      run += c;
     }
-    if (lane == 0) counts[e] = c;
+    counts[e] = run;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -153,32 +163,33 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
       const int padded = counts[e] == 0 ? 128 : (counts[e] + 127) / 128 * 128;
       group_k[2 * e] = off;
       group_k[2 * e + 1] = padded / 64;
-      for (int tl = off / 128; tl < (off + padded) / 128; ++tl) tile_group[tl] = e;
       off += padded;
       if (counts_out) counts_out[e] = counts[e];
     }
     offs[E] = off;
-    for (int tl = off / 128; tl < r_cap / 128; ++tl) tile_group[tl] = -1;
   }
   __syncthreads();
   const int total = offs[E];
+  // tile -> expert table, padding rows of every segment, everything past the last segment
+  for (int e = warp; e < E; e += 32) {
+    for (int tl = offs[e] / 128 + lane; tl < offs[e + 1] / 128; tl += 32) tile_group[tl] = e;
+    for (int r = offs[e] + counts[e] + lane; r < offs[e + 1]; r += 32) src_entry[r] = -1;
+  }
+  for (int tl = total / 128 + threadIdx.x; tl < r_cap / 128; tl += blockDim.x) tile_group[tl] = -1;
   for (int r = total + threadIdx.x; r < r_cap; r += blockDim.x) src_entry[r] = -1;
-  for (int e = warp; e < E; e += nwarps) {
-    int rank = 0;
-    const int off = offs[e];
-    for (int base = 0; base < n_entries; base += 32) {
-      const int n = base + lane;
-      const bool hit = n < n_entries && idx[n] == e;
-      const unsigned m = __ballot_sync(0xffffffffu, hit);
-      if (hit) {
-        const int row = off + rank + __popc(m & ((1u << lane) - 1u));
-        dest[n] = row;
-        src_entry[row] = n;
-      }
-      rank += __popc(m);
+  for (int base = c0; base < c1; base += 32) {
+    const int n = base + lane;
+    const bool valid = n < c1;
+    const int e = valid ? idx[n] : -1 - lane;                 // invalid lanes match nobody
+    const unsigned m = __match_any_sync(0xffffffffu, e);
+    if (valid) {
+      const int row = offs[e] + hist[warp][e] + __popc(m & ((1u << lane) - 1u));
+      dest[n] = row;
+      src_entry[row] = n;
     }
-    const int end = offs[e + 1];
-    for (int r = off + rank + lane; r < end; r += 32) src_entry[r] = -1;
+    __syncwarp();
+    if (valid && (m >> lane) == 1u) hist[warp][e] += __popc(m);   // highest lane of each match group
+    __syncwarp();
   }
 }
 

@@ -174,6 +174,16 @@ class DecoderRuntime:
         with torch.cuda.stream(side):
             G.linear_wgrad(dy, x, out=out, sumsq=sumsq)
 
+    def _wgrad_call(self, fn) -> None:
+        """Runs ``fn`` (a weight-gradient launch) on the weight-gradient stream, ordered after everything issued so far."""
+        side = self._wstream
+        if side is None:
+            fn()
+            return
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            fn()
+
     def _wgrad_join(self) -> None:
         """Later work on the main stream (which may overwrite the operands) waits for the weight gradients issued so far."""
         if self._wstream is not None:
@@ -315,17 +325,18 @@ class DecoderRuntime:
                 K.moe_combine_bwd(dx, a["ye"], plan, ws["dwts"])
                 K.moe_gather(dx, plan, ws["dye"], entry_scale=plan.wts)
                 # expert weight gradients: one grouped GEMM per matrix, reduction range of expert e = its row segment
-                G.gemm(ws["dye"], a["act"], a_mn=True, b_mn=True, out=g[p + "experts.wd"], epilogue=G.EPI_SUMSQ, sumsq=sumsq,
-                       group_k=plan.group_k, sumsq_shared=True)
+                self._wgrad_call(lambda: G.gemm(ws["dye"], a["act"], a_mn=True, b_mn=True, out=g[p + "experts.wd"],
+                                                epilogue=G.EPI_SUMSQ, sumsq=sumsq, group_k=plan.group_k, sumsq_shared=True))
                 G.swiglu_dgrad(ws["dye"], w[p + "experts.wd"], a["gu"], out=ws["dgu"], tile_group=plan.tile_group)
-                G.gemm(ws["dgu"], a["xs"], a_mn=True, b_mn=True, out=g[p + "experts.wgu"], epilogue=G.EPI_SUMSQ, sumsq=sumsq,
-                       group_k=plan.group_k, sumsq_shared=True)
+                self._wgrad_call(lambda: G.gemm(ws["dgu"], a["xs"], a_mn=True, b_mn=True, out=g[p + "experts.wgu"],
+                                                epilogue=G.EPI_SUMSQ, sumsq=sumsq, group_k=plan.group_k, sumsq_shared=True))
                 G.gemm(ws["dgu"], w[p + "experts.wgu"], b_mn=True, out=ws["dxs"], tile_group=plan.tile_group)
                 dxn2 = K.moe_combine(ws["dxs"], plan, ws["dx2"])
                 # router: d weights -> d logits -> router weight gradient and the second path into dxn2
                 K.moe_route_bwd(plan, ws["dwts"], ws["drl"], cfg.norm_topk_prob)
                 G.linear_wgrad(ws["drl"], a["xn2"], out=g[p + "router"], sumsq=sumsq)
                 G.gemm(ws["drl"], w[p + "router"], b_mn=True, out=dxn2, residual=dxn2)
+                self._wgrad_join()            # dye / dgu are rewritten by the next layer, dx by the norm backward below
             elif cfg.act in ("swiglu", "geglu"):
                 self._wgrad(dx, a["act"], g[p + "wd"], sumsq)
                 dgu = ws["dwide"]
