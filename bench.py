@@ -83,6 +83,8 @@ class ClockSampler:
 
 
 def run_reference(args) -> None:
+    if int(os.environ.get("RANK", "0")) != 0:      # one line per job, also under torchrun
+        return
     print(json.dumps({
         "impl": "reference",
         "unavailable": "reference packages import optree and torchopt, which are neither installed nor in /opt/wheelhouse; "
