@@ -102,6 +102,45 @@ __global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __
   }
 }
 
+// One warp per row, the row held in registers (VPL vectors of 8 per lane): one pass over memory, no block barrier.
+template <int VPL>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x,
+                                                               const __nv_bfloat16* __restrict__ w,
+                                                               __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int T,
+                                                               float eps, float w_off, long long ldx, long long ldy) {
+  constexpr int D = VPL * 32 * 8;
+  const int lane = threadIdx.x & 31;
+  const long long row = blockIdx.x * 8ll + (threadIdx.x >> 5);
+  if (row >= T) return;
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * ldx);
+  bf16x8 v[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) v[i] = xr[lane + 32 * i];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    float f[8];
+    unpack8(v[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float rs = rsqrtf(ss / (float)D + eps);
+  if (lane == 0 && rstd) rstd[row] = rs;
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * ldy);
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    float f[8], g[8];
+    unpack8(v[i], f);
+    unpack8(wr[lane + 32 * i], g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = f[j] * rs * (g[j] + w_off);
+    yr[lane + 32 * i] = pack8(f);
+  }
+}
+
 // RMSNorm backward. A CTA of 512 threads walks rows with a grid stride; every thread owns the same columns for
 // all rows (ITERS vectors of 8), so the weight gradient accumulates in registers without atomics and is written once
 // per CTA to partial[blockIdx][D]. A second kernel adds the column sums of `partial` into dw.
@@ -658,7 +697,15 @@ extern "C" int opk_rmsnorm_fwd_ld(const void* x, int64_t ldx, const void* w, voi
                                   float eps, float w_offset, void* stream) {
   if (T <= 0) return 0;
   if (D % 8 || ldx % 8 || ldy % 8 || ldx < D || ldy < D) return -1;
-  rmsnorm_fwd_kernel<false><<<T, NT, 0, ST(stream)>>>(BF(x), nullptr, BF(w), nullptr, BFM(y), rstd, D, eps, w_offset, ldx, ldy);
+  const int warp_grid = (T + 7) / 8;
+  if (D == 4096)
+    rmsnorm_fwd_warp_kernel<16><<<warp_grid, 256, 0, ST(stream)>>>(BF(x), BF(w), BFM(y), rstd, T, eps, w_offset, ldx, ldy);
+  else if (D == 2048)
+    rmsnorm_fwd_warp_kernel<8><<<warp_grid, 256, 0, ST(stream)>>>(BF(x), BF(w), BFM(y), rstd, T, eps, w_offset, ldx, ldy);
+  else if (D == 1024)
+    rmsnorm_fwd_warp_kernel<4><<<warp_grid, 256, 0, ST(stream)>>>(BF(x), BF(w), BFM(y), rstd, T, eps, w_offset, ldx, ldy);
+  else
+    rmsnorm_fwd_kernel<false><<<T, NT, 0, ST(stream)>>>(BF(x), nullptr, BF(w), nullptr, BFM(y), rstd, D, eps, w_offset, ldx, ldy);
   OPK_LAUNCH_CHECK();
   return 0;
 }

@@ -1,4 +1,4 @@
-"""DP-SGD / DP-FTRL / accounting / optimizers on CPU, plus BASELINE config (a): a complete functional DP-SGD loop."""
+"""DP-SGD / DP-FTRL / accounting / optimizers on CPU, plus benchmark configuration (a): a complete functional DP-SGD loop."""
 import json
 import math
 

@@ -17,10 +17,11 @@ def _close(a, b, tol=2e-2):
     assert (a - b).abs().max().item() <= tol * (b.abs().max().item() + 1e-6)
 
 
-def test_rmsnorm_fwd_bwd(cuda):
+@pytest.mark.parametrize("T,D", [(300, 1024), (77, 4096), (130, 2048), (65, 768)])
+def test_rmsnorm_fwd_bwd(cuda, T, D):
+    """Widths 1024 / 2048 / 4096 take the warp-per-row forward kernel, the others the block-per-row one."""
     from opake_b200.ops import kernels as K
 
-    T, D = 300, 1024
     x, w, dy, dres = _rand((T, D), cuda), _rand((D,), cuda), _rand((T, D), cuda), _rand((T, D), cuda)
     y, rstd = K.rmsnorm_fwd(x, w, eps=1e-5)
     xf = x.float().requires_grad_()
