@@ -82,8 +82,16 @@ struct Gemm2Cfg {
   static constexpr int TMEM_COLS = 2 * BN;                        // two accumulator buffers
 };
 
-template <bool A_MN, bool B_MN, int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * gemm_epi_warps(EPI), 1)
+constexpr int kStageWarps = 4;     // copier warps per CTA of the staged variant
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <bool A_MN, bool B_MN, int EPI, bool STAGE = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * gemm_epi_warps(EPI) + (STAGE ? 32 * kStageWarps : 0), 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   using Cfg = Gemm2Cfg;
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, STAGES = Cfg::STAGES;
@@ -139,11 +147,24 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      int have_band = -1;
       for (int tile = cluster_id; tile < total && ok; tile += n_clusters) {
         const int b = tile / per_batch;
         const int r = tile - b * per_batch;
         int tm, tn;
         tile_coords(r, tiles_m, tiles_n, tm, tn);
+        if (STAGE && tn / kRasterBand > have_band) {
+          // the band's rows of B must have been copied into the local scratch by the copier warps of every CTA
+          const int band = tn / kRasterBand;
+          const int* ready = p.stage_ready + band;
+          const long long t0 = clock64();
+          while (ld_acquire_gpu(ready) < (int)gridDim.x) {
+            if (*abort_flag || clock64() - t0 > kWaitBudgetCycles) { *abort_flag = 1; ok = false; break; }
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy stores -> TMA (async proxy) loads
+          have_band = band;
+        }
         const int bb = b / p.b_batch_div;
         const int row0 = tm * 2 * BM + (int)rank * BM;          // this CTA's rows of A
         const int col0 = tn * BN + (int)rank * (BN / 2);        // this CTA's columns of B
@@ -202,6 +223,40 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
     }
     __syncwarp();
+  } else if (STAGE && warp >= 2 + gemm_epi_warps(EPI)) {
+    // ------------------------------------------------------------ copiers: remote B -> local scratch, band by band
+    const int ctid = (warp - 2 - gemm_epi_warps(EPI)) * 32 + lane;
+    const long long nthreads = (long long)gridDim.x * (32 * kStageWarps);
+    const long long gtid = (long long)blockIdx.x * (32 * kStageWarps) + ctid;
+    const int kv = p.K >> 3;                                   // 16-byte vectors per row
+    const int band_rows = kRasterBand * BN;
+    const int n_bands = (p.N + band_rows - 1) / band_rows;
+    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.stage_src);
+    uint4* dst = reinterpret_cast<uint4*>(p.stage_dst);
+    for (int band = 0; band < n_bands; ++band) {
+      const int r0 = band * band_rows, r1 = min(p.N, r0 + band_rows);
+      const long long nvec = (long long)(r1 - r0) * kv;
+      constexpr int U = 8;                                     // remote loads in flight per thread
+      for (long long i0 = gtid; i0 < nvec; i0 += U * nthreads) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * nthreads;
+          if (i < nvec) {
+            const long long row = r0 + i / kv;
+            v[u] = __ldcg(reinterpret_cast<const uint4*>(src + row * p.stage_ld) + (i % kv));
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * nthreads;
+          if (i < nvec) dst[(r0 + i / kv) * kv + (i % kv)] = v[u];
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kStageWarps) : "memory");
+      if (ctid == 0) atomicAdd(p.stage_ready + band, 1);
+    }
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows each)
     const int quad = warp & 3;

@@ -97,10 +97,10 @@ bool pair_mode() {
   return g_pair_mode == 1;
 }
 
-template <bool A_MN, bool B_MN, int EPI>
+template <bool A_MN, bool B_MN, int EPI, bool STAGE = false>
 int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const opk::GemmParams& p, int max_ctas, cudaStream_t st) {
   using Cfg = opk::Gemm2Cfg;
-  auto kern = opk::gemm2_bf16_kernel<A_MN, B_MN, EPI>;
+  auto kern = opk::gemm2_bf16_kernel<A_MN, B_MN, EPI, STAGE>;
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
@@ -111,7 +111,7 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const opk::GemmParams&
   int grid = (max_ctas > 0 ? max_ctas : num_sms()) & ~1;   // whole CTA pairs
   if (grid < 2) grid = 2;
   if (grid > 2 * tiles) grid = 2 * tiles;
-  kern<<<grid, 64 + 32 * opk::gemm_epi_warps(EPI), Cfg::SMEM_BYTES, st>>>(ta, tb, p);
+  kern<<<grid, 64 + 32 * opk::gemm_epi_warps(EPI) + (STAGE ? 32 * opk::kStageWarps : 0), Cfg::SMEM_BYTES, st>>>(ta, tb, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_err(cudaGetErrorString(e)); return (int)e; }
   return 0;
@@ -151,7 +151,16 @@ extern "C" int opk_gemm(const OpkGemmArgs* a, void* stream) {
   }
   const int bdiv = a->b_batch_div > 0 ? a->b_batch_div : 1;
   const int bbatch = a->tile_group ? a->n_groups : (a->group_k ? 1 : (a->batch + bdiv - 1) / bdiv);
-  if (a->b_mn) {
+  const bool stage = a->stage_dst != nullptr;
+  if (stage) {
+    // B is read once over NVLink by the kernel's copier warps into stage_dst; the tensor map covers the scratch
+    if (!pair || a->b_mn || a->a_mn || a->epilogue != opk::EPI_STORE || a->batch != 1 || !a->stage_ready || (a->K % 8) ||
+        (a->ldb % 8) || (reinterpret_cast<uintptr_t>(a->B) & 15) || (reinterpret_cast<uintptr_t>(a->stage_dst) & 15)) {
+      set_err("opk_gemm: staged B needs a plain K-major product with at least 256 rows, 256-wide tiles and 16-byte aligned rows");
+      return -1;
+    }
+    if (!make_map(&tb, a->stage_dst, a->K, a->N, 1, a->K, 0, 128)) return -2;
+  } else if (a->b_mn) {
     if (!make_map(&tb, a->B, a->N, a->K, bbatch, a->ldb, a->strideB, 64)) return -2;
   } else {
     if (!make_map(&tb, a->B, a->K, a->N, bbatch, a->ldb, a->strideB, pair ? 128 : bn)) return -2;
@@ -167,6 +176,13 @@ extern "C" int opk_gemm(const OpkGemmArgs* a, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int key = (a->a_mn ? 1 : 0) | (a->b_mn ? 2 : 0);
   const int mc = a->max_ctas;
+  if (stage) {
+    const int n_bands = (a->N + opk::kRasterBand * 256 - 1) / (opk::kRasterBand * 256);
+    cudaError_t e = cudaMemsetAsync(a->stage_ready, 0, sizeof(int32_t) * n_bands, st);
+    if (e != cudaSuccess) { set_err(cudaGetErrorString(e)); return (int)e; }
+    p.stage_src = a->B; p.stage_ld = a->ldb; p.stage_dst = a->stage_dst; p.stage_ready = a->stage_ready;
+    return launch2<false, false, opk::EPI_STORE, true>(ta, tb, p, mc, st);
+  }
   if (pair) {
     switch (a->epilogue) {
       case opk::EPI_STORE:

@@ -56,6 +56,13 @@ struct GemmParams {
   const int* tile_group;
   const int* group_k;
   int sumsq_stride;      // EPI_SUMSQ accumulator index = b * sumsq_stride (0: all batch entries share sumsq[0])
+  // Staged B operand (two-CTA kernel only): B lives in ANOTHER GPU's memory. Extra warps of every CTA copy it, one
+  // band of column tiles at a time, into a local scratch matrix [N][K]; the TMA producers read the scratch and wait
+  // per band for stage_ready[band] to reach the number of CTAs. Each remote byte crosses NVLink exactly once.
+  const void* stage_src;   // remote [N][stage_ld] bf16
+  long long stage_ld;
+  void* stage_dst;         // local [N][K] bf16
+  int* stage_ready;        // [ceil(N / (kRasterBand * BN))] counters, zero at launch
 };
 
 // Epilogue warps per CTA: four (one per TMEM lane quadrant) for the epilogues that only store; eight (two per

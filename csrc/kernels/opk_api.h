@@ -39,6 +39,10 @@ typedef struct OpkGemmArgs {
   int32_t n_groups;
   const int32_t* group_k;     // device [batch][2]: {first reduction element, number of 64-element blocks} per batch entry
   int32_t sumsq_shared;       // epilogue 1: every batch entry adds into sumsq[0]
+  // Staged B (see opk_gemm): B is another GPU's memory; stage_dst = local scratch [N][K] bf16, stage_ready = int32
+  // counters, one per band of 2048 rows of B (zeroed by opk_gemm on the stream before the launch).
+  void* stage_dst;
+  int32_t* stage_ready;
 } OpkGemmArgs;
 
 int opk_gemm(const OpkGemmArgs* args, void* stream);

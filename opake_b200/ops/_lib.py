@@ -26,6 +26,7 @@ class GemmArgs(Structure):
         ("labels", c_void_p), ("pmax", c_void_p), ("psum", c_void_p), ("tgt", c_void_p),
         ("lse", c_void_p), ("coef", c_void_p), ("err", c_void_p), ("max_ctas", c_int32),
         ("tile_group", c_void_p), ("n_groups", c_int32), ("group_k", c_void_p), ("sumsq_shared", c_int32),
+        ("stage_dst", c_void_p), ("stage_ready", c_void_p),
     ]
 
 

@@ -48,6 +48,7 @@ def gemm(
     group_k: torch.Tensor | None = None,
     sumsq_shared: bool = False,
     norm_only: bool = False,
+    stage: tuple[torch.Tensor, torch.Tensor] | None = None,
 ) -> torch.Tensor | None:
     """General entry: ``out[b] = alpha * op(a[b]) @ op(b[b // b_batch_div])^T`` with an epilogue.
 
@@ -109,6 +110,11 @@ def gemm(
     if group_k is not None:         # per-batch reduction ranges over un-batched operands (mixture of experts wgrad)
         args.group_k = group_k.data_ptr()
     args.sumsq_shared = int(sumsq_shared)
+    if stage is not None:           # b lives on another GPU: (local scratch [N, K] bf16, int32 band counters)
+        scratch, ready = stage
+        if scratch.numel() < N * K or scratch.dtype != torch.bfloat16 or ready.dtype != torch.int32 or ready.numel() * 2048 < N:
+            raise ValueError("stage: scratch must hold N * K bf16 values and the counters one int32 per 2048 rows of b")
+        args.stage_dst, args.stage_ready = scratch.data_ptr(), ready.data_ptr()
     _lib.check(_lib.lib().opk_gemm(args, _lib.stream_ptr(a.device)), "opk_gemm")
     return out
 

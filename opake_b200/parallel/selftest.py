@@ -24,11 +24,16 @@ def main() -> None:
     ap.add_argument("--blt", action="store_true")
     ap.add_argument("--sharded-linear", action="store_true", help="check the sharded-weight GEMMs instead of the engine")
     ap.add_argument("--ep-fused", action="store_true", help="check the expert-parallel dispatch / combine kernels")
+    ap.add_argument("--sharded-linear-bench", action="store_true",
+                    help="time the sharded-weight GEMM (peer shards read in place) against the same GEMM on a local weight")
     a = ap.parse_args()
     rank, world, local = comm.init_distributed()
     dev = torch.device("cuda", local)
     if a.sharded_linear:
         _sharded_linear_check(rank, world, dev, a.out)
+        return
+    if a.sharded_linear_bench:
+        _sharded_linear_bench(rank, world, dev, a.out)
         return
     if a.ep_fused:
         res = ep_fused_check(rank, world, dev)
@@ -89,6 +94,62 @@ def _sharded_linear_check(rank: int, world: int, dev: torch.device, out: str) ->
         dist.barrier()
         dist.destroy_process_group()
 
+
+
+def _sharded_linear_bench(rank: int, world: int, dev: torch.device, out: str, M: int = 2048, N: int = 28672, Kd: int = 4096,
+                          iters: int = 10) -> None:
+    """Llama-3-8B gate/up projection with the weight row-sharded over the ranks: device time of the sharded forward
+    (``world`` GEMMs, ``world - 1`` of them fed by TMA loads from a peer's memory over NVLink) against the same product
+    on a local full weight. Maximum over ranks; a 256 MB buffer is overwritten before every timed call. The NVLink
+    roofline is the bytes of the remote shards divided by 770 GB/s (measured peer-copy bandwidth per direction)."""
+    import json
+
+    from .sharded_linear import ShardedWeight, sharded_linear_forward
+    from ..ops import gemm as G
+
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(M, Kd, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+    sw = ShardedWeight(N, Kd, dev)
+    sw.local.normal_(0, 0.05)
+    sw.publish()
+    full = torch.randn(N, Kd, device=dev).mul_(0.05).to(torch.bfloat16)
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+
+    def timed(fn) -> float:
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            if world > 1:
+                sw.publish()                     # ranks start each call together
+            a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a_.record()
+            fn()
+            b_.record()
+            torch.cuda.synchronize(dev)
+            ts.append(a_.elapsed_time(b_) * 1e3)
+        t = torch.tensor([sorted(ts)[len(ts) // 2]], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    t_sharded = timed(lambda: sharded_linear_forward(x, sw, out=y))
+    t_local = timed(lambda: G.gemm(x, full, out=y))
+    remote_bytes = (world - 1) / world * N * Kd * 2
+    res = {"case": "sharded_linear_forward", "world": world, "M": M, "N": N, "K": Kd, "sharded_us": round(t_sharded, 1),
+           "local_weight_us": round(t_local, 1), "tflops_sharded": round(2.0 * M * N * Kd / t_sharded / 1e6, 1),
+           "nvlink_roofline_us": round(remote_bytes / 770e3, 1),
+           "roofline_us": round(max(remote_bytes / 770e3, t_local), 1)}
+    if world > 1:
+        sw.publish()
+    if rank == 0:
+        print(json.dumps(res))
+        torch.save(res, out)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def ep_fused_check(rank: int, world: int, dev: torch.device, T: int = 256, d: int = 128, I: int = 64, E: int = 8, k: int = 2,

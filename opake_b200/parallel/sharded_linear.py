@@ -1,10 +1,12 @@
 """Linear layers whose weight stays sharded over the ranks: the all-gather is fused into the consuming GEMM.
 
 Each rank stores ``N / world`` rows of a ``[N, K]`` weight in peer-addressable memory. ``forward`` computes
-``x @ W.T`` as ``world`` tcgen05 GEMMs, one per shard, whose B operand is the peer's shard itself: the kernel's TMA
-producer pulls weight tiles straight from the remote GPU's memory over NVLink into shared memory, stage by stage,
-while the tensor cores work on the previous stages. No gathered copy of the weight ever exists, no collective is
-called, and transfer overlaps math tile by tile inside the kernel's normal pipeline. Shards are visited starting with
+``x @ W.T`` as ``world`` tcgen05 GEMMs, one per shard, whose B operand is the peer's shard itself. For products with
+at least 256 rows the two-CTA kernel runs with four extra warps per CTA that copy the remote shard over NVLink into a
+local scratch matrix, one band of 2048 weight rows at a time, while the tensor-core warps consume the bands that
+have arrived (per-band counters, bounded waits): every remote byte crosses NVLink once, no collective is called and
+the transfer overlaps the math band by band inside one kernel. Smaller products let the TMA producer pull tiles
+straight from the remote memory. Shards are visited starting with
 the local one and continuing with rank+1, rank+2, ... so that at any moment the ranks read from different peers.
 The loads are ordinary TMA tile loads that each CTA issues for itself.
 
@@ -37,6 +39,16 @@ class ShardedWeight:
         self.buf = comm.alloc_peer_buffer(self.rows * n_in, torch.bfloat16, device, group)
         self.local = self.buf.local.view(self.rows, n_in)
         self.shards = [self.local if r == self.rank else self.buf.peer_view(r, (self.rows, n_in)) for r in range(self.world)]
+        self._scratch = None
+
+    def scratch(self):
+        """Local staging matrix for ONE remote shard plus its band counters (created on first use, reused for every
+        remote shard in turn: the products are ordered on one stream)."""
+        if self._scratch is None:
+            dev = self.local.device
+            self._scratch = (torch.empty(self.rows, self.n_in, dtype=torch.bfloat16, device=dev),
+                             torch.zeros((self.rows + 2047) // 2048, dtype=torch.int32, device=dev))
+        return self._scratch
 
     def order(self) -> list[int]:
         return [(self.rank + i) % self.world for i in range(self.world)]
@@ -51,8 +63,12 @@ def sharded_linear_forward(x: torch.Tensor, w: ShardedWeight, out: torch.Tensor 
     M = x.shape[0]
     if out is None:
         out = torch.empty(M, w.n_out, dtype=torch.bfloat16, device=x.device)
+    staged = M >= 256 and w.rows > 128 and G.pair_mode()
     for s in w.order():
-        G.gemm(x, w.shards[s], out=out[:, s * w.rows:(s + 1) * w.rows])
+        remote = s != w.rank
+        # a remote shard is copied once, band by band, by extra warps of the GEMM kernel itself while its tensor-core
+        # warps work on the bands that have arrived; reading it directly would fetch every tile once per row tile
+        G.gemm(x, w.shards[s], out=out[:, s * w.rows:(s + 1) * w.rows], stage=w.scratch() if (remote and staged) else None)
     return out
 
 
