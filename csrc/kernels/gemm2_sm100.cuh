@@ -82,7 +82,7 @@ struct Gemm2Cfg {
   static constexpr int TMEM_COLS = 2 * BN;                        // two accumulator buffers
 };
 
-constexpr int kStageWarps = 4;     // copier warps per CTA of the staged variant
+constexpr int kStageWarps = 8;     // copier warps per CTA of the staged variant
 
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   int v;
