@@ -41,6 +41,53 @@ def _time(fn, iters: int, warmup: int, dev) -> float:
     return t.item() * 1e3   # microseconds
 
 
+def _layer_bench(a, rank: int, world: int, dev) -> None:
+    """One OLMoE-shaped MoE layer with the experts sharded over the ranks, one example (``tokens`` rows) per rank:
+    device time of forward, of backward pass 1 (input gradients + per-source squared norms) and of pass 2 (clipped
+    accumulation of the expert weight gradients), maximum over ranks. FLOPs counted: 3 products per pass direction
+    over the routed rows (gate/up, down; forward, input gradient, weight gradient twice: norms and accumulation)."""
+    from .ep_fused import FusedExpertParallelLayer
+
+    T, d, E, k, I = a.tokens, a.d, a.experts, a.top_k, a.ffn
+    El = E // world
+    gen = torch.Generator().manual_seed(5 + rank)
+    bf = lambda t: t.to(torch.bfloat16).to(dev)
+    router = bf(torch.randn(E, d, generator=torch.Generator().manual_seed(1)) * 0.05)
+    wgu = bf(torch.randn(El, 2 * I, d, generator=gen) * 0.02)
+    wd = bf(torch.randn(El, d, I, generator=gen) * 0.02)
+    ctx = EpContext(E, T * k, dev)
+    layer = FusedExpertParallelLayer(ctx, router, wgu, wd, T, k)
+    x, dy = bf(torch.randn(T, d, generator=gen)), bf(torch.randn(T, d, generator=gen) * 0.1)
+    scales = torch.full((world,), 0.5, device=dev)
+    acc_wgu = torch.zeros(El, 2 * I, d, dtype=torch.float32, device=dev)
+    acc_wd = torch.zeros(El, d, I, dtype=torch.float32, device=dev)
+    out = torch.empty(T, d, dtype=torch.bfloat16, device=dev)
+    t_fwd = _time(lambda: layer.forward(x, residual=x, out=out), a.iters, a.warmup, dev)
+
+    def fwd_bwd():
+        layer.forward(x, residual=x, out=out)
+        layer.backward(dy)
+
+    def full():
+        fwd_bwd()
+        layer.accumulate_clipped(scales, acc_wgu, acc_wd)
+
+    t_fb = _time(fwd_bwd, a.iters, a.warmup, dev)
+    t_all = _time(full, a.iters, a.warmup, dev)
+    _lib.raise_if_device_error(dev)
+    rows = T * k                                        # routed rows per rank on average
+    flops = 2.0 * rows * d * 3 * I * 5                  # fwd, dgrad, wgrad (norm pass), wgrad (accumulate) + swiglu pairs
+    if rank == 0:
+        print(json.dumps({"case": "ep_layer", "world": world, "tokens_per_rank": T, "d": d, "experts": E, "top_k": k, "ffn": I,
+                          "forward_us": round(t_fwd, 1), "forward_backward_us": round(t_fb, 1),
+                          "with_clipped_accumulation_us": round(t_all, 1),
+                          "expert_tflops_per_gpu": round(flops / t_all / 1e6, 1),
+                          "tokens_per_s_per_layer_all_ranks": round(world * T / (t_all * 1e-6))}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=2048)
@@ -50,9 +97,16 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--phases", action="store_true", help="also report the device time of every kernel of the fused arm")
+    ap.add_argument("--layer", action="store_true",
+                    help="time a whole expert-parallel MoE layer instead (forward, backward with per-source norms, clipped "
+                         "accumulation) on the native kernels")
+    ap.add_argument("--ffn", type=int, default=1024, help="expert hidden size for --layer")
     a = ap.parse_args()
     rank, world, local = comm.init_distributed()
     dev = torch.device("cuda", local)
+    if a.layer:
+        _layer_bench(a, rank, world, dev)
+        return
     T, d, E, k = a.tokens, a.d, a.experts, a.top_k
     n = T * k
     gen = torch.Generator().manual_seed(3 + rank)
