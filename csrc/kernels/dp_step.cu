@@ -151,35 +151,6 @@ __global__ void __launch_bounds__(256) clip_accumulate_kernel(const bf16x8* __re
     __stcs(acc + 2 * i + 1, a1);
   }
 }
-// Two examples in one pass over the fp32 sums: acc += stored(g0 * s0) + stored(g1 * s1). Per example this moves
-// 2 + 4 bytes per parameter instead of 2 + 8 (the sum is read and written once for both).
-__global__ void __launch_bounds__(256) clip_accumulate_pair_kernel(const bf16x8* __restrict__ g0, const float* __restrict__ scale0,
-                                                                   const bf16x8* __restrict__ g1, const float* __restrict__ scale1,
-                                                                   float4* __restrict__ acc, long long nvec, int overwrite) {
-  const float s0 = *scale0, s1 = *scale1;
-  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < nvec; i += (long long)gridDim.x * 256) {
-    const uint4 r0 = __ldcs(reinterpret_cast<const uint4*>(g0) + i);
-    const uint4 r1 = __ldcs(reinterpret_cast<const uint4*>(g1) + i);
-    const bf16x8 v0 = *reinterpret_cast<const bf16x8*>(&r0);
-    const bf16x8 v1 = *reinterpret_cast<const bf16x8*>(&r1);
-    float f[8];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 a = __bfloat1622float2(v0.h[j]), b = __bfloat1622float2(v1.h[j]);
-      f[2 * j] = clip_store(a.x, s0) + clip_store(b.x, s1);
-      f[2 * j + 1] = clip_store(a.y, s0) + clip_store(b.y, s1);
-    }
-    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
-    if (!overwrite) {
-      a0 = __ldcs(acc + 2 * i);
-      a1 = __ldcs(acc + 2 * i + 1);
-    }
-    a0.x += f[0]; a0.y += f[1]; a0.z += f[2]; a0.w += f[3];
-    a1.x += f[4]; a1.y += f[5]; a1.z += f[6]; a1.w += f[7];
-    __stcs(acc + 2 * i, a0);
-    __stcs(acc + 2 * i + 1, a1);
-  }
-}
 // N examples in one pass over the fp32 sums: acc += sum_j stored(g_j * s_j). Per example this moves 2 + 8 / N bytes per
 // parameter; N is bounded by how many whole-model gradient buffers fit next to the optimizer state.
 struct AccGroup {
@@ -421,24 +392,6 @@ extern "C" int opk_clip_accumulate2(const void* g, const float* scale, float* ac
   if (tail > 0)
     clip_accumulate_tail_kernel<<<1, 32, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(g), scale, acc,
                                                          nvec << 3, n, overwrite);
-  OPK_LAUNCH_CHECK();
-  return 0;
-}
-extern "C" int opk_clip_accumulate_pair(const void* g0, const float* scale0, const void* g1, const float* scale1, float* acc,
-                                        int64_t n, int overwrite, void* stream) {
-  if (n <= 0) return 0;
-  if ((reinterpret_cast<uintptr_t>(g0) & 15) || (reinterpret_cast<uintptr_t>(g1) & 15) || (reinterpret_cast<uintptr_t>(acc) & 15))
-    return -1;
-  const long long nvec = n >> 3;
-  if (nvec > 0)
-    clip_accumulate_pair_kernel<<<grid_for(nvec, 256, 148 * 16), 256, 0, ST(stream)>>>(
-        reinterpret_cast<const bf16x8*>(g0), scale0, reinterpret_cast<const bf16x8*>(g1), scale1,
-        reinterpret_cast<float4*>(acc), nvec, overwrite);
-  const long long tail = n - (nvec << 3);
-  if (tail > 0) {
-    clip_accumulate_tail_kernel<<<1, 32, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(g0), scale0, acc, nvec << 3, n, overwrite);
-    clip_accumulate_tail_kernel<<<1, 32, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(g1), scale1, acc, nvec << 3, n, 0);
-  }
   OPK_LAUNCH_CHECK();
   return 0;
 }

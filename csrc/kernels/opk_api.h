@@ -214,10 +214,7 @@ int opk_clip_scale(double* sumsq, float clip, int mode_auto, float gamma, int n_
 int opk_clip_accumulate(const void* g, const float* scale, float* acc, int64_t n, void* stream);
 // Same with overwrite != 0 meaning acc = bf16(g * scale) (first example of a step: no separate zeroing pass).
 int opk_clip_accumulate2(const void* g, const float* scale, float* acc, int64_t n, int overwrite, void* stream);
-// Two examples at once: acc (+)= stored(g0 * scale0) + stored(g1 * scale1) in one pass over acc.
-int opk_clip_accumulate_pair(const void* g0, const float* scale0, const void* g1, const float* scale1, float* acc, int64_t n,
-                             int overwrite, void* stream);
-// The same for a group of up to OPK_ACC_GROUP_MAX examples: acc += sum_j stored(g[j] * *scale[j]) in one pass over acc.
+// A group of up to OPK_ACC_GROUP_MAX examples at once: acc (+)= sum_j stored(g[j] * *scale[j]) in one pass over acc.
 // g and scale are HOST arrays of device pointers.
 #define OPK_ACC_GROUP_MAX 8
 int opk_clip_accumulate_group(const void* const* g, const float* const* scale, int n_group, float* acc, int64_t n, int overwrite,

@@ -421,16 +421,6 @@ class DecoderRuntime:
             acc_emb = acc[emb.offset : emb.offset + emb.numel].view(emb.shape)
             K.embedding_accumulate(tok, ws["embs"][slot], self.scales[slot], acc_emb, tok.numel())
 
-    def accumulate_pair(self, acc: torch.Tensor, ws: dict, tok0: torch.Tensor, tok1: torch.Tensor, *, overwrite: bool = False) -> None:
-        """Adds the clipped gradients of the examples held in slots 0 and 1 in one pass over ``acc``."""
-        K.clip_accumulate_pair(self.Gs[0], self.scales[0], self.Gs[1], self.scales[1], acc[: self.layout.dense_total],
-                               overwrite=overwrite)
-        if not self.cfg.tie_embeddings:
-            emb = self.layout.slot("embed")
-            acc_emb = acc[emb.offset : emb.offset + emb.numel].view(emb.shape)
-            K.embedding_accumulate(tok0, ws["embs"][0], self.scales[0], acc_emb, tok0.numel())
-            K.embedding_accumulate(tok1, ws["embs"][1], self.scales[1], acc_emb, tok1.numel())
-
     def accumulate_group(self, acc: torch.Tensor, ws: dict, n: int, *, overwrite: bool = False, toks=None) -> None:
         """Adds the clipped gradients of the examples held in slots ``0 .. n-1`` in one pass over ``acc``: the fp32
         sums are read and written once for the whole group. ``toks``: the token tensors of the slots when they are not

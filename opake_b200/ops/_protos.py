@@ -81,7 +81,6 @@ PROTOTYPES: dict = {
     "opk_clip_scale": (I, [P, F, I, F, I, L, P, P, P, I, P]),
     "opk_clip_accumulate": (I, [P, P, P, L, P]),
     "opk_clip_accumulate2": (I, [P, P, P, L, I, P]),
-    "opk_clip_accumulate_pair": (I, [P, P, P, P, P, L, I, P]),
     "opk_clip_accumulate_group": (I, [POINTER(c_void_p), POINTER(c_void_p), I, P, L, I, P]),
     "opk_philox_normal": (I, [P, L, c_uint64, c_uint32, c_uint32, c_uint64, F, I, P]),
     "opk_dp_step": (I, [POINTER(DpStepArgs), P]),

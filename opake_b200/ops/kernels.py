@@ -259,12 +259,6 @@ def clip_accumulate(g, scale, acc, overwrite: bool = False):
     _chk(_L().opk_clip_accumulate2(_p(g), _p(scale), _p(acc), g.numel(), int(overwrite), _s(g)), "clip_accumulate")
 
 
-def clip_accumulate_pair(g0, scale0, g1, scale1, acc, overwrite: bool = False):
-    """``acc (+)= stored(g0 * scale0) + stored(g1 * scale1)``: two examples in one pass over the fp32 sums."""
-    _chk(_L().opk_clip_accumulate_pair(_p(g0), _p(scale0), _p(g1), _p(scale1), _p(acc), g0.numel(), int(overwrite), _s(acc)),
-         "clip_accumulate_pair")
-
-
 def clip_accumulate_group(gs, scales, acc, overwrite: bool = False):
     """``acc (+)= sum_j stored(gs[j] * scales[j])`` for up to 8 examples in one pass over the fp32 sums."""
     import ctypes

@@ -82,10 +82,10 @@ class ShardedDPEngine:
             self.blt_state = torch.zeros(nb, self.shard_len, dtype=torch.float32, device=device)
             self.blt_decay = torch.tensor(cfg.blt_decay, dtype=torch.float32, device=device)
             self.blt_scale = torch.tensor(cfg.blt_scale, dtype=torch.float32, device=device)
-        # how clipped gradients reach the fp32 sums: "pair" (default: groups of examples share one pass over the
+        # how clipped gradients reach the fp32 sums: "group" (default: groups of examples share one pass over the
         # sums), or the diagnostic modes overlap | serial | off
-        self._acc_mode = os.environ.get("OPK_ACC_MODE", "pair")
-        self.group = self._pick_group_size() if self._acc_mode == "pair" else 2
+        self._acc_mode = os.environ.get("OPK_ACC_MODE", "group")
+        self.group = self._pick_group_size() if self._acc_mode == "group" else 2
         self.runtime = DecoderRuntime(model_cfg, self.params, layout=self.layout, attn_impl=cfg.attn_impl, n_slots=self.group)
         self._side = torch.cuda.Stream(device=device)
         self._warm: dict[int, bool] = {}
@@ -121,7 +121,7 @@ class ShardedDPEngine:
         rt, cfg = self.runtime, self.cfg
         main = torch.cuda.current_stream(self.device)
         mode = self._acc_mode
-        if mode == "pair":
+        if mode == "group":
             # examples cycle through the gradient buffers; when the last buffer of the group is full, all of them are
             # clipped and added in a single pass over the fp32 sums (2 + 8 / group bytes of HBM traffic per parameter
             # and example instead of 10)
@@ -162,7 +162,7 @@ class ShardedDPEngine:
     def _run_example(self, tok_host: torch.Tensor, labels_host: torch.Tensor, index: int) -> None:
         T = tok_host.numel()
         ws = self.runtime.workspace(T)
-        slot = index % self.group if self._acc_mode == "pair" else index & 1
+        slot = index % self.group if self._acc_mode == "group" else index & 1
         drain = index > 0
         ws["toks"][slot].copy_(tok_host, non_blocking=True)
         ws["labels"].copy_(labels_host, non_blocking=True)
@@ -217,7 +217,7 @@ class ShardedDPEngine:
         for i in range(B_local):
             self._run_example(tokens[i], labels[i], i)
         last = (B_local - 1) & 1
-        if self._acc_mode == "pair":
+        if self._acc_mode == "group":
             # the last group (complete or not) has not been added yet: every earlier one was added at the start of
             # the example that followed it
             n_last = B_local % self.group or min(self.group, B_local)
