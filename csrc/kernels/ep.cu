@@ -185,30 +185,48 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const OpkEpGroup g, co
     }
   }
   if (ok) {
+    // four (entry, 16-byte chunk) items per thread and step: their index, rank and row loads form four independent
+    // dependency chains, so the latency of one chain is not what paces the stores
     const int nv = D >> 3;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)n_entries * nv;
-         i += (long long)gridDim.x * blockDim.x) {
-      const int n = (int)(i / nv), c = (int)(i - (long long)n * nv);
-      int pos;
-      if (replay) {
-        pos = entry_pos[n];
-      } else {
-        const int e = idx[n];
-        pos = ((e / El) << 26) | (base[e] + entry_rank[n]);
-        if (c == 0) entry_pos[n] = pos;
-      }
-      uint4 v = *reinterpret_cast<const uint4*>(x + (long long)(n / k) * ldx + c * 8);
-      if (entry_scale) {
-        const float s = entry_scale[n];
-        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+    constexpr int U = 4;
+    const long long total = (long long)n_entries * nv, stride = (long long)gridDim.x * blockDim.x;
+    for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < total; i0 += U * stride) {
+      uint4 v[U];
+      int pos[U], cc[U];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __bfloat1622float2(h[j]);
-          h[j] = __floats2bfloat162_rn(f.x * s, f.y * s);
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        pos[u] = -1;
+        if (i < total) {
+          const int n = (int)(i / nv), c = (int)(i - (long long)n * nv);
+          cc[u] = c;
+          if (replay) {
+            pos[u] = entry_pos[n];
+          } else {
+            const int e = idx[n];
+            pos[u] = ((e / El) << 26) | (base[e] + entry_rank[n]);
+            if (c == 0) entry_pos[n] = pos[u];
+          }
+          v[u] = *reinterpret_cast<const uint4*>(x + (long long)(n / k) * ldx + c * 8);
+          if (entry_scale) {
+            const float sc = entry_scale[n];
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v[u]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __bfloat1622float2(h[j]);
+              h[j] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+            }
+          }
         }
       }
-      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(rows.p[pos >> 26]) + (long long)(pos & 0x3FFFFFF) * D + c * 8;
-      *reinterpret_cast<uint4*>(dst) = v;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (pos[u] >= 0) {
+          __nv_bfloat16* dst =
+              reinterpret_cast<__nv_bfloat16*>(rows.p[pos[u] >> 26]) + (long long)(pos[u] & 0x3FFFFFF) * D + cc[u] * 8;
+          *reinterpret_cast<uint4*>(dst) = v[u];
+        }
+      }
     }
   } else if (threadIdx.x == 0 && err) {
     atomicCAS(err, 0, 1);
@@ -341,12 +359,13 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const OpkEpGroup g, con
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     }
-    // the remote loads of four slots are issued together, then summed in slot order (deterministic)
-    for (int s0 = 0; s0 < k; s0 += 4) {
-      uint4 v[4];
-      float w[4];
+    // the remote loads of eight slots are issued together, then summed in slot order (deterministic)
+    constexpr int B = 8;
+    for (int s0 = 0; s0 < k; s0 += B) {
+      uint4 v[B];
+      float w[B];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
+      for (int q = 0; q < B; ++q) {
         v[q] = make_uint4(0, 0, 0, 0);
         w[q] = 0.f;
         if (s0 + q < k) {
@@ -358,7 +377,7 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const OpkEpGroup g, con
         }
       }
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
+      for (int q = 0; q < B; ++q) {
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[q]);
 #pragma unroll
         for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); acc[2 * j] += w[q] * f.x; acc[2 * j + 1] += w[q] * f.y; }
