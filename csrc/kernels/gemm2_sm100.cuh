@@ -228,14 +228,17 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int ctid = (warp - 2 - gemm_epi_warps(EPI)) * 32 + lane;
     const long long nthreads = (long long)gridDim.x * (32 * kStageWarps);
     const long long gtid = (long long)blockIdx.x * (32 * kStageWarps) + ctid;
-    const int kv = p.K >> 3;                                   // 16-byte vectors per row
-    const int band_rows = kRasterBand * BN;
-    const int n_bands = (p.N + band_rows - 1) / band_rows;
+    // K-major B ([N][K], a band = 2048 whole rows) or MN-major B ([K][N], a band = 2048 columns of every row)
+    const int band_span = kRasterBand * BN;
+    const int n_bands = (p.N + band_span - 1) / band_span;
     const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.stage_src);
     uint4* dst = reinterpret_cast<uint4*>(p.stage_dst);
     for (int band = 0; band < n_bands; ++band) {
-      const int r0 = band * band_rows, r1 = min(p.N, r0 + band_rows);
-      const long long nvec = (long long)(r1 - r0) * kv;
+      const int n0 = band * band_span, n1 = min(p.N, n0 + band_span);
+      const int vec_per_row = B_MN ? (n1 - n0) >> 3 : p.K >> 3;     // 16-byte vectors per copied row segment
+      const int n_rows = B_MN ? p.K : n1 - n0;
+      const long long dst_ld = B_MN ? p.N >> 3 : p.K >> 3;           // scratch row pitch in vectors
+      const long long nvec = (long long)n_rows * vec_per_row;
       constexpr int U = 8;                                     // remote loads in flight per thread
       for (long long i0 = gtid; i0 < nvec; i0 += U * nthreads) {
         uint4 v[U];
@@ -243,14 +246,20 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         for (int u = 0; u < U; ++u) {
           const long long i = i0 + u * nthreads;
           if (i < nvec) {
-            const long long row = r0 + i / kv;
-            v[u] = __ldcg(reinterpret_cast<const uint4*>(src + row * p.stage_ld) + (i % kv));
+            const long long rr = i / vec_per_row, cv = i % vec_per_row;
+            const long long row = B_MN ? rr : n0 + rr;
+            const long long col = B_MN ? n0 + cv * 8 : cv * 8;
+            v[u] = __ldcg(reinterpret_cast<const uint4*>(src + row * p.stage_ld + col));
           }
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const long long i = i0 + u * nthreads;
-          if (i < nvec) dst[(r0 + i / kv) * kv + (i % kv)] = v[u];
+          if (i < nvec) {
+            const long long rr = i / vec_per_row, cv = i % vec_per_row;
+            const long long row = B_MN ? rr : n0 + rr;
+            dst[row * dst_ld + (B_MN ? (n0 >> 3) + cv : cv)] = v[u];
+          }
         }
       }
       __threadfence();

@@ -154,12 +154,16 @@ extern "C" int opk_gemm(const OpkGemmArgs* a, void* stream) {
   const bool stage = a->stage_dst != nullptr;
   if (stage) {
     // B is read once over NVLink by the kernel's copier warps into stage_dst; the tensor map covers the scratch
-    if (!pair || a->b_mn || a->a_mn || a->epilogue != opk::EPI_STORE || a->batch != 1 || !a->stage_ready || (a->K % 8) ||
+    if (!pair || a->a_mn || a->epilogue != opk::EPI_STORE || a->batch != 1 || !a->stage_ready || (a->K % 8) || (a->N % 8) ||
         (a->ldb % 8) || (reinterpret_cast<uintptr_t>(a->B) & 15) || (reinterpret_cast<uintptr_t>(a->stage_dst) & 15)) {
-      set_err("opk_gemm: staged B needs a plain K-major product with at least 256 rows, 256-wide tiles and 16-byte aligned rows");
+      set_err("opk_gemm: staged B needs a plain product with at least 256 rows, 256-wide tiles and 16-byte aligned rows");
       return -1;
     }
-    if (!make_map(&tb, a->stage_dst, a->K, a->N, 1, a->K, 0, 128)) return -2;
+    if (a->b_mn) {
+      if (!make_map(&tb, a->stage_dst, a->N, a->K, 1, a->N, 0, 64)) return -2;
+    } else {
+      if (!make_map(&tb, a->stage_dst, a->K, a->N, 1, a->K, 0, 128)) return -2;
+    }
   } else if (a->b_mn) {
     if (!make_map(&tb, a->B, a->N, a->K, bbatch, a->ldb, a->strideB, 64)) return -2;
   } else {
@@ -181,7 +185,8 @@ extern "C" int opk_gemm(const OpkGemmArgs* a, void* stream) {
     cudaError_t e = cudaMemsetAsync(a->stage_ready, 0, sizeof(int32_t) * n_bands, st);
     if (e != cudaSuccess) { set_err(cudaGetErrorString(e)); return (int)e; }
     p.stage_src = a->B; p.stage_ld = a->ldb; p.stage_dst = a->stage_dst; p.stage_ready = a->stage_ready;
-    return launch2<false, false, opk::EPI_STORE, true>(ta, tb, p, mc, st);
+    return a->b_mn ? launch2<false, true, opk::EPI_STORE, true>(ta, tb, p, mc, st)
+                   : launch2<false, false, opk::EPI_STORE, true>(ta, tb, p, mc, st);
   }
   if (pair) {
     switch (a->epilogue) {

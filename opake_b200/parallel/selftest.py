@@ -135,13 +135,20 @@ def _sharded_linear_bench(rank: int, world: int, dev: torch.device, out: str, M:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item()
 
+    from .sharded_linear import sharded_linear_dgrad
+
     t_sharded = timed(lambda: sharded_linear_forward(x, sw, out=y))
     t_local = timed(lambda: G.gemm(x, full, out=y))
+    dy = torch.randn(M, N, device=dev).mul_(0.1).to(torch.bfloat16)
+    dx = torch.empty(M, Kd, dtype=torch.bfloat16, device=dev)
+    t_dgrad = timed(lambda: sharded_linear_dgrad(dy, sw, out=dx))
+    t_dgrad_local = timed(lambda: G.gemm(dy, full, b_mn=True, out=dx))
     remote_bytes = (world - 1) / world * N * Kd * 2
     res = {"case": "sharded_linear_forward", "world": world, "M": M, "N": N, "K": Kd, "sharded_us": round(t_sharded, 1),
            "local_weight_us": round(t_local, 1), "tflops_sharded": round(2.0 * M * N * Kd / t_sharded / 1e6, 1),
            "nvlink_roofline_us": round(remote_bytes / 770e3, 1),
-           "roofline_us": round(max(remote_bytes / 770e3, t_local), 1)}
+           "roofline_us": round(max(remote_bytes / 770e3, t_local), 1),
+           "dgrad_sharded_us": round(t_dgrad, 1), "dgrad_local_weight_us": round(t_dgrad_local, 1)}
     if world > 1:
         sw.publish()
     if rank == 0:

@@ -47,7 +47,7 @@ class ShardedWeight:
         if self._scratch is None:
             dev = self.local.device
             self._scratch = (torch.empty(self.rows, self.n_in, dtype=torch.bfloat16, device=dev),
-                             torch.zeros((self.rows + 2047) // 2048, dtype=torch.int32, device=dev))
+                             torch.zeros((max(self.rows, self.n_in) + 2047) // 2048, dtype=torch.int32, device=dev))
         return self._scratch
 
     def order(self) -> list[int]:
@@ -78,7 +78,9 @@ def sharded_linear_dgrad(dy: torch.Tensor, w: ShardedWeight, out: torch.Tensor |
     if out is None:
         out = torch.empty(M, w.n_in, dtype=torch.bfloat16, device=dy.device)
     first = True
+    staged = M >= 256 and w.n_in > 128 and G.pair_mode()
     for s in w.order():
-        G.gemm(dy[:, s * w.rows:(s + 1) * w.rows], w.shards[s], b_mn=True, out=out, residual=None if first else out)
+        G.gemm(dy[:, s * w.rows:(s + 1) * w.rows], w.shards[s], b_mn=True, out=out, residual=None if first else out,
+               stage=w.scratch() if (s != w.rank and staged) else None)
         first = False
     return out
