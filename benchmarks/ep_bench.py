@@ -1,6 +1,6 @@
 """Times the expert-parallel exchange: fused peer-memory kernels against ``all_to_all_single``.
 
-``torchrun --nproc-per-node N -m opake_b200.parallel.ep_bench`` (OLMoE-1B-7B layer shape by default: 2048 tokens per
+``torchrun --nproc-per-node N -m benchmarks.ep_bench`` (OLMoE-1B-7B layer shape by default: 2048 tokens per
 rank, d = 2048, 64 experts, top-8). Both arms move the same rows: dispatch = every (token, slot) entry's activation row
 to the rank that owns its expert, grouped by expert there; combine = the expert output rows back, summed over the slots
 with the routing weights. The library arm is what a framework without its own kernels does: exchange the split sizes,
@@ -16,9 +16,9 @@ import json
 import torch
 import torch.distributed as dist
 
-from ..ops import _lib
-from . import comm
-from .ep_fused import PHASE_COUNTS, PHASE_OUT, PHASE_ROWS, EpContext, _L, _p
+from opake_b200.ops import _lib
+from opake_b200.parallel import comm
+from opake_b200.parallel.ep_fused import PHASE_COUNTS, PHASE_OUT, PHASE_ROWS, EpContext, _L, _p
 
 PEER_COPY_GBS = 770.0
 
@@ -46,7 +46,7 @@ def _layer_bench(a, rank: int, world: int, dev) -> None:
     device time of forward, of backward pass 1 (input gradients + per-source squared norms) and of pass 2 (clipped
     accumulation of the expert weight gradients), maximum over ranks. FLOPs counted: 3 products per pass direction
     over the routed rows (gate/up, down; forward, input gradient, weight gradient twice: norms and accumulation)."""
-    from .ep_fused import FusedExpertParallelLayer
+    from opake_b200.parallel.ep_fused import FusedExpertParallelLayer
 
     T, d, E, k, I = a.tokens, a.d, a.experts, a.top_k, a.ffn
     El = E // world

@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: ``python -m opake_b200.ops.microbench <case> [options]``.
+"""Kernel micro-benchmarks: ``python -m benchmarks.microbench <case> [options]``.
 
 Each case times ONE native kernel (or a short kernel sequence) in isolation with CUDA events on the launching
 stream, after warm-up, writing a buffer larger than L2 between timed launches so that every launch starts cold, and
@@ -67,7 +67,7 @@ def _emit(case: str, shape: dict, us: float, *, flops: float = 0.0, bytes_: floa
 
 
 def case_gemm(t: _Timer, a) -> None:
-    from . import gemm as G
+    from opake_b200.ops import gemm as G
     dev = t.device
     T = 1024 if a.small else 2048
     d, f, qkv = (2048, 8192, 3072) if a.small else (4096, 14336, 6144)
@@ -89,7 +89,7 @@ def case_gemm(t: _Timer, a) -> None:
     us = t.run(lambda: G.linear_wgrad(dy, x, out=dw, sumsq=ss), a.iters)
     _emit("gemm", {"kind": "wgrad_gate_up_sumsq", "M": 2 * f, "N": d, "K": T}, us, flops=2.0 * T * d * 2 * f)
     # down projection's input gradient: plain product + separate SwiGLU backward against the fused epilogue
-    from . import kernels as K
+    from opake_b200.ops import kernels as K
     dyd, wd = torch.randn(T, d, device=dev, dtype=bf), torch.randn(d, f, device=dev, dtype=bf) * 0.05
     gu, dgu = torch.randn(T, 2 * f, device=dev, dtype=bf), torch.empty(T, 2 * f, device=dev, dtype=bf)
     dact = torch.empty(T, f, device=dev, dtype=bf)
@@ -105,7 +105,7 @@ def case_gemm(t: _Timer, a) -> None:
 
 
 def case_attention(t: _Timer, a) -> None:
-    from .flash import flash_bwd, flash_fwd
+    from opake_b200.ops.flash import flash_bwd, flash_fwd
     dev = t.device
     T, H, KV, hd = (1024, 16, 4, 128) if a.small else (2048, 32, 8, 128)
     qkv = (torch.randn(T, (H + 2 * KV) * hd, device=dev) * 0.5).to(torch.bfloat16)
@@ -120,7 +120,7 @@ def case_attention(t: _Timer, a) -> None:
 
 
 def case_dp_step(t: _Timer, a) -> None:
-    from . import kernels as K
+    from opake_b200.ops import kernels as K
     dev = t.device
     n = (64 if a.small else 1024) << 20
     acc = torch.randn(n, device=dev)
@@ -138,7 +138,7 @@ def case_dp_step(t: _Timer, a) -> None:
 
 
 def case_clip_accumulate(t: _Timer, a) -> None:
-    from . import kernels as K
+    from opake_b200.ops import kernels as K
     dev = t.device
     n = (64 if a.small else 1024) << 20
     g = torch.randn(n, device=dev).to(torch.bfloat16)
@@ -149,7 +149,7 @@ def case_clip_accumulate(t: _Timer, a) -> None:
 
 
 def case_rmsnorm(t: _Timer, a) -> None:
-    from . import kernels as K
+    from opake_b200.ops import kernels as K
     dev = t.device
     T, D = (8192, 4096) if a.small else (32768, 4096)
     x = torch.randn(T, D, device=dev).to(torch.bfloat16)
@@ -164,7 +164,7 @@ def case_rmsnorm(t: _Timer, a) -> None:
 
 
 def case_lce(t: _Timer, a) -> None:
-    from . import gemm as G, kernels as K
+    from opake_b200.ops import gemm as G, kernels as K
     dev = t.device
     T, D, V = (1024, 2048, 32000) if a.small else (2048, 4096, 128256)
     h = (torch.randn(T, D, device=dev) * 0.3).to(torch.bfloat16)
@@ -183,7 +183,7 @@ def case_lce(t: _Timer, a) -> None:
 
 
 def case_clip_sum(t: _Timer, a) -> None:
-    from .clip_sum import fused_clip_sum
+    from opake_b200.ops.clip_sum import fused_clip_sum
     dev = t.device
     B, n = (8, 16 << 20) if a.small else (16, 64 << 20)
     leaves = [torch.randn(B, n, device=dev).to(torch.bfloat16)]
@@ -211,7 +211,7 @@ def main(argv=None) -> int:
     timer = _Timer(dev)
     for name in (sorted(CASES) if a.case == "all" else [a.case]):
         CASES[name](timer, a)
-    from ._lib import raise_if_device_error
+    from opake_b200.ops._lib import raise_if_device_error
     raise_if_device_error(dev)
     return 0
 

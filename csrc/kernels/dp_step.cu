@@ -381,9 +381,7 @@ extern "C" int opk_clip_accumulate2(const void* g, const float* scale, float* ac
     // Same shared-memory carve-out as the GEMM kernels, so that CTAs of this kernel can be co-resident with them
     // on an SM (an SM does not mix carve-out configurations).
     cudaFuncSetAttribute(clip_accumulate_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    const char* e = getenv("OPK_ACC_CTAS");
-    cap_ctas = e ? atoi(e) : 148 * 16;
-    if (cap_ctas <= 0) cap_ctas = 148 * 16;
+    cap_ctas = 148 * 16;
   }
   if (nvec > 0)
     clip_accumulate_kernel<<<grid_for(nvec, 256, cap_ctas), 256, 0, ST(stream)>>>(

@@ -489,23 +489,30 @@ __global__ void embedding_fwd_kernel(const int* __restrict__ tok, const __nv_bfl
     }
   }
 }
-__global__ void emb_first_pos_kernel(const int* __restrict__ tok, int* __restrict__ first_pos, int T) {
+// Token ids outside [0, vocab) are skipped by all three table kernels (their rep[] entry becomes -1, which the
+// accumulate / add-rows kernels treat as "not a representative row"), so a bad id can never index past the table.
+__device__ __forceinline__ bool emb_tok_ok(int tok, int vocab) { return (unsigned)tok < (unsigned)vocab; }
+__global__ void emb_first_pos_kernel(const int* __restrict__ tok, int* __restrict__ first_pos, int T, int vocab) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t < T) atomicMin(&first_pos[tok[t]], t);
+  if (t < T && emb_tok_ok(tok[t], vocab)) atomicMin(&first_pos[tok[t]], t);
 }
 __global__ void emb_scatter_kernel(const int* __restrict__ tok, const __nv_bfloat16* __restrict__ dx,
                                    const int* __restrict__ first_pos, int* __restrict__ rep, float* __restrict__ gc,
-                                   int D) {
+                                   int D, int vocab) {
   const long long t = blockIdx.x;
+  if (!emb_tok_ok(tok[t], vocab)) {
+    if (threadIdx.x == 0) rep[t] = -1;
+    return;
+  }
   const int r = first_pos[tok[t]];
   if (threadIdx.x == 0) rep[t] = r;
   const __nv_bfloat16* src = dx + t * D;
   float* dst = gc + (long long)r * D;
   for (int d = threadIdx.x; d < D; d += blockDim.x) atomicAdd(&dst[d], __bfloat162float(src[d]));
 }
-__global__ void emb_reset_kernel(const int* __restrict__ tok, int* __restrict__ first_pos, int T) {
+__global__ void emb_reset_kernel(const int* __restrict__ tok, int* __restrict__ first_pos, int T, int vocab) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t < T) first_pos[tok[t]] = INT_MAX;
+  if (t < T && emb_tok_ok(tok[t], vocab)) first_pos[tok[t]] = INT_MAX;
 }
 __global__ void emb_accumulate_kernel(const int* __restrict__ tok, const int* __restrict__ rep,
                                       const float* __restrict__ gc, const float* __restrict__ scale,
@@ -835,14 +842,15 @@ extern "C" int opk_embedding_fwd(const int32_t* tok, const void* table, const vo
   return 0;
 }
 extern "C" int opk_embedding_bwd_compact(const int32_t* tok, const void* dx, int32_t* first_pos, int32_t* rep,
-                                         float* gc, double* sumsq, int T, int D, void* stream) {
+                                         float* gc, double* sumsq, int T, int D, int vocab, void* stream) {
   if (T <= 0) return 0;
+  if (vocab <= 0) return -1;
   cudaStream_t st = ST(stream);
   cudaError_t e = cudaMemsetAsync(gc, 0, sizeof(float) * (size_t)T * D, st);
   if (e != cudaSuccess) return (int)e;
-  emb_first_pos_kernel<<<(T + 255) / 256, 256, 0, st>>>(tok, first_pos, T);
-  emb_scatter_kernel<<<T, 256, 0, st>>>(tok, BF(dx), first_pos, rep, gc, D);
-  emb_reset_kernel<<<(T + 255) / 256, 256, 0, st>>>(tok, first_pos, T);
+  emb_first_pos_kernel<<<(T + 255) / 256, 256, 0, st>>>(tok, first_pos, T, vocab);
+  emb_scatter_kernel<<<T, 256, 0, st>>>(tok, BF(dx), first_pos, rep, gc, D, vocab);
+  emb_reset_kernel<<<(T + 255) / 256, 256, 0, st>>>(tok, first_pos, T, vocab);
   if (sumsq) sumsq_kernel<true, true><<<grid_for((long long)T * D, NT, 148 * 4), NT, 0, st>>>(gc, (long long)T * D, sumsq);
   OPK_LAUNCH_CHECK();
   return 0;
@@ -961,10 +969,10 @@ extern "C" int opk_embedding_bwd_compact_noalloc(const int32_t* tok, const void*
   if (e != cudaSuccess) return (int)e;
   // entries touched by this call are forced to the idle value first: the table keeps whatever the previous call
   // (possibly one that was interrupted) left behind
-  emb_reset_kernel<<<(T + 255) / 256, 256, 0, st>>>(tok, first_pos, T);
-  emb_first_pos_kernel<<<(T + 255) / 256, 256, 0, st>>>(tok, first_pos, T);
-  emb_scatter_kernel<<<T, 256, 0, st>>>(tok, BF(dx), first_pos, rep, gc, D);
-  emb_reset_kernel<<<(T + 255) / 256, 256, 0, st>>>(tok, first_pos, T);
+  emb_reset_kernel<<<(T + 255) / 256, 256, 0, st>>>(tok, first_pos, T, vocab);
+  emb_first_pos_kernel<<<(T + 255) / 256, 256, 0, st>>>(tok, first_pos, T, vocab);
+  emb_scatter_kernel<<<T, 256, 0, st>>>(tok, BF(dx), first_pos, rep, gc, D, vocab);
+  emb_reset_kernel<<<(T + 255) / 256, 256, 0, st>>>(tok, first_pos, T, vocab);
   if (sumsq) sumsq_kernel<true, true><<<grid_for((long long)T * D, NT, 148 * 4), NT, 0, st>>>(gc, (long long)T * D, sumsq);
   OPK_LAUNCH_CHECK();
   return 0;

@@ -98,8 +98,9 @@ int opk_embedding_fwd(const int32_t* tok, const void* table, const void* pos_tab
 // Per-example embedding gradient without a dense [V][D] buffer: rows with equal tokens are summed into the row of
 // their first occurrence. first_pos is an int32 [V] scratch that must hold INT32_MAX on entry and is restored.
 // Outputs: rep[T] (first position of the same token), gc[T][D] fp32 (zeroed here), sumsq += sum(bf16(gc)^2).
+// vocab is the length of first_pos; a token id outside [0, vocab) is skipped (rep[t] = -1, no row written).
 int opk_embedding_bwd_compact(const int32_t* tok, const void* dx, int32_t* first_pos, int32_t* rep, float* gc,
-                              double* sumsq, int T, int D, void* stream);
+                              double* sumsq, int T, int D, int vocab, void* stream);
 // acc[tok[t]] += bf16(gc[t] * scale) for the representative rows (rep[t] == t).
 int opk_embedding_accumulate(const int32_t* tok, const int32_t* rep, const float* gc, const float* scale, float* acc,
                              int T, int D, void* stream);

@@ -20,7 +20,7 @@ extern "C" {
 // first occurrence), but the first-occurrence table lives in a static device array inside the library instead of a
 // caller-provided scratch buffer.
 //
-//   tok   int32 [T]      token ids, each in [0, vocab)
+//   tok   int32 [T]      token ids; an id outside [0, vocab) is skipped (rep[t] = -1, no row written)
 //   dx    bf16  [T][D]   gradient with respect to the embedding output
 //   rep   int32 [T]      out: first position holding the same token
 //   gc    fp32  [T][D]   out: summed rows (row rep[t] holds the sum; other rows are zero)
@@ -29,7 +29,8 @@ extern "C" {
 // Returns 0 on success, -1 for invalid sizes, -2 when vocab exceeds OPK_NOALLOC_MAX_VOCAB, otherwise a cudaError_t.
 // Calls no cudaMalloc / cudaFree and no allocating library routine.
 //
-// The first call on a device looks up the device address of the scratch array (cudaGetSymbolAddress) and fills it
+// The device that owns `stream` must be the current device (cudaSetDevice) when the call is made: the scratch
+// array is looked up per current device. The first call on a device looks up the device address of the scratch array (cudaGetSymbolAddress) and fills it
 // with its idle value; make that first call before starting a stream capture. Every call shares the one scratch array
 // of its device and leaves it in the idle state again, so calls must not overlap on the GPU (two streams, or two host
 // threads on different streams, would race on the table).

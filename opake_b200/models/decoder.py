@@ -38,7 +38,7 @@ class DecoderRuntime:
     """Forward + per-example backward for dense decoders (Llama-style and GPT-2-style blocks)."""
 
     def __init__(self, cfg: DecoderConfig, params: torch.Tensor, *, layout: Layout | None = None,
-                 attn_impl: str = "auto", n_slots: int = 1):
+                 attn_impl: str = "auto", n_slots: int = 1, wgrad_overlap: bool = True):
         if cfg.n_experts and (cfg.act != "swiglu" or cfg.n_experts > 256 or cfg.top_k > 32 or cfg.d_model % 8):
             raise ValueError("mixture-of-experts layers need SwiGLU experts, at most 256 experts and top_k <= 32")
         self.cfg = cfg
@@ -61,11 +61,9 @@ class DecoderRuntime:
         self._rope = None
         # Weight-gradient GEMMs run on a second stream next to the input-gradient GEMMs of the same layer: both are
         # persistent kernels that want every SM, so the second one's CTAs fill the SMs that the first one's last
-        # (partial) wave of tiles leaves idle, and launch gaps disappear. OPK_WGRAD_OVERLAP=0 keeps one stream.
-        import os
-
+        # (partial) wave of tiles leaves idle, and launch gaps disappear. ``wgrad_overlap=False`` keeps one stream.
         self._wstream = None
-        if self.device.type == "cuda" and os.environ.get("OPK_WGRAD_OVERLAP", "1") != "0":
+        if self.device.type == "cuda" and wgrad_overlap:
             self._wstream = torch.cuda.Stream(device=self.device)
         # small-vector gradients (norm weights, biases) are produced in fp32 rows and scattered into G at the end
         self._vec_names = [s.name for s in self.layout.slots

@@ -186,7 +186,7 @@ class EmbeddingGradWorkspace:
 def embedding_bwd_compact(tok, dx, ws: EmbeddingGradWorkspace, sumsq):
     T, D = dx.shape
     _chk(_L().opk_embedding_bwd_compact(_p(tok), _p(dx), _p(ws.first_pos), _p(ws.rep), _p(ws.gc), _p(sumsq), T, D,
-                                        _s(dx)), "embedding_bwd_compact")
+                                        ws.first_pos.numel(), _s(dx)), "embedding_bwd_compact")
 
 
 def embedding_accumulate(tok, ws: EmbeddingGradWorkspace, scale, acc, T: int):

@@ -18,7 +18,6 @@ gradients.py:150-200) with CPU-generated noise (packages/opake-dpsgd/src/opake/a
 from __future__ import annotations
 
 import math
-import os
 from dataclasses import dataclass, field
 
 import torch
@@ -54,6 +53,7 @@ class EngineConfig:
     blt_decay: tuple[float, ...] = ()
     blt_scale: tuple[float, ...] = ()
     noise_stream_tag: str = "opake.dpsgd.gaussian"
+    accumulate_group: int = 0           # whole-model gradient buffers per accumulation pass; 0 = as many as fit (2..6)
 
 
 class ShardedDPEngine:
@@ -82,10 +82,9 @@ class ShardedDPEngine:
             self.blt_state = torch.zeros(nb, self.shard_len, dtype=torch.float32, device=device)
             self.blt_decay = torch.tensor(cfg.blt_decay, dtype=torch.float32, device=device)
             self.blt_scale = torch.tensor(cfg.blt_scale, dtype=torch.float32, device=device)
-        # how clipped gradients reach the fp32 sums: "group" (default: groups of examples share one pass over the
-        # sums), or the diagnostic modes overlap | serial | off
-        self._acc_mode = os.environ.get("OPK_ACC_MODE", "group")
-        self.group = self._pick_group_size() if self._acc_mode == "group" else 2
+        if cfg.accumulate_group and not 2 <= int(cfg.accumulate_group) <= 8:
+            raise ValueError(f"accumulate_group must be 0 (automatic) or between 2 and 8, got {cfg.accumulate_group}")
+        self.group = int(cfg.accumulate_group) or self._pick_group_size()
         self.runtime = DecoderRuntime(model_cfg, self.params, layout=self.layout, attn_impl=cfg.attn_impl, n_slots=self.group)
         self._side = torch.cuda.Stream(device=device)
         self._warm: dict[int, bool] = {}
@@ -102,10 +101,8 @@ class ShardedDPEngine:
     def _pick_group_size(self) -> int:
         """How many whole-model bf16 gradient buffers to keep: the clipped accumulation reads and writes the fp32
         sums once per GROUP of examples (2 + 8 / group bytes per parameter and example), so more buffers mean less HBM
-        traffic. Sharding the optimizer state over more ranks frees the memory for them. ``OPK_ACC_GROUP`` overrides."""
-        forced = os.environ.get("OPK_ACC_GROUP")
-        if forced:
-            return max(2, min(8, int(forced)))
+        traffic. Sharding the optimizer state over more ranks frees the memory for them.
+        ``EngineConfig.accumulate_group`` overrides the automatic choice."""
         if self.device.type != "cuda":
             return 2
         free, _ = torch.cuda.mem_get_info(self.device)
@@ -124,40 +121,23 @@ class ShardedDPEngine:
         the SMs, so the accumulation is hidden."""
         rt, cfg = self.runtime, self.cfg
         main = torch.cuda.current_stream(self.device)
-        mode = self._acc_mode
-        if mode == "group":
-            # examples cycle through the gradient buffers; when the last buffer of the group is full, all of them are
-            # clipped and added in a single pass over the fp32 sums (2 + 8 / group bytes of HBM traffic per parameter
-            # and example instead of 10)
-            # The pass itself is deferred to the start of the NEXT group's first example and runs on the side stream
-            # under that example's forward GEMMs (HBM-bound next to tensor-core-bound work); the example waits for it
-            # right before its first weight-gradient GEMM, the first kernel that overwrites a gradient buffer.
-            hook = None
-            if drain_prev and slot == 0:
-                self._side.wait_stream(main)
-                with torch.cuda.stream(self._side):
-                    rt.accumulate_group(self.acc, ws, self.group, toks=self._group_toks(ws, self.group))
-                hook = lambda: main.wait_stream(self._side)
-            st = rt.example_grad(ws["toks"][slot], ws["labels"], ws=ws, slot=slot, before_wgrad=hook)
-            rt.clip_factor(cfg.clip_norm, auto=cfg.auto_clip, gamma=cfg.auto_gamma, slot=slot)
-            ws["loss_sum"].add_(st.loss.reshape(1))
-            if slot == 0:
-                ws["tok_keep"].copy_(ws["toks"][0])      # slot 0's tokens are replaced before its deferred pass runs
-            return
-        if drain_prev and mode == "serial":
-            rt.accumulate(self.acc, ws, ws["toks"][slot ^ 1], slot=slot ^ 1)
-            drain_prev = False
-        elif mode == "off":
-            drain_prev = False
-        if drain_prev:
+        # examples cycle through the gradient buffers; when the last buffer of the group is full, all of them are
+        # clipped and added in a single pass over the fp32 sums (2 + 8 / group bytes of HBM traffic per parameter
+        # and example instead of 10)
+        # The pass itself is deferred to the start of the NEXT group's first example and runs on the side stream
+        # under that example's forward GEMMs (HBM-bound next to tensor-core-bound work); the example waits for it
+        # right before its first weight-gradient GEMM, the first kernel that overwrites a gradient buffer.
+        hook = None
+        if drain_prev and slot == 0:
             self._side.wait_stream(main)
             with torch.cuda.stream(self._side):
-                rt.accumulate(self.acc, ws, ws["toks"][slot ^ 1], slot=slot ^ 1)
-        st = rt.example_grad(ws["toks"][slot], ws["labels"], ws=ws, slot=slot)
+                rt.accumulate_group(self.acc, ws, self.group, toks=self._group_toks(ws, self.group))
+            hook = lambda: main.wait_stream(self._side)
+        st = rt.example_grad(ws["toks"][slot], ws["labels"], ws=ws, slot=slot, before_wgrad=hook)
         rt.clip_factor(cfg.clip_norm, auto=cfg.auto_clip, gamma=cfg.auto_gamma, slot=slot)
         ws["loss_sum"].add_(st.loss.reshape(1))
-        if drain_prev:
-            main.wait_stream(self._side)
+        if slot == 0:
+            ws["tok_keep"].copy_(ws["toks"][0])      # slot 0's tokens are replaced before its deferred pass runs
 
     @staticmethod
     def _group_toks(ws, n: int):
@@ -166,7 +146,7 @@ class ShardedDPEngine:
     def _run_example(self, tok_host: torch.Tensor, labels_host: torch.Tensor, index: int) -> None:
         T = tok_host.numel()
         ws = self.runtime.workspace(T)
-        slot = index % self.group if self._acc_mode == "group" else index & 1
+        slot = index % self.group
         drain = index > 0
         ws["toks"][slot].copy_(tok_host, non_blocking=True)
         ws["labels"].copy_(labels_host, non_blocking=True)
@@ -220,15 +200,11 @@ class ShardedDPEngine:
         ws["loss_sum"].zero_()
         for i in range(B_local):
             self._run_example(tokens[i], labels[i], i)
-        last = (B_local - 1) & 1
-        if self._acc_mode == "group":
-            # the last group (complete or not) has not been added yet: every earlier one was added at the start of
-            # the example that followed it
-            n_last = B_local % self.group or min(self.group, B_local)
-            if n_last:
-                self.runtime.accumulate_group(self.acc, ws, n_last, toks=self._group_toks(ws, n_last))
-        elif B_local > 0:
-            self.runtime.accumulate(self.acc, ws, ws["toks"][last], slot=last)   # drain the final example
+        # the last group (complete or not) has not been added yet: every earlier one was added at the start of the
+        # example that followed it
+        n_last = B_local % self.group or min(self.group, B_local)
+        if n_last:
+            self.runtime.accumulate_group(self.acc, ws, n_last, toks=self._group_toks(ws, n_last))
         loss_sum = ws["loss_sum"].clone()
         self.apply_update()
         return loss_sum

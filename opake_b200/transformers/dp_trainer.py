@@ -93,6 +93,31 @@ def _batch_len(batch) -> int:
     return -1
 
 
+def _rank_local_sampler_state(saved_state, template_sampler, world_size: int):
+    """Re-key a sampler snapshot onto this rank's own stream (``trainer/_dp_trainer.py:216-252`` of the reference).
+
+    Only the main rank writes the snapshot, so it carries the main rank's rank-folded stream key and the length of the
+    main rank's data shard. Installing it verbatim would give every rank the same Poisson coins (perfectly correlated
+    inclusion across shards, which the amplification analysis does not allow) and fail the length check whenever the
+    shards differ in size. Under DDP the key and the shard length therefore come from this rank's freshly built
+    sampler and only the cursor (and the sampler's hyper-parameters) from the snapshot."""
+    if world_size <= 1 or "key_seed" not in saved_state:
+        return saved_state
+    key = getattr(template_sampler, "_stream_key", None)
+    if key is None:
+        raise CheckpointError(f"sampler snapshot carries a stream key but {type(template_sampler).__name__} exposes none; "
+                              "cannot restore a rank-local sampling stream under DDP")
+    local = dict(saved_state)
+    local["key_seed"] = int(key.seed)
+    if "key_impl" in local:
+        local["key_impl"] = str(key.impl)
+    own = template_sampler.state_dict()
+    for name in ("num_samples",):
+        if name in local and name in own:
+            local[name] = own[name]
+    return local
+
+
 class DPTrainer:
     def __init__(self, model: nn.Module | None = None, args: TrainingArguments | None = None, data_collator: Callable | None = None,
                  train_dataset=None, eval_dataset=None, processing_class=None, compute_loss_func: Callable | None = None,
@@ -914,12 +939,19 @@ class DPTrainer:
             raise CheckpointError("the sampler stream key differs from the checkpoint (seed / data_seed changed); resuming would "
                                   "re-draw examples the accountant already paid for. Set ignore_data_skip=True to start a fresh stream.")
         if a.ignore_data_skip:
-            # fresh, independent sampling stream: the skipped draws are not replayed
-            rt["sampler"] = mf.build_sampler(a.resolved_sampling_mode, rt["sampler"].data_source if hasattr(rt["sampler"], "data_source") else self.train_dataset,
-                                             sample_rate=rt["sample_rate"], n_steps=rt["total_steps"], ctx=rt.get("mf_ctx"),
-                                             key=fold_in(self._sampler_key(), _IGNORE_DATA_SKIP_TAG), sampling_kwargs=a.sampling_kwargs)
+            # fresh, independent sampling stream: the skipped draws are not replayed. The data loader already holds the
+            # sampler object as its batch sampler, so the replacement is installed IN PLACE; under DDP the rank is folded
+            # into the fresh key like it is into the original one, so ranks never share coins.
+            old = rt["sampler"]
+            fresh_key = fold_in(self._sampler_key(), _IGNORE_DATA_SKIP_TAG)
+            if self.ddp.is_distributed:
+                fresh_key = fold_in(fresh_key, self.ddp.rank)
+            new = mf.build_sampler(a.resolved_sampling_mode, old.data_source if hasattr(old, "data_source") else self.train_dataset,
+                                   sample_rate=rt["sample_rate"], n_steps=rt["total_steps"], ctx=rt.get("mf_ctx"),
+                                   key=fresh_key, sampling_kwargs=a.sampling_kwargs)
+            old.__dict__.update(new.__dict__)
         else:
-            rt["sampler"].load_state_dict(saved.sampler_state)
+            rt["sampler"].load_state_dict(_rank_local_sampler_state(saved.sampler_state, rt["sampler"], self.ddp.world_size))
         if self._native is None:
             rt["clip_state"] = from_state_dict(rt["clip_state"], saved.clip_state)
             rt["noise_state"] = from_state_dict(rt["noise_state"], saved.noise_state)

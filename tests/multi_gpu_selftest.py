@@ -1,4 +1,4 @@
-"""Multi-rank self-test of the sharded engine: ``torchrun ... -m opake_b200.parallel.selftest --out file.pt``.
+"""Multi-rank self-test of the sharded engine: ``torchrun ... -m tests.multi_gpu_selftest --out file.pt``.
 
 Runs two DP steps of a tiny decoder on a fixed logical batch split over the ranks and stores the resulting parameters
 (rank 0). Comparing the files of a 1-rank and an N-rank run checks the fused reduce-scatter / noise / AdamW / all-gather
@@ -11,9 +11,9 @@ import argparse
 import torch
 import torch.distributed as dist
 
-from ..models.config import tiny_llama
-from . import comm
-from .engine import EngineConfig, ShardedDPEngine
+from opake_b200.models.config import tiny_llama
+from opake_b200.parallel import comm
+from opake_b200.parallel.engine import EngineConfig, ShardedDPEngine
 
 
 def main() -> None:
@@ -70,7 +70,7 @@ def main() -> None:
 def _sharded_linear_check(rank: int, world: int, dev: torch.device, out: str) -> None:
     """Every rank builds the same full weight, keeps its row shard in peer memory, and compares the sharded forward
     and input-gradient GEMMs (peer shards read in place) with the full-weight products."""
-    from .sharded_linear import ShardedWeight, sharded_linear_dgrad, sharded_linear_forward
+    from opake_b200.parallel.sharded_linear import ShardedWeight, sharded_linear_dgrad, sharded_linear_forward
     N, Kd, M = 1024, 512, 384
     g = torch.Generator().manual_seed(3)
     W = (torch.randn(N, Kd, generator=g) * 0.1).to(torch.bfloat16).to(dev)
@@ -104,8 +104,8 @@ def _sharded_linear_bench(rank: int, world: int, dev: torch.device, out: str, M:
     roofline is the bytes of the remote shards divided by 770 GB/s (measured peer-copy bandwidth per direction)."""
     import json
 
-    from .sharded_linear import ShardedWeight, sharded_linear_forward
-    from ..ops import gemm as G
+    from opake_b200.parallel.sharded_linear import ShardedWeight, sharded_linear_forward
+    from opake_b200.ops import gemm as G
 
     g = torch.Generator().manual_seed(3)
     x = (torch.randn(M, Kd, generator=g) * 0.5).to(torch.bfloat16).to(dev)
@@ -135,7 +135,7 @@ def _sharded_linear_bench(rank: int, world: int, dev: torch.device, out: str, M:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item()
 
-    from .sharded_linear import sharded_linear_dgrad
+    from opake_b200.parallel.sharded_linear import sharded_linear_dgrad
 
     t_sharded = timed(lambda: sharded_linear_forward(x, sw, out=y))
     t_local = timed(lambda: G.gemm(x, full, out=y))
@@ -166,8 +166,8 @@ def ep_fused_check(rank: int, world: int, dev: torch.device, T: int = 256, d: in
     Every rank generates all ranks' inputs, so the oracle needs no communication beyond gathering the routing."""
     import torch.nn.functional as F
 
-    from ..ops._lib import raise_if_device_error
-    from .ep_fused import EpContext, FusedExpertParallelLayer
+    from opake_b200.ops._lib import raise_if_device_error
+    from opake_b200.parallel.ep_fused import EpContext, FusedExpertParallelLayer
 
     gen = torch.Generator().manual_seed(11)
     bf = lambda t: t.to(torch.bfloat16).to(dev)

@@ -29,12 +29,8 @@ def test_accumulation_group_follows_free_memory(monkeypatch):
 
 
 def test_accumulation_group_override_and_cpu(monkeypatch):
-    e = _engine(1000)
-    monkeypatch.setenv("OPK_ACC_GROUP", "3")
-    assert e._pick_group_size() == 3
-    monkeypatch.setenv("OPK_ACC_GROUP", "99")
-    assert e._pick_group_size() == 8
-    monkeypatch.delenv("OPK_ACC_GROUP")
+    from opake_b200.parallel.engine import EngineConfig
+    assert EngineConfig().accumulate_group == 0                # automatic unless the configuration names a size
     assert _engine(1000, "cpu")._pick_group_size() == 2
     # small models: the reserve scales with the model instead of the fixed 32 GB
     monkeypatch.setattr(torch.cuda, "mem_get_info", lambda dev=None: (64 << 30, 183 << 30))

@@ -97,7 +97,7 @@ def test_grouped_gemm_modes(cuda):
 def test_expert_parallel_fused_single_rank(cuda):
     """The expert-parallel kernels with a group of one rank (every peer pointer is the rank's own buffer): dispatch,
     grouped GEMMs, combine, per-source norms and clipped accumulation against a dense fp32 oracle."""
-    from opake_b200.parallel.selftest import ep_fused_check
+    from tests.multi_gpu_selftest import ep_fused_check
 
     res = ep_fused_check(0, 1, cuda)
     for name in ("out", "dx", "d_router", "acc_wgu", "acc_wd", "norms"):

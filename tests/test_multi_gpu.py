@@ -13,10 +13,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def _run(world: int, out: str, extra=()):
     env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
     if world == 1:
-        cmd = [sys.executable, "-m", "opake_b200.parallel.selftest", "--out", out, *extra]
+        cmd = [sys.executable, "-m", "tests.multi_gpu_selftest", "--out", out, *extra]
     else:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-               "--master-addr", "127.0.0.1", "--master-port", "29533", "-m", "opake_b200.parallel.selftest", "--out", out,
+               "--master-addr", "127.0.0.1", "--master-port", "29533", "-m", "tests.multi_gpu_selftest", "--out", out,
                *extra]
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]

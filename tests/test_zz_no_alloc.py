@@ -56,3 +56,28 @@ def test_noalloc_rejects_oversized_vocab(cuda):
     dx = torch.zeros(8, 64, dtype=torch.bfloat16, device=cuda)
     rc, *_ = _call_noalloc(L, tok, dx, 262144 + 1)
     assert rc == -2
+
+
+def test_out_of_range_token_ids_are_skipped(cuda):
+    """Ids outside [0, vocab) never index the table: their position gets rep = -1 and contributes no row, in both
+    entry points; the in-range positions are unaffected."""
+    from opake_b200.ops import _lib
+    from opake_b200.ops import kernels as K
+
+    L = _lib.lib()
+    V, T, D = 1000, 64, 128
+    g = torch.Generator(device=cuda).manual_seed(3)
+    tok = torch.randint(0, V, (T,), generator=g, device=cuda, dtype=torch.int32)
+    dx = torch.randn(T, D, generator=g, device=cuda).to(torch.bfloat16)
+    bad = tok.clone()
+    bad[5], bad[17], bad[40] = V, -1, 2 ** 30
+    ws = K.EmbeddingGradWorkspace(V, T, D, cuda)
+    K.embedding_bwd_compact(bad, dx, ws, None)
+    rc, rep, gc, _ = _call_noalloc(L, bad, dx, V)
+    torch.cuda.synchronize()
+    assert rc == 0
+    for r, rows in ((rep, gc), (ws.rep, ws.gc)):
+        assert r[5].item() == -1 and r[17].item() == -1 and r[40].item() == -1
+        assert rows[[5, 17, 40]].abs().max().item() == 0.0
+    assert torch.equal(rep, ws.rep)
+    assert int((ws.first_pos != 2 ** 31 - 1).sum().item()) == 0      # the scratch table came back idle
