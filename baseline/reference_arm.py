@@ -26,6 +26,7 @@ import os
 import sys
 import time
 
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")   # allocator setting only; the reference is untouched
 HERE = os.path.dirname(os.path.abspath(__file__))
 T_PROCESS_START = time.perf_counter()
 
@@ -112,7 +113,7 @@ def run(args) -> None:
         torch.set_default_dtype(prev)
     model.train()
 
-    budget_s = float(os.environ.get("OPK_REF_BUDGET_S", "690"))
+    budget_s = float(os.environ.get("OPK_REF_BUDGET_S", "640"))
     b_local = args.batch // world
     kernels_mode = "triton kernels + fused linear-CE" if use_cuda else "eager"
     apply_runtime_patches()
@@ -166,49 +167,56 @@ def run(args) -> None:
         state["trainable"] = torchopt.apply_updates(state["trainable"], upd)
         return float(aux.loss_values.sum()), clip_state                        # device -> host read of the step's summed per-example loss
 
-    # ---- pick the largest microbatch of the candidates that survives one step (the reference's DPTrainer steps down the same way)
+    # ---- warm-up with step-down: a step that runs out of memory (the optimizer state and the fp32 clip-sum buffer appear
+    # during the first steps) moves on to the next smaller microbatch, as the reference's DPTrainer does on OOM, and the
+    # warm-up starts over. Every rank takes the same decision.
     candidates = [int(x) for x in os.environ.get("OPK_REF_MICROBATCH", "2,1").split(",")]
+    note = lambda msg: print(f"[reference arm rank {rank}] {msg}", file=sys.stderr, flush=True)  # noqa: E731
     grad_fn = clip_state = None
-    mb_used, oom_msg, first_step_s = None, "", None
-    for mb in candidates:
-        try:
+    mb_used, oom_msg, step_s, warm_done = None, "", None, 0
+    ci = 0
+    while ci < len(candidates) and warm_done < max(1, args.warmup):
+        mb = candidates[ci]
+        if grad_fn is None:
             grad_fn, clip_state = build(mb)
+        failed = 0
+        try:
             sync()
             t0 = time.perf_counter()
             _, clip_state = one_step(grad_fn, clip_state)
-            sync()
-            first_step_s = time.perf_counter() - t0
-            mb_used = mb
-            break
+            if use_cuda:
+                torch.cuda.synchronize(dev)
+            step_s = time.perf_counter() - t0
         except torch.OutOfMemoryError as exc:
-            oom_msg = str(exc)[:300]
+            failed, oom_msg = 1, str(exc)[:300]
+        flag = torch.tensor([failed], device=dev)
+        if world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        if int(flag.item()):
+            note(f"out of memory at microbatch {mb}: {oom_msg[:120]}")
             grad_fn = clip_state = None
-            state["noise"] = noise_state
+            warm_done, ci = 0, ci + 1
             if use_cuda:
                 torch.cuda.empty_cache()
-    ok = torch.tensor([1 if mb_used is not None else 0], device=dev)
-    if world > 1:
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-    if int(ok.item()) == 0:
+            continue
+        mb_used, warm_done = mb, warm_done + 1
+        note(f"warm-up step {warm_done} at microbatch {mb}: {step_s:.1f} s")
+        # stop warming up early when the remaining budget only holds one timed step
+        elapsed = time.perf_counter() - T_PROCESS_START
+        stop = torch.tensor([1 if budget_s - elapsed < 2.2 * step_s else 0], device=dev)
+        if world > 1:
+            dist.broadcast(stop, 0)
+        if int(stop.item()):
+            break
+    if mb_used is None or grad_fn is None:
         _say({"impl": "reference", "unavailable": f"out of memory at microbatch sizes {candidates} on the headline configuration: {oom_msg}"})
         return
-
-    # ---- plan warm-up and timed steps against the wall budget (rank 0 decides, every rank follows)
     elapsed = time.perf_counter() - T_PROCESS_START
-    fit = int(max(0.0, budget_s - elapsed) // max(first_step_s, 1e-3))
-    warm_left = max(0, args.warmup - 1)                      # the probing step above was the first warm-up step
-    if fit >= warm_left + args.steps:
-        steps = args.steps
-    else:
-        steps = max(1, fit - warm_left)
-        if fit < warm_left + 1:
-            warm_left = max(0, fit - 1)
-    plan = torch.tensor([warm_left, steps], device=dev)
+    plan = torch.tensor([max(1, min(args.steps, int(max(0.0, budget_s - elapsed) // max(step_s, 1e-3))))], device=dev)
     if world > 1:
         dist.broadcast(plan, 0)
-    warm_left, steps = (int(x) for x in plan.tolist())
-    for _ in range(warm_left):
-        _, clip_state = one_step(grad_fn, clip_state)
+    steps = int(plan.item())
+    first_step_s = step_s
 
     sync()
     if use_cuda:
@@ -216,8 +224,9 @@ def run(args) -> None:
         e0.record()
     t0 = time.perf_counter()
     last = 0.0
-    for _ in range(steps):
+    for k in range(steps):
         last, clip_state = one_step(grad_fn, clip_state)
+        note(f"timed step {k + 1} of {steps} issued")
     if use_cuda:
         e1.record()
     sync()
@@ -233,7 +242,7 @@ def run(args) -> None:
         "metric": "DP tokens/sec/box (max over ranks), Llama-3-8B FSDP DP-SGD" if model_name == "llama3-8b" else
                   f"DP tokens/sec/box (max over ranks), {model_name}",
         "impl": "reference", "value": tokens / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": steps,
-        "warmup": warm_left + 1, "steps_requested": args.steps, "warmup_requested": args.warmup,
+        "warmup": warm_done, "steps_requested": args.steps, "warmup_requested": args.warmup,
         "ms_per_step": dev_ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16" if use_cuda else "fp32", "data": "synthetic Zipf(1.1) tokens, random-init weights",
         "config": {"model": model_name, "layers": layers, "global_batch": args.batch, "seq_len": args.seq,

@@ -210,10 +210,11 @@ struct PeerTable {
 };
 
 // One parameter update given the averaged, noised gradient. Returns the new parameter value.
+template <bool ADAM>
 __device__ __forceinline__ float dp_update(const OpkDpStepArgs& a, float inv_bc1, float inv_bc2, float grad, float p_old,
                                            float& m, float& v) {
   float upd;
-  if (a.sgd_mode) {
+  if (!ADAM) {
     upd = grad + a.weight_decay * p_old;
   } else {
     m = a.beta1 * m + (1.f - a.beta1) * grad;
@@ -226,103 +227,244 @@ __device__ __forceinline__ float dp_update(const OpkDpStepArgs& a, float inv_bc1
   return p_old - a.lr * upd;
 }
 
+// Correlated-noise transforms of the iid draw z (DP-FTRL), applied element-wise on the shard:
+//   CORR_BLT       buffered linear Toeplitz C^{-1}: zhat = z - <scale, state>; state_k = decay_k * state_k + zhat
+//   CORR_TOEPLITZ  banded Toeplitz C^{-1} (band-MF, banded square root): zhat = (z - sum_{k>=1} c_k zhat_{t-k}) / c_0
+//                  with the last nlag outputs kept in a ring; lag k lives in ring slot (pos + k - 1) mod nlag and the
+//                  new output overwrites the oldest slot, (pos + nlag - 1) mod nlag, which the host makes the next pos
+enum { CORR_NONE = 0, CORR_BLT = 1, CORR_TOEPLITZ = 2 };
+
+template <int CORR>
+__device__ __forceinline__ void correlate_quad(const OpkDpStepArgs& a, long long i0, float (&z)[4]) {
+  if (CORR == CORR_BLT) {
+    float rd[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < a.blt_nbuf; ++k) {
+      const float4 st = *reinterpret_cast<const float4*>(a.blt_state + (long long)k * a.shard_len + i0);
+      const float sc = a.blt_scale[k];
+      rd[0] += sc * st.x; rd[1] += sc * st.y; rd[2] += sc * st.z; rd[3] += sc * st.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) z[j] -= rd[j];
+    for (int k = 0; k < a.blt_nbuf; ++k) {
+      float4* sp = reinterpret_cast<float4*>(a.blt_state + (long long)k * a.shard_len + i0);
+      float4 st = *sp;
+      const float dc = a.blt_decay[k];
+      st.x = dc * st.x + z[0]; st.y = dc * st.y + z[1]; st.z = dc * st.z + z[2]; st.w = dc * st.w + z[3];
+      *sp = st;
+    }
+  } else if (CORR == CORR_TOEPLITZ) {
+    float rd[4] = {0.f, 0.f, 0.f, 0.f};
+    int slot = a.toep_pos;
+    for (int k = 1; k <= a.toep_nlag; ++k) {
+      const float4 st = __ldcs(reinterpret_cast<const float4*>(a.toep_state + (long long)slot * a.shard_len + i0));
+      const float c = a.toep_coef[k];
+      rd[0] += c * st.x; rd[1] += c * st.y; rd[2] += c * st.z; rd[3] += c * st.w;
+      if (++slot == a.toep_nlag) slot = 0;
+    }
+    const float inv_c0 = 1.f / a.toep_coef[0];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) z[j] = (z[j] - rd[j]) * inv_c0;
+    if (a.toep_nlag > 0) {
+      const int oldest = a.toep_pos == 0 ? a.toep_nlag - 1 : a.toep_pos - 1;
+      __stcs(reinterpret_cast<float4*>(a.toep_state + (long long)oldest * a.shard_len + i0), make_float4(z[0], z[1], z[2], z[3]));
+    }
+  }
+}
+template <int CORR>
+__device__ __forceinline__ float correlate_one(const OpkDpStepArgs& a, long long i, float z) {
+  if (CORR == CORR_BLT) {
+    float rd = 0.f;
+    for (int k = 0; k < a.blt_nbuf; ++k) rd += a.blt_scale[k] * a.blt_state[(long long)k * a.shard_len + i];
+    z -= rd;
+    for (int k = 0; k < a.blt_nbuf; ++k) {
+      float* sp = &a.blt_state[(long long)k * a.shard_len + i];
+      *sp = a.blt_decay[k] * (*sp) + z;
+    }
+  } else if (CORR == CORR_TOEPLITZ) {
+    float rd = 0.f;
+    int slot = a.toep_pos;
+    for (int k = 1; k <= a.toep_nlag; ++k) {
+      rd += a.toep_coef[k] * a.toep_state[(long long)slot * a.shard_len + i];
+      if (++slot == a.toep_nlag) slot = 0;
+    }
+    z = (z - rd) / a.toep_coef[0];
+    if (a.toep_nlag > 0) a.toep_state[(long long)(a.toep_pos == 0 ? a.toep_nlag - 1 : a.toep_pos - 1) * a.shard_len + i] = z;
+  }
+  return z;
+}
+
+// Everything a full quad needs from memory, fetched before any arithmetic so that two quads per thread keep eight to
+// ten 16-byte loads in flight.
+struct QuadIn {
+  float4 g, m, v, mw;
+  uint2 pw;
+};
+template <bool ADAM, bool MASTER>
+__device__ __forceinline__ void load_quad(const OpkDpStepArgs& a, const PeerTable& pt, long long i0, long long e0, QuadIn& q) {
+  // reduce-scatter: sum the owned quad over every rank's buffer (peer reads travel over NVLink)
+  q.g = __ldcs(reinterpret_cast<const float4*>(pt.grad[0] + e0));
+  for (int r = 1; r < a.n_src; ++r) {
+    const float4 t = __ldcs(reinterpret_cast<const float4*>(pt.grad[r] + e0));
+    q.g.x += t.x; q.g.y += t.y; q.g.z += t.z; q.g.w += t.w;
+  }
+  if (MASTER) q.mw = __ldcs(reinterpret_cast<const float4*>(a.master + i0));
+  else q.pw = __ldcs(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.param_src) + e0));
+  if (ADAM) {
+    q.m = __ldcs(reinterpret_cast<const float4*>(a.m + i0));
+    q.v = __ldcs(reinterpret_cast<const float4*>(a.v + i0));
+  }
+}
+template <bool ADAM, bool MASTER, int CORR>
+__device__ __forceinline__ void finish_quad(const OpkDpStepArgs& a, const PeerTable& pt, float inv_bc1, float inv_bc2,
+                                            long long i0, long long e0, const QuadIn& q) {
+  float z[4] = {0.f, 0.f, 0.f, 0.f};
+  if (a.sigma != 0.f) normal4((uint64_t)e0 >> 2, a.seed, a.stream_id, a.step, z);
+  correlate_quad<CORR>(a, i0, z);
+  float po[4];
+  if (MASTER) {
+    po[0] = q.mw.x; po[1] = q.mw.y; po[2] = q.mw.z; po[3] = q.mw.w;
+  } else {
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.pw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.pw.y));
+    po[0] = lo.x; po[1] = lo.y; po[2] = hi.x; po[3] = hi.y;
+  }
+  const float gr[4] = {q.g.x, q.g.y, q.g.z, q.g.w};
+  float mm[4] = {q.m.x, q.m.y, q.m.z, q.m.w}, vv[4] = {q.v.x, q.v.y, q.v.z, q.v.w};
+  float pn[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    pn[j] = dp_update<ADAM>(a, inv_bc1, inv_bc2, gr[j] * a.inv_batch + a.sigma * z[j], po[j], mm[j], vv[j]);
+  if (ADAM) {
+    __stcs(reinterpret_cast<float4*>(a.m + i0), make_float4(mm[0], mm[1], mm[2], mm[3]));
+    __stcs(reinterpret_cast<float4*>(a.v + i0), make_float4(vv[0], vv[1], vv[2], vv[3]));
+  }
+  if (MASTER) __stcs(reinterpret_cast<float4*>(a.master + i0), make_float4(pn[0], pn[1], pn[2], pn[3]));
+  // all-gather: write the updated bf16 quad into every destination parameter buffer
+  uint2 o;
+  __nv_bfloat162 lo = __floats2bfloat162_rn(pn[0], pn[1]), hi = __floats2bfloat162_rn(pn[2], pn[3]);
+  o.x = *reinterpret_cast<uint32_t*>(&lo);
+  o.y = *reinterpret_cast<uint32_t*>(&hi);
+  for (int r = 0; r < a.n_dst; ++r) *reinterpret_cast<uint2*>(pt.param[r] + e0) = o;
+  if (a.zero_grad) *reinterpret_cast<float4*>(const_cast<float*>(pt.grad[0]) + e0) = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+template <bool ADAM, bool MASTER, int CORR>
 __global__ void __launch_bounds__(256) dp_step_kernel(const OpkDpStepArgs a, const PeerTable pt) {
-  // Each thread owns aligned quads of the shard; shard_begin and shard_len are multiples of 4 except for a possible
-  // ragged last quad, which takes the scalar path. Everything is touched exactly once: streaming loads and stores.
-  const long long nq = (a.shard_len + 3) >> 2;
-  const bool adam = !a.sgd_mode;
+  // Each thread owns aligned quads of the shard, two per iteration; shard_begin is a multiple of 4 and a ragged last
+  // quad takes the scalar path. Everything is touched exactly once: streaming loads and stores.
+  const long long nfull = a.shard_len >> 2;                // whole quads
   const float inv_bc1 = 1.f / a.bc1, inv_bc2 = 1.f / a.bc2;
-  for (long long q = blockIdx.x * 256ll + threadIdx.x; q < nq; q += (long long)gridDim.x * 256) {
-    const long long i0 = q << 2;
-    const long long e0 = a.shard_begin + i0;
-    const int cnt = (int)((a.shard_len - i0) < 4 ? (a.shard_len - i0) : 4);
+  const long long stride = (long long)gridDim.x * 256;
+  long long q = blockIdx.x * 256ll + threadIdx.x;
+  for (; q + stride < nfull; q += 2 * stride) {
+    const long long ia = q << 2, ib = (q + stride) << 2;
+    QuadIn qa, qb;
+    qa.m = qa.v = qb.m = qb.v = make_float4(0.f, 0.f, 0.f, 0.f);
+    load_quad<ADAM, MASTER>(a, pt, ia, a.shard_begin + ia, qa);
+    load_quad<ADAM, MASTER>(a, pt, ib, a.shard_begin + ib, qb);
+    finish_quad<ADAM, MASTER, CORR>(a, pt, inv_bc1, inv_bc2, ia, a.shard_begin + ia, qa);
+    finish_quad<ADAM, MASTER, CORR>(a, pt, inv_bc1, inv_bc2, ib, a.shard_begin + ib, qb);
+  }
+  if (q < nfull) {
+    const long long ia = q << 2;
+    QuadIn qa;
+    qa.m = qa.v = make_float4(0.f, 0.f, 0.f, 0.f);
+    load_quad<ADAM, MASTER>(a, pt, ia, a.shard_begin + ia, qa);
+    finish_quad<ADAM, MASTER, CORR>(a, pt, inv_bc1, inv_bc2, ia, a.shard_begin + ia, qa);
+  }
+  // ragged tail (fewer than 4 elements): one thread
+  const int cnt = (int)(a.shard_len & 3);
+  if (cnt && blockIdx.x == 0 && threadIdx.x == 0) {
+    const long long i0 = nfull << 2, e0 = a.shard_begin + i0;
     float z[4] = {0.f, 0.f, 0.f, 0.f};
     if (a.sigma != 0.f) normal4((uint64_t)e0 >> 2, a.seed, a.stream_id, a.step, z);
-    if (cnt == 4) {
-      // reduce-scatter: sum the owned quad over every rank's buffer (peer reads travel over NVLink)
-      float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-      for (int r = 0; r < a.n_src; ++r) {
-        const float4 v = __ldcs(reinterpret_cast<const float4*>(pt.grad[r] + e0));
-        g.x += v.x; g.y += v.y; g.z += v.z; g.w += v.w;
-      }
-      float gr[4] = {g.x, g.y, g.z, g.w};
-      if (a.blt_nbuf > 0) {
-        // streaming multiply by C^{-1} of a buffered linear Toeplitz factor: xhat = z - <scale, state>;
-        // state_k = decay_k * state_k + xhat
-        float rd[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int k = 0; k < a.blt_nbuf; ++k) {
-          const float4 st = *reinterpret_cast<const float4*>(a.blt_state + (long long)k * a.shard_len + i0);
-          const float sc = a.blt_scale[k];
-          rd[0] += sc * st.x; rd[1] += sc * st.y; rd[2] += sc * st.z; rd[3] += sc * st.w;
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) z[j] -= rd[j];
-        for (int k = 0; k < a.blt_nbuf; ++k) {
-          float4* sp = reinterpret_cast<float4*>(a.blt_state + (long long)k * a.shard_len + i0);
-          float4 st = *sp;
-          const float dc = a.blt_decay[k];
-          st.x = dc * st.x + z[0]; st.y = dc * st.y + z[1]; st.z = dc * st.z + z[2]; st.w = dc * st.w + z[3];
-          *sp = st;
-        }
-      }
-      float po[4];
-      if (a.master) {
-        const float4 mw = __ldcs(reinterpret_cast<const float4*>(a.master + i0));
-        po[0] = mw.x; po[1] = mw.y; po[2] = mw.z; po[3] = mw.w;
-      } else {
-        const uint2 pw = __ldcs(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.param_src) + e0));
-        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pw.x));
-        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pw.y));
-        po[0] = lo.x; po[1] = lo.y; po[2] = hi.x; po[3] = hi.y;
-      }
-      float mm[4] = {0.f, 0.f, 0.f, 0.f}, vv[4] = {0.f, 0.f, 0.f, 0.f};
-      if (adam) {
-        const float4 m4 = __ldcs(reinterpret_cast<const float4*>(a.m + i0));
-        const float4 v4 = __ldcs(reinterpret_cast<const float4*>(a.v + i0));
-        mm[0] = m4.x; mm[1] = m4.y; mm[2] = m4.z; mm[3] = m4.w;
-        vv[0] = v4.x; vv[1] = v4.y; vv[2] = v4.z; vv[3] = v4.w;
-      }
-      float pn[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) pn[j] = dp_update(a, inv_bc1, inv_bc2, gr[j] * a.inv_batch + a.sigma * z[j], po[j], mm[j], vv[j]);
-      if (adam) {
-        __stcs(reinterpret_cast<float4*>(a.m + i0), make_float4(mm[0], mm[1], mm[2], mm[3]));
-        __stcs(reinterpret_cast<float4*>(a.v + i0), make_float4(vv[0], vv[1], vv[2], vv[3]));
-      }
-      if (a.master) __stcs(reinterpret_cast<float4*>(a.master + i0), make_float4(pn[0], pn[1], pn[2], pn[3]));
-      // all-gather: write the updated bf16 quad into every rank's parameter buffer
-      uint2 o;
-      __nv_bfloat162 lo = __floats2bfloat162_rn(pn[0], pn[1]), hi = __floats2bfloat162_rn(pn[2], pn[3]);
-      o.x = *reinterpret_cast<uint32_t*>(&lo);
-      o.y = *reinterpret_cast<uint32_t*>(&hi);
-#pragma unroll 4
-      for (int r = 0; r < a.n_dst; ++r) *reinterpret_cast<uint2*>(pt.param[r] + e0) = o;
-      if (a.zero_grad) *reinterpret_cast<float4*>(const_cast<float*>(pt.grad[0]) + e0) = make_float4(0.f, 0.f, 0.f, 0.f);
-      continue;
-    }
-    // ragged tail (fewer than 4 elements)
     for (int j = 0; j < cnt; ++j) {
       const long long i = i0 + j;
       float g = 0.f;
       for (int r = 0; r < a.n_src; ++r) g += pt.grad[r][e0 + j];
-      float noise = z[j];
-      if (a.blt_nbuf > 0) {
-        float rd = 0.f;
-        for (int k = 0; k < a.blt_nbuf; ++k) rd += a.blt_scale[k] * a.blt_state[(long long)k * a.shard_len + i];
-        noise = z[j] - rd;
-        for (int k = 0; k < a.blt_nbuf; ++k) {
-          float* sp = &a.blt_state[(long long)k * a.shard_len + i];
-          *sp = a.blt_decay[k] * (*sp) + noise;
-        }
-      }
-      const float p_old = a.master ? a.master[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.param_src)[e0 + j]);
-      float m = adam ? a.m[i] : 0.f, v = adam ? a.v[i] : 0.f;
-      const float p_new = dp_update(a, inv_bc1, inv_bc2, g * a.inv_batch + a.sigma * noise, p_old, m, v);
-      if (adam) { a.m[i] = m; a.v[i] = v; }
-      if (a.master) a.master[i] = p_new;
+      const float noise = correlate_one<CORR>(a, i, z[j]);
+      const float p_old = MASTER ? a.master[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.param_src)[e0 + j]);
+      float m = ADAM ? a.m[i] : 0.f, v = ADAM ? a.v[i] : 0.f;
+      const float p_new = dp_update<ADAM>(a, inv_bc1, inv_bc2, g * a.inv_batch + a.sigma * noise, p_old, m, v);
+      if (ADAM) { a.m[i] = m; a.v[i] = v; }
+      if (MASTER) a.master[i] = p_new;
       for (int r = 0; r < a.n_dst; ++r) pt.param[r][e0 + j] = __float2bfloat16(p_new);
       if (a.zero_grad) const_cast<float*>(pt.grad[0])[e0 + j] = 0.f;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------- sharded sums (push)
+// The fp32 sums are sharded: rank o owns elements [begin[o], begin[o+1]) of the flat parameter vector and keeps them in
+// a peer-addressable buffer. A group of clipped per-example gradients is added with reductions sent to the owner
+// (red.add over NVLink for remote owners), so no rank ever holds a full-size fp32 sum. Peers add into the same shard
+// concurrently, hence reductions for the local part as well.
+struct ShardTable {
+  float* acc[MAX_PEERS];
+  long long begin[MAX_PEERS + 1];
+  int n;
+};
+__device__ __forceinline__ void red_add_f32x4(float* dst, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+template <int N>
+__global__ void __launch_bounds__(256) clip_accumulate_group_push_kernel(const AccGroup grp, const ShardTable sh, long long nvec,
+                                                                         long long rot) {
+  float s[N];
+#pragma unroll
+  for (int j = 0; j < N; ++j) s[j] = *grp.scale[j];
+  for (long long t = blockIdx.x * 256ll + threadIdx.x; t < nvec; t += (long long)gridDim.x * 256) {
+    // every rank starts at its own shard and walks the owners in rank order: at any moment the ranks push to
+    // different owners
+    long long i = t + rot;
+    if (i >= nvec) i -= nvec;
+    uint4 r[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) r[j] = __ldcs(reinterpret_cast<const uint4*>(grp.g[j]) + i);
+    float f[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) f[q] = 0.f;
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      const bf16x8 v = *reinterpret_cast<const bf16x8*>(&r[j]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 u = __bfloat1622float2(v.h[q]);
+        f[2 * q] += clip_store(u.x, s[j]);
+        f[2 * q + 1] += clip_store(u.y, s[j]);
+      }
+    }
+    const long long e = i << 3;
+    int o = 0;
+    while (o + 1 < sh.n && e >= sh.begin[o + 1]) ++o;
+    float* dst = sh.acc[o] + (e - sh.begin[o]);
+    red_add_f32x4(dst, f[0], f[1], f[2], f[3]);
+    red_add_f32x4(dst + 4, f[4], f[5], f[6], f[7]);
+  }
+}
+template <int N>
+void launch_acc_group_push(const AccGroup& grp, const ShardTable& sh, long long nvec, long long rot, cudaStream_t st) {
+  long long g = (nvec + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  clip_accumulate_group_push_kernel<N><<<(int)g, 256, 0, st>>>(grp, sh, nvec, rot);
+}
+
+// Plain copy between two device buffers that may live on different GPUs (peer-mapped memory): 16-byte vectors, eight
+// loads in flight per thread. Used to refresh the parts of a parameter replica that no GEMM stages for itself.
+__global__ void __launch_bounds__(256) copy_vec_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, long long nvec) {
+  constexpr int U = 8;
+  const long long stride = (long long)gridDim.x * 256;
+  for (long long i0 = blockIdx.x * 256ll + threadIdx.x; i0 < nvec; i0 += U * stride) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < nvec) v[u] = __ldcg(src + i);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < nvec) dst[i] = v[u];
     }
   }
 }
@@ -436,8 +578,76 @@ extern "C" int opk_dp_step(const OpkDpStepArgs* args, void* stream) {
     pt.grad[r] = r < args->n_src ? args->grad_src[r] : nullptr;
     pt.param[r] = r < args->n_dst ? reinterpret_cast<__nv_bfloat16*>(args->param_dst[r]) : nullptr;
   }
+  if (args->blt_nbuf > 0 && args->toep_nlag > 0) return -3;       // one correlation transform per step
+  if (args->toep_nlag > 0 && (!args->toep_state || !args->toep_coef || args->toep_pos < 0 || args->toep_pos >= args->toep_nlag)) return -3;
   const long long nq = (args->shard_len + 3) >> 2;
-  dp_step_kernel<<<grid_for(nq, 256, 148 * 8), 256, 0, ST(stream)>>>(*args, pt);
+  const int grid = grid_for((nq + 1) / 2, 256, 148 * 8);
+  cudaStream_t st = ST(stream);
+  const int corr = args->blt_nbuf > 0 ? CORR_BLT : (args->toep_coef ? CORR_TOEPLITZ : CORR_NONE);
+  const bool adam = !args->sgd_mode, master = args->master != nullptr;
+#define OPK_DP_STEP_LAUNCH(A, M, C) dp_step_kernel<A, M, C><<<grid, 256, 0, st>>>(*args, pt)
+#define OPK_DP_STEP_CORR(A, M)                                      \
+  do {                                                              \
+    if (corr == CORR_BLT) OPK_DP_STEP_LAUNCH(A, M, CORR_BLT);       \
+    else if (corr == CORR_TOEPLITZ) OPK_DP_STEP_LAUNCH(A, M, CORR_TOEPLITZ); \
+    else OPK_DP_STEP_LAUNCH(A, M, CORR_NONE);                       \
+  } while (0)
+  if (adam && master) OPK_DP_STEP_CORR(true, true);
+  else if (adam) OPK_DP_STEP_CORR(true, false);
+  else if (master) OPK_DP_STEP_CORR(false, true);
+  else OPK_DP_STEP_CORR(false, false);
+#undef OPK_DP_STEP_CORR
+#undef OPK_DP_STEP_LAUNCH
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+
+// Sharded fp32 sums: acc_shards[o] is the base of owner o's shard (a peer-mapped address for o != this rank), which
+// holds the elements [bounds[o], bounds[o+1]) of the flat vector; bounds are multiples of 8. rank selects where this
+// rank starts walking (its own shard first).
+extern "C" int opk_clip_accumulate_group_push(const void* const* g, const float* const* scale, int n_group,
+                                              float* const* acc_shards, const int64_t* bounds, int n_shards, int rank,
+                                              int64_t n, void* stream) {
+  if (n <= 0 || n_group <= 0) return 0;
+  if (n_group > OPK_ACC_GROUP_MAX || n_shards < 1 || n_shards > MAX_PEERS || rank < 0 || rank >= n_shards || (n & 7)) return -1;
+  AccGroup grp;
+  for (int j = 0; j < OPK_ACC_GROUP_MAX; ++j) {
+    grp.g[j] = j < n_group ? reinterpret_cast<const bf16x8*>(g[j]) : nullptr;
+    grp.scale[j] = j < n_group ? scale[j] : nullptr;
+    if (j < n_group && (reinterpret_cast<uintptr_t>(g[j]) & 15)) return -1;
+  }
+  ShardTable sh;
+  sh.n = n_shards;
+  for (int o = 0; o < MAX_PEERS; ++o) sh.acc[o] = o < n_shards ? acc_shards[o] : nullptr;
+  for (int o = 0; o <= MAX_PEERS; ++o) sh.begin[o] = o <= n_shards ? bounds[o] : bounds[n_shards];
+  for (int o = 0; o < n_shards; ++o) {
+    if ((bounds[o] & 7) || bounds[o + 1] < bounds[o] || (reinterpret_cast<uintptr_t>(acc_shards[o]) & 15)) return -1;
+  }
+  if (bounds[0] != 0 || bounds[n_shards] < n) return -1;
+  const long long nvec = n >> 3;
+  long long rot = bounds[rank] >> 3;
+  if (rot >= nvec) rot = 0;
+  cudaStream_t st = ST(stream);
+  switch (n_group) {
+    case 1: launch_acc_group_push<1>(grp, sh, nvec, rot, st); break;
+    case 2: launch_acc_group_push<2>(grp, sh, nvec, rot, st); break;
+    case 3: launch_acc_group_push<3>(grp, sh, nvec, rot, st); break;
+    case 4: launch_acc_group_push<4>(grp, sh, nvec, rot, st); break;
+    case 5: launch_acc_group_push<5>(grp, sh, nvec, rot, st); break;
+    case 6: launch_acc_group_push<6>(grp, sh, nvec, rot, st); break;
+    case 7: launch_acc_group_push<7>(grp, sh, nvec, rot, st); break;
+    default: launch_acc_group_push<8>(grp, sh, nvec, rot, st); break;
+  }
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int opk_copy_bytes(void* dst, const void* src, int64_t nbytes, void* stream) {
+  if (nbytes <= 0) return 0;
+  if ((nbytes & 15) || (reinterpret_cast<uintptr_t>(dst) & 15) || (reinterpret_cast<uintptr_t>(src) & 15)) return -1;
+  const long long nvec = nbytes >> 4;
+  copy_vec_kernel<<<grid_for((nvec + 7) / 8, 256, 148 * 8), 256, 0, ST(stream)>>>(reinterpret_cast<uint4*>(dst),
+                                                                                  reinterpret_cast<const uint4*>(src), nvec);
   OPK_LAUNCH_CHECK();
   return 0;
 }

@@ -514,6 +514,9 @@ __global__ void emb_reset_kernel(const int* __restrict__ tok, int* __restrict__ 
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t < T && emb_tok_ok(tok[t], vocab)) first_pos[tok[t]] = INT_MAX;
 }
+// ATOMIC: the rows of acc are shared with other GPUs' kernels (sharded sums, acc may be peer-mapped), so the add is a
+// reduction instead of a read-modify-write.
+template <bool ATOMIC>
 __global__ void emb_accumulate_kernel(const int* __restrict__ tok, const int* __restrict__ rep,
                                       const float* __restrict__ gc, const float* __restrict__ scale,
                                       float* __restrict__ acc, int D) {
@@ -524,7 +527,9 @@ __global__ void emb_accumulate_kernel(const int* __restrict__ tok, const int* __
   float* dst = acc + (long long)tok[t] * D;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     const float g = __bfloat162float(__float2bfloat16(src[d]));            // the stored per-example gradient
-    dst[d] += __bfloat162float(__float2bfloat16(g * s));                   // clipped in storage precision
+    const float c = __bfloat162float(__float2bfloat16(g * s));             // clipped in storage precision
+    if (ATOMIC) atomicAdd(&dst[d], c);
+    else dst[d] += c;
   }
 }
 
@@ -858,7 +863,14 @@ extern "C" int opk_embedding_bwd_compact(const int32_t* tok, const void* dx, int
 extern "C" int opk_embedding_accumulate(const int32_t* tok, const int32_t* rep, const float* gc, const float* scale,
                                         float* acc, int T, int D, void* stream) {
   if (T <= 0) return 0;
-  emb_accumulate_kernel<<<T, 256, 0, ST(stream)>>>(tok, rep, gc, scale, acc, D);
+  emb_accumulate_kernel<false><<<T, 256, 0, ST(stream)>>>(tok, rep, gc, scale, acc, D);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_embedding_accumulate_shared(const int32_t* tok, const int32_t* rep, const float* gc, const float* scale,
+                                               float* acc, int T, int D, void* stream) {
+  if (T <= 0) return 0;
+  emb_accumulate_kernel<true><<<T, 256, 0, ST(stream)>>>(tok, rep, gc, scale, acc, D);
   OPK_LAUNCH_CHECK();
   return 0;
 }

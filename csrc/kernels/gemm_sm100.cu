@@ -154,9 +154,10 @@ extern "C" int opk_gemm(const OpkGemmArgs* a, void* stream) {
   const bool stage = a->stage_dst != nullptr;
   if (stage) {
     // B is read once over NVLink by the kernel's copier warps into stage_dst; the tensor map covers the scratch
-    if (!pair || a->a_mn || a->epilogue != opk::EPI_STORE || a->batch != 1 || !a->stage_ready || (a->K % 8) || (a->N % 8) ||
+    if (!pair || a->a_mn || (a->epilogue != opk::EPI_STORE && !(a->epilogue == opk::EPI_SWIGLU && !a->b_mn && a->act && !(a->N & 1))) ||
+        a->batch != 1 || !a->stage_ready || (a->K % 8) || (a->N % 8) ||
         (a->ldb % 8) || (reinterpret_cast<uintptr_t>(a->B) & 15) || (reinterpret_cast<uintptr_t>(a->stage_dst) & 15)) {
-      set_err("opk_gemm: staged B needs a plain product with at least 256 rows, 256-wide tiles and 16-byte aligned rows");
+      set_err("opk_gemm: staged B needs a plain or SwiGLU product with at least 256 rows, 256-wide tiles and 16-byte aligned rows");
       return -1;
     }
     if (a->b_mn) {
@@ -185,6 +186,7 @@ extern "C" int opk_gemm(const OpkGemmArgs* a, void* stream) {
     cudaError_t e = cudaMemsetAsync(a->stage_ready, 0, sizeof(int32_t) * n_bands, st);
     if (e != cudaSuccess) { set_err(cudaGetErrorString(e)); return (int)e; }
     p.stage_src = a->B; p.stage_ld = a->ldb; p.stage_dst = a->stage_dst; p.stage_ready = a->stage_ready;
+    if (a->epilogue == opk::EPI_SWIGLU) return launch2<false, false, opk::EPI_SWIGLU, true>(ta, tb, p, mc, st);
     return a->b_mn ? launch2<false, true, opk::EPI_STORE, true>(ta, tb, p, mc, st)
                    : launch2<false, false, opk::EPI_STORE, true>(ta, tb, p, mc, st);
   }

@@ -104,6 +104,10 @@ int opk_embedding_bwd_compact(const int32_t* tok, const void* dx, int32_t* first
 // acc[tok[t]] += bf16(gc[t] * scale) for the representative rows (rep[t] == t).
 int opk_embedding_accumulate(const int32_t* tok, const int32_t* rep, const float* gc, const float* scale, float* acc,
                              int T, int D, void* stream);
+// Same, with reductions (red.add) instead of read-modify-write: for an acc whose rows other GPUs add to at the same time
+// (sharded sums; acc may be the peer-mapped shard of the rank that owns the embedding table).
+int opk_embedding_accumulate_shared(const int32_t* tok, const int32_t* rep, const float* gc, const float* scale, float* acc,
+                                    int T, int D, void* stream);
 // Fused linear-cross-entropy finalisation: lse[t] from the per-tile partials, nll[t] = lse - tgt (0 if ignored).
 int opk_lce_finalize(const float* pmax, const float* psum, const float* tgt, const int32_t* labels, float* lse,
                      float* nll, int T, int tiles, void* stream);
@@ -253,8 +257,26 @@ typedef struct OpkDpStepArgs {
   const float* blt_decay;  // device [nbuf]
   const float* blt_scale;  // device [nbuf]
   int32_t sgd_mode;      // 1: plain SGD update p -= lr * g (no moments)
+  // optional banded-Toeplitz correlated noise (band-MF, banded square root): ring of the last toep_nlag outputs, each
+  // shard_len fp32; toep_coef is a device array of toep_nlag + 1 coefficients (c_0 first). Lag k sits in ring slot
+  // (toep_pos + k - 1) mod toep_nlag; the kernel overwrites slot (toep_pos - 1) mod toep_nlag, the caller's next toep_pos.
+  // toep_coef != NULL with toep_nlag == 0 divides the draw by c_0 only. Exclusive with the BLT buffers.
+  float* toep_state;
+  int32_t toep_nlag;
+  const float* toep_coef;
+  int32_t toep_pos;
 } OpkDpStepArgs;
 int opk_dp_step(const OpkDpStepArgs* args, void* stream);
+
+// Sharded fp32 sums ("push" reduce-scatter of one accumulation group): owner o keeps elements [bounds[o], bounds[o+1])
+// of the flat vector at acc_shards[o] (peer-mapped for remote owners); the group's clipped sum is sent there with
+// vector reductions. bounds: host array of n_shards + 1 multiples of 8 starting at 0; n: elements to add (multiple
+// of 8, <= bounds[n_shards]); rank: this rank (it starts with its own shard).
+int opk_clip_accumulate_group_push(const void* const* g, const float* const* scale, int n_group, float* const* acc_shards,
+                                   const int64_t* bounds, int n_shards, int rank, int64_t n, void* stream);
+// dst[0 .. nbytes) = src[0 .. nbytes) with this library's own copy kernel; either side may be peer-mapped memory of
+// another GPU. Addresses and size are multiples of 16 bytes.
+int opk_copy_bytes(void* dst, const void* src, int64_t nbytes, void* stream);
 
 #ifdef __cplusplus
 }

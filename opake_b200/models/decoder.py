@@ -59,6 +59,10 @@ class DecoderRuntime:
         self.clip_count = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._ws: dict[int, dict] = {}
         self._rope = None
+        # weights to pull from their owner during the NEXT forward pass (name -> the owner's copy, a peer-mapped
+        # tensor): the consuming GEMM copies the matrix into this rank's replica band by band while it multiplies
+        self._fetch: dict[str, torch.Tensor] | None = None
+        self._stage_ready = torch.zeros(64, dtype=torch.int32, device=self.device) if self.device.type == "cuda" else None
         # Weight-gradient GEMMs run on a second stream next to the input-gradient GEMMs of the same layer: both are
         # persistent kernels that want every SM, so the second one's CTAs fill the SMs that the first one's last
         # (partial) wave of tiles leaves idle, and launch gaps disappear. ``wgrad_overlap=False`` keeps one stream.
@@ -204,6 +208,24 @@ class DecoderRuntime:
         return K.layernorm_bwd(dy, x, w[prefix + ".weight"], stats[0], stats[1], dres=dres,
                                dw=self._vec(ws, prefix + ".weight"), db=self._vec(ws, prefix + ".bias"), out=out)
 
+    def _wop(self, name: str):
+        """Operand and staging arguments of a forward GEMM on weight ``name``: the local replica, or (when the engine
+        marked the weight for fetching) the owner's copy together with the replica as the staging destination."""
+        src = self._fetch.get(name) if self._fetch else None
+        if src is None:
+            return self.w[name], None
+        return src, (self.w[name], self._stage_ready)
+
+    @staticmethod
+    def stageable(name: str, shape: tuple, T: int, act: str) -> bool:
+        """Whether the forward GEMM that consumes weight ``name`` can fetch it from another GPU while it multiplies:
+        plain or SwiGLU epilogue, at least 256 rows and more than 128 columns (the two-CTA kernel), 16-byte rows."""
+        leaf = name.rsplit(".", 1)[-1]
+        if leaf not in ("wqkv", "wo", "wgu", "wd", "wfc", "wproj") or len(shape) != 2:
+            return False
+        n, k = shape
+        return T >= 256 and n > 128 and n % 8 == 0 and k % 8 == 0 and G.pair_mode()
+
     # ------------------------------------------------------------------ forward
     def forward(self, tok: torch.Tensor, labels: torch.Tensor | None, ws: dict | None = None):
         """Runs the decoder on one sequence. Returns ``(per-token nll [T], lse, saved)``.
@@ -220,7 +242,8 @@ class DecoderRuntime:
             a = ws["layers"][li]
             p = f"layers.{li}."
             xn, st1 = self._norm_fwd(x, p + "norm1", out=a["xn"])
-            G.gemm(xn, w[p + "wqkv"], out=a["qkv"], bias=w.get(p + "bqkv"))
+            wsrc, stg = self._wop(p + "wqkv")
+            G.gemm(xn, wsrc, out=a["qkv"], bias=w.get(p + "bqkv"), stage=stg)
             stq = None
             if cfg.qk_norm:
                 nq, nk = H * hd, KV * hd
@@ -232,7 +255,8 @@ class DecoderRuntime:
                 K.rope_(a["qkv"], self._rope_table(T), H + KV, hd)
             _, actx = A.attention_fwd(a["qkv"], H, KV, hd, self.attn_impl, out=a["attn"])
             # output projection with the residual add fused into the GEMM epilogue
-            G.gemm(a["attn"], w[p + "wo"], out=a["x_mid"], residual=x, bias=w.get(p + "bo"))
+            wsrc, stg = self._wop(p + "wo")
+            G.gemm(a["attn"], wsrc, out=a["x_mid"], residual=x, bias=w.get(p + "bo"), stage=stg)
             xn2, st2 = self._norm_fwd(a["x_mid"], p + "norm2", out=a["xn2"])
             nxt = ws["layers"][li + 1]["x"] if li + 1 < cfg.n_layers else ws["x_last"]
             if cfg.n_experts:
@@ -244,16 +268,22 @@ class DecoderRuntime:
                 G.gemm(a["act"], w[p + "experts.wd"], out=a["ye"], tile_group=plan.tile_group)
                 K.moe_combine(a["ye"], plan, nxt, wts=plan.wts, residual=a["x_mid"])
             elif cfg.act == "swiglu":
-                G.gemm(xn2, w[p + "wgu"], out=a["gu"], epilogue=G.EPI_SWIGLU, act=a["act"])
-                G.gemm(a["act"], w[p + "wd"], out=nxt, residual=a["x_mid"])
+                wsrc, stg = self._wop(p + "wgu")
+                G.gemm(xn2, wsrc, out=a["gu"], epilogue=G.EPI_SWIGLU, act=a["act"], stage=stg)
+                wsrc, stg = self._wop(p + "wd")
+                G.gemm(a["act"], wsrc, out=nxt, residual=a["x_mid"], stage=stg)
             elif cfg.act == "geglu":
-                G.gemm(xn2, w[p + "wgu"], out=a["gu"])
+                wsrc, stg = self._wop(p + "wgu")
+                G.gemm(xn2, wsrc, out=a["gu"], stage=stg)
                 K.geglu_fwd(a["gu"], True, out=a["act"])
-                G.gemm(a["act"], w[p + "wd"], out=nxt, residual=a["x_mid"])
+                wsrc, stg = self._wop(p + "wd")
+                G.gemm(a["act"], wsrc, out=nxt, residual=a["x_mid"], stage=stg)
             else:
-                G.gemm(xn2, w[p + "wfc"], out=a["fc"], bias=w.get(p + "bfc"))
+                wsrc, stg = self._wop(p + "wfc")
+                G.gemm(xn2, wsrc, out=a["fc"], bias=w.get(p + "bfc"), stage=stg)
                 K.gelu_fwd(a["fc"], out=a["act"])
-                G.gemm(a["act"], w[p + "wproj"], out=nxt, residual=a["x_mid"], bias=w.get(p + "bproj"))
+                wsrc, stg = self._wop(p + "wproj")
+                G.gemm(a["act"], wsrc, out=nxt, residual=a["x_mid"], bias=w.get(p + "bproj"), stage=stg)
             saved.append((st1, st2, actx, stq))
             x = nxt
         xf, stf = self._norm_fwd(x, "norm_f", out=ws["xf"])
@@ -430,6 +460,17 @@ class DecoderRuntime:
             for j in range(n):
                 tok = ws["toks"][j] if toks is None else toks[j]
                 K.embedding_accumulate(tok, ws["embs"][j], self.scales[j], acc_emb, tok.numel())
+
+    def accumulate_group_sharded(self, acc_ptrs: list[int], bounds: list[int], rank: int, ws: dict, n: int, *,
+                                 emb_acc: torch.Tensor | None, toks=None) -> None:
+        """Sharded sums: the clipped gradients of the examples in slots ``0 .. n-1`` are reduced into the owners' fp32
+        shards (``acc_ptrs`` / ``bounds`` as in ``ops.kernels.clip_accumulate_group_push``). ``emb_acc``: the ``[V, d]``
+        rows of the embedding table's sum inside its owner's shard (possibly on another GPU)."""
+        K.clip_accumulate_group_push(self.Gs[:n], self.scales[:n], acc_ptrs, bounds, rank, self.layout.dense_total)
+        if not self.cfg.tie_embeddings and emb_acc is not None:
+            for j in range(n):
+                tok = ws["toks"][j] if toks is None else toks[j]
+                K.embedding_accumulate(tok, ws["embs"][j], self.scales[j], emb_acc, tok.numel(), shared=True)
 
     def clip_and_accumulate(self, acc: torch.Tensor, clip: float, ws: dict, tok: torch.Tensor, *, auto: bool = False,
                             gamma: float = 0.01, overwrite: bool = False, slot: int = 0) -> None:

@@ -46,6 +46,27 @@ class Layout:
                 return s
         raise KeyError(name)
 
+    def shard_bounds(self, world: int) -> list[int]:
+        """``world + 1`` offsets cutting the flat vector into contiguous shards of nearly equal size whose boundaries
+        fall on tensor boundaries, so every tensor has exactly one owner: a weight matrix can then be fetched from its
+        owner by one GEMM, and the embedding rows are accumulated on one rank. Offsets are multiples of ``ALIGN``.
+        A model with fewer tensors than ranks leaves some shards empty."""
+        cuts = sorted({s.offset for s in self.slots} | {self.total})
+        bounds = [0]
+        for r in range(1, world):
+            target = self.total * r / world
+            cand = [c for c in cuts if c >= bounds[-1]]
+            bounds.append(min(cand, key=lambda c: abs(c - target)))
+        bounds.append(self.total)
+        return bounds
+
+    def owner_of(self, name: str, bounds: list[int]) -> int:
+        off = self.slot(name).offset
+        for r in range(len(bounds) - 1):
+            if bounds[r] <= off < bounds[r + 1]:
+                return r
+        raise KeyError(name)
+
     def views(self, buf: torch.Tensor, dense_only: bool = False) -> dict[str, torch.Tensor]:
         out = {}
         for s in self.slots:

@@ -16,6 +16,7 @@ class DpStepArgs(Structure):
         ("bc1", c_float), ("bc2", c_float), ("phi_hat", c_float), ("zero_grad", c_int32),
         ("blt_state", c_void_p), ("blt_nbuf", c_int32), ("blt_decay", c_void_p), ("blt_scale", c_void_p),
         ("sgd_mode", c_int32),
+        ("toep_state", c_void_p), ("toep_nlag", c_int32), ("toep_coef", c_void_p), ("toep_pos", c_int32),
     ]
 
 
@@ -82,6 +83,9 @@ PROTOTYPES: dict = {
     "opk_clip_accumulate": (I, [P, P, P, L, P]),
     "opk_clip_accumulate2": (I, [P, P, P, L, I, P]),
     "opk_clip_accumulate_group": (I, [POINTER(c_void_p), POINTER(c_void_p), I, P, L, I, P]),
+    "opk_clip_accumulate_group_push": (I, [POINTER(c_void_p), POINTER(c_void_p), I, POINTER(c_void_p), POINTER(c_int64), I, I, L, P]),
+    "opk_copy_bytes": (I, [P, P, L, P]),
+    "opk_embedding_accumulate_shared": (I, [P, P, P, P, P, I, I, P]),
     "opk_philox_normal": (I, [P, L, c_uint64, c_uint32, c_uint32, c_uint64, F, I, P]),
     "opk_dp_step": (I, [POINTER(DpStepArgs), P]),
 }

@@ -189,10 +189,12 @@ def embedding_bwd_compact(tok, dx, ws: EmbeddingGradWorkspace, sumsq):
                                         ws.first_pos.numel(), _s(dx)), "embedding_bwd_compact")
 
 
-def embedding_accumulate(tok, ws: EmbeddingGradWorkspace, scale, acc, T: int):
+def embedding_accumulate(tok, ws: EmbeddingGradWorkspace, scale, acc, T: int, shared: bool = False):
+    """``acc[tok[t]] += bf16(gc[t] * scale)`` for representative rows. ``shared``: other GPUs add to the same rows at the
+    same time (sharded sums; ``acc`` may alias the owner's shard on another GPU), so reductions are used."""
     D = acc.shape[1]
-    _chk(_L().opk_embedding_accumulate(_p(tok), _p(ws.rep), _p(ws.gc), _p(scale), _p(acc), T, D, _s(acc)),
-         "embedding_accumulate")
+    fn = _L().opk_embedding_accumulate_shared if shared else _L().opk_embedding_accumulate
+    _chk(fn(_p(tok), _p(ws.rep), _p(ws.gc), _p(scale), _p(acc), T, D, _s(tok)), "embedding_accumulate")
 
 
 # ------------------------------------------------------------------------------------------------ losses
@@ -271,6 +273,27 @@ def clip_accumulate_group(gs, scales, acc, overwrite: bool = False):
     _chk(_L().opk_clip_accumulate_group(gp, sp, n, _p(acc), gs[0].numel(), int(overwrite), _s(acc)), "clip_accumulate_group")
 
 
+def clip_accumulate_group_push(gs, scales, acc_ptrs: list[int], bounds: list[int], rank: int, n: int):
+    """Sharded sums: the group's clipped sum ``sum_j stored(gs[j] * scales[j])`` over the first ``n`` elements is added
+    to the owners' shards with reductions (``acc_ptrs[o]`` = device address of owner ``o``'s fp32 shard, peer-mapped for
+    remote owners; owner ``o`` holds the elements ``[bounds[o], bounds[o+1])``)."""
+    import ctypes
+
+    k = len(gs)
+    if not 1 <= k <= 8 or len(scales) != k:
+        raise ValueError("a group holds 1 to 8 gradient buffers with one scale each")
+    gp = (ctypes.c_void_p * k)(*[g.data_ptr() for g in gs])
+    sp = (ctypes.c_void_p * k)(*[t.data_ptr() for t in scales])
+    ap = (ctypes.c_void_p * len(acc_ptrs))(*acc_ptrs)
+    bp = (ctypes.c_int64 * len(bounds))(*bounds)
+    _chk(_L().opk_clip_accumulate_group_push(gp, sp, k, ap, bp, len(acc_ptrs), rank, n, _s(gs[0])), "clip_accumulate_group_push")
+
+
+def copy_bytes(dst_ptr: int, src_ptr: int, nbytes: int, device) -> None:
+    """Copy with the library's own kernel; either address may be peer-mapped memory of another GPU."""
+    _chk(_L().opk_copy_bytes(dst_ptr, src_ptr, nbytes, _lib.stream_ptr(device)), "copy_bytes")
+
+
 def philox_normal_(out, seed: int, step: int, *, stream_id: int = 0, offset: int = 0, sigma: float = 1.0,
                    accumulate: bool = False):
     _chk(_L().opk_philox_normal(_p(out), out.numel(), seed & (2**64 - 1), stream_id, step, offset, sigma,
@@ -281,7 +304,8 @@ def philox_normal_(out, seed: int, step: int, *, stream_id: int = 0, offset: int
 def dp_step(*, grad_src: list[int], shard_begin: int, shard_len: int, inv_batch: float, sigma: float, seed: int,
             step: int, m, v, master, param_dst: list[int], param_src, lr: float, beta1: float, beta2: float, eps: float,
             weight_decay: float, bc1: float, bc2: float, phi_hat: float, stream_id: int = 0, zero_grad: bool = False,
-            blt_state=None, blt_decay=None, blt_scale=None, sgd_mode: bool = False, device=None):
+            blt_state=None, blt_decay=None, blt_scale=None, toep_state=None, toep_coef=None, toep_pos: int = 0,
+            sgd_mode: bool = False, device=None):
     """Launch the fused reduce-scatter + noise + DP-AdamW(-BC) + all-gather kernel for this rank's shard.
 
     ``grad_src`` / ``param_dst`` are raw device addresses (this rank first, then its peers).
@@ -300,6 +324,12 @@ def dp_step(*, grad_src: list[int], shard_begin: int, shard_len: int, inv_batch:
     if blt_state is not None:
         a.blt_state, a.blt_nbuf = _p(blt_state), blt_state.shape[0]
         a.blt_decay, a.blt_scale = _p(blt_decay), _p(blt_scale)
+    if toep_coef is not None:       # banded Toeplitz C^-1: ring of the last len(coef) - 1 outputs (none for one coefficient)
+        a.toep_coef = _p(toep_coef)
+        a.toep_nlag = 0 if toep_state is None else toep_state.shape[0]
+        a.toep_state, a.toep_pos = _p(toep_state), toep_pos
+        if toep_coef.numel() != a.toep_nlag + 1:
+            raise ValueError("toep_coef holds one coefficient more than the ring has slots")
     a.sgd_mode = int(sgd_mode)
     dev = device if device is not None else (m.device if m is not None else torch.device("cuda"))
     _chk(_L().opk_dp_step(ctypes.byref(a), _lib.stream_ptr(dev)), "dp_step")

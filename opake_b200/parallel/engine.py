@@ -54,6 +54,15 @@ class EngineConfig:
     blt_scale: tuple[float, ...] = ()
     noise_stream_tag: str = "opake.dpsgd.gaussian"
     accumulate_group: int = 0           # whole-model gradient buffers per accumulation pass; 0 = as many as fit (2..6)
+    # DP-FTRL with a banded Toeplitz strategy (band-MF, banded square root): first column of C; () = not used
+    toeplitz_coef: tuple[float, ...] = ()
+    # Full sharding (both need more than one rank to change anything):
+    #   shard_params  every parameter tensor has one owner; the optimizer step writes only the owner's copy and the
+    #                 other ranks fetch it inside the first forward GEMM that consumes it (all-gather fused into the GEMM)
+    #   shard_sums    the fp32 clipped-gradient sums are sharded like the optimizer state; each accumulation group is
+    #                 reduce-scattered to the owners with reductions over NVLink while the next group's forward runs
+    shard_params: bool = False
+    shard_sums: bool = False
 
 
 class ShardedDPEngine:
@@ -63,12 +72,23 @@ class ShardedDPEngine:
         self.rank = dist.get_rank() if dist.is_initialized() else 0
         self.layout = build_layout(model_cfg, shard_multiple=self.world)
         total = self.layout.total
-        self.shard_len = total // self.world
-        self.shard_begin = self.rank * self.shard_len
+        self.shard_params = bool(cfg.shard_params) and self.world > 1
+        self.shard_sums = bool(cfg.shard_sums) and self.world > 1
+        if self.shard_params or self.shard_sums:
+            self.bounds = self.layout.shard_bounds(self.world)      # every tensor has exactly one owner
+        else:
+            self.bounds = [r * (total // self.world) for r in range(self.world)] + [total]
+        self.shard_begin = self.bounds[self.rank]
+        self.shard_len = self.bounds[self.rank + 1] - self.shard_begin
         # peer-addressable buffers
         self.params_pb = comm.alloc_peer_buffer(total, _bf16, device)
-        self.acc_pb = comm.alloc_peer_buffer(total, torch.float32, device)
-        self.params, self.acc = self.params_pb.local, self.acc_pb.local
+        self.params = self.params_pb.local
+        if self.shard_sums:
+            longest = max(self.bounds[r + 1] - self.bounds[r] for r in range(self.world))
+            self.acc_pb = comm.alloc_peer_buffer(max(longest, 8), torch.float32, device)    # this rank's shard only
+        else:
+            self.acc_pb = comm.alloc_peer_buffer(total, torch.float32, device)
+        self.acc = self.acc_pb.local
         init_params_(model_cfg, self.params, self.layout, seed=init_seed)  # same seed on every rank -> same replica
         self.acc.zero_()
         self.m = torch.zeros(self.shard_len, dtype=torch.float32, device=device)
@@ -82,6 +102,19 @@ class ShardedDPEngine:
             self.blt_state = torch.zeros(nb, self.shard_len, dtype=torch.float32, device=device)
             self.blt_decay = torch.tensor(cfg.blt_decay, dtype=torch.float32, device=device)
             self.blt_scale = torch.tensor(cfg.blt_scale, dtype=torch.float32, device=device)
+        self.toep_state = self.toep_coef = None
+        self.toep_pos = 0
+        if cfg.toeplitz_coef:
+            if cfg.blt_decay:
+                raise ValueError("choose one correlated-noise strategy: buffered linear Toeplitz or banded Toeplitz")
+            if cfg.toeplitz_coef[0] == 0:
+                raise ValueError("the leading Toeplitz coefficient must be non-zero")
+            self.toep_coef = torch.tensor(cfg.toeplitz_coef, dtype=torch.float32, device=device)
+            nlag = len(cfg.toeplitz_coef) - 1
+            if nlag:
+                self.toep_state = torch.zeros(nlag, self.shard_len, dtype=torch.float32, device=device)
+        self._stale = False      # shard_params: the replica's remote parts are older than their owners' copies
+        self._refresh: dict[int, tuple] = {}
         if cfg.accumulate_group and not 2 <= int(cfg.accumulate_group) <= 8:
             raise ValueError(f"accumulate_group must be 0 (automatic) or between 2 and 8, got {cfg.accumulate_group}")
         self.group = int(cfg.accumulate_group) or self._pick_group_size()
@@ -115,7 +148,47 @@ class ShardedDPEngine:
         return int(max(2, min(cap, (free - reserve) // max(g_bytes, 1))))
 
     # ------------------------------------------------------------------ one example
-    def _example_body(self, ws, slot: int, drain_prev: bool) -> None:
+    # ------------------------------------------------------------------ sharding helpers
+    def _refresh_plan(self, T: int) -> tuple:
+        """What a refresh of the replica fetches from other ranks, for sequences of ``T`` tokens: ``fetch`` maps the
+        weights whose first forward GEMM can pull them itself (staged two-CTA kernel) to the owner's copy; ``copies``
+        lists the remaining remote ranges (norm weights, biases, embeddings, LM head) as (element offset, elements,
+        owner), merged into maximal runs, for the plain peer-copy kernel."""
+        plan = self._refresh.get(T)
+        if plan is not None:
+            return plan
+        fetch, copies = {}, []
+        act = self.model_cfg.act
+        for sl in self.layout.slots:
+            owner = self.layout.owner_of(sl.name, self.bounds)
+            if owner == self.rank:
+                continue
+            if DecoderRuntime.stageable(sl.name, sl.shape, T, act) and not self.model_cfg.n_experts:
+                fetch[sl.name] = self.params_pb.peer_view(owner, sl.shape, offset=sl.offset)
+                continue
+            n = (sl.numel + 127) // 128 * 128
+            if copies and copies[-1][2] == owner and copies[-1][0] + copies[-1][1] == sl.offset:
+                copies[-1] = (copies[-1][0], copies[-1][1] + n, owner)
+            else:
+                copies.append((sl.offset, n, owner))
+        plan = (fetch, copies)
+        self._refresh[T] = plan
+        return plan
+
+    def _accumulate(self, ws, n: int, toks) -> None:
+        """Adds the clipped gradients held in slots ``0 .. n-1`` to the fp32 sums (local pass, or reductions into the
+        owners' shards when the sums are sharded)."""
+        if not self.shard_sums:
+            self.runtime.accumulate_group(self.acc, ws, n, toks=toks)
+            return
+        emb_acc = None
+        if not self.model_cfg.tie_embeddings:
+            emb = self.layout.slot("embed")
+            owner = self.layout.owner_of("embed", self.bounds)
+            emb_acc = self.acc_pb.peer_view(owner, emb.shape, offset=emb.offset - self.bounds[owner])
+        self.runtime.accumulate_group_sharded(self.acc_pb.ptrs, self.bounds, self.rank, ws, n, emb_acc=emb_acc, toks=toks)
+
+    def _example_body(self, ws, slot: int, drain_prev: bool, refresh: bool = False) -> None:
         """Gradient of the example staged in slot ``slot``; meanwhile (side stream) the clipped accumulation of the
         previous example, which sits in the other slot. HBM-bound accumulation and tensor-core-bound GEMMs share
         the SMs, so the accumulation is hidden."""
@@ -131,9 +204,19 @@ class ShardedDPEngine:
         if drain_prev and slot == 0:
             self._side.wait_stream(main)
             with torch.cuda.stream(self._side):
-                rt.accumulate_group(self.acc, ws, self.group, toks=self._group_toks(ws, self.group))
+                self._accumulate(ws, self.group, self._group_toks(ws, self.group))
             hook = lambda: main.wait_stream(self._side)
-        st = rt.example_grad(ws["toks"][slot], ws["labels"], ws=ws, slot=slot, before_wgrad=hook)
+        if refresh:
+            # first example after an optimizer step with sharded parameters: small tensors come over with the copy
+            # kernel, the layer matrices inside the forward GEMMs that consume them
+            fetch, copies = self._refresh_plan(ws["toks"][slot].numel())
+            for off, n, owner in copies:
+                K.copy_bytes(self.params.data_ptr() + 2 * off, self.params_pb.ptrs[owner] + 2 * off, 2 * n, self.device)
+            rt._fetch = fetch
+        try:
+            st = rt.example_grad(ws["toks"][slot], ws["labels"], ws=ws, slot=slot, before_wgrad=hook)
+        finally:
+            rt._fetch = None
         rt.clip_factor(cfg.clip_norm, auto=cfg.auto_clip, gamma=cfg.auto_gamma, slot=slot)
         ws["loss_sum"].add_(st.loss.reshape(1))
         if slot == 0:
@@ -148,32 +231,35 @@ class ShardedDPEngine:
         ws = self.runtime.workspace(T)
         slot = index % self.group
         drain = index > 0
+        refresh = index == 0 and self._stale
+        if refresh:
+            self._stale = False
         ws["toks"][slot].copy_(tok_host, non_blocking=True)
         ws["labels"].copy_(labels_host, non_blocking=True)
         if not self.cfg.use_cuda_graph:
-            self._example_body(ws, slot, drain)
+            self._example_body(ws, slot, drain, refresh)
             return
-        key = (T, slot, drain)
+        key = (T, slot, drain, refresh)
         entry = self._graphs.get(key)
         if entry is None:
             from ..ops import _lib
 
-            if not self._warm.get(T):
+            if not self._warm.get((T, refresh)):
                 # eager warm-up (lazy workspaces, library autotuning) on a side stream, state restored afterwards
                 saved = (ws["loss_sum"].clone(), self.acc.clone() if self.acc.numel() < (1 << 28) else None)
                 s = torch.cuda.Stream(device=self.device)
                 s.wait_stream(torch.cuda.current_stream(self.device))
                 with torch.cuda.stream(s):
-                    self._example_body(ws, slot, False)
+                    self._example_body(ws, slot, False, refresh)
                 torch.cuda.current_stream(self.device).wait_stream(s)
                 torch.cuda.synchronize(self.device)
                 ws["loss_sum"].copy_(saved[0])
                 self.runtime.clip_count.zero_()
-                self._warm[T] = True
+                self._warm[(T, refresh)] = True
             g = torch.cuda.CUDAGraph()
             before = _lib.LAUNCHES[0]
             with torch.cuda.graph(g):
-                self._example_body(ws, slot, drain)
+                self._example_body(ws, slot, drain, refresh)
             entry = (g, _lib.LAUNCHES[0] - before)
             self._graphs[key] = entry
             # capture does not execute: fall through to the first replay
@@ -204,7 +290,7 @@ class ShardedDPEngine:
         # example that followed it
         n_last = B_local % self.group or min(self.group, B_local)
         if n_last:
-            self.runtime.accumulate_group(self.acc, ws, n_last, toks=self._group_toks(ws, n_last))
+            self._accumulate(ws, n_last, self._group_toks(ws, n_last))
         loss_sum = ws["loss_sum"].clone()
         self.apply_update()
         return loss_sum
@@ -220,18 +306,43 @@ class ShardedDPEngine:
             self.phi = b2 * self.phi + (1.0 - b2) * sigma * sigma
             phi_hat = self.phi / (1.0 - b2**t)
         if self.world > 1:
-            self.acc_pb.barrier()       # every rank finished accumulating before anyone reads peers' sums
+            self.acc_pb.barrier()       # every rank finished accumulating before anyone reads (or owns) the sums
+        if self.shard_sums:
+            # the owner's shard already holds the sum over all ranks; addressed with global offsets like a full buffer
+            grad_src = [self.acc.data_ptr() - 4 * self.shard_begin]
+        else:
+            grad_src = self._rotate(self.acc_pb.ptrs)
+        # sharded parameters: only the owner's copy is written here, the other ranks fetch it in their next forward pass
+        param_dst = [self.params.data_ptr()] if self.shard_params else self._rotate(self.params_pb.ptrs)
         K.dp_step(
-            grad_src=self._rotate(self.acc_pb.ptrs), shard_begin=self.shard_begin, shard_len=self.shard_len,
+            grad_src=grad_src, shard_begin=self.shard_begin, shard_len=self.shard_len,
             inv_batch=1.0 / cfg.logical_batch, sigma=sigma, seed=step_key.seed, step=self.step_count,
-            m=self.m, v=self.v, master=self.master, param_dst=self._rotate(self.params_pb.ptrs), param_src=self.params,
+            m=self.m, v=self.v, master=self.master, param_dst=param_dst, param_src=self.params,
             lr=cfg.lr, beta1=b1, beta2=b2, eps=cfg.eps, weight_decay=cfg.weight_decay, bc1=1.0 - b1**t,
-            bc2=1.0 - b2**t, phi_hat=phi_hat, zero_grad=False, blt_state=self.blt_state, blt_decay=self.blt_decay,
-            blt_scale=self.blt_scale, sgd_mode=(cfg.optimizer == "sgd"), device=self.device)
+            bc2=1.0 - b2**t, phi_hat=phi_hat, zero_grad=self.shard_sums, blt_state=self.blt_state, blt_decay=self.blt_decay,
+            blt_scale=self.blt_scale, toep_state=self.toep_state, toep_coef=self.toep_coef, toep_pos=self.toep_pos,
+            sgd_mode=(cfg.optimizer == "sgd"), device=self.device)
+        if self.toep_state is not None:
+            self.toep_pos = (self.toep_pos - 1) % self.toep_state.shape[0]
         if self.world > 1:
-            self.params_pb.barrier()    # all shards of the new parameters have landed everywhere
-        self.acc.zero_()
+            self.params_pb.barrier()    # the new parameters (and, sharded sums, the zeroed shards) are in place everywhere
+        if not self.shard_sums:
+            self.acc.zero_()
+        if self.shard_params:
+            self._stale = True
         self.step_count += 1
+
+    def gather_params(self) -> None:
+        """Brings this rank's replica up to date outside a training step (evaluation, checkpointing): every remote
+        range is copied from its owner with the peer-copy kernel. No-op unless the parameters are sharded and stale."""
+        if not self._stale:
+            return
+        for r in range(self.world):
+            if r == self.rank or self.bounds[r + 1] == self.bounds[r]:
+                continue
+            off, n = self.bounds[r], self.bounds[r + 1] - self.bounds[r]
+            K.copy_bytes(self.params.data_ptr() + 2 * off, self.params_pb.ptrs[r] + 2 * off, 2 * n, self.device)
+        self._stale = False
 
     # ------------------------------------------------------------------ checkpointing
     def state_dict(self) -> dict:
@@ -240,8 +351,11 @@ class ShardedDPEngine:
                "shard_len": self.shard_len, "world": self.world, "m": self.m.cpu(), "v": self.v.cpu(),
                "master": None if self.master is None else self.master.cpu(),
                "blt_state": None if self.blt_state is None else self.blt_state.cpu(),
+               "toep_state": None if self.toep_state is None else self.toep_state.cpu(), "toep_pos": self.toep_pos,
+               "bounds": list(self.bounds),
                "noise_key": {"seed": self._noise_key.seed, "impl": self._noise_key.impl}}
         if self.rank == 0:
+            self.gather_params()
             out["params"] = self.params.cpu()
         return out
 
@@ -256,6 +370,9 @@ class ShardedDPEngine:
             self.master.copy_(sd["master"])
         if self.blt_state is not None and sd.get("blt_state") is not None:
             self.blt_state.copy_(sd["blt_state"])
+        if self.toep_state is not None and sd.get("toep_state") is not None:
+            self.toep_state.copy_(sd["toep_state"])
+            self.toep_pos = int(sd.get("toep_pos", 0))
         p = sd.get("params") if params is None else params
         if p is not None:
             self.params.copy_(p)

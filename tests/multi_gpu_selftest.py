@@ -22,6 +22,11 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--blt", action="store_true")
+    ap.add_argument("--toeplitz", action="store_true", help="banded Toeplitz correlated noise (band-MF / banded square root)")
+    ap.add_argument("--seq", type=int, default=128)
+    ap.add_argument("--shard-params", action="store_true", help="owners keep the parameters; fetched inside the forward GEMMs")
+    ap.add_argument("--shard-sums", action="store_true", help="fp32 sums sharded, accumulation groups reduce-scattered")
+    ap.add_argument("--graph", action="store_true", help="run the examples through CUDA graphs")
     ap.add_argument("--sharded-linear", action="store_true", help="check the sharded-weight GEMMs instead of the engine")
     ap.add_argument("--ep-fused", action="store_true", help="check the expert-parallel dispatch / combine kernels")
     ap.add_argument("--sharded-linear-bench", action="store_true",
@@ -44,11 +49,15 @@ def main() -> None:
             dist.destroy_process_group()
         return
     cfg = tiny_llama()
-    ecfg = EngineConfig(logical_batch=a.batch, noise_multiplier=0.7, lr=1e-2, seed=5, use_cuda_graph=False,
-                        blt_decay=(0.9, 0.5) if a.blt else (), blt_scale=(0.3, 0.2) if a.blt else ())
+    if a.seq > cfg.max_seq:
+        cfg = tiny_llama(max_seq=a.seq)
+    ecfg = EngineConfig(logical_batch=a.batch, noise_multiplier=0.7, lr=1e-2, seed=5, use_cuda_graph=a.graph,
+                        blt_decay=(0.9, 0.5) if a.blt else (), blt_scale=(0.3, 0.2) if a.blt else (),
+                        toeplitz_coef=(1.0, 0.5, 0.375, 0.3125) if a.toeplitz else (),
+                        shard_params=a.shard_params, shard_sums=a.shard_sums, accumulate_group=2)
     eng = ShardedDPEngine(cfg, ecfg, dev)
     g = torch.Generator().manual_seed(0)
-    tok = torch.randint(0, cfg.vocab_size, (a.batch, 128), generator=g, dtype=torch.int32)
+    tok = torch.randint(0, cfg.vocab_size, (a.batch, a.seq), generator=g, dtype=torch.int32)
     labels = torch.roll(tok, -1, 1).clone()
     labels[:, -1] = -100
     per = a.batch // world
@@ -59,9 +68,15 @@ def main() -> None:
         if world > 1:
             dist.all_reduce(l)
         losses.append(l.item() / a.batch)
+    eng.gather_params()
     torch.cuda.synchronize()
+    from opake_b200.ops._lib import raise_if_device_error
+
+    raise_if_device_error(dev)
     if rank == 0:
-        torch.save({"params": eng.params.float().cpu(), "losses": losses, "world": world}, a.out)
+        staged = sorted(eng._refresh_plan(a.seq)[0]) if eng.shard_params else []
+        torch.save({"params": eng.params.float().cpu(), "losses": losses, "world": world, "staged": staged,
+                    "bounds": list(eng.bounds)}, a.out)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

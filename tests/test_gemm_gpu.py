@@ -145,3 +145,35 @@ def test_gemm_lce(cuda):
     onehot[valid, labels[valid].long()] = 1
     ref_d = (p - onehot) * coef[:, None]
     assert (d.float() - ref_d).abs().max().item() < 2e-2 * ref_d.abs().max().item() + 1e-6
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_staged_weight_fetch_inside_the_gemm(cuda, swiglu):
+    """The staged two-CTA GEMM copies its weight operand into a local destination band by band while it multiplies
+    (the all-gather of a sharded weight fused into its first consumer): same product as the plain kernel, and the
+    destination ends up holding the weight. The 'remote' source is local memory here."""
+    from opake_b200.ops import gemm as G
+
+    if not G.pair_mode():
+        pytest.skip("staging runs on the two-CTA kernel")
+    M, N, K_ = 512, 4608, 320
+    g = torch.Generator(device=cuda).manual_seed(11)
+    x = (torch.randn(M, K_, generator=g, device=cuda) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K_, generator=g, device=cuda) * 0.1).to(torch.bfloat16)
+    dst = torch.zeros_like(w)
+    ready = torch.zeros(64, dtype=torch.int32, device=cuda)
+    if swiglu:
+        act_a = torch.empty(M, N // 2, dtype=torch.bfloat16, device=cuda)
+        act_b = torch.empty_like(act_a)
+        want = G.gemm(x, w, epilogue=G.EPI_SWIGLU, act=act_a)
+        got = G.gemm(x, w, epilogue=G.EPI_SWIGLU, act=act_b, stage=(dst, ready))
+        assert torch.equal(act_a, act_b)
+    else:
+        want = G.gemm(x, w)
+        got = G.gemm(x, w, stage=(dst, ready))
+    torch.cuda.synchronize()
+    from opake_b200.ops._lib import raise_if_device_error
+
+    raise_if_device_error(cuda)
+    assert torch.equal(got, want)
+    assert torch.equal(dst, w)

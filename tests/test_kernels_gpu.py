@@ -251,3 +251,78 @@ def test_bounded_wait_expires_and_reports(cuda):
     assert err.item() == 3 and budget <= waited.item() < 20 * budget
     x = torch.ones(1024, device=cuda)
     assert x.sum().item() == 1024.0          # context still usable
+
+
+def test_dp_step_banded_toeplitz_ring_matches_streaming_inverse(cuda):
+    """Band-MF / banded-square-root correlated noise in the fused step: with zero gradients, SGD, lr = 1 and fp32 master
+    weights the parameter moves by exactly -sigma * zhat_t, where zhat = C^{-1} z is the banded Toeplitz recursion
+    ``zhat_t = (z_t - sum_k c_k zhat_{t-k}) / c_0`` (packages/opake-dpftrl/src/opake/api/dpftrl/noise/_toeplitz.py:177-326)."""
+    import numpy as np
+
+    from opake_b200.ops import kernels as K
+    from opake_b200.ops.philox_ref import normal
+
+    n, off = 1024 + 6, 64              # ragged tail and a shard that does not start at element 0
+    coef = [1.25, 0.5, -0.25, 0.125]
+    nlag = len(coef) - 1
+    acc = torch.zeros(off + n, device=cuda)
+    p = torch.zeros(off + n, dtype=torch.bfloat16, device=cuda)
+    master = torch.zeros(n, device=cuda)
+    ring = torch.zeros(nlag, n, device=cuda)
+    c_dev = torch.tensor(coef, device=cuda)
+    sigma, seed, pos = 0.5, 7, 0
+    hist, want = [], np.zeros(n, dtype=np.float64)
+    for step in range(6):
+        K.dp_step(grad_src=[acc.data_ptr()], shard_begin=off, shard_len=n, inv_batch=1.0, sigma=sigma, seed=seed, step=step,
+                  m=None, v=None, master=master, param_dst=[p.data_ptr()], param_src=p, lr=1.0, beta1=0.9, beta2=0.999,
+                  eps=1e-8, weight_decay=0.0, bc1=1.0, bc2=1.0, phi_hat=0.0, toep_state=ring, toep_coef=c_dev, toep_pos=pos,
+                  sgd_mode=True, device=cuda)
+        pos = (pos - 1) % nlag
+        z = normal(n, seed, step, offset=off).astype(np.float64)
+        zhat = (z - sum(coef[k] * hist[-k] for k in range(1, min(nlag, len(hist)) + 1))) / coef[0]
+        hist.append(zhat)
+        want -= sigma * zhat
+        got = master.double().cpu().numpy()
+        assert np.abs(got - want).max() < 5e-5 * (step + 1), step
+    assert p[off:].float().sub(master).abs().max().item() <= 2 ** -8 * master.abs().max().item()
+
+
+def test_sharded_sum_push_matches_local_group_pass(cuda):
+    """The reduce-scatter form of the group accumulation (reductions into per-owner shards) gives the sums of the local
+    one-pass kernel; here both 'owners' live on this GPU."""
+    from opake_b200.ops import kernels as K
+
+    n, k = 8 * 1000 + 8 * 37, 3
+    gs = [_rand((n,), cuda, 2.0) for _ in range(k)]
+    scales = [torch.tensor([s], device=cuda) for s in (0.5, 1.0, 0.125)]
+    want = torch.randn(n, device=cuda)
+    base = want.clone()
+    K.clip_accumulate_group(gs, scales, want)
+    bounds = [0, 8 * 600, n]
+    shards = [base[bounds[o]:bounds[o + 1]].clone() for o in range(2)]
+    for rank in (0, 1):         # the starting owner changes the walk, not the result
+        cur = [s.clone() for s in shards]
+        K.clip_accumulate_group_push(gs, scales, [t.data_ptr() for t in cur], bounds, rank, n)
+        torch.cuda.synchronize()
+        got = torch.cat(cur)
+        assert (got - want).abs().max().item() <= 1e-5 * want.abs().max().item()
+
+
+def test_copy_bytes_and_shared_embedding_accumulate(cuda):
+    from opake_b200.ops import kernels as K
+
+    src = torch.randn(1 << 16, device=cuda)
+    dst = torch.zeros_like(src)
+    K.copy_bytes(dst.data_ptr(), src.data_ptr(), src.numel() * 4, cuda)
+    assert torch.equal(dst, src)
+    V, T, D = 300, 96, 64
+    g = torch.Generator(device=cuda).manual_seed(5)
+    tok = torch.randint(0, V, (T,), generator=g, device=cuda, dtype=torch.int32)
+    dx = torch.randn(T, D, generator=g, device=cuda).to(torch.bfloat16)
+    ws = K.EmbeddingGradWorkspace(V, T, D, cuda)
+    K.embedding_bwd_compact(tok, dx, ws, None)
+    scale = torch.tensor([0.37], device=cuda)
+    a, b = torch.zeros(V, D, device=cuda), torch.zeros(V, D, device=cuda)
+    K.embedding_accumulate(tok, ws, scale, a, T)
+    K.embedding_accumulate(tok, ws, scale, b, T, shared=True)
+    assert torch.equal(a, b)

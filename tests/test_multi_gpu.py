@@ -35,6 +35,39 @@ def test_two_ranks_match_one_rank(tmp_path, blt):
     assert diff <= 2e-2 * one["params"].abs().max().item(), diff
 
 
+@pytest.mark.parametrize("mode", ["params", "sums", "full", "full-graph"])
+def test_two_ranks_fully_sharded_match_one_rank(tmp_path, mode):
+    """Sharded parameters (fetched inside the forward GEMMs of the first example after each optimizer step) and sharded
+    fp32 sums (accumulation groups reduce-scattered with reductions over NVLink) give the parameters of a 1-rank run.
+    Sequences of 256 tokens so that the layer matrices take the staged two-CTA GEMM."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    extra = ["--seq", "256", "--steps", "3"]
+    one = _run(1, str(tmp_path / "w1.pt"), extra)
+    if mode in ("params", "full", "full-graph"):
+        extra.append("--shard-params")
+    if mode in ("sums", "full", "full-graph"):
+        extra.append("--shard-sums")
+    if mode == "full-graph":
+        extra.append("--graph")
+    two = _run(2, str(tmp_path / "w2.pt"), extra)
+    if "--shard-params" in extra:
+        assert any(n.endswith("wgu") for n in two["staged"]) and any(n.endswith("wqkv") for n in two["staged"])
+    assert one["losses"] == pytest.approx(two["losses"], rel=2e-3)
+    diff = (one["params"] - two["params"]).abs().max().item()
+    assert diff <= 2e-2 * one["params"].abs().max().item(), diff
+
+
+def test_two_ranks_match_one_rank_toeplitz(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    one = _run(1, str(tmp_path / "w1.pt"), ("--toeplitz", "--steps", "4"))
+    two = _run(2, str(tmp_path / "w2.pt"), ("--toeplitz", "--steps", "4"))
+    assert one["losses"] == pytest.approx(two["losses"], rel=2e-3)
+    diff = (one["params"] - two["params"]).abs().max().item()
+    assert diff <= 2e-2 * one["params"].abs().max().item(), diff
+
+
 def test_sharded_linear_reads_peer_shards(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
