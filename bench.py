@@ -145,6 +145,11 @@ def main() -> None:
     ap.add_argument("--attn", default="auto")
     ap.add_argument("--sigma", type=float, default=0.9)
     ap.add_argument("--blt-buffers", type=int, default=0, help="DP-FTRL: buffered-linear-Toeplitz correlated noise buffers")
+    ap.add_argument("--shard", default="auto", choices=["auto", "state", "params", "full"],
+                    help="what is sharded over the ranks: 'state' = optimizer moments only (replicated bf16 parameters and fp32 "
+                         "sums, all-gather by peer stores in the step kernel); 'params' = also the parameters (fetched inside the "
+                         "first forward GEMMs after a step); 'full' = parameters and fp32 sums; 'auto' = full when N > 1")
+    ap.add_argument("--group", type=int, default=0, help="gradient buffers per accumulation pass (0 = as many as fit)")
     ap.add_argument("--config", default="d", choices=["a", "b", "c", "d", "e"],
                     help="benchmark configuration: d = headline (Llama-3-8B DP-SGD); a = CPU MLP plumbing; b = GPT-2-small "
                          "DP-SGD; c = Llama-3.2-1B DP-FTRL (BLT); e = OLMoE-1B-7B")
@@ -187,9 +192,11 @@ def main() -> None:
         k = args.blt_buffers
         blt = dict(blt_decay=tuple(1.0 - 0.5 ** (i + 1) * 0.9 for i in range(k)), blt_scale=tuple(0.5 / k for _ in range(k)),
                    noise_stream_tag="opake.dpftrl.mf_gaussian")
+    shard = args.shard if args.shard != "auto" else ("full" if world > 1 else "state")
     ecfg = EngineConfig(clip_norm=1.0, noise_multiplier=args.sigma, logical_batch=args.batch, lr=3e-4, weight_decay=0.01,
                         noise_bias_correction=True, master_weights=False, use_cuda_graph=not args.no_graph,
-                        attn_impl=args.attn, seed=1234, **blt)
+                        attn_impl=args.attn, seed=1234, accumulate_group=args.group,
+                        shard_params=shard in ("params", "full"), shard_sums=shard == "full", **blt)
     eng = ShardedDPEngine(mcfg, ecfg, dev)
 
     tok = _zipf_tokens(b_local, args.seq, mcfg.vocab_size, seed=1000 + rank)
@@ -240,12 +247,20 @@ def main() -> None:
             "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic Zipf(1.1) tokens, random-init weights", "impl": "ours",
             "config": {"model": mcfg.name, "layers": mcfg.n_layers, "global_batch": args.batch, "seq_len": args.seq,
-                       "parallelism": f"fsdp{world} (sharded fp32 AdamW-BC state, fused P2P reduce-scatter/all-gather step; "
-                                      f"bf16 parameter replica cached across the {b_local} accumulation micro-steps)",
+                       "parallelism": f"fsdp{world} " + {
+                           "state": "(optimizer moments sharded; bf16 parameters and fp32 sums replicated, reduce-scatter by peer "
+                                    "loads and all-gather by peer stores inside the fused step kernel)",
+                           "params": "(optimizer moments and parameters sharded: each tensor has one owner and is fetched inside "
+                                     "the first forward GEMMs after a step; fp32 sums replicated)",
+                           "full": "(full shard: optimizer moments, parameters and fp32 sums; parameters fetched inside the first "
+                                   "forward GEMMs after a step, accumulation groups reduce-scattered by reductions over NVLink)",
+                       }[shard] + f"; gathered bf16 parameters cached across the {b_local} accumulation micro-steps",
+                       "shard": shard,
                        "clip_norm": 1.0, "noise_multiplier": args.sigma, "optimizer": "adamw-bc", "sft_mask": "first 25%",
                        "mechanism": f"dp-ftrl blt x{args.blt_buffers}" if args.blt_buffers else "dp-sgd gaussian",
                        "per_example_microbatch": 1, "cuda_graph": not args.no_graph,
                        "accumulate_group": getattr(eng, "group", None),
+                       "device_memory_in_use_gib": round((lambda f, t: (t - f) / 2 ** 30)(*torch.cuda.mem_get_info(dev)), 1),
                        "l2_policy": "inputs larger than L2: every step streams the 16 GB bf16 weights and 32 GB fp32 sums",
                        "final_loss_per_example": last_loss / b_local},
             "clocks": clocks,

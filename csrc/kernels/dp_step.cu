@@ -579,6 +579,13 @@ extern "C" int opk_dp_step(const OpkDpStepArgs* args, void* stream) {
     pt.param[r] = r < args->n_dst ? reinterpret_cast<__nv_bfloat16*>(args->param_dst[r]) : nullptr;
   }
   if (args->blt_nbuf > 0 && args->toep_nlag > 0) return -3;       // one correlation transform per step
+  // rows of the [buffers][shard_len] state are read as 16-byte vectors: every row must start on a 16-byte boundary
+  if ((args->blt_nbuf > 1 || args->toep_nlag > 1) && (args->shard_len & 3)) return -2;
+  if ((args->blt_nbuf > 0 && (reinterpret_cast<uintptr_t>(args->blt_state) & 15)) ||
+      (args->toep_nlag > 0 && (reinterpret_cast<uintptr_t>(args->toep_state) & 15)) ||
+      (reinterpret_cast<uintptr_t>(args->m) & 15) || (reinterpret_cast<uintptr_t>(args->v) & 15) ||
+      (reinterpret_cast<uintptr_t>(args->master) & 15))
+    return -2;
   if (args->toep_nlag > 0 && (!args->toep_state || !args->toep_coef || args->toep_pos < 0 || args->toep_pos >= args->toep_nlag)) return -3;
   const long long nq = (args->shard_len + 3) >> 2;
   const int grid = grid_for((nq + 1) / 2, 256, 148 * 8);

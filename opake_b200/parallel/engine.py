@@ -130,6 +130,10 @@ class ShardedDPEngine:
         self._graphs: dict[int, tuple] = {}
         self._losses = None
         self.graph_kernel_launches = 0   # native launches replayed through CUDA graphs (not seen by the ctypes counter)
+        if self.world > 1:
+            # every rank's buffers are initialised before any peer reads or adds to them
+            torch.cuda.synchronize(device)
+            dist.barrier()
 
     def _pick_group_size(self) -> int:
         """How many whole-model bf16 gradient buffers to keep: the clipped accumulation reads and writes the fp32
