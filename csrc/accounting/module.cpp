@@ -4,7 +4,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
-#include "mf.hpp"
+#include "amplification.hpp"
 
 namespace py = pybind11;
 using namespace opkacc;
@@ -12,20 +12,11 @@ using namespace opkacc;
 namespace {
 
 CorpusRegistry g_bnb;
-struct MinSepCorpus { std::vector<double> coef; int64_t n; double p; };
 std::mutex g_ms_mu;
-std::unordered_map<int64_t, MinSepCorpus> g_ms;
+std::unordered_map<int64_t, std::shared_ptr<MinSepCorpus>> g_ms;
 int64_t g_ms_next = 0;
 
 int64_t opt_k(const py::object& o) { return o.is_none() ? 0 : o.cast<int64_t>(); }
-
-Pld minsep_bound_pld(const std::vector<double>& coef, int64_t n, double sigma, const Config& cfg) {
-  // No amplification is claimed for b-min-sep sampling: the run is accounted as one Gaussian mechanism whose
-  // sensitivity is the worst-case participation pattern with separation = number of bands.
-  const int64_t b = std::max<int64_t>(1, (int64_t)coef.size());
-  const double s2 = toeplitz_minsep_sensitivity_squared(coef, n, b, 0);
-  return gaussian_pld(sigma / std::sqrt(s2), cfg);
-}
 
 std::string pld_repr(const Pld& p) {
   return "Pld(grid=" + std::to_string(p.remove.size()) + ", discretization=" + std::to_string(p.remove.h) +
@@ -124,7 +115,7 @@ PYBIND11_MODULE(_opake_accounting, m) {
   m.def("truncated_poisson_gaussian_pld", [](double nm, double q, int64_t cap, int64_t n, const Config& c) {
           if (cap < 1 || n < 1) throw std::invalid_argument("batch_size_max and dataset_size must be >= 1");
           py::gil_scoped_release r;
-          return truncated_poisson_gaussian_pld(nm, q, (size_t)cap, (size_t)n, c);
+          return truncated_poisson_gaussian_pld_exact(nm, q, (size_t)cap, (size_t)n, c);
         }, py::arg("noise_multiplier"), py::arg("rate"), py::arg("batch_size_max"), py::arg("dataset_size"), py::arg("config"));
   m.def("parallel_poisson_gaussian_pld", [](double nm, double q, int64_t mb, const Config& c) {
           if (mb < 1) throw std::invalid_argument("microbatches must be > 0");
@@ -134,20 +125,7 @@ PYBIND11_MODULE(_opake_accounting, m) {
   m.def("random_allocation_gaussian_pld", [](double nm, int64_t t, int64_t k, const Config& c) {
           if (t < 1 || k < 1 || k > t) throw std::invalid_argument("need t >= 1 and k in [1, t]");
           py::gil_scoped_release r;
-          // k blocks of about t/k steps, one use per block; each block is a 1-of-b allocation estimated by sampling
-          // its dominating pair with an orthonormal Gram (each step's contribution is a distinct coordinate).
-          const int64_t lo = t / k, n_hi = t - lo * k;
-          auto block = [&](int64_t b) {
-            if (b == 1) return gaussian_pld(nm, c);
-            std::vector<double> G((size_t)(b * b), 0.0);
-            for (int64_t i = 0; i < b; ++i) G[(size_t)(i * b + i)] = 1.0;
-            auto corpus = make_bnb_corpus(b, c.resolved_num_mc_samples(), c.seed);
-            return bnb_pld_from_corpus(corpus, G, nm, c);
-          };
-          const int64_t n_lo = k - n_hi;   // n_lo blocks of `lo` steps, n_hi blocks of `lo + 1` steps
-          Pld out = n_lo > 0 ? self_compose(block(lo), (size_t)n_lo) : self_compose(block(lo + 1), (size_t)n_hi);
-          if (n_lo > 0 && n_hi > 0) out = compose(out, self_compose(block(lo + 1), (size_t)n_hi));
-          return out;
+          return random_allocation_gaussian_pld(nm, (size_t)t, (size_t)k, c);
         }, py::arg("noise_multiplier"), py::arg("t"), py::arg("k"), py::arg("config"));
   m.def("balls_in_bins_gaussian_pld", [](double nm, int64_t bins, const Config& c) {
           if (bins < 2) throw std::invalid_argument("num_bins must be >= 2");
@@ -180,19 +158,29 @@ PYBIND11_MODULE(_opake_accounting, m) {
         }, py::arg("handle"), py::arg("gram"), py::arg("num_bins"), py::arg("sigma"), py::arg("config"));
 
   m.def("bandmf_b_min_sep_warm_mc_pld", [](const std::vector<double>& coef, int64_t n, double p, double sigma, const Config& c) {
-          if (!(p > 0 && p <= 1)) throw std::invalid_argument("p must be in (0, 1]");
-          return minsep_bound_pld(coef, n, sigma, c);
+          if (coef.empty() || n < 1 || !(p > 0 && p <= 1)) throw std::invalid_argument("need strategy coefficients, n_steps >= 1 and p in (0, 1]");
+          py::gil_scoped_release r;
+          auto corpus = make_minsep_corpus((int64_t)coef.size(), n, p, c.resolved_num_mc_samples(), c.seed);
+          return minsep_pld_from_corpus(corpus, coef, sigma, c);
         }, py::arg("strategy_coef"), py::arg("n_steps"), py::arg("p"), py::arg("sigma"), py::arg("config"));
-  m.def("register_b_min_sep_transcript_corpus", [](const std::vector<double>& coef, int64_t n, double p, int64_t, uint64_t) {
+  m.def("register_b_min_sep_transcript_corpus", [](const std::vector<double>& coef, int64_t n, double p, int64_t samples, uint64_t seed) {
+          if (coef.empty() || samples < 1) throw std::invalid_argument("need strategy coefficients and num_samples >= 1");
+          std::shared_ptr<MinSepCorpus> corpus;
+          {
+            py::gil_scoped_release r;
+            corpus = std::make_shared<MinSepCorpus>(make_minsep_corpus((int64_t)coef.size(), n, p, (size_t)samples, seed));
+          }
           std::lock_guard<std::mutex> g(g_ms_mu);
-          g_ms[++g_ms_next] = MinSepCorpus{coef, n, p};
+          g_ms[++g_ms_next] = corpus;
           return g_ms_next;
         }, py::arg("strategy_coef"), py::arg("n_steps"), py::arg("p"), py::arg("num_samples"), py::arg("seed"));
   m.def("drop_b_min_sep_transcript_corpus", [](int64_t h) { std::lock_guard<std::mutex> g(g_ms_mu); g_ms.erase(h); }, py::arg("handle"));
-  m.def("bandmf_b_min_sep_pld_from_transcript_handle", [](int64_t h, const std::vector<double>& coef, double, double sigma, const Config& c) {
-          int64_t n;
-          { std::lock_guard<std::mutex> g(g_ms_mu); auto it = g_ms.find(h); if (it == g_ms.end()) throw std::invalid_argument("unknown corpus handle"); n = it->second.n; }
-          return minsep_bound_pld(coef, n, sigma, c);
+  m.def("bandmf_b_min_sep_pld_from_transcript_handle", [](int64_t h, const std::vector<double>& coef, double p, double sigma, const Config& c) {
+          std::shared_ptr<MinSepCorpus> corpus;
+          { std::lock_guard<std::mutex> g(g_ms_mu); auto it = g_ms.find(h); if (it == g_ms.end()) throw std::invalid_argument("unknown corpus handle"); corpus = it->second; }
+          if (std::fabs(corpus->p - p) > 1e-12) throw std::invalid_argument("p differs from the registered corpus");
+          py::gil_scoped_release r;
+          return minsep_pld_from_corpus(*corpus, coef, sigma, c);
         }, py::arg("handle"), py::arg("strategy_coef"), py::arg("p"), py::arg("sigma"), py::arg("config"));
 
   m.def("mf_gaussian_pld", [](double nm, double sens, const Config& c) {
@@ -243,6 +231,8 @@ PYBIND11_MODULE(_opake_accounting, m) {
           return toeplitz_gram_matrix(bisr_strategy_coefficients(c, n), n, b, opt_k(k), normalized);
         }, py::arg("coefficients"), py::arg("n_steps"), py::arg("min_sep") = 1, py::arg("max_participations") = py::none(),
         py::arg("normalized") = true, py::arg("momentum") = 0.0);
+  // The reference's learning-rate-weighted Gram functions are compatibility tombstones that raise ValueError on every
+  // call (opake_accounting.pyi:760-778 and :816-826: "Raises: ValueError: Always"); the same contract is kept here.
   m.def("bisr_gram_matrix_lr", [](const std::vector<double>&, double, int64_t, int64_t, const py::object&, bool, const std::vector<double>&) -> std::vector<double> {
           throw std::invalid_argument("learning-rate-weighted BISR accounting is not supported: omit the schedule and recalibrate, or use BandMF/BLT");
         }, py::arg("coefficients"), py::arg("momentum"), py::arg("n_steps"), py::arg("min_sep"), py::arg("max_participations"),

