@@ -196,7 +196,8 @@ def main() -> None:
     ecfg = EngineConfig(clip_norm=1.0, noise_multiplier=args.sigma, logical_batch=args.batch, lr=3e-4, weight_decay=0.01,
                         noise_bias_correction=True, master_weights=False, use_cuda_graph=not args.no_graph,
                         attn_impl=args.attn, seed=1234, accumulate_group=args.group,
-                        shard_params=shard in ("params", "full"), shard_sums=shard == "full", **blt)
+                        shard_params=shard in ("params", "full"), shard_sums=shard == "full",
+                        expert_parallel=bool(mcfg.n_experts) and world > 1, seq_len=args.seq, **blt)
     eng = ShardedDPEngine(mcfg, ecfg, dev)
 
     tok = _zipf_tokens(b_local, args.seq, mcfg.vocab_size, seed=1000 + rank)
@@ -255,7 +256,7 @@ def main() -> None:
                            "full": "(full shard: optimizer moments, parameters and fp32 sums; parameters fetched inside the first "
                                    "forward GEMMs after a step, accumulation groups reduce-scattered by reductions over NVLink)",
                        }[shard] + f"; gathered bf16 parameters cached across the {b_local} accumulation micro-steps",
-                       "shard": shard,
+                       "shard": shard, "expert_parallel": f"ep{world}" if (mcfg.n_experts and world > 1) else None,
                        "clip_norm": 1.0, "noise_multiplier": args.sigma, "optimizer": "adamw-bc", "sft_mask": "first 25%",
                        "mechanism": f"dp-ftrl blt x{args.blt_buffers}" if args.blt_buffers else "dp-sgd gaussian",
                        "per_example_microbatch": 1, "cuda_graph": not args.no_graph,

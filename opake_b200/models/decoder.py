@@ -38,11 +38,14 @@ class DecoderRuntime:
     """Forward + per-example backward for dense decoders (Llama-style and GPT-2-style blocks)."""
 
     def __init__(self, cfg: DecoderConfig, params: torch.Tensor, *, layout: Layout | None = None,
-                 attn_impl: str = "auto", n_slots: int = 1, wgrad_overlap: bool = True):
+                 attn_impl: str = "auto", n_slots: int = 1, wgrad_overlap: bool = True, ep=None):
         if cfg.n_experts and (cfg.act != "swiglu" or cfg.n_experts > 256 or cfg.top_k > 32 or cfg.d_model % 8):
             raise ValueError("mixture-of-experts layers need SwiGLU experts, at most 256 experts and top_k <= 32")
         self.cfg = cfg
-        self.layout = layout or build_layout(cfg)
+        # expert parallelism: an ``ExpertParallelRuntime`` that owns this rank's experts of every layer (the layout
+        # then holds no expert matrices); ``None`` = all experts local, inside the flat parameter buffer
+        self.ep = ep
+        self.layout = layout or build_layout(cfg, skip_experts=ep is not None)
         self.device = params.device
         self.params = params
         self.w = self.layout.views(params)
@@ -116,7 +119,9 @@ class DecoderRuntime:
                  "x_mid": e(T, d), "xn2": e(T, d)}
             if cfg.qk_norm:      # pre-normalisation queries and keys, needed by the norm's backward
                 a["qk_raw"] = e(T, (cfg.n_heads + cfg.n_kv_heads) * cfg.head_dim)
-            if cfg.n_experts:
+            if cfg.n_experts and self.ep is not None:
+                pass        # token rows, pre-activations and routing state live in the expert-parallel layers
+            elif cfg.n_experts:
                 plan = K.MoePlan(T, cfg.n_experts, cfg.top_k, dev)
                 I = cfg.expert_ffn
                 a.update(plan=plan, rlogits=e(T, cfg.n_experts), xs=e(plan.R, d), gu=e(plan.R, 2 * I), act=e(plan.R, I),
@@ -147,7 +152,7 @@ class DecoderRuntime:
         ws["vec_offsets"] = torch.tensor([self.layout.slot(n).offset for n in self._vec_names], dtype=torch.int64,
                                          device=dev)
         ws["emb"], ws["tok"] = ws["embs"][0], ws["toks"][0]
-        if cfg.n_experts:
+        if cfg.n_experts and self.ep is None:
             R, I = layers[0]["plan"].R, cfg.expert_ffn
             ws.update(dye=e(R, d), dgu=e(R, 2 * I).zero_(), dxs=e(R, d).zero_(),
                       dwts=e(T, cfg.top_k, dtype=torch.float32), drl=e(T, cfg.n_experts))
@@ -259,7 +264,9 @@ class DecoderRuntime:
             G.gemm(a["attn"], wsrc, out=a["x_mid"], residual=x, bias=w.get(p + "bo"), stage=stg)
             xn2, st2 = self._norm_fwd(a["x_mid"], p + "norm2", out=a["xn2"])
             nxt = ws["layers"][li + 1]["x"] if li + 1 < cfg.n_layers else ws["x_last"]
-            if cfg.n_experts:
+            if cfg.n_experts and self.ep is not None:
+                self.ep.forward(li, xn2, a["x_mid"], nxt)
+            elif cfg.n_experts:
                 plan = a["plan"]
                 G.gemm(xn2, w[p + "router"], out=a["rlogits"])
                 K.moe_route(a["rlogits"], plan, cfg.norm_topk_prob)
@@ -348,7 +355,11 @@ class DecoderRuntime:
             p = f"layers.{li}."
             st1, st2, actx, stq = saved[li]
             # ---- MLP
-            if cfg.n_experts:
+            if cfg.n_experts and self.ep is not None:
+                # expert parallel: rows travel to the experts' owners; only squared norms of the expert gradients are
+                # formed in this pass, the router gradient is this rank's own
+                dxn2 = self.ep.backward(li, dx, router_grad_out=g[p + "router"], sumsq=sumsq, dx_out=ws["dx2"])
+            elif cfg.n_experts:
                 plan = a["plan"]
                 K.moe_combine_bwd(dx, a["ye"], plan, ws["dwts"])
                 K.moe_gather(dx, plan, ws["dye"], entry_scale=plan.wts)
@@ -478,9 +489,24 @@ class DecoderRuntime:
         self.accumulate(acc, ws, tok, slot=slot, overwrite=overwrite)
 
 
+def expert_seed(seed: int, layer: int, expert: int) -> int:
+    """Seed of one expert's initial weights: a function of the GLOBAL expert id, so the model is the same whether its
+    experts sit in one flat buffer or are spread over expert-parallel ranks."""
+    return seed * 1_000_003 + layer * 4099 + expert + 1
+
+
+def init_expert_(wgu: torch.Tensor, wd: torch.Tensor, seed: int, layer: int, expert: int, n_layers: int, std: float = 0.02) -> None:
+    gen = torch.Generator(device=wgu.device).manual_seed(expert_seed(seed, layer, expert))
+    wgu.copy_(torch.randn(wgu.shape, generator=gen, device=wgu.device, dtype=torch.float32) * std)
+    wd.copy_(torch.randn(wd.shape, generator=gen, device=wd.device, dtype=torch.float32) * (std / (2 * n_layers) ** 0.5))
+
+
 def init_params_(cfg: DecoderConfig, params: torch.Tensor, layout: Layout, seed: int = 0, std: float = 0.02) -> None:
-    """Random-normal weights (std 0.02, output projections scaled by 1/sqrt(2L)), unit norm weights, zero biases."""
-    gen = torch.Generator(device=params.device).manual_seed(seed)
+    """Random-normal weights (std 0.02, output projections scaled by 1/sqrt(2L)), unit norm weights, zero biases.
+    Every tensor draws from its own generator, seeded by the tensor's name: the values do not depend on which other
+    tensors the layout holds (expert matrices may live elsewhere under expert parallelism)."""
+    import zlib
+
     params.zero_()
     for s in layout.slots:
         v = params[s.offset : s.offset + s.numel]
@@ -488,10 +514,20 @@ def init_params_(cfg: DecoderConfig, params: torch.Tensor, layout: Layout, seed:
             v.fill_(1.0)
         elif len(s.shape) == 1:
             v.zero_()
+        elif s.name.endswith("experts.wgu"):
+            li = int(s.name.split(".")[1])
+            wd_slot = layout.slot(s.name[: -len("wgu")] + "wd")
+            wd_all = params[wd_slot.offset : wd_slot.offset + wd_slot.numel].view(wd_slot.shape)
+            wgu_all = v.view(s.shape)
+            for e in range(s.shape[0]):
+                init_expert_(wgu_all[e], wd_all[e], seed, li, e, cfg.n_layers, std)
+        elif s.name.endswith("experts.wd"):
+            continue            # filled together with the gate / up matrices above
         else:
             scale = std
-            if s.name.endswith(("wo", "wd", "wproj", "experts.wd")):
+            if s.name.endswith(("wo", "wd", "wproj")):
                 scale = std / (2 * cfg.n_layers) ** 0.5
+            gen = torch.Generator(device=params.device).manual_seed((seed * 2654435761 + zlib.crc32(s.name.encode())) & 0x7FFFFFFFFFFFFFFF)
             # chunked fill keeps the fp32 temporary small for multi-GB tensors
             step = 1 << 26
             for b in range(0, s.numel, step):

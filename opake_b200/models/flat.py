@@ -80,7 +80,9 @@ def _round_up(n: int, a: int) -> int:
     return (n + a - 1) // a * a
 
 
-def build_layout(cfg: DecoderConfig, shard_multiple: int = 1) -> Layout:
+def build_layout(cfg: DecoderConfig, shard_multiple: int = 1, skip_experts: bool = False) -> Layout:
+    """``skip_experts``: leave the expert matrices of mixture-of-experts layers out (expert parallelism keeps every
+    rank's experts in a separate, rank-private buffer; the router stays here)."""
     slots: list[Slot] = []
     off = 0
     n_params = 0
@@ -112,8 +114,9 @@ def build_layout(cfg: DecoderConfig, shard_multiple: int = 1) -> Layout:
             add(p + "norm2.bias", d)
         if cfg.n_experts:
             add(p + "router", cfg.n_experts, d)
-            add(p + "experts.wgu", cfg.n_experts, 2 * cfg.expert_ffn, d)
-            add(p + "experts.wd", cfg.n_experts, d, cfg.expert_ffn)
+            if not skip_experts:
+                add(p + "experts.wgu", cfg.n_experts, 2 * cfg.expert_ffn, d)
+                add(p + "experts.wd", cfg.n_experts, d, cfg.expert_ffn)
         elif cfg.act in ("swiglu", "geglu"):
             add(p + "wgu", 2 * cfg.ffn, d)   # rows interleaved: 2j = gate_j, 2j+1 = up_j
             add(p + "wd", d, cfg.ffn)

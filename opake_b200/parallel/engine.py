@@ -63,6 +63,10 @@ class EngineConfig:
     #                 reduce-scattered to the owners with reductions over NVLink while the next group's forward runs
     shard_params: bool = False
     shard_sums: bool = False
+    # Expert parallelism for mixture-of-experts models on more than one rank: every rank keeps n_experts / world experts
+    # of every layer (parameters, sums and moments), tokens travel to the owners; needs the sequence length up front
+    expert_parallel: bool = False
+    seq_len: int = 0
 
 
 class ShardedDPEngine:
@@ -70,7 +74,10 @@ class ShardedDPEngine:
         self.model_cfg, self.cfg, self.device = model_cfg, cfg, device
         self.world = dist.get_world_size() if dist.is_initialized() else 1
         self.rank = dist.get_rank() if dist.is_initialized() else 0
-        self.layout = build_layout(model_cfg, shard_multiple=self.world)
+        self.expert_parallel = bool(cfg.expert_parallel) and bool(model_cfg.n_experts) and self.world > 1
+        if self.expert_parallel and cfg.seq_len <= 0:
+            raise ValueError("expert parallelism sizes its token buffers at start-up: set EngineConfig.seq_len")
+        self.layout = build_layout(model_cfg, shard_multiple=self.world, skip_experts=self.expert_parallel)
         total = self.layout.total
         self.shard_params = bool(cfg.shard_params) and self.world > 1
         self.shard_sums = bool(cfg.shard_sums) and self.world > 1
@@ -118,7 +125,15 @@ class ShardedDPEngine:
         if cfg.accumulate_group and not 2 <= int(cfg.accumulate_group) <= 8:
             raise ValueError(f"accumulate_group must be 0 (automatic) or between 2 and 8, got {cfg.accumulate_group}")
         self.group = int(cfg.accumulate_group) or self._pick_group_size()
-        self.runtime = DecoderRuntime(model_cfg, self.params, layout=self.layout, attn_impl=cfg.attn_impl, n_slots=self.group)
+        self.ep = None
+        if self.expert_parallel:
+            from .ep_runtime import ExpertParallelRuntime
+
+            views = self.layout.views(self.params)
+            routers = [views[f"layers.{i}.router"] for i in range(model_cfg.n_layers)]
+            self.ep = ExpertParallelRuntime(model_cfg, routers, cfg.seq_len, device, init_seed=init_seed)
+        self.runtime = DecoderRuntime(model_cfg, self.params, layout=self.layout, attn_impl=cfg.attn_impl, n_slots=self.group,
+                                      ep=self.ep)
         self._side = torch.cuda.Stream(device=device)
         self._warm: dict[int, bool] = {}
         self.step_count = 0
@@ -148,7 +163,8 @@ class ShardedDPEngine:
         # an 8B model: 142 GB in use with a group of 2, 14 GB more per additional buffer; 20 GB of reserve leave at
         # least 21 GB free in every 1 / 2 / 4 / 8-GPU configuration. Groups above 6 are not used automatically.
         reserve = 20 << 30 if g_bytes > (4 << 30) else 4 * g_bytes + (2 << 30)
-        cap = 6 if g_bytes > (4 << 30) else 8
+        # with sharded sums every accumulation pass crosses NVLink, so a larger group pays directly: up to 8 there
+        cap = 8 if (g_bytes <= (4 << 30) or getattr(self, "shard_sums", False)) else 6
         return int(max(2, min(cap, (free - reserve) // max(g_bytes, 1))))
 
     # ------------------------------------------------------------------ one example
@@ -217,11 +233,22 @@ class ShardedDPEngine:
             for off, n, owner in copies:
                 K.copy_bytes(self.params.data_ptr() + 2 * off, self.params_pb.ptrs[owner] + 2 * off, 2 * n, self.device)
             rt._fetch = fetch
+        if self.ep is not None:
+            self.ep.begin_example()
         try:
             st = rt.example_grad(ws["toks"][slot], ws["labels"], ws=ws, slot=slot, before_wgrad=hook)
         finally:
             rt._fetch = None
-        rt.clip_factor(cfg.clip_norm, auto=cfg.auto_clip, gamma=cfg.auto_gamma, slot=slot)
+        if self.ep is not None:
+            # the example's squared norm has parts on every rank that owns experts: combine them, derive every
+            # example's clip factor, and form the clipped expert-gradient sums (pass 2) while the rows are still there
+            scales = self.ep.clip_factors(rt.sumsqs[slot], cfg.clip_norm, auto=cfg.auto_clip, gamma=cfg.auto_gamma,
+                                          n_leaves=rt._n_leaves + 2 * self.model_cfg.n_layers,
+                                          widest_leaf=max(rt._widest, self.ep.n_wgu), counters=rt.clip_count)
+            rt.scales[slot].copy_(scales[self.rank : self.rank + 1])
+            self.ep.accumulate_clipped()
+        else:
+            rt.clip_factor(cfg.clip_norm, auto=cfg.auto_clip, gamma=cfg.auto_gamma, slot=slot)
         ws["loss_sum"].add_(st.loss.reshape(1))
         if slot == 0:
             ws["tok_keep"].copy_(ws["toks"][0])      # slot 0's tokens are replaced before its deferred pass runs
@@ -240,7 +267,9 @@ class ShardedDPEngine:
             self._stale = False
         ws["toks"][slot].copy_(tok_host, non_blocking=True)
         ws["labels"].copy_(labels_host, non_blocking=True)
-        if not self.cfg.use_cuda_graph:
+        if not self.cfg.use_cuda_graph or self.ep is not None:
+            # expert-parallel layers pass a new epoch number to their exchange kernels on every call, which a captured
+            # graph would freeze: those examples are launched directly
             self._example_body(ws, slot, drain, refresh)
             return
         key = (T, slot, drain, refresh)
@@ -282,6 +311,12 @@ class ShardedDPEngine:
         """
         cfg = self.cfg
         B_local = tokens.shape[0]
+        if self.ep is not None:
+            if tokens.shape[1] != self.cfg.seq_len:
+                raise ValueError(f"expert-parallel buffers were sized for sequences of {self.cfg.seq_len} tokens")
+            # the exchange kernels wait for their peers with a bounded budget: start every step together
+            torch.cuda.synchronize(self.device)
+            dist.barrier()
         ws = self.runtime.workspace(tokens.shape[1])
         if "loss_sum" not in ws:
             ws["loss_sum"] = torch.zeros(1, dtype=torch.float32, device=self.device)
@@ -326,6 +361,10 @@ class ShardedDPEngine:
             bc2=1.0 - b2**t, phi_hat=phi_hat, zero_grad=self.shard_sums, blt_state=self.blt_state, blt_decay=self.blt_decay,
             blt_scale=self.blt_scale, toep_state=self.toep_state, toep_coef=self.toep_coef, toep_pos=self.toep_pos,
             sgd_mode=(cfg.optimizer == "sgd"), device=self.device)
+        if self.ep is not None:
+            self.ep.apply_update(noise_offset=self.layout.total, inv_batch=1.0 / cfg.logical_batch, sigma=sigma, seed=step_key.seed,
+                                 step=self.step_count, lr=cfg.lr, beta1=b1, beta2=b2, eps=cfg.eps, weight_decay=cfg.weight_decay,
+                                 bc1=1.0 - b1**t, bc2=1.0 - b2**t, phi_hat=phi_hat, sgd_mode=(cfg.optimizer == "sgd"))
         if self.toep_state is not None:
             self.toep_pos = (self.toep_pos - 1) % self.toep_state.shape[0]
         if self.world > 1:
@@ -361,6 +400,8 @@ class ShardedDPEngine:
         if self.rank == 0:
             self.gather_params()
             out["params"] = self.params.cpu()
+        if self.ep is not None:
+            out["experts"] = self.ep.state_dict()
         return out
 
     def load_state_dict(self, sd: dict, params: torch.Tensor | None = None) -> None:
@@ -380,6 +421,8 @@ class ShardedDPEngine:
         p = sd.get("params") if params is None else params
         if p is not None:
             self.params.copy_(p)
+        if self.ep is not None and sd.get("experts") is not None:
+            self.ep.load_state_dict(sd["experts"])
 
     def _rotate(self, ptrs: list[int]) -> list[int]:
         """This rank's buffer first, then the peers starting at rank+1 (spreads NVLink traffic across peers)."""

@@ -120,6 +120,7 @@ class FusedExpertParallelLayer:
         self.ss = torch.zeros(2, El * ctx.world, dtype=torch.float64, device=dev)
         self.epoch = 0
         self.x = None
+        self._one = self._gwd = self._gwgu = None
 
     # ------------------------------------------------------------------ forward
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
@@ -155,12 +156,17 @@ class FusedExpertParallelLayer:
         return out
 
     # ------------------------------------------------------------------ backward, pass 1
-    def backward(self, dy: torch.Tensor):
+    def backward(self, dy: torch.Tensor, *, router_grad_out: torch.Tensor | None = None, sumsq: torch.Tensor | None = None,
+                 dx_out: torch.Tensor | None = None):
         """Returns ``(dx, d_router, expert_sq_norms)``: input gradient and router weight gradient of THIS rank's
         example, and for every source rank the squared norm of its example's gradient w.r.t. the local experts
         (float64 ``[world]``). No expert weight gradient is stored; see :meth:`accumulate_clipped`."""
         c, L, s = self.ctx, _L(), self.ctx._s()
-        T, k, d, n, ep = self.T, self.k, self.d, self.ctx.n_entries, self.epoch
+        T, k, d, n = self.T, self.k, self.d, self.ctx.n_entries
+        # the backward phases take a fresh epoch: layers run backward in the opposite order of their forward epochs,
+        # and a flag wait is "flag >= epoch", so reusing the forward epoch would let a layer pass on a later layer's flag
+        c.epoch += 1
+        ep = c.epoch
         err = _p(c.err)
         x = self.x
         # d(combination weights) needs the expert outputs of the owners; the upstream rows go out weighted
@@ -179,13 +185,14 @@ class FusedExpertParallelLayer:
         G.gemm(self.dgu, self.wgu, b_mn=True, out=self.dxs, tile_group=self.tile_group)
         _lib.check(L.opk_ep_signal(c.g, PHASE_DOUT, ep, s), "ep_signal")
         norms = self.ss.sum(0).view(self.El, c.world).sum(0)
-        dx = torch.empty(T, d, dtype=_bf16, device=dy.device)
+        dx = dx_out if dx_out is not None else torch.empty(T, d, dtype=_bf16, device=dy.device)
         _lib.check(L.opk_ep_combine(c.g, self.dxs_peers, _p(self.entry_pos), None, k, None, T, d, _p(dx), PHASE_DOUT, ep, err, s),
                    "ep_combine")
         # router (replicated weight, this rank's example only)
         _lib.check(L.opk_moe_route_bwd(_p(self.probs), _p(self.idx), _p(self.dwts), T, self.E, k, int(self.norm_topk),
                                        _p(self.drl), self.drl.stride(0), s), "moe_route_bwd")
-        d_router = G.linear_wgrad(self.drl, x)
+        # ``router_grad_out`` / ``sumsq``: the caller's per-example gradient slot and squared-norm accumulator
+        d_router = G.linear_wgrad(self.drl, x, out=router_grad_out, sumsq=sumsq)
         G.gemm(self.drl, self.router_w, b_mn=True, out=dx, residual=dx)
         return dx, d_router, norms
 
@@ -199,7 +206,13 @@ class FusedExpertParallelLayer:
                    "ep_scale_rows")
         _lib.check(L.opk_ep_scale_rows(_p(self.dgu), _p(self.row_src), _p(scales), c.r_cap, 2 * self.I, _p(self.scaled_f), s),
                    "ep_scale_rows")
-        gwd = G.gemm(self.scaled_d, self.act, a_mn=True, b_mn=True, group_k=self.gk_expert)
-        gwgu = G.gemm(self.scaled_f, self.recv_x, a_mn=True, b_mn=True, group_k=self.gk_expert)
-        acc_wd.add_(gwd)
-        acc_wgu.add_(gwgu)
+        from ..ops import kernels as K
+
+        if self._one is None:
+            self._one = torch.ones(1, dtype=torch.float32, device=self.gu.device)
+            self._gwd = torch.empty(self.El, self.d, self.I, dtype=_bf16, device=self.gu.device)
+            self._gwgu = torch.empty(self.El, 2 * self.I, self.d, dtype=_bf16, device=self.gu.device)
+        G.gemm(self.scaled_d, self.act, a_mn=True, b_mn=True, group_k=self.gk_expert, out=self._gwd)
+        G.gemm(self.scaled_f, self.recv_x, a_mn=True, b_mn=True, group_k=self.gk_expert, out=self._gwgu)
+        K.clip_accumulate(self._gwd.view(-1), self._one, acc_wd.view(-1))
+        K.clip_accumulate(self._gwgu.view(-1), self._one, acc_wgu.view(-1))

@@ -27,6 +27,8 @@ def main() -> None:
     ap.add_argument("--shard-params", action="store_true", help="owners keep the parameters; fetched inside the forward GEMMs")
     ap.add_argument("--shard-sums", action="store_true", help="fp32 sums sharded, accumulation groups reduce-scattered")
     ap.add_argument("--graph", action="store_true", help="run the examples through CUDA graphs")
+    ap.add_argument("--ep-train", action="store_true",
+                    help="train a tiny mixture-of-experts decoder: all experts local on one rank, expert parallel on several")
     ap.add_argument("--sharded-linear", action="store_true", help="check the sharded-weight GEMMs instead of the engine")
     ap.add_argument("--ep-fused", action="store_true", help="check the expert-parallel dispatch / combine kernels")
     ap.add_argument("--sharded-linear-bench", action="store_true",
@@ -47,6 +49,9 @@ def main() -> None:
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
+        return
+    if a.ep_train:
+        _ep_train(rank, world, dev, a)
         return
     cfg = tiny_llama()
     if a.seq > cfg.max_seq:
@@ -77,6 +82,58 @@ def main() -> None:
         staged = sorted(eng._refresh_plan(a.seq)[0]) if eng.shard_params else []
         torch.save({"params": eng.params.float().cpu(), "losses": losses, "world": world, "staged": staged,
                     "bounds": list(eng.bounds)}, a.out)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _ep_train(rank: int, world: int, dev: torch.device, a) -> None:
+    """DP steps of a tiny mixture-of-experts decoder without noise. On one rank every expert is local (grouped GEMMs
+    inside the flat runtime); on several ranks the experts are sharded and tokens travel (expert-parallel layers,
+    two-pass clipping across ranks). Same logical batch, same initial weights: the losses of every step and the final
+    router and expert weights must agree."""
+    from opake_b200.ops._lib import raise_if_device_error
+
+    cfg = tiny_llama(n_experts=8, top_k=2, expert_ffn=64, d_model=128, n_heads=2, n_kv_heads=2, head_dim=64, ffn=0, max_seq=256,
+                     name="tiny-moe", family="olmoe")
+    T = 256
+    ecfg = EngineConfig(logical_batch=a.batch, noise_multiplier=0.0, clip_norm=0.5, lr=2e-2, seed=5, use_cuda_graph=False,
+                        accumulate_group=2, expert_parallel=True, seq_len=T)
+    eng = ShardedDPEngine(cfg, ecfg, dev)
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(0, cfg.vocab_size, (a.batch, T), generator=g, dtype=torch.int32)
+    labels = torch.roll(tok, -1, 1).clone()
+    labels[:, -1] = -100
+    per = a.batch // world
+    mine = slice(rank * per, (rank + 1) * per)
+    losses = []
+    for _ in range(a.steps):
+        l = eng.step(tok[mine].pin_memory(), labels[mine].pin_memory())
+        if world > 1:
+            dist.all_reduce(l)
+        losses.append(l.item() / a.batch)
+    torch.cuda.synchronize()
+    raise_if_device_error(dev)
+    views = eng.layout.views(eng.params)
+    routers = torch.stack([views[f"layers.{i}.router"].float().cpu() for i in range(cfg.n_layers)])
+    if eng.ep is None:
+        wgu = torch.stack([views[f"layers.{i}.experts.wgu"].float().cpu() for i in range(cfg.n_layers)])
+        wd = torch.stack([views[f"layers.{i}.experts.wd"].float().cpu() for i in range(cfg.n_layers)])
+        clipped = int(eng.runtime.clip_count.item())
+    else:
+        parts = [torch.empty_like(eng.ep.params) for _ in range(world)]
+        dist.all_gather(parts, eng.ep.params)
+        wgu_l, wd_l = [], []
+        for i in range(cfg.n_layers):
+            per_rank = [eng.ep.views(p, i) for p in parts]
+            wgu_l.append(torch.cat([v[0] for v in per_rank]).float().cpu())
+            wd_l.append(torch.cat([v[1] for v in per_rank]).float().cpu())
+        wgu, wd = torch.stack(wgu_l), torch.stack(wd_l)
+        c = eng.runtime.clip_count.clone().to(torch.int64)
+        dist.all_reduce(c)
+        clipped = int(c.item())
+    if rank == 0:
+        torch.save({"losses": losses, "routers": routers, "wgu": wgu, "wd": wd, "world": world, "clipped": clipped}, a.out)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
