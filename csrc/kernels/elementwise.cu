@@ -589,6 +589,66 @@ __global__ void lce_finalize_kernel(const float* __restrict__ pmax, const float*
   }
 }
 
+// Per-example RMSNorm weight gradient: dw[b][c] += sum over the rows of example b of dy * x * rstd (the normalised
+// input). One thread per column, grid.y = example, grid.z = row chunk; fp32 atomics combine the row chunks.
+__global__ void __launch_bounds__(256) rmsnorm_dw_per_example_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                                     const __nv_bfloat16* __restrict__ x,
+                                                                     const float* __restrict__ rstd, float* __restrict__ dw,
+                                                                     int rows, int D) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= D) return;
+  const long long b = blockIdx.y;
+  const int chunk = (rows + gridDim.z - 1) / gridDim.z;
+  const int r0 = blockIdx.z * chunk, r1 = min(rows, r0 + chunk);
+  float acc = 0.f;
+  for (int r = r0; r < r1; ++r) {
+    const long long row = b * rows + r;
+    acc += __bfloat162float(dy[row * D + c]) * __bfloat162float(x[row * D + c]) * rstd[row];
+  }
+  if (r1 > r0) atomicAdd(&dw[b * D + c], acc);
+}
+
+// Per-example loss bookkeeping in one CTA: ntok = max(1, #labels >= 0); coef[t] = [label >= 0] / ntok (* *weight);
+// loss = sum_t nll[t] * coef[t]. Two block reductions; T is a sequence length.
+__global__ void __launch_bounds__(1024) loss_coef_kernel(const int* __restrict__ labels, const float* __restrict__ nll,
+                                                         const float* __restrict__ weight, float* __restrict__ coef,
+                                                         float* __restrict__ loss, float* __restrict__ ntok, int T) {
+  __shared__ float red[32];
+  __shared__ float bcast;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float cnt = 0.f;
+  for (int t = threadIdx.x; t < T; t += blockDim.x) cnt += labels[t] >= 0 ? 1.f : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  if (lane == 0) red[warp] = cnt;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += red[w];
+    bcast = fmaxf(s, 1.f);
+  }
+  __syncthreads();
+  const float n = bcast;
+  const float w = weight ? *weight : 1.f;
+  float acc = 0.f;
+  for (int t = threadIdx.x; t < T; t += blockDim.x) {
+    const float c = labels[t] >= 0 ? w / n : 0.f;
+    coef[t] = c;
+    acc += nll[t] * c;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  __syncthreads();
+  if (lane == 0) red[warp] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int wi = 0; wi < (int)(blockDim.x >> 5); ++wi) s += red[wi];
+    *loss = s;
+    if (ntok) *ntok = n;
+  }
+}
+
 template <bool FP32>
 __device__ __forceinline__ float load_logit(const void* p, long long i) {
   return FP32 ? reinterpret_cast<const float*>(p)[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
@@ -878,6 +938,24 @@ extern "C" int opk_lce_finalize(const float* pmax, const float* psum, const floa
                                 float* lse, float* nll, int T, int tiles, void* stream) {
   if (T <= 0) return 0;
   lce_finalize_kernel<<<(T + 7) / 8, 256, 0, ST(stream)>>>(pmax, psum, tgt, labels, lse, nll, T, tiles);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_rmsnorm_dw_per_example(const void* dy, const void* x, const float* rstd, float* dw, int B, int rows, int D,
+                                          void* stream) {
+  if (B <= 0 || rows <= 0 || D <= 0) return 0;
+  if (B > 65535) return -1;
+  int z = (rows + 63) / 64;
+  if (z > 32) z = 32;
+  dim3 grid((D + 255) / 256, B, z);
+  rmsnorm_dw_per_example_kernel<<<grid, 256, 0, ST(stream)>>>(BF(dy), BF(x), rstd, dw, rows, D);
+  OPK_LAUNCH_CHECK();
+  return 0;
+}
+extern "C" int opk_loss_coef(const int32_t* labels, const float* nll, const float* weight, float* coef, float* loss, float* ntok,
+                             int T, void* stream) {
+  if (T <= 0 || !labels || !nll || !coef || !loss) return -1;
+  loss_coef_kernel<<<1, 1024, 0, ST(stream)>>>(labels, nll, weight, coef, loss, ntok, T);
   OPK_LAUNCH_CHECK();
   return 0;
 }

@@ -111,6 +111,13 @@ int opk_embedding_accumulate_shared(const int32_t* tok, const int32_t* rep, cons
 // Fused linear-cross-entropy finalisation: lse[t] from the per-tile partials, nll[t] = lse - tgt (0 if ignored).
 int opk_lce_finalize(const float* pmax, const float* psum, const float* tgt, const int32_t* labels, float* lse,
                      float* nll, int T, int tiles, void* stream);
+// Per-example RMSNorm weight gradients under a batched (vmapped) backward: dy, x are [B * rows][D] bf16 (example b owns
+// rows b*rows .. (b+1)*rows - 1), rstd [B * rows]; dw [B][D] fp32 is ACCUMULATED into (zero it first).
+int opk_rmsnorm_dw_per_example(const void* dy, const void* x, const float* rstd, float* dw, int B, int rows, int D, void* stream);
+// Per-example loss bookkeeping: ntok = max(1, number of labels >= 0); coef[t] = (label >= 0) / ntok, times *weight when
+// weight != NULL; *loss = sum_t nll[t] * coef[t]; *ntok (may be NULL) = ntok. One CTA.
+int opk_loss_coef(const int32_t* labels, const float* nll, const float* weight, float* coef, float* loss, float* ntok, int T,
+                  void* stream);
 // Row-wise cross entropy over materialised logits (bf16 or fp32): nll[t], optional lse[t]; softcap / scale as LCE.
 int opk_cross_entropy_fwd(const void* logits, int is_fp32, const int32_t* labels, float* nll, float* lse, int T, int V,
                           int64_t ld, float scale, float softcap, void* stream);

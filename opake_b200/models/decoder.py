@@ -148,6 +148,7 @@ class DecoderRuntime:
             "toks": [torch.zeros(T, dtype=torch.int32, device=dev) for _ in range(self.n_slots)],
             "labels": torch.zeros(T, dtype=torch.int32, device=dev),
             "loss": torch.zeros(1, dtype=torch.float32, device=dev), "ntok": torch.zeros(1, dtype=torch.float32, device=dev),
+            "coef": torch.zeros(T, dtype=torch.float32, device=dev),
         }
         ws["vec_offsets"] = torch.tensor([self.layout.slot(n).offset for n in self._vec_names], dtype=torch.int64,
                                          device=dev)
@@ -328,12 +329,8 @@ class DecoderRuntime:
         emb_ws = ws["embs"][slot]
         H, KV, hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
         nll, lse, (saved, stf) = self.forward(tok, labels, ws)
-        valid = (labels >= 0).to(torch.float32)
-        ntok = valid.sum().clamp_(min=1.0)
-        coef = valid / ntok
-        if loss_weight is not None:
-            coef = coef * loss_weight
-        loss = (nll * coef).sum()
+        coef, loss, ntok = ws["coef"], ws["loss"], ws["ntok"]
+        K.loss_coef(labels, nll, coef, loss, ntok, weight=loss_weight)
         ws["vec"].zero_()
         sumsq.zero_()
 

@@ -60,6 +60,8 @@ PROTOTYPES: dict = {
     "opk_embedding_bwd_compact": (I, [P, P, P, P, P, P, I, I, I, P]),
     "opk_embedding_accumulate": (I, [P, P, P, P, P, I, I, P]),
     "opk_lce_finalize": (I, [P, P, P, P, P, P, I, I, P]),
+    "opk_loss_coef": (I, [P, P, P, P, P, P, I, P]),
+    "opk_rmsnorm_dw_per_example": (I, [P, P, P, P, I, I, I, P]),
     "opk_cross_entropy_fwd": (I, [P, I, P, P, P, I, I, L, F, F, P]),
     "opk_cross_entropy_bwd": (I, [P, I, P, P, P, P, I, I, L, F, F, P]),
     "opk_sumsq": (I, [P, I, I, L, P, P]),

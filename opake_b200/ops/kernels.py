@@ -207,6 +207,22 @@ def lce_finalize(pmax, psum, tgt, labels):
     return lse, nll
 
 
+def rmsnorm_dw_per_example(dy, x, rstd, batch: int):
+    """``[batch, D]`` fp32 RMSNorm weight gradients, one per example, of a batch folded into rows (``dy``, ``x``:
+    ``[batch * rows, D]`` bf16 contiguous; ``rstd``: ``[batch * rows]``)."""
+    D = x.shape[-1]
+    rows = x.numel() // D // batch
+    dw = torch.zeros(batch, D, dtype=torch.float32, device=x.device)
+    _chk(_L().opk_rmsnorm_dw_per_example(_p(dy), _p(x), _p(rstd), _p(dw), batch, rows, D, _s(x)), "rmsnorm_dw_per_example")
+    return dw
+
+
+def loss_coef(labels, nll, coef, loss, ntok=None, weight=None):
+    """Mean-over-supervised-tokens loss of one example and the per-token coefficients of its gradient:
+    ``coef[t] = (labels[t] >= 0) / max(1, n_supervised)`` (times ``weight``), ``loss = sum(nll * coef)``."""
+    _chk(_L().opk_loss_coef(_p(labels), _p(nll), _p(weight), _p(coef), _p(loss), _p(ntok), labels.numel(), _s(nll)), "loss_coef")
+
+
 def cross_entropy_fwd(logits, labels, scale: float = 1.0, softcap: float = 0.0):
     T, V = logits.shape
     nll = torch.empty(T, dtype=torch.float32, device=logits.device)

@@ -61,8 +61,10 @@ class _RMSNormBwd(torch.autograd.Function):
         D = x.shape[-1]
         dx = K.rmsnorm_bwd(dy.reshape(-1, D).contiguous(), x.reshape(-1, D).contiguous(), w, rstd.reshape(-1).contiguous(),
                            dw=None, w_offset=offset).view_as(x)
-        xhat = x.reshape(B, -1, D).float() * rstd.reshape(B, -1, 1)
-        dw = (dy.reshape(B, -1, D).float() * xhat).sum(1).to(w.dtype)         # stays per example
+        # the weight gradient stays per example: one reduction kernel over each example's rows
+        # (packages/opake-patches/src/opake/api/patches/kernels/rms_norm.py:292-373)
+        dw = K.rmsnorm_dw_per_example(dy.reshape(-1, D).contiguous(), x.reshape(-1, D).contiguous(),
+                                      rstd.reshape(-1).contiguous(), B).to(w.dtype)
         return (dx, dw), (0, 0)
 
 
@@ -103,8 +105,84 @@ def opake_rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, off
     return _rms_ref(x, weight, eps, offset)
 
 
+class _AddRMSNormBwd(torch.autograd.Function):
+    """``d(x) = d(residual) = ds + d(rmsnorm)/d(sum)``: the residual gradient is added inside the norm-backward kernel."""
+
+    @staticmethod
+    def forward(dy, ds, s, w, rstd, offset):
+        from ...ops import kernels as K
+        D = s.shape[-1]
+        dw = torch.zeros(D, dtype=torch.float32, device=s.device)
+        dx = K.rmsnorm_bwd(dy.reshape(-1, D).contiguous(), s.reshape(-1, D).contiguous(), w, rstd.reshape(-1),
+                           dres=ds.reshape(-1, D).contiguous(), dw=dw, w_offset=offset)
+        return dx.view_as(s), dw.to(w.dtype)
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        pass
+
+    @staticmethod
+    def backward(ctx, *g):
+        raise NotImplementedError("double backward through the fused add + RMSNorm is not supported")
+
+    @staticmethod
+    def vmap(info, in_dims, dy, ds, s, w, rstd, offset):
+        from ...ops import kernels as K
+        if in_dims[3] is not None:
+            raise NotImplementedError("per-example norm weights are not supported")
+        B = info.batch_size
+        dy, ds, s, rstd = (_front(t, d, B) for t, d in zip((dy, ds, s, rstd), (in_dims[0], in_dims[1], in_dims[2], in_dims[4])))
+        D = s.shape[-1]
+        dy2, s2, r1 = dy.reshape(-1, D).contiguous(), s.reshape(-1, D).contiguous(), rstd.reshape(-1).contiguous()
+        dx = K.rmsnorm_bwd(dy2, s2, w, r1, dres=ds.reshape(-1, D).contiguous(), dw=None, w_offset=offset).view_as(s)
+        dw = K.rmsnorm_dw_per_example(dy2, s2, r1, B).to(w.dtype)
+        return (dx, dw), (0, 0)
+
+
+class _AddRMSNorm(torch.autograd.Function):
+    """``s = x + residual; y = rmsnorm(s)`` in one kernel (packages/opake-patches/src/opake/api/patches/kernels/
+    fused_add_rms_norm.py:68-134); returns ``(y, s, rstd)``."""
+
+    @staticmethod
+    def forward(x, residual, w, eps, offset):
+        from ...ops import kernels as K
+        D = x.shape[-1]
+        s, y, rstd = K.add_rmsnorm_fwd(x.reshape(-1, D).contiguous(), residual.reshape(-1, D).contiguous(), w, eps, offset)
+        return y.view_as(x), s.view_as(x), rstd.view(x.shape[:-1])
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        _x, _r, w, _eps, offset = inputs
+        ctx.save_for_backward(output[1], w, output[2])
+        ctx.mark_non_differentiable(output[2])
+        ctx.offset = offset
+
+    @staticmethod
+    def backward(ctx, dy, ds, _drstd):
+        s, w, rstd = ctx.saved_tensors
+        if ds is None:
+            ds = torch.zeros_like(s)
+        if dy is None:
+            dy = torch.zeros_like(s)
+        dx, dw = _AddRMSNormBwd.apply(dy.contiguous(), ds.contiguous(), s, w, rstd, ctx.offset)
+        return dx, dx, dw, None, None
+
+    @staticmethod
+    def vmap(info, in_dims, x, residual, w, eps, offset):
+        if in_dims[2] is not None:
+            raise NotImplementedError("per-example norm weights are not supported")
+        B = info.batch_size
+        x, residual = _front(x, in_dims[0], B), _front(residual, in_dims[1], B)
+        y, s, rstd = _AddRMSNorm.apply(x, residual, w, eps, offset)
+        return (y, s, rstd), (0, 0, 0)
+
+
 def opake_fused_add_rms_norm(x, residual, weight, eps: float = 1e-6, offset: float = 0.0):
-    """Returns ``(normed, new_residual)`` with ``new_residual = x + residual``."""
+    """Returns ``(normed, new_residual)`` with ``new_residual = x + residual``; one kernel forward, and the residual
+    gradient is folded into the norm's backward kernel."""
+    if native_rows(x) and residual.dtype == x.dtype and residual.shape == x.shape and weight.dtype == torch.bfloat16:
+        y, s, _ = _AddRMSNorm.apply(x, residual, weight, float(eps), float(offset))
+        return y, s
     s = x + residual
     return opake_rms_norm(s, weight, eps, offset), s
 

@@ -194,9 +194,10 @@ class DPTrainer:
             raise ConfigurationError("native_engine=True needs a NativeCausalLM model and a CUDA device")
         if want is False:
             return False
-        if ok and (self.args.is_dpftrl and self.args.privacy_noise_mechanism not in ("mf_blt", "mf_identity")):
+        if ok and (self.args.is_dpftrl and self.args.privacy_noise_mechanism not in ("mf_blt", "mf_identity", "mf_band", "mf_bsr")):
             if want is True:
-                raise ConfigurationError("the native engine implements Gaussian and buffered-linear-Toeplitz noise")
+                raise ConfigurationError("the native engine implements Gaussian, buffered-linear-Toeplitz, band-MF and "
+                                         "banded-square-root noise")
             return False
         if ok and self.args.clipping_mode == "adaptive":
             return False
@@ -439,7 +440,15 @@ class DPTrainer:
             # the injected noise is sigma * sens(C) * C^-1 z: the engine's buffers apply C^-1, the factor goes here
             nm_eff *= math.sqrt(rt["strategy"].sensitivity_squared(n_steps=ctx.n_steps, min_sep=ctx.min_sep,
                                                                    max_participations=ctx.max_participations))
-        ecfg = EngineConfig(clip_norm=float(norm), noise_multiplier=nm_eff, logical_batch=int(rt["expected_batch"]),
+        toeplitz_coef: tuple = ()
+        if a.privacy_noise_mechanism in ("mf_band", "mf_bsr"):
+            ctx = rt["mf_ctx"]
+            # banded Toeplitz strategies: the engine's ring applies C^{-1} (first column = strategy coefficients), the
+            # sensitivity factor of the injected noise sigma * sens(C) * C^{-1} z goes into the multiplier
+            toeplitz_coef = tuple(float(x) for x in rt["strategy"].strategy_coefficients(ctx.n_steps))
+            nm_eff *= math.sqrt(rt["strategy"].sensitivity_squared(n_steps=ctx.n_steps, min_sep=ctx.min_sep,
+                                                                   max_participations=ctx.max_participations))
+        ecfg = EngineConfig(clip_norm=float(norm), noise_multiplier=nm_eff, toeplitz_coef=toeplitz_coef, logical_batch=int(rt["expected_batch"]),
                             lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon, weight_decay=a.weight_decay,
                             noise_bias_correction=name in ("adamw-bc", "adamw_bc"), optimizer="sgd" if name == "sgd" else "adamw",
                             auto_clip=a.clipping_mode == "auto", seed=a.seed, use_cuda_graph=bool(a.cuda_graphs) or True,

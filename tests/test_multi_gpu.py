@@ -80,7 +80,8 @@ def test_expert_parallel_training_matches_local_experts(tmp_path):
     assert one["losses"] == pytest.approx(two["losses"], rel=3e-3)
     for name in ("routers", "wgu", "wd"):
         diff = (one[name] - two[name]).abs().max().item()
-        assert diff <= 3e-2 * one[name].abs().max().item(), (name, diff)
+        assert diff <= 2e-2 * one[name].abs().max().item(), (name, diff)
+    assert one["moved"] > 1e-3                                              # the weights did change
 
 
 def test_sharded_linear_reads_peer_shards(tmp_path):

@@ -80,6 +80,40 @@ def test_rowwise_wrappers_under_vmap_grad(cuda):
     assert (a - F.gelu(x.float(), approximate="tanh") * u.float()).abs().max() < 5e-2
 
 
+def test_fused_add_rms_norm_under_vmap_grad(cuda):
+    """One-kernel ``s = x + r; y = rmsnorm(s)`` with the residual gradient folded into the norm backward, under
+    ``vmap(grad)``: per-example weight gradients come from the per-example reduction kernel."""
+    from opake_b200.patches.kernels import opake_fused_add_rms_norm
+    torch.manual_seed(1)
+    B, T, D = 4, 50, 128
+    x = (torch.randn(B, T, D, device=cuda) * 0.7).to(torch.bfloat16)
+    r = (torch.randn(B, T, D, device=cuda) * 0.7).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(D, device=cuda)).to(torch.bfloat16)
+    t1 = torch.randn(T, D, device=cuda)
+    t2 = torch.randn(T, D, device=cuda)
+
+    def ours(w_, xe, re):
+        y, s = opake_fused_add_rms_norm(xe, re, w_, 1e-6)
+        return (y.float() * t1).sum() + (s.float() * t2).sum()
+
+    def ref(w_, xe, re):
+        s = xe + re
+        y = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * w_
+        return (y * t1).sum() + (s * t2).sum()
+
+    g1 = torch.func.vmap(torch.func.grad(ours, argnums=(0, 1, 2)), in_dims=(None, 0, 0))(w, x, r)
+    g2 = torch.func.vmap(torch.func.grad(ref, argnums=(0, 1, 2)), in_dims=(None, 0, 0))(w.float(), x.float(), r.float())
+    for a, b in zip(g1, g2):
+        assert a.shape == b.shape
+        assert (a.float() - b).abs().max() <= 4e-2 * b.abs().max() + 1e-3
+    # un-batched call
+    y, s = opake_fused_add_rms_norm(x[0], r[0], w, 1e-6)
+    sf = x[0].float() + r[0].float()
+    assert (s.float() - sf).abs().max() <= 2 ** -7 * sf.abs().max()
+    yf = sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+    assert (y.float() - yf).abs().max() <= 3e-2 * yf.abs().max()
+
+
 def test_linear_cross_entropy_native_matches_portable(cuda):
     from opake_b200.ops.lce import linear_cross_entropy
     torch.manual_seed(0)
