@@ -45,6 +45,14 @@ def _leaf(node: dict[str, Any]) -> DpProcess:
     name = node.get("type")
     cls = _PROCESS_REGISTRY.get(name)
     if cls is None:
+        # mechanism classes register themselves when their module is imported: a process file may be read before
+        # the DP-SGD / DP-FTRL accounting modules were touched
+        import importlib
+
+        for mod in ("opake_b200.dpsgd.accounting", "opake_b200.dpftrl.accounting"):
+            importlib.import_module(mod)
+        cls = _PROCESS_REGISTRY.get(name)
+    if cls is None:
         raise CheckpointError(f"unknown DpProcess type {name!r}")
     pair = lookup_serializer(cls)
     if pair is not None and pair[1] is not _generic_load:

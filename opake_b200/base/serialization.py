@@ -123,7 +123,7 @@ def _rebuild(template: Any, restored: list[Any]) -> Any:
     if _is_namedtuple(template):
         return type(template)(*restored)
     if isinstance(template, tuple):
-        return tuple(restored)
+        return type(template)(restored) if type(template) is not tuple else tuple(restored)
     if isinstance(template, list):
         return list(restored)
     return dict(zip(template.keys(), restored))

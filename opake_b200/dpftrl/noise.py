@@ -25,6 +25,7 @@ from ..engine.types import ClippedPytree, NoisedPytree, NoiseState, PerGroup, Se
 from .strategies import IdentityStrategy, MfStrategy, serialize_strategy
 
 MF_STREAM_FOLD = "opake.dpftrl.mf_gaussian"
+MF_COLUMN_FOLD = "mf_gaussian_column"
 SECOND_MOMENT_FIRST_FOLD = "opake.dpftrl.second_moment.first"
 SECOND_MOMENT_SECOND_FOLD = "opake.dpftrl.second_moment.second"
 STATE_LAYOUT_VERSION = 1
@@ -94,22 +95,20 @@ def mf_gaussian_noise(grad_template, strategy: MfStrategy, *, n_steps: int, min_
                 raise ConfigurationError("matrix-factorisation noise requires a constant max_norm over the run; got "
                                          f"{mn!r} after {st._first_max_norm!r}")
             base = per_group_noise_stddev(mn, nm) if isinstance(mn, PerGroup) else (0.0 if nm == 0 else nm * mn)
-            z = iid_normal_like(clipped_grads.pytree, fold_in(st._rng_key, MF_STREAM_FOLD, t), compute_dtype=compute_dtype,
-                                backend=backend)
-            w, inner = streaming.multiply_next(z, st._inner_state)
+            # column key and order of operations as in the reference's streaming engine (_engine.py:41-52,415-432): the iid
+            # column is scaled by the noise stddev BEFORE it goes through C^{-1}, so the streaming state holds scaled
+            # values and a state written by either implementation continues correctly in the other
+            z = iid_normal_like(clipped_grads.pytree, fold_in(st._rng_key, MF_STREAM_FOLD, MF_COLUMN_FOLD, t),
+                                compute_dtype=compute_dtype, backend=backend)
+            from ..engine.pytree import tree_flatten_with_paths, tree_unflatten
+
+            paths, zl, td = tree_flatten_with_paths(z)
             if isinstance(base, PerGroup):
-                from ..engine.pytree import tree_map_with_path
-
-                noisy = tree_map_with_path(lambda p, g: g, clipped_grads.pytree)
-                from ..engine.pytree import tree_flatten_with_paths, tree_unflatten
-
-                paths, gl, td = tree_flatten_with_paths(clipped_grads.pytree)
-                wl = tree_flatten_with_paths(w)[1]
-                noisy = tree_unflatten(td, [(g.to(compute_dtype) + base.for_path(p) * x.to(compute_dtype)).to(g.dtype)
-                                            for p, g, x in zip(paths, gl, wl)])
+                z = tree_unflatten(td, [x * base.for_path(p) for p, x in zip(paths, zl)])
             else:
-                noisy = tree_map(lambda g, x: (g.to(compute_dtype) + base * x.to(compute_dtype)).to(g.dtype),
-                                 clipped_grads.pytree, w)
+                z = tree_unflatten(td, [x * base for x in zl])
+            w, inner = streaming.multiply_next(z, st._inner_state)
+            noisy = tree_map(lambda g, x: (g.to(compute_dtype) + x.to(compute_dtype)).to(g.dtype), clipped_grads.pytree, w)
             r = 1.0 if row_l2 is None else float(row_l2[t])
             return (NoisedPytree(noisy, mn, base * r),
                     replace(st, _inner_state=inner, _step_counter=t + 1, _first_max_norm=mn))
@@ -118,37 +117,112 @@ def mf_gaussian_noise(grad_template, strategy: MfStrategy, *, n_steps: int, min_
 
 
 # ------------------------------------------------------------------------------------------------ state codec
-def _save_state(s: MFNoiseState) -> dict[str, Any]:
-    out = {"layout_version": STATE_LAYOUT_VERSION, "_step_counter": s._step_counter, "_rng_key.seed": s._rng_key.seed,
-           "_rng_key.impl": s._rng_key.impl, "_strategy_fingerprint": s._strategy_fingerprint, "_n_steps": s._n_steps}
-    for k, v in _sd({"_inner_state": s._inner_state}).items():
-        out[k] = v
-    mn = s._first_max_norm
+# Wire layout of packages/opake-dpftrl/src/opake/api/dpftrl/noise/_state_codec.py:348-446 (layout version 1):
+#   layout_version, _step_counter, _rng_key.seed, _rng_key.impl,
+#   _inner_state[1][i]                  the i-th tensor of the streaming state, leaves in sorted-key order
+#   _inner_state_fields                 JSON list of those keys
+#   _first_max_norm                     JSON: {"kind": "none"} | {"kind": "scalar", "value": c} | {"kind": "per_group", ...}
+#   _first_max_norm_sync_fingerprint    leading signed 64 bits of SHA-256 over a canonical JSON of the latched norm
+def _json(value) -> str:
+    import json
+
+    return json.dumps(value, sort_keys=True, separators=(",", ":"))
+
+
+def _encode_max_norm(mn) -> str:
+    if mn is None:
+        return _json({"kind": "none"})
     if isinstance(mn, PerGroup):
-        for g, v in mn.values.items():
-            out[f"_first_max_norm.values.{g}"] = v
-    elif mn is not None:
-        out["_first_max_norm"] = float(mn)
+        return _json({"kind": "per_group", "groups": [[list(p), g] for p, g in mn.groups.items()],
+                      "values": [[g, v] for g, v in mn.values.items()]})
+    return _json({"kind": "scalar", "value": float(mn)})
+
+
+def _decode_max_norm(text, template):
+    import json
+
+    if not isinstance(text, str):
+        return None if text is None else float(text)
+    obj = json.loads(text)
+    if obj["kind"] == "none":
+        return None
+    if obj["kind"] == "scalar":
+        return float(obj["value"])
+    return PerGroup({tuple(p): g for p, g in obj["groups"]}, {g: v for g, v in obj["values"]})
+
+
+def max_norm_fingerprint(mn) -> int | None:
+    import hashlib
+
+    if mn is None:
+        return None
+    if isinstance(mn, PerGroup):
+        payload = {"kind": "mf_noise_per_group_max_norm", "groups": sorted(mn.groups.items()), "values": sorted(mn.values.items())}
+    else:
+        payload = {"kind": "mf_noise_scalar_max_norm", "c": float(mn)}
+    return int.from_bytes(hashlib.sha256(_json(payload).encode()).digest()[:8], "big", signed=True)
+
+
+def _inner_tensors(inner) -> list[torch.Tensor]:
+    from ..engine.pytree import tree_flatten
+
+    return [t for t in tree_flatten(inner)[0] if isinstance(t, torch.Tensor)]
+
+
+def _save_state(s: MFNoiseState) -> dict[str, Any]:
+    out: dict[str, Any] = {"layout_version": STATE_LAYOUT_VERSION}
+    fields = []
+    for i, t in enumerate(_inner_tensors(s._inner_state)):
+        name = f"_inner_state[1][{i}]"
+        out[name] = t
+        fields.append(name)
+    out.update({"_step_counter": int(s._step_counter), "_rng_key.seed": s._rng_key.seed, "_rng_key.impl": s._rng_key.impl,
+                "_first_max_norm_sync_fingerprint": max_norm_fingerprint(s._first_max_norm),
+                "_first_max_norm": _encode_max_norm(s._first_max_norm), "_inner_state_fields": _json(sorted(fields))})
     return out
 
 
 def _load_state(template: MFNoiseState, sd) -> MFNoiseState:
-    ver = sd.get("layout_version", STATE_LAYOUT_VERSION)
+    from ..base.exceptions import CheckpointError
+    from ..engine.pytree import tree_flatten, tree_unflatten
+
+    ver = sd.get("layout_version")
     if ver != STATE_LAYOUT_VERSION:
-        raise ConfigurationError(f"unsupported MFNoiseState layout version {ver}")
-    fp = sd.get("_strategy_fingerprint", template._strategy_fingerprint)
-    if template._strategy_fingerprint and fp != template._strategy_fingerprint:
-        raise ConfigurationError("MFNoiseState checkpoint was written for a different strategy than the template")
-    inner = _fsd({"_inner_state": template._inner_state}, sd)["_inner_state"]
-    mn = template._first_max_norm
-    if "_first_max_norm" in sd:
-        mn = float(sd["_first_max_norm"])
-    elif isinstance(mn, PerGroup):
-        mn = PerGroup(mn.groups, {g: sd.get(f"_first_max_norm.values.{g}", v) for g, v in mn.values.items()})
-    return MFNoiseState(inner, int(sd.get("_step_counter", 0)),
+        raise CheckpointError(f"unsupported MF noise-state layout version {ver!r}; expected {STATE_LAYOUT_VERSION}")
+    step = int(sd.get("_step_counter", 0))
+    if "_inner_state_fields" in sd:
+        import json
+
+        fields = json.loads(sd["_inner_state_fields"])
+        leaves, td = tree_flatten(template._inner_state)
+        slots = [i for i, t in enumerate(leaves) if isinstance(t, torch.Tensor)]
+        if len(fields) != len(slots):
+            raise CheckpointError(f"MF noise-state holds {len(fields)} tensors, the configured strategy and parameter tree "
+                                  f"need {len(slots)}: rebuild the mechanism with the checkpoint's strategy")
+        for i, name in zip(slots, sorted(fields, key=lambda f: [int(x) for x in f.replace("]", "").split("[")[1:]])):
+            saved, want = sd[name], leaves[i]
+            if tuple(saved.shape) != tuple(want.shape):
+                raise CheckpointError(f"MF noise-state tensor {name} has shape {tuple(saved.shape)}, the configured strategy "
+                                      f"needs {tuple(want.shape)}")
+            leaves[i] = saved.to(device=want.device, dtype=want.dtype)
+        # streaming states that count their own steps (banded Toeplitz ring) follow the mechanism's step counter
+        leaves = [step if (isinstance(t, int) and not isinstance(t, bool)) else t for t in leaves]
+        inner = tree_unflatten(td, leaves)
+        mn = _decode_max_norm(sd.get("_first_max_norm"), template._first_max_norm)
+        fp = sd.get("_first_max_norm_sync_fingerprint")
+        if mn is not None and fp is not None and fp != max_norm_fingerprint(mn):
+            raise CheckpointError("MF max-norm latch fingerprint does not match its saved value")
+    else:       # files of earlier versions of this package: dotted inner-state keys, plain max norm
+        inner = _fsd({"_inner_state": template._inner_state}, sd)["_inner_state"]
+        mn = template._first_max_norm
+        if "_first_max_norm" in sd:
+            mn = float(sd["_first_max_norm"])
+        elif isinstance(mn, PerGroup):
+            mn = PerGroup(mn.groups, {g: sd.get(f"_first_max_norm.values.{g}", v) for g, v in mn.values.items()})
+    return MFNoiseState(inner, step,
                         RngKey(int(sd.get("_rng_key.seed", template._rng_key.seed)),
-                               str(sd.get("_rng_key.impl", template._rng_key.impl))), mn, fp,
-                        int(sd.get("_n_steps", template._n_steps)))
+                               str(sd.get("_rng_key.impl", template._rng_key.impl))), mn, template._strategy_fingerprint,
+                        template._n_steps)
 
 
 register_serializer(MFNoiseState, _save_state, _load_state)

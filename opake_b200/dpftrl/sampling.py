@@ -51,10 +51,11 @@ def _key_of(sd) -> RngKey:
     return RngKey(int(sd["key_seed"]), str(sd["key_impl"]))
 
 
-def _check_len(name: str, template_n: int, sd) -> None:
-    if int(sd["num_samples"]) != template_n:
+def _check_len(name: str, template_n: int, sd, key: str = "num_samples") -> None:
+    saved = sd[key] if key in sd else sd["num_samples" if key == "num_examples" else "num_examples"]
+    if int(saved) != template_n:
         raise ConfigurationError(f"{name}.from_state_dict: template dataset length {template_n} does not match snapshot "
-                                 f"num_samples={int(sd['num_samples'])}.")
+                                 f"{key}={int(saved)}.")
 
 
 class _Resumable(Sampler):
@@ -135,15 +136,17 @@ class CyclicPoissonSampler(_Resumable):
 
 def _save_cyclic(s):
     return {"key_seed": int(s._stream_key.seed), "key_impl": str(s._stream_key.impl), "consumed": int(s._consumed),
-            "num_samples": int(s.num_examples), "sample_rate": float(s.sample_rate), "bands": int(s.bands),
-            "n_steps": int(s.n_steps), "partition_type": s.partition_type.value,
+            "num_examples": int(s.num_examples), "sample_rate": float(s.sample_rate), "bands": int(s.bands),
+            "n_steps": int(s.n_steps), "partition_type": s.partition_type.name,
             "truncated_batch_size": s.truncated_batch_size}
 
 
 def _load_cyclic(t, sd):
-    _check_len("CyclicPoissonSampler", len(t.data_source), sd)
+    _check_len("CyclicPoissonSampler", len(t.data_source), sd, "num_examples")
+    pt = sd["partition_type"]
+    pt = PartitionType[pt] if pt in PartitionType.__members__ else PartitionType(pt)
     s = CyclicPoissonSampler._from_stream_key(t.data_source, float(sd["sample_rate"]), int(sd["bands"]), t.n_steps,
-                                              PartitionType(sd["partition_type"]), sd.get("truncated_batch_size"),
+                                              pt, sd.get("truncated_batch_size"),
                                               stream_key=_key_of(sd))
     for i in range(int(sd["consumed"])):
         s._sample_step(i)
@@ -218,12 +221,12 @@ class BMinSepSampler(_Resumable):
 
 def _save_bms(s):
     return {"key_seed": int(s._stream_key.seed), "key_impl": str(s._stream_key.impl), "consumed": int(s._consumed),
-            "num_samples": int(s.num_examples), "bands": int(s.bands), "sampling_prob": float(s.sampling_prob),
+            "num_examples": int(s.num_examples), "bands": int(s.bands), "sampling_prob": float(s.sampling_prob),
             "n_steps": int(s.n_steps)}
 
 
 def _load_bms(t, sd):
-    _check_len("BMinSepSampler", len(t.data_source), sd)
+    _check_len("BMinSepSampler", len(t.data_source), sd, "num_examples")
     s = BMinSepSampler._from_stream_key(t.data_source, int(sd["bands"]), float(sd["sampling_prob"]), t.n_steps,
                                         stream_key=_key_of(sd))
     for _ in range(int(sd["consumed"])):

@@ -274,6 +274,8 @@ class BandMfStrategy(MfStrategy):
         c0 = T.bsr_coefficients(b)
         if b == 1:
             return replace(self, coefficients=(1.0,))
+        # the optimised column is rescaled to unit L2 norm (single-participation sensitivity 1), the normalisation of
+        # packages/opake-dpftrl/src/opake/api/dpftrl/noise/_band_mf.py:101-187: streaming states are then interchangeable
         wl = T.workload_coefficients(n_steps, 0.0 if self.momentum in (0.0, 1.0) else self.momentum)
         n_eval = min(n_steps, 4096)
 
@@ -288,6 +290,8 @@ class BandMfStrategy(MfStrategy):
             c = np.concatenate([[1.0], res.x]) if res.fun < loss(c0[1:]) else c0
         except Exception:
             c = c0
+        c = np.asarray(c, dtype=np.float64)
+        c = c / math.sqrt(float(np.dot(c, c)))
         return replace(self, coefficients=tuple(float(x) for x in c))
 
     def strategy_coefficients(self, n_steps):

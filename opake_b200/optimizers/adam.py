@@ -25,19 +25,22 @@ from .chain import GradientTransformation, make_optimizer_chain
 class AdamState:
     mu: Any
     nu: Any
-    phi: Any      # float, or dict[ParamPath -> float] for per-group noise
+    phi: Any      # dict[ParamPath -> float]: EMA of the noise variance per leaf (None without bias correction)
     step: int
 
 
 def update_phi_ema(phi, noise_stddev, beta2: float, paths):
-    """EMA of the per-leaf noise variance; scalar when the noise is isotropic."""
+    """EMA of the noise variance, one entry per parameter leaf keyed by its path (the layout of
+    packages/opake-optimizers/src/opake/api/optimizers/_bias_correction.py:53-152, which serializes as
+    ``phi.<path>``); the entries are equal when the noise is isotropic."""
+    if isinstance(phi, dict):
+        old = phi
+    else:
+        old = {p: float(phi or 0.0) for p in paths}
     if isinstance(noise_stddev, PerGroup):
-        old = phi if isinstance(phi, dict) else {p: float(phi) for p in paths}
         return {p: beta2 * old.get(p, 0.0) + (1 - beta2) * noise_stddev.for_path(p) ** 2 for p in paths}
     s = 0.0 if noise_stddev is None else float(noise_stddev)
-    if isinstance(phi, dict):
-        return {p: beta2 * v + (1 - beta2) * s * s for p, v in phi.items()}
-    return beta2 * float(phi) + (1 - beta2) * s * s
+    return {p: beta2 * old.get(p, 0.0) + (1 - beta2) * s * s for p in paths}
 
 
 def scale_by_adam(b1: float, b2: float, eps: float, noise_bias_correction: bool) -> GradientTransformation:
@@ -45,7 +48,8 @@ def scale_by_adam(b1: float, b2: float, eps: float, noise_bias_correction: bool)
 
     def init(params):
         z = (lambda p: torch.zeros_like(p, dtype=torch.float32 if p.dtype in (torch.bfloat16, torch.float16) else p.dtype))
-        return AdamState(tree_map(z, params), tree_map(z, params), 0.0, 0)
+        phi = {p: 0.0 for p in tree_flatten_with_paths(params)[0]} if noise_bias_correction else None
+        return AdamState(tree_map(z, params), tree_map(z, params), phi, 0)
 
     def update(grads, state: AdamState, *, params=None, noise_stddev=None, noisy_squared_grads=None):
         t = state.step + 1

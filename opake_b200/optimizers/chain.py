@@ -27,10 +27,40 @@ class GradientTransformation(NamedTuple):
     update: Callable[..., tuple[Any, Any]]
 
 
-@dataclass(frozen=True)
-class ChainState:
-    moment: Any
-    count: int = 0
+class ScaleByScheduleState(NamedTuple):
+    """State of the ``-lr`` scaling when ``lr`` is a schedule: the number of updates so far."""
+
+    count: torch.Tensor
+
+
+class ChainState(tuple):
+    """State of an optimizer chain: one entry per stage, in stage order, as the reference's chain keeps it
+    (packages/opake-optimizers/src/opake/api/optimizers/_chain.py:224-284), so that serialized optimizer states have
+    the same flat keys (``[0].mu.<leaf>``, ``[0].step``, ``[3].count``, ...). Decoupled decay (AdamW):
+    ``(moment, rms clip, weight decay, lr)``; L2 decay: ``(weight decay, moment, rms clip, lr)``. Stages without state
+    hold an empty tuple."""
+
+    __slots__ = ()
+
+    def __new__(cls, stages):
+        return super().__new__(cls, stages)
+
+    @property
+    def moment(self):
+        return self[_moment_index(self)]
+
+    @property
+    def count(self) -> int:
+        lr_state = self[3]
+        return int(lr_state.count) if isinstance(lr_state, ScaleByScheduleState) else 0
+
+
+def _moment_index(state: tuple) -> int:
+    # the moment stage is the first one that carries state other than the (stateless) decay / clip stages
+    for i in (0, 1):
+        if state[i] != ():
+            return i
+    return 0
 
 
 def apply_updates(params: Any, updates: Any, *, inplace: bool = False) -> Any:
@@ -90,8 +120,17 @@ def make_optimizer_chain(moment_scaler: GradientTransformation, lr: LR, weight_d
                                  "explicitly for non-private use.")
         return updates, {}
 
+    scheduled = callable(lr)
+    m_at = 0 if decoupled_weight_decay else 1
+
+    def pack(mom, count):
+        lr_state = ScaleByScheduleState(torch.tensor(int(count), dtype=torch.int64)) if scheduled else ()
+        stages = [(), (), (), lr_state]
+        stages[m_at] = mom
+        return ChainState(stages)
+
     def init(params):
-        return ChainState(moment_scaler.init(params), 0)
+        return pack(moment_scaler.init(params), 0)
 
     def update(updates, state: ChainState, *, params=None, inplace: bool = False):
         g, extra = route(updates)
@@ -99,18 +138,19 @@ def make_optimizer_chain(moment_scaler: GradientTransformation, lr: LR, weight_d
             if params is None:
                 raise ConfigurationError("weight decay needs `params`")
             g = tree_map(lambda u, p: u + weight_decay * p.to(u.dtype), g, params)
-        d, mom = moment_scaler.update(g, state.moment, params=params, **extra)
+        count = int(state[3].count) if scheduled else 0
+        d, mom = moment_scaler.update(g, state[m_at], params=params, **extra)
         if update_rms_clip is not None:
             d = clip_by_global_rms(d, float(update_rms_clip))
         if weight_decay and decoupled_weight_decay:
             if params is None:
                 raise ConfigurationError("weight decay needs `params`")
             d = tree_map(lambda u, p: u + weight_decay * p.to(u.dtype), d, params)
-        step = -resolve_lr(lr, state.count)
-        return tree_map(lambda u: u * step, d), ChainState(mom, state.count + 1)
+        step = -resolve_lr(lr, count)
+        return tree_map(lambda u: u * step, d), pack(mom, count + 1)
 
     return GradientTransformation(init, update)
 
 
-__all__ = ["GradientTransformation", "ChainState", "apply_updates", "make_optimizer_chain", "clip_by_global_rms",
+__all__ = ["GradientTransformation", "ChainState", "ScaleByScheduleState", "apply_updates", "make_optimizer_chain", "clip_by_global_rms",
            "resolve_lr"]

@@ -111,15 +111,73 @@ def rotate_checkpoints(output_dir: str, limit: int | None, keep: str | None = No
     return removed
 
 
+_REFERENCE_MODULE = "opake.api.transformers.trainer._checkpoint"
+
+
+class _ReferenceAlias:
+    """While active, ``opake.api.transformers.trainer._checkpoint.RuntimeCheckpoint`` resolves to this package's
+    ``RuntimeCheckpoint``. The reference pickles its bundle as an instance of that dataclass
+    (``trainer/_checkpoint.py:313-389``), so a ``dp_state.pt`` is portable in both directions only if that class path
+    can be pickled and unpickled here. Nothing is registered when a real ``opake`` distribution is importable."""
+
+    def __enter__(self):
+        import importlib.util
+        import sys
+        import types
+
+        self._added: list[str] = []
+        self._names = None
+        try:
+            real = importlib.util.find_spec(_REFERENCE_MODULE) is not None
+        except (ImportError, ValueError):
+            real = False
+        if real:
+            return self
+        parts = _REFERENCE_MODULE.split(".")
+        for i in range(1, len(parts) + 1):
+            name = ".".join(parts[:i])
+            if name not in sys.modules:
+                mod = types.ModuleType(name)
+                mod.__path__ = []          # a package, so that sub-module lookups consult sys.modules
+                sys.modules[name] = mod
+                self._added.append(name)
+        sys.modules[_REFERENCE_MODULE].RuntimeCheckpoint = RuntimeCheckpoint
+        self._names = (RuntimeCheckpoint.__module__, RuntimeCheckpoint.__qualname__)
+        RuntimeCheckpoint.__module__, RuntimeCheckpoint.__qualname__ = _REFERENCE_MODULE, "RuntimeCheckpoint"
+        return self
+
+    def __exit__(self, *exc):
+        import sys
+
+        if self._names is not None:
+            RuntimeCheckpoint.__module__, RuntimeCheckpoint.__qualname__ = self._names
+        for name in reversed(self._added):
+            sys.modules.pop(name, None)
+        return False
+
+
 def save_runtime(path: str, rt: RuntimeCheckpoint) -> None:
-    torch.save(dataclasses.asdict(rt), path)
+    """Writes ``dp_state.pt`` as the reference does: a pickled ``RuntimeCheckpoint`` instance under the reference's
+    class path, so either implementation can resume from the file."""
+    with _ReferenceAlias() as alias:
+        if alias._names is None:        # the reference itself is importable: hand it a plain mapping-free instance of its class
+            import importlib
+
+            ref_cls = importlib.import_module(_REFERENCE_MODULE).RuntimeCheckpoint
+            names = {f.name for f in dataclasses.fields(ref_cls)}
+            torch.save(ref_cls(**{k: v for k, v in dataclasses.asdict(rt).items() if k in names}), path)
+        else:
+            torch.save(rt, path)
 
 
 def load_runtime(path: str) -> RuntimeCheckpoint:
     try:
-        raw = torch.load(path, map_location="cpu", weights_only=False)
+        with _ReferenceAlias():
+            raw = torch.load(path, map_location="cpu", weights_only=False)
     except Exception as e:
         raise CheckpointError(f"cannot read DP runtime state {path}: {e}") from e
+    if dataclasses.is_dataclass(raw) and not isinstance(raw, type):
+        raw = {f.name: getattr(raw, f.name) for f in dataclasses.fields(raw)}
     if not isinstance(raw, dict) or "version" not in raw:
         raise CheckpointError(f"{path} is not a DP runtime bundle")
     if raw["version"] != BUNDLE_VERSION:

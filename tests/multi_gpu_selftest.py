@@ -99,10 +99,28 @@ def _ep_train(rank: int, world: int, dev: torch.device, a) -> None:
     T = 256
     # plain SGD: the update is linear in the summed gradient, so differences in summation order stay small (Adam's
     # normalised update flips sign on near-zero gradient entries)
-    ecfg = EngineConfig(logical_batch=a.batch, noise_multiplier=0.0, clip_norm=0.5, lr=0.5, optimizer="sgd", weight_decay=0.0,
+    ecfg = EngineConfig(logical_batch=a.batch, noise_multiplier=0.0, clip_norm=0.5, lr=20.0, optimizer="sgd", weight_decay=0.0,
                         seed=5, use_cuda_graph=False, accumulate_group=2, expert_parallel=True, seq_len=T)
     eng = ShardedDPEngine(cfg, ecfg, dev)
-    router0 = eng.layout.views(eng.params)["layers.0.router"].float().clone()
+    def snapshot():
+        views = eng.layout.views(eng.params)
+        routers = torch.stack([views[f"layers.{i}.router"].float().cpu() for i in range(cfg.n_layers)])
+        if eng.ep is None:
+            wgu = torch.stack([views[f"layers.{i}.experts.wgu"].float().cpu() for i in range(cfg.n_layers)])
+            wd = torch.stack([views[f"layers.{i}.experts.wd"].float().cpu() for i in range(cfg.n_layers)])
+        else:
+            parts = [torch.empty_like(eng.ep.params) for _ in range(world)]
+            dist.all_gather(parts, eng.ep.params)
+            wgu_l, wd_l = [], []
+            for i in range(cfg.n_layers):
+                per_rank = [eng.ep.views(p, i) for p in parts]
+                wgu_l.append(torch.cat([v[0] for v in per_rank]).float().cpu())
+                wd_l.append(torch.cat([v[1] for v in per_rank]).float().cpu())
+            wgu, wd = torch.stack(wgu_l), torch.stack(wd_l)
+        wqkv = views["layers.0.wqkv"].float().cpu()
+        return {"routers": routers, "wgu": wgu, "wd": wd, "wqkv": wqkv}
+
+    before = snapshot()
     g = torch.Generator().manual_seed(0)
     tok = torch.randint(0, cfg.vocab_size, (a.batch, T), generator=g, dtype=torch.int32)
     labels = torch.roll(tok, -1, 1).clone()
@@ -117,28 +135,13 @@ def _ep_train(rank: int, world: int, dev: torch.device, a) -> None:
         losses.append(l.item() / a.batch)
     torch.cuda.synchronize()
     raise_if_device_error(dev)
-    views = eng.layout.views(eng.params)
-    routers = torch.stack([views[f"layers.{i}.router"].float().cpu() for i in range(cfg.n_layers)])
-    if eng.ep is None:
-        wgu = torch.stack([views[f"layers.{i}.experts.wgu"].float().cpu() for i in range(cfg.n_layers)])
-        wd = torch.stack([views[f"layers.{i}.experts.wd"].float().cpu() for i in range(cfg.n_layers)])
-        clipped = int(eng.runtime.clip_count.item())
-    else:
-        parts = [torch.empty_like(eng.ep.params) for _ in range(world)]
-        dist.all_gather(parts, eng.ep.params)
-        wgu_l, wd_l = [], []
-        for i in range(cfg.n_layers):
-            per_rank = [eng.ep.views(p, i) for p in parts]
-            wgu_l.append(torch.cat([v[0] for v in per_rank]).float().cpu())
-            wd_l.append(torch.cat([v[1] for v in per_rank]).float().cpu())
-        wgu, wd = torch.stack(wgu_l), torch.stack(wd_l)
-        c = eng.runtime.clip_count.clone().to(torch.int64)
+    after = snapshot()
+    c = eng.runtime.clip_count.clone().to(torch.int64)
+    if world > 1:
         dist.all_reduce(c)
-        clipped = int(c.item())
     if rank == 0:
-        moved = (routers[0] - router0.cpu()).abs().max().item()
-        torch.save({"losses": losses, "routers": routers, "wgu": wgu, "wd": wd, "world": world, "clipped": clipped,
-                    "moved": moved}, a.out)
+        torch.save({"losses": losses, "world": world, "clipped": int(c.item()), "init": before,
+                    "delta": {k: after[k] - before[k] for k in after}}, a.out)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
