@@ -66,7 +66,8 @@ def vmap_sdpa_attention_forward(module, query, key, value, attention_mask=None, 
     return out.transpose(-3, -2).contiguous(), None
 
 
-def eager_attention_forward(module, query, key, value, attention_mask=None, scaling: float | None = None, softcap: float | None = None, **_kw):
+def eager_attention_forward(module, query, key, value, attention_mask=None, scaling: float | None = None, softcap: float | None = None,
+                            sliding_window: int | None = None, **_kw):
     n_rep = query.shape[-3] // key.shape[-3]
     key, value = repeat_kv(key, n_rep), repeat_kv(value, n_rep)
     scale = scaling if scaling is not None else 1.0 / math.sqrt(query.shape[-1])
@@ -74,7 +75,12 @@ def eager_attention_forward(module, query, key, value, attention_mask=None, scal
     if softcap:
         s = softcap * torch.tanh(s / softcap)
     q_len, kv_len = query.shape[-2], key.shape[-2]
-    m = causal_mask(q_len, kv_len, query.device)
+    # local-attention layers (Gemma-2 / Gemma-3, Mistral, ...) pass their window; the library may hand over no mask at
+    # all for an unpadded batch, so the window is rebuilt here from the shapes
+    if sliding_window is not None and sliding_window < kv_len:
+        m = sliding_window_mask(q_len, kv_len, int(sliding_window), query.device)
+    else:
+        m = causal_mask(q_len, kv_len, query.device)
     if attention_mask is not None:
         m = m & (attention_mask[..., :kv_len] if attention_mask.dtype == torch.bool else attention_mask[..., :kv_len] == 0)
     s = s.masked_fill(~m, torch.finfo(s.dtype).min)

@@ -37,10 +37,12 @@ for _s in (
     FamilySpec("qwen2", notes="q/k/v bias"), FamilySpec("qwen3", notes="q/k norm"), FamilySpec("olmo2", notes="post-norm, q/k norm"),
     FamilySpec("olmo3", sliding_window=True, notes="post-norm, q/k norm"), FamilySpec("phi3", notes="fused qkv and gate_up"),
     FamilySpec("glm4", notes="fused gate_up, extra norms"), FamilySpec("exaone4", sliding_window=True, notes="q/k norm"),
-    FamilySpec("cohere", norm_suffixes=("LayerNorm",), notes="parallel block, bias-free layer norm"),
-    FamilySpec("cohere2", norm_suffixes=("LayerNorm",), sliding_window=True),
+    # Cohere's "LayerNorm" subtracts the mean: it is not an RMSNorm and keeps its stock forward
+    FamilySpec("cohere", norm_suffixes=(), notes="parallel block, bias-free mean-subtracting layer norm"),
+    FamilySpec("cohere2", norm_suffixes=(), sliding_window=True),
     FamilySpec("gemma", act="tanh", norm_offset=1.0), FamilySpec("gemma2", act="tanh", norm_offset=1.0, softcap=50.0, sliding_window=True),
     FamilySpec("gemma3", act="tanh", norm_offset=1.0, sliding_window=True, notes="q/k norm, local/global rope"),
+    FamilySpec("gemma3_text", act="tanh", norm_offset=1.0, sliding_window=True, notes="text tower of gemma3"),
     FamilySpec("gpt2", norm_suffixes=(), mlp_suffixes=(), act="none", native=True, notes="LayerNorm, learned positions, Conv1D"),
     FamilySpec("gpt_oss", moe=True, sliding_window=True, notes="attention sinks, clamped swiglu"),
     FamilySpec("mixtral", moe=True, sliding_window=True), FamilySpec("qwen3_moe", moe=True), FamilySpec("qwen3_5_moe", moe=True),
