@@ -259,10 +259,11 @@ def main() -> None:
                        "shard": shard, "expert_parallel": f"ep{world}" if (mcfg.n_experts and world > 1) else None,
                        "clip_norm": 1.0, "noise_multiplier": args.sigma, "optimizer": "adamw-bc", "sft_mask": "first 25%",
                        "mechanism": f"dp-ftrl blt x{args.blt_buffers}" if args.blt_buffers else "dp-sgd gaussian",
-                       "per_example_microbatch": 1, "cuda_graph": not args.no_graph,
+                       "per_example_microbatch": 1, "cuda_graph": (not args.no_graph) and eng.ep is None,
                        "accumulate_group": getattr(eng, "group", None),
                        "device_memory_in_use_gib": round((lambda f, t: (t - f) / 2 ** 30)(*torch.cuda.mem_get_info(dev)), 1),
-                       "l2_policy": "inputs larger than L2: every step streams the 16 GB bf16 weights and 32 GB fp32 sums",
+                       "l2_policy": "inputs larger than L2: every example streams all bf16 weights and a full-size bf16 gradient, "
+                                    f"{2 * eng.layout.total / 2 ** 30:.1f} GiB each, far beyond the 126 MB L2",
                        "final_loss_per_example": last_loss / b_local},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,

@@ -13,9 +13,11 @@ from __future__ import annotations
 import re
 from typing import Any
 
+import torch
+
 from ..base.exceptions import ConfigurationError
 
-__all__ = ["apply_chat_template_with_mask", "clone_chat_template", "get_training_chat_template"]
+__all__ = ["SyntheticLM", "SyntheticPreferences", "apply_chat_template_with_mask", "clone_chat_template", "get_training_chat_template"]
 
 _GEN_START, _GEN_END = "{% generation %}", "{% endgeneration %}"
 _MARKER_RE = re.compile(r"\{%-?\s*generation\s*-?%\}")
@@ -183,3 +185,38 @@ def apply_chat_template_with_mask(tokenizer, conversation: list[dict[str, Any]],
     if enc.get("attention_mask") is not None:
         out["attention_mask"] = enc["attention_mask"]
     return out
+
+
+# ------------------------------------------------------------------------------------------------ synthetic data
+class SyntheticLM(torch.utils.data.Dataset):
+    """Zipf-distributed token sequences with a completion mask on the last 75 % of every sequence."""
+
+    def __init__(self, n: int, vocab: int, seq: int, seed: int = 0):
+        self.n, self.vocab, self.seq, self.seed = n, vocab, seq, seed
+        ranks = torch.arange(1, vocab + 1, dtype=torch.float64)
+        self.p = (ranks ** -1.1 / (ranks ** -1.1).sum()).float()
+        self._fingerprint = f"synthetic-lm-{n}-{vocab}-{seq}-{seed}"
+
+    def __len__(self):
+        return self.n
+
+    def __getitem__(self, i):
+        g = torch.Generator().manual_seed(self.seed * 1_000_003 + i)
+        ids = torch.multinomial(self.p, self.seq, replacement=True, generator=g).tolist()
+        cut = self.seq // 4
+        return {"input_ids": ids, "completion_mask": [0] * cut + [1] * (self.seq - cut)}
+
+
+class SyntheticPreferences(torch.utils.data.Dataset):
+    def __init__(self, n: int, vocab: int, prompt: int = 16, completion: int = 16, seed: int = 0):
+        self.n, self.vocab, self.prompt, self.completion, self.seed = n, vocab, prompt, completion, seed
+        self._fingerprint = f"synthetic-pref-{n}-{vocab}-{prompt}-{completion}-{seed}"
+
+    def __len__(self):
+        return self.n
+
+    def __getitem__(self, i):
+        g = torch.Generator().manual_seed(self.seed * 1_000_003 + i)
+        p, c, r = (torch.randint(0, self.vocab, (k,), generator=g).tolist() for k in (self.prompt, self.completion, self.completion))
+        return {"chosen_input_ids": p + c, "rejected_input_ids": p + r, "chosen_completion_mask": [0] * len(p) + [1] * len(c),
+                "rejected_completion_mask": [0] * len(p) + [1] * len(r)}

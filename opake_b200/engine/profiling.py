@@ -279,5 +279,36 @@ def sync_perf_state(state: PerfState) -> PerfState:
                    max_peak_memory_gb=D.reduce_scalar(state.max_peak_memory_gb, "max", dev))
 
 
-__all__ = ["PerfStage", "PerfState", "PerfTracker", "StepPerf", "MemoryStats", "empty_cache", "get_memory_stats",
+__all__ = ["nvtx_range", "PerfStage", "PerfState", "PerfTracker", "StepPerf", "MemoryStats", "empty_cache", "get_memory_stats",
            "perf_tracker", "print_memory", "reset_peak_memory", "step_perf", "sync_perf_state"]
+
+
+class nvtx_range:
+    """NVTX range around a phase (shows up in Nsight Systems / Compute timelines); a no-op without CUDA. Also opens a
+    ``torch.profiler.record_function`` range of the same name, so the phase is visible to both kinds of tools."""
+
+    def __init__(self, name: str):
+        self.name = name
+        self._rf = None
+        self._pushed = False
+
+    def __enter__(self):
+        import torch
+
+        if torch.cuda.is_available():
+            try:
+                torch.cuda.nvtx.range_push(self.name)
+                self._pushed = True
+            except Exception:       # NVTX not built into this torch
+                self._pushed = False
+        self._rf = torch.profiler.record_function(self.name)
+        self._rf.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        import torch
+
+        self._rf.__exit__(*exc)
+        if self._pushed:
+            torch.cuda.nvtx.range_pop()
+        return False

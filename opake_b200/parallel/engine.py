@@ -26,6 +26,7 @@ import torch.distributed as dist
 from ..models.config import DecoderConfig
 from ..models.decoder import DecoderRuntime, init_params_
 from ..models.flat import build_layout
+from ..engine.profiling import nvtx_range
 from ..ops import kernels as K
 from . import comm
 
@@ -67,6 +68,10 @@ class EngineConfig:
     # of every layer (parameters, sums and moments), tokens travel to the owners; needs the sequence length up front
     expert_parallel: bool = False
     seq_len: int = 0
+    # "peer": the fused step reads / writes the other ranks' buffers itself (NVLink loads and stores inside the kernel).
+    # "nccl": the same step with library collectives around a local kernel (reduce_scatter_tensor before, in-place
+    # all_gather_into_tensor after): the baseline and fallback implementation of the same interface.
+    comm_backend: str = "peer"
 
 
 class ShardedDPEngine:
@@ -120,6 +125,12 @@ class ShardedDPEngine:
             nlag = len(cfg.toeplitz_coef) - 1
             if nlag:
                 self.toep_state = torch.zeros(nlag, self.shard_len, dtype=torch.float32, device=device)
+        if cfg.comm_backend not in ("peer", "nccl"):
+            raise ValueError(f"comm_backend must be 'peer' or 'nccl', got {cfg.comm_backend!r}")
+        self.nccl_step = cfg.comm_backend == "nccl" and self.world > 1
+        if self.nccl_step and (self.shard_params or self.shard_sums):
+            raise ValueError("the NCCL baseline step works on replicated parameters and sums (shard_params / shard_sums off)")
+        self._rs_out = torch.empty(self.shard_len, dtype=torch.float32, device=device) if self.nccl_step else None
         self._stale = False      # shard_params: the replica's remote parts are older than their owners' copies
         self._refresh: dict[int, tuple] = {}
         if cfg.accumulate_group and not 2 <= int(cfg.accumulate_group) <= 8:
@@ -323,15 +334,17 @@ class ShardedDPEngine:
         if "tok_keep" not in ws:
             ws["tok_keep"] = torch.zeros_like(ws["toks"][0])
         ws["loss_sum"].zero_()
-        for i in range(B_local):
-            self._run_example(tokens[i], labels[i], i)
+        with nvtx_range("opake::examples"):
+            for i in range(B_local):
+                self._run_example(tokens[i], labels[i], i)
         # the last group (complete or not) has not been added yet: every earlier one was added at the start of the
         # example that followed it
         n_last = B_local % self.group or min(self.group, B_local)
         if n_last:
             self._accumulate(ws, n_last, self._group_toks(ws, n_last))
         loss_sum = ws["loss_sum"].clone()
-        self.apply_update()
+        with nvtx_range("opake::dp_step"):
+            self.apply_update()
         return loss_sum
 
     def apply_update(self) -> None:
@@ -344,6 +357,9 @@ class ShardedDPEngine:
         if cfg.noise_bias_correction and cfg.optimizer == "adamw":
             self.phi = b2 * self.phi + (1.0 - b2) * sigma * sigma
             phi_hat = self.phi / (1.0 - b2**t)
+        if self.nccl_step:
+            self._apply_update_nccl(sigma, step_key, phi_hat, t)
+            return
         if self.world > 1:
             self.acc_pb.barrier()       # every rank finished accumulating before anyone reads (or owns) the sums
         if self.shard_sums:
@@ -373,6 +389,29 @@ class ShardedDPEngine:
             self.acc.zero_()
         if self.shard_params:
             self._stale = True
+        self.step_count += 1
+
+    def _apply_update_nccl(self, sigma: float, step_key, phi_hat: float, t: int) -> None:
+        """The optimizer step on library collectives: NCCL reduce-scatter of the fp32 sums, the step kernel on local
+        memory only, NCCL all-gather of the updated bf16 shards (in place: every rank's shard already sits at its
+        offset of the replica)."""
+        cfg = self.cfg
+        b1, b2 = cfg.betas
+        with nvtx_range("opake::dp_step/nccl"):
+            dist.reduce_scatter_tensor(self._rs_out, self.acc[: self.shard_len * self.world], op=dist.ReduceOp.SUM)
+            K.dp_step(
+                grad_src=[self._rs_out.data_ptr() - 4 * self.shard_begin], shard_begin=self.shard_begin, shard_len=self.shard_len,
+                inv_batch=1.0 / cfg.logical_batch, sigma=sigma, seed=step_key.seed, step=self.step_count,
+                m=self.m, v=self.v, master=self.master, param_dst=[self.params.data_ptr()], param_src=self.params,
+                lr=cfg.lr, beta1=b1, beta2=b2, eps=cfg.eps, weight_decay=cfg.weight_decay, bc1=1.0 - b1**t,
+                bc2=1.0 - b2**t, phi_hat=phi_hat, zero_grad=False, blt_state=self.blt_state, blt_decay=self.blt_decay,
+                blt_scale=self.blt_scale, toep_state=self.toep_state, toep_coef=self.toep_coef, toep_pos=self.toep_pos,
+                sgd_mode=(cfg.optimizer == "sgd"), device=self.device)
+            if self.toep_state is not None:
+                self.toep_pos = (self.toep_pos - 1) % self.toep_state.shape[0]
+            mine = self.params[self.shard_begin : self.shard_begin + self.shard_len]
+            dist.all_gather_into_tensor(self.params[: self.shard_len * self.world], mine)
+        self.acc.zero_()
         self.step_count += 1
 
     def gather_params(self) -> None:
@@ -423,6 +462,39 @@ class ShardedDPEngine:
             self.params.copy_(p)
         if self.ep is not None and sd.get("experts") is not None:
             self.ep.load_state_dict(sd["experts"])
+
+    @staticmethod
+    def consolidate(shards: list[dict]) -> dict:
+        """One full-size training state from the per-rank ``state_dict()`` results of a run (any order): parameters from
+        the rank that stored them, the optimizer moments (and master weights, correlated-noise state) concatenated in
+        flat-parameter order. This is the layout a one-rank engine of the same model loads, and the one to convert
+        into framework-neutral checkpoints."""
+        if not shards:
+            raise ValueError("no shards")
+        world = int(shards[0]["world"])
+        by_begin = sorted(shards, key=lambda sd: (int(sd["shard_begin"]), int(sd["shard_len"])))
+        if len(by_begin) != world or any(int(sd["world"]) != world for sd in by_begin):
+            raise ValueError(f"expected the {world} shards of one run")
+        cursor = 0
+        for sd in by_begin:
+            if int(sd["shard_begin"]) != cursor:
+                raise ValueError("shards do not tile the parameter vector (missing or duplicated rank)")
+            cursor += int(sd["shard_len"])
+        params = next((sd["params"] for sd in by_begin if sd.get("params") is not None), None)
+        if params is None:
+            raise ValueError("no shard carries the parameters (rank 0's file is missing)")
+        if params.numel() != cursor:
+            raise ValueError(f"shards cover {cursor} elements, the parameter vector has {params.numel()}")
+
+        def cat(name: str, dim: int = 0):
+            parts = [sd.get(name) for sd in by_begin]
+            return None if any(p is None for p in parts) else torch.cat(parts, dim=dim)
+
+        first = by_begin[0]
+        return {"world": 1, "shard_begin": 0, "shard_len": cursor, "bounds": [0, cursor], "params": params, "m": cat("m"),
+                "v": cat("v"), "master": cat("master"), "blt_state": cat("blt_state", 1), "toep_state": cat("toep_state", 1),
+                "toep_pos": first.get("toep_pos", 0), "step_count": first["step_count"], "phi": first["phi"],
+                "noise_key": first["noise_key"]}
 
     def _rotate(self, ptrs: list[int]) -> list[int]:
         """This rank's buffer first, then the peers starting at rank+1 (spreads NVLink traffic across peers)."""

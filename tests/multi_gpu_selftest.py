@@ -27,6 +27,7 @@ def main() -> None:
     ap.add_argument("--shard-params", action="store_true", help="owners keep the parameters; fetched inside the forward GEMMs")
     ap.add_argument("--shard-sums", action="store_true", help="fp32 sums sharded, accumulation groups reduce-scattered")
     ap.add_argument("--graph", action="store_true", help="run the examples through CUDA graphs")
+    ap.add_argument("--comm", default="peer", choices=["peer", "nccl"], help="optimizer-step communication backend")
     ap.add_argument("--ep-train", action="store_true",
                     help="train a tiny mixture-of-experts decoder: all experts local on one rank, expert parallel on several")
     ap.add_argument("--sharded-linear", action="store_true", help="check the sharded-weight GEMMs instead of the engine")
@@ -59,7 +60,7 @@ def main() -> None:
     ecfg = EngineConfig(logical_batch=a.batch, noise_multiplier=0.7, lr=1e-2, seed=5, use_cuda_graph=a.graph,
                         blt_decay=(0.9, 0.5) if a.blt else (), blt_scale=(0.3, 0.2) if a.blt else (),
                         toeplitz_coef=(1.0, 0.5, 0.375, 0.3125) if a.toeplitz else (),
-                        shard_params=a.shard_params, shard_sums=a.shard_sums, accumulate_group=2)
+                        shard_params=a.shard_params, shard_sums=a.shard_sums, accumulate_group=2, comm_backend=a.comm)
     eng = ShardedDPEngine(cfg, ecfg, dev)
     g = torch.Generator().manual_seed(0)
     tok = torch.randint(0, cfg.vocab_size, (a.batch, a.seq), generator=g, dtype=torch.int32)

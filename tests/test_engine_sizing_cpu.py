@@ -35,3 +35,23 @@ def test_accumulation_group_override_and_cpu(monkeypatch):
     # small models: the reserve scales with the model instead of the fixed 32 GB
     monkeypatch.setattr(torch.cuda, "mem_get_info", lambda dev=None: (64 << 30, 183 << 30))
     assert _engine(1 << 20)._pick_group_size() == 8
+
+
+def test_consolidate_per_rank_shards_into_one_state():
+    """The per-rank optimizer shards of a run concatenate, in flat-parameter order, into the state of a one-rank run."""
+    total = 24
+    params = torch.arange(total, dtype=torch.float32)
+    bounds = [0, 8, 8, 24]            # one rank owns nothing (a model with fewer tensors than ranks)
+    shards = []
+    for r in range(3):
+        b, e = bounds[r], bounds[r + 1]
+        shards.append({"world": 3, "shard_begin": b, "shard_len": e - b, "m": params[b:e] * 2, "v": params[b:e] * 3, "master": None,
+                       "blt_state": torch.stack([params[b:e], -params[b:e]]), "toep_state": None, "toep_pos": 1, "step_count": 5,
+                       "phi": 0.25, "noise_key": {"seed": 1, "impl": "x"}, "params": params if r == 0 else None})
+    full = ShardedDPEngine.consolidate([shards[2], shards[0], shards[1]])
+    assert full["world"] == 1 and full["shard_len"] == total and full["step_count"] == 5
+    assert torch.equal(full["m"], params * 2) and torch.equal(full["v"], params * 3)
+    assert torch.equal(full["blt_state"], torch.stack([params, -params])) and full["master"] is None
+    import pytest
+    with pytest.raises(ValueError):
+        ShardedDPEngine.consolidate(shards[:2])

@@ -58,6 +58,18 @@ def test_two_ranks_fully_sharded_match_one_rank(tmp_path, mode):
     assert diff <= 2e-2 * one["params"].abs().max().item(), diff
 
 
+def test_two_ranks_nccl_baseline_step_matches_one_rank(tmp_path):
+    """The library-collective implementation of the optimizer step (reduce_scatter_tensor, local kernel,
+    all_gather_into_tensor) gives the parameters of the fused peer-memory step."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    one = _run(1, str(tmp_path / "w1.pt"))
+    two = _run(2, str(tmp_path / "w2.pt"), ("--comm", "nccl"))
+    assert one["losses"] == pytest.approx(two["losses"], rel=2e-3)
+    diff = (one["params"] - two["params"]).abs().max().item()
+    assert diff <= 2e-2 * one["params"].abs().max().item(), diff
+
+
 def test_two_ranks_match_one_rank_toeplitz(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
