@@ -181,6 +181,11 @@ def _register():
     D.register_sync_type(AdaptiveClipState, sync_adaptive_clip_state)
     D.register_sync_type(FixedClipState, lambda s: s)
     D.register_sync_type(AutoClipState, lambda s: s)
+    # per-example aux outputs and clipping statistics: gathered / summed over the ranks by sync()
+    from ..engine.clipping.core import ClippedFunAux
+    from ..engine.clipping.distributed import sync_clipping_aux
+    for aux_type in (ClippedGradAux, ClippedFunAux, ClippingStats):
+        D.register_sync_type(aux_type, sync_clipping_aux)
 
 
 _register()

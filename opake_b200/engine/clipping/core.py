@@ -27,6 +27,7 @@ from ..pytree import param_path_display, tree_flatten_with_paths, tree_map, tree
 from ..types import ClippedPytree, ClipState, PerGroup, SecondMomentClippingOutput, clipped
 from . import numerics as N
 from .kernel_backend import get_fused_clip_backend
+from .streaming import resolve_stream_impl, stream_clip_and_sum
 
 
 @dataclass(frozen=True)
@@ -168,20 +169,17 @@ def clipped_fun(fun: Callable, has_aux: bool = False, *, batch_argnums=0, clippi
             norms = torch.sqrt(sum(v * v for v in group_norms.values()))
             mask = masks
         else:
-            fused = get_fused_clip_backend()
-            if (fused is not None and _scale_fn is None and builtin.kind != "auto" and not second_moment
-                    and compute_dtype is None and not isinstance(norm_value, torch.Tensor) and fused.supported(leaves)):
+            impl = resolve_stream_impl(leaves, norm_value, scale_fn=_scale_fn, builtin_kind=builtin.kind, second_moment=second_moment,
+                                       compute_dtype=compute_dtype)
+            if impl == "fused":
                 # CUDA: two multi-tensor kernels replace the per-leaf square / scale / sum passes
-                sums, norms, mask, cn = fused.fused_clip_sum(leaves, float(norm_value), with_postsq=return_aux)
+                sums, norms, mask, cn = get_fused_clip_backend().fused_clip_sum(leaves, float(norm_value), with_postsq=return_aux)
                 return td, sums, None, norms, mask, cn, None
-            sq = sum(N.per_example_sq(l, sqd) for l in leaves)
-            if _scale_fn is not None:
-                norms = torch.sqrt(sq)
-                f = _scale_fn(norms)
-                factors, mask = [f for _ in leaves], norms > float(norm_value)
-            else:
-                factors, norms, mask = N.clip_factors(sq, norm_value, leaves, auto=builtin.kind == "auto",
-                                                      gamma=builtin.gamma)
+            # portable two-pass streaming path: no scaled copy of the whole per-example gradient
+            sums, sq_sums, norms, mask, cn = stream_clip_and_sum(leaves, norm_value, scale_fn=_scale_fn, auto=builtin.kind == "auto",
+                                                                 gamma=builtin.gamma, second_moment=second_moment,
+                                                                 compute_dtype=compute_dtype, with_postsq=return_aux)
+            return td, sums, sq_sums, norms, mask, cn, None
         scaled = [N.scale_leaf(l, f) for l, f in zip(leaves, factors)]
         sums = [s.sum(0, dtype=N.acc_dtype_of(s.dtype)) for s in scaled]
         sq_sums = None

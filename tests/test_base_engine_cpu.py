@@ -167,3 +167,33 @@ def test_auto_and_per_group_clipping():
         per_group(w, {"nope": 1.0})
     with pytest.raises(ValueError, match="multiple patterns"):
         per_group(w, {"lin": 1.0, "w": 1.0}, allow_unused_patterns=True)
+
+
+def test_streaming_clip_and_sum_matches_materialised_scaling():
+    """The two-pass streaming path (one leaf at a time) equals scaling a full copy of the per-example gradients, for
+    fixed clipping, AUTO-S, a custom scale function and the second-moment stream; the backend choice follows the rules
+    of the reference's resolver."""
+    import torch
+
+    from opake_b200.engine.clipping import numerics as N
+    from opake_b200.engine.clipping.streaming import resolve_stream_impl, stream_clip_and_sum
+
+    g = torch.Generator().manual_seed(0)
+    leaves = [torch.randn(6, 5, 3, generator=g) * 3, torch.randn(6, 7, generator=g), torch.randn(6, generator=g)]
+    sq = sum(N.per_example_sq(l, torch.float64) for l in leaves)
+    for auto in (False, True):
+        sums, sq_sums, norms, mask, post = stream_clip_and_sum(leaves, 1.5, auto=auto, second_moment=True, with_postsq=True)
+        factors, norms_ref, mask_ref = N.clip_factors(sq, 1.5, leaves, auto=auto, gamma=0.01)
+        scaled = [N.scale_leaf(l, f) for l, f in zip(leaves, factors)]
+        for a, b in zip(sums, scaled):
+            assert torch.equal(a, b.sum(0, dtype=N.acc_dtype_of(b.dtype)))
+        for a, b in zip(sq_sums, scaled):
+            assert torch.allclose(a, (b ** 2).sum(0))
+        assert torch.equal(norms, norms_ref) and torch.equal(mask, mask_ref)
+        assert torch.allclose(post, torch.sqrt(sum(N.per_example_sq(s, torch.float64) for s in scaled)))
+        if not auto:
+            assert float(post.max()) <= 1.5
+    sums, _, norms, mask, _ = stream_clip_and_sum(leaves, 1.0, scale_fn=lambda n: torch.clamp(0.5 / n, max=1.0).to(torch.float32))
+    assert sums[0].shape == (5, 3) and mask.dtype == torch.bool
+    assert resolve_stream_impl(leaves, 1.0) == "stream"                       # CPU leaves: no fused backend applies
+    assert resolve_stream_impl(leaves, 1.0, second_moment=True) == "stream"

@@ -153,3 +153,35 @@ def _ep_worker(rank, world, port, q):
 def test_expert_parallel_two_pass_clipping_matches_single_process():
     out = _run(_ep_worker)
     assert out == {0: "ok", 1: "ok"}, out
+
+
+def _aux_sync_worker(rank, world, port, q):
+    _init(rank, world, port)
+    from opake_b200.dpsgd import clipped_grad  # noqa: F401  (registers the sync handlers)
+    from opake_b200.engine import distributed as D
+    from opake_b200.engine.clipping.core import ClippedGradAux, ClippingStats, FixedClipState
+    from opake_b200.engine.clipping.distributed import sync_clip_state, sync_clipping_rate
+
+    b = 3 + rank                                       # ranks hold different numbers of examples
+    base = 10.0 * rank
+    aux = ClippedGradAux(loss_values=torch.arange(b, dtype=torch.float32) + base, grad_norms=torch.full((b,), 2.0 + rank),
+                         clipped_grad_norms=torch.ones(b), loss_aux={"logits": torch.arange(b * 2, dtype=torch.float32).view(b, 2) + base},
+                         clipping_rate=1.0 if rank == 0 else 0.5, batch_size=b)
+    got = D.sync(aux)
+    stats = D.sync(ClippingStats(num_clipped=float(rank + 1), clipping_rate=None, batch_size=b))
+    c, n, r = sync_clipping_rate({"a": 1.0 + rank, "b": 0.0}, b)
+    assert sync_clip_state(FixedClipState()) == FixedClipState()
+    q.put((rank, (got.loss_values.tolist(), got.grad_norms.tolist(), got.loss_aux["logits"].shape, got.batch_size, got.clipping_rate,
+                  stats.num_clipped, stats.batch_size, stats.clipping_rate, c, n, r)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_clipping_aux_and_statistics_are_gathered_over_ranks():
+    out = _run(_aux_sync_worker)
+    assert out[0] == out[1]                                                   # every rank ends with the same global view
+    losses, norms, shape, b, rate, nclip, nb, srate, c, n, r = out[0]
+    assert losses == [0.0, 1.0, 2.0, 10.0, 11.0, 12.0, 13.0] and norms == [2.0] * 3 + [3.0] * 4
+    assert tuple(shape) == (7, 2) and b == 7 and rate == pytest.approx((3 * 1.0 + 4 * 0.5) / 7)
+    assert (nclip, nb) == (3.0, 7) and srate == pytest.approx(3 / 7)
+    assert c == {"a": 3.0, "b": 0.0} and n == 7 and r["a"] == pytest.approx(3 / 7)
