@@ -15,7 +15,8 @@ from typing import Callable
 
 import torch
 
-__all__ = ["checkpoint_under_vmap", "native_support", "offload_activations", "apply_gradient_checkpointing"]
+__all__ = ["checkpoint_under_vmap", "hf_checkpoint_under_transforms", "native_support", "offload_activations",
+           "apply_gradient_checkpointing"]
 
 
 def native_support() -> bool:
@@ -32,10 +33,13 @@ def native_support() -> bool:
         return False
 
 
-def checkpoint_under_vmap(fn: Callable, *args):
+def checkpoint_under_vmap(fn: Callable, *args, offload: bool = False):
     """Runs ``fn(*args)`` keeping only its inputs; the backward pass recomputes the segment. Implemented with a
     custom ``autograd.Function`` whose backward calls ``torch.func.vjp`` on ``fn`` (``generate_vmap_rule`` lets the
-    whole thing sit under vmap)."""
+    whole thing sit under vmap). Everything ``fn`` needs a gradient for must be among ``args``: tensors it merely
+    closes over are constants of the segment. ``offload``: the kept inputs wait in host memory between forward and
+    backward (the functional counterpart of ``save_on_cpu``, which relies on saved-tensor hooks and is therefore not
+    available inside ``torch.func`` transforms)."""
     tensors = [a for a in args if isinstance(a, torch.Tensor)]
     if not tensors or not any(t.requires_grad or torch._C._functorch.is_gradtrackingtensor(t) for t in tensors):
         return fn(*args)
@@ -50,16 +54,52 @@ def checkpoint_under_vmap(fn: Callable, *args):
 
         @staticmethod
         def setup_context(ctx, inputs, output):
-            ctx.save_for_backward(*inputs)
+            ctx.devices = [x.device for x in inputs]
+            ctx.save_for_backward(*[(x.to("cpu") if offload and x.is_cuda else x) for x in inputs])
 
         @staticmethod
         def backward(ctx, *gs):
-            xs = ctx.saved_tensors
+            xs = [x.to(d) for x, d in zip(ctx.saved_tensors, ctx.devices)]
             with torch.enable_grad():
                 _, pull = torch.func.vjp(fn, *xs)
             return pull(gs[0] if len(gs) == 1 else gs)
 
     return _Segment.apply(*args)
+
+
+def hf_checkpoint_under_transforms(fn, *args, offload: bool = False, **_kw):
+    """Drop-in for the ``_gradient_checkpointing_func`` of Hugging Face ``GradientCheckpointingLayer`` modules that works
+    inside ``vmap(grad(...))``. ``fn`` is the ``partial(layer.__call__, **kwargs)`` the library builds. The layer's
+    current parameters (under ``functional_call`` these are the transform-level tensors) and every floating-point
+    tensor among the arguments become explicit inputs of a ``checkpoint_under_vmap`` segment, which re-runs the layer
+    through ``torch.func.functional_call`` in the backward pass; integer tensors, masks and flags are constants."""
+    from torch.func import functional_call
+
+    from ..engine.pytree import tree_flatten, tree_unflatten
+
+    layer = getattr(getattr(fn, "func", None), "__self__", None)
+    if layer is None or not isinstance(layer, torch.nn.Module):
+        return fn(*args)
+    kwargs = dict(getattr(fn, "keywords", None) or {})
+    named = list(layer.named_parameters())
+    names = [n for n, _ in named]
+    leaves, spec = tree_flatten((list(args), kwargs))
+    idx = [i for i, l in enumerate(leaves) if isinstance(l, torch.Tensor) and l.is_floating_point()]
+
+    def segment(*flat):
+        ps, rest = flat[: len(names)], flat[len(names):]
+        cur = list(leaves)
+        for i, t in zip(idx, rest):
+            cur[i] = t
+        a, kw = tree_unflatten(spec, cur)
+        was = getattr(layer, "gradient_checkpointing", False)
+        layer.gradient_checkpointing = False          # the recomputation runs the layer itself, not another checkpoint
+        try:
+            return functional_call(layer, dict(zip(names, ps)), tuple(a), kw)
+        finally:
+            layer.gradient_checkpointing = was
+
+    return checkpoint_under_vmap(segment, *[p for _, p in named], *[leaves[i] for i in idx], offload=offload)
 
 
 @contextlib.contextmanager
@@ -69,12 +109,33 @@ def offload_activations(pin_memory: bool = True):
         yield
 
 
-def apply_gradient_checkpointing(model, enable: bool = True, **kwargs) -> bool:
-    """Turns on the model's own checkpointing in the non-reentrant form when PyTorch supports it under transforms;
-    returns whether it is active."""
-    if not enable:
+def apply_gradient_checkpointing(model, enable: bool = True, offload: bool = False, **kwargs) -> bool:
+    """Turns on the model's own layer checkpointing for use under ``vmap(grad)``; returns whether it is active.
+    Where PyTorch runs non-reentrant checkpoints inside functorch transforms by itself, the library's function is kept;
+    otherwise every checkpointing layer is pointed at ``hf_checkpoint_under_transforms``. ``offload`` keeps the layer
+    inputs in host memory between the passes (activation offloading)."""
+    if not enable or not hasattr(model, "gradient_checkpointing_enable"):
         return False
-    if hasattr(model, "gradient_checkpointing_enable") and native_support():
-        model.gradient_checkpointing_enable(gradient_checkpointing_kwargs={"use_reentrant": False, **kwargs})
+    model.gradient_checkpointing_enable(gradient_checkpointing_kwargs={"use_reentrant": False, **kwargs})
+    # the library also hooks the embedding output with ``requires_grad_()`` (needed by its reentrant checkpoint for
+    # frozen-embedding PEFT runs); in-place autograd flags are illegal inside functorch transforms, and the functional
+    # path tracks gradients through the transform itself
+    for owner in {model, getattr(model, "base_model", model)}:
+        if hasattr(owner, "disable_input_require_grads"):
+            try:
+                owner.disable_input_require_grads()
+            except Exception:
+                pass
+        hook = getattr(owner, "_require_grads_hook", None)
+        if hook is not None:
+            hook.remove()
+    if native_support() and not offload:
         return True
-    return False
+    import functools
+
+    n = 0
+    for m in model.modules():
+        if hasattr(m, "_gradient_checkpointing_func") and getattr(m, "gradient_checkpointing", False):
+            m._gradient_checkpointing_func = functools.partial(hf_checkpoint_under_transforms, offload=offload)
+            n += 1
+    return n > 0

@@ -375,6 +375,20 @@ class DPTrainer:
             except ImportError:
                 pass
         self.model.train(False)          # dropout etc. would need per-example RNG; DP fine-tuning runs deterministic forward
+        if a.gradient_checkpointing or a.activation_offloading:
+            # layer checkpointing that is legal under vmap(grad) (packages/opake-transformers/src/opake/api/transformers/
+            # trainer/_dp_trainer.py:1499-1528): the layers re-run in the backward pass; with activation offloading the
+            # kept layer inputs wait in host memory. The library checkpoints only in training mode, so dropout is zeroed.
+            from ..patches.torch_checkpoint import apply_gradient_checkpointing
+            from ..patches.transformers.components import disable_dropout
+
+            disable_dropout(self.model)
+            kw = {k: v for k, v in (a.gradient_checkpointing_kwargs or {}).items() if k != "use_reentrant"}
+            rt["gradient_checkpointing"] = apply_gradient_checkpointing(self.model, offload=bool(a.activation_offloading), **kw)
+            if rt["gradient_checkpointing"]:
+                self.model.train(True)
+            else:
+                warnings.warn("gradient checkpointing was requested but the model exposes no checkpointing layers", stacklevel=2)
         fmodel, params, frozen = make_functional(self.model, disable_autograd_tracking=True, partition_trainable=True)
         if not params:
             raise ConfigurationError("the model has no trainable parameters")

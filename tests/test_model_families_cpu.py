@@ -71,3 +71,36 @@ def test_family_patched_loss_and_per_example_gradients(family):
     # sanity: the examples do have different gradients
     some = next(k for k in g_v if g_v[k].abs().sum() > 0)
     assert not torch.allclose(g_v[some][0], g_v[some][1])
+
+
+@pytest.mark.parametrize("offload", [False, True])
+def test_gradient_checkpointing_under_vmap_grad(offload):
+    """Layer checkpointing of a Hugging Face model inside ``vmap(grad)``: same per-example gradients, and every decoder
+    layer runs twice (forward, then recomputation in the backward pass)."""
+    from opake_b200 import patches
+    from opake_b200.patches.torch_checkpoint import apply_gradient_checkpointing
+    torch.manual_seed(0)
+    model = _tiny("qwen3")
+    patches.apply_model_patches(model)
+    model.train()
+    params = {k: v.detach() for k, v in model.named_parameters()}
+    ids = torch.randint(1, 97, (3, 12))
+
+    def loss(p, x):
+        return functional_call(model, p, (x.unsqueeze(0),), {"labels": x.unsqueeze(0)}).loss
+
+    want = vmap(grad(loss), in_dims=(None, 0))(params, ids)
+    assert apply_gradient_checkpointing(model, offload=offload)
+    calls = {"n": 0}
+    layer = model.model.layers[1]
+    inner = layer.forward
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        return inner(*a, **k)
+
+    layer.forward = counting
+    got = vmap(grad(loss), in_dims=(None, 0))(params, ids)
+    assert calls["n"] == 2
+    for k in want:
+        assert torch.allclose(got[k], want[k], rtol=1e-5, atol=1e-7), k
