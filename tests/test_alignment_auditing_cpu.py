@@ -150,3 +150,55 @@ def test_loss_and_gradient_scores_bind_identifiers():
     assert np.allclose(g.scores, -(gw ** 2).sum(-1).numpy(), rtol=1e-4)
     cal = loss_scores(fn, w, batch_argnums=(1, 2), coin_flip=cf, dataset=ds, reference_scores=s)
     assert np.allclose(cal.scores, 0.0, atol=1e-6)
+
+
+def test_fused_lora_qkv_and_mlp_match_autograd_under_vmap():
+    """The fused LoRA functions (three projections of one input; the adapted gated MLP) against plain autograd, both as
+    ordinary calls and as per-example gradients under ``vmap(grad)``."""
+    import torch
+    import torch.nn.functional as F
+
+    from opake_b200.patches.kernels.lora import lora_mlp, lora_qkv
+
+    torch.manual_seed(0)
+    n, T, d, r, f = 3, 5, 8, 2, 12
+    x = torch.randn(n, T, d)
+
+    def mk(o, i):
+        return [torch.randn(o, i) * 0.3, torch.randn(r, i) * 0.3, torch.randn(o, r) * 0.3, 0.5]
+
+    q, k, v = mk(d, d), mk(4, d), mk(4, d)
+    gate, up, down = mk(f, d), mk(f, d), mk(d, f)
+    adapters = {"q": (q[1], q[2]), "k": (k[1], k[2]), "v": (v[1], v[2]), "g": (gate[1], gate[2]), "u": (up[1], up[2]), "d": (down[1], down[2])}
+
+    def plain(p, W, xx):
+        return xx @ W[0].t() + W[3] * (xx @ p[0].t()) @ p[1].t()
+
+    def loss_fused(ad, xe):
+        qq, kk, vv = lora_qkv(xe, (q[0], *ad["q"], q[3]), (k[0], *ad["k"], k[3]), (v[0], *ad["v"], v[3]))
+        y = lora_mlp(xe, (gate[0], *ad["g"], gate[3]), (up[0], *ad["u"], up[3]), (down[0], *ad["d"], down[3]))
+        return (qq.sum() + (kk * vv).sum() + (y ** 2).sum())
+
+    def loss_plain(ad, xe):
+        qq, kk, vv = plain(ad["q"], q, xe), plain(ad["k"], k, xe), plain(ad["v"], v, xe)
+        h = F.silu(plain(ad["g"], gate, xe)) * plain(ad["u"], up, xe)
+        y = plain(ad["d"], down, h)
+        return (qq.sum() + (kk * vv).sum() + (y ** 2).sum())
+
+    assert torch.allclose(loss_fused(adapters, x[0]), loss_plain(adapters, x[0]), rtol=1e-5)
+    g1 = torch.func.vmap(torch.func.grad(loss_fused), in_dims=(None, 0))(adapters, x)
+    g2 = torch.func.vmap(torch.func.grad(loss_plain), in_dims=(None, 0))(adapters, x)
+    for name in adapters:
+        for a, b in zip(g1[name], g2[name]):
+            assert a.shape == b.shape and torch.allclose(a, b, rtol=1e-4, atol=1e-5), name
+    # input gradient of the un-batched call
+    xr = x[0].clone().requires_grad_()
+    loss_fused(adapters, xr).backward()
+    gx = xr.grad.clone()
+    xr.grad = None
+    loss_plain(adapters, xr).backward()
+    assert torch.allclose(gx, xr.grad, rtol=1e-4, atol=1e-5)
+    # tanh-GELU gate
+    y1 = lora_mlp(x[0], (gate[0], *adapters["g"], gate[3]), (up[0], *adapters["u"], up[3]), (down[0], *adapters["d"], down[3]), act="gelu_tanh")
+    h = F.gelu(plain(adapters["g"], gate, x[0]), approximate="tanh") * plain(adapters["u"], up, x[0])
+    assert torch.allclose(y1, plain(adapters["d"], down, h), rtol=1e-5, atol=1e-6)
