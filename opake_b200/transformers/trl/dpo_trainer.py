@@ -61,6 +61,12 @@ class DPOConfig(TrainingArguments):
         if self.sync_ref_model and self.precompute_ref_log_probs:
             raise ConfigurationError("sync_ref_model changes the reference during training; set precompute_ref_log_probs=False")
 
+    @classmethod
+    def from_trl(cls, trl_config, **dp_overrides):
+        """From a TRL ``DPOConfig`` (or a mapping with its field names)."""
+        from ..hf_convert import convert_trl_config
+        return convert_trl_config(trl_config, cls, **dp_overrides)
+
 
 class DPOTrainer(DPTrainer):
     def __init__(self, model=None, ref_model=None, args: DPOConfig | None = None, data_collator=None, train_dataset=None,

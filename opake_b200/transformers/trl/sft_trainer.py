@@ -36,6 +36,12 @@ class SFTConfig(TrainingArguments):
             raise ConfigurationError("packing merges several examples into one sequence, which breaks the per-example "
                                      "privacy unit; it is not supported")
 
+    @classmethod
+    def from_trl(cls, trl_config, **dp_overrides):
+        """From a TRL ``SFTConfig`` (or a mapping with its field names)."""
+        from ..hf_convert import convert_trl_config
+        return convert_trl_config(trl_config, cls, **dp_overrides)
+
 
 class SFTTrainer(DPTrainer):
     def __init__(self, model=None, args: SFTConfig | None = None, data_collator=None, train_dataset=None, eval_dataset=None,

@@ -270,3 +270,32 @@ def test_accountant_engine_under_address_and_ub_sanitizers(tmp_path):
     assert build.returncode == 0, build.stderr[-2000:]
     run = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     assert run.returncode == 0 and "all checks passed" in run.stdout, run.stdout[-2000:] + run.stderr[-2000:]
+
+
+def test_hf_and_trl_argument_conversion_report_and_rejections():
+    """Hugging Face / TRL argument objects convert with the DP rules: accumulation collapses into the logical batch,
+    ``max_grad_norm`` becomes the per-example clipping norm, optimizer spellings collapse, old field names are
+    renamed, and settings that would silently change what is trained are refused."""
+    import warnings
+
+    from opake_b200.base.exceptions import ConfigurationError
+    from opake_b200.transformers import SFTConfig, TrainingArguments
+    from opake_b200.transformers.hf_convert import convert_hf_training_arguments
+
+    src = dict(output_dir="o", per_device_train_batch_size=4, gradient_accumulation_steps=8, optim="adamw_torch_fused",
+               lr_scheduler_type="cosine", warmup_ratio=0.1, max_grad_norm=0.7, learning_rate=2e-4, torch_compile=True,
+               gradient_checkpointing=True, gradient_checkpointing_kwargs={"use_reentrant": True}, group_by_length=True)
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        args, report = convert_hf_training_arguments(src, TrainingArguments, return_report=True, privacy_noise_multiplier=1.0)
+    assert args.per_device_train_batch_size == 32 and args.microbatch_size == 4
+    assert args.optim == "adamw" and args.lr_scheduler == "cosine" and args.warmup_steps == 0.1
+    assert args.clipping_norm == 0.7 and args.gradient_checkpointing and args.gradient_checkpointing_kwargs == {}
+    assert not args.torch_compile and "torch_compile" in report.dropped and "group_by_length" in report.dropped
+    assert report.renamed["max_grad_norm"].startswith("clipping_norm") and "gradient_accumulation_steps" in report.renamed
+    assert any("group_by_length" in str(x.message) for x in w)
+    sft = SFTConfig.from_trl(dict(output_dir="o", max_seq_length=256, per_device_train_batch_size=2), privacy_noise_multiplier=1.0)
+    assert sft.max_length == 256
+    for bad in ({"deepspeed": "ds.json"}, {"packing": True}, {"padding_free": True}):
+        with pytest.raises(ConfigurationError):
+            convert_hf_training_arguments({"output_dir": "o", **bad}, SFTConfig)
