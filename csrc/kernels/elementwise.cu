@@ -2,6 +2,7 @@
 // embedding gather and per-example compact embedding gradient, cross-entropy helpers.
 // All activations are bf16 in memory with fp32 arithmetic; rows are processed with 16-byte vector accesses.
 #include "opk_api.h"
+#include "debug_bounds.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -471,16 +472,19 @@ __global__ void gelu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv
 // ------------------------------------------------------------------------------------------- embedding
 __global__ void embedding_fwd_kernel(const int* __restrict__ tok, const __nv_bfloat16* __restrict__ table,
                                      const __nv_bfloat16* __restrict__ pos_table, __nv_bfloat16* __restrict__ out,
-                                     int D) {
+                                     int D, int vocab) {
   const long long t = blockIdx.x;
-  const bf16x8* src = reinterpret_cast<const bf16x8*>(table + (long long)tok[t] * D);
+  // an id outside the table yields a zero embedding row: never an address outside the table
+  const bool in_table = tok[t] >= 0 && tok[t] < vocab;
+  (void)OPK_IDX_OK(tok[t], vocab);
+  const bf16x8* src = reinterpret_cast<const bf16x8*>(table + (long long)(in_table ? tok[t] : 0) * D);
   const bf16x8* ps = pos_table ? reinterpret_cast<const bf16x8*>(pos_table + t * D) : nullptr;
   bf16x8* dst = reinterpret_cast<bf16x8*>(out + t * D);
   for (int i = threadIdx.x; i < (D >> 3); i += blockDim.x) {
-    if (ps) {
-      float a[8], b[8];
-      unpack8(src[i], a);
-      unpack8(ps[i], b);
+    if (ps || !in_table) {
+      float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (in_table) unpack8(src[i], a);
+      if (ps) unpack8(ps[i], b);
 #pragma unroll
       for (int j = 0; j < 8; ++j) a[j] += b[j];
       dst[i] = pack8(a);
@@ -491,7 +495,11 @@ __global__ void embedding_fwd_kernel(const int* __restrict__ tok, const __nv_bfl
 }
 // Token ids outside [0, vocab) are skipped by all three table kernels (their rep[] entry becomes -1, which the
 // accumulate / add-rows kernels treat as "not a representative row"), so a bad id can never index past the table.
-__device__ __forceinline__ bool emb_tok_ok(int tok, int vocab) { return (unsigned)tok < (unsigned)vocab; }
+__device__ __forceinline__ bool emb_tok_ok(int tok, int vocab) {
+  (void)OPK_IDX_OK(tok, vocab);
+  return (unsigned)tok < (unsigned)vocab;
+}
+OPK_DEBUG_BOUNDS_UNIT();
 __global__ void emb_first_pos_kernel(const int* __restrict__ tok, int* __restrict__ first_pos, int T, int vocab) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t < T && emb_tok_ok(tok[t], vocab)) atomicMin(&first_pos[tok[t]], t);
@@ -686,7 +694,8 @@ __global__ void __launch_bounds__(NT) ce_fwd_kernel(const void* __restrict__ log
     const float l = bm + logf(tot);
     if (lse) lse[row] = l;
     const int lab = labels[row];
-    nll[row] = lab >= 0 ? l - cap(load_logit<FP32>(logits, base + lab), scale, softcap) : 0.f;
+    if (lab >= 0) (void)OPK_IDX_OK(lab, V);
+    nll[row] = (lab >= 0 && lab < V) ? l - cap(load_logit<FP32>(logits, base + lab), scale, softcap) : 0.f;
   }
 }
 
@@ -899,10 +908,10 @@ extern "C" int opk_gelu_bwd(const void* dy, const void* x, void* dx, int64_t n, 
   return 0;
 }
 extern "C" int opk_embedding_fwd(const int32_t* tok, const void* table, const void* pos_table, void* out, int T, int D,
-                                 void* stream) {
+                                 int vocab, void* stream) {
   if (T <= 0) return 0;
-  if (D % 8) return -1;
-  embedding_fwd_kernel<<<T, 128, 0, ST(stream)>>>(tok, BF(table), BF(pos_table), BFM(out), D);
+  if (D % 8 || vocab <= 0) return -1;
+  embedding_fwd_kernel<<<T, 128, 0, ST(stream)>>>(tok, BF(table), BF(pos_table), BFM(out), D, vocab);
   OPK_LAUNCH_CHECK();
   return 0;
 }

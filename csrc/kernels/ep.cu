@@ -31,6 +31,7 @@
 #include <stdint.h>
 
 #include "opk_api.h"
+#include "debug_bounds.cuh"
 
 namespace {
 
@@ -94,7 +95,9 @@ __global__ void __launch_bounds__(1024) ep_count_kernel(const OpkEpGroup g, cons
   __syncthreads();
   const int chunk = ((n_entries + 31) / 32 + 31) / 32 * 32;   // entries per warp, a multiple of 32
   const int c0 = warp * chunk, c1 = min(c0 + chunk, n_entries);
-  for (int n = c0 + lane; n < c1; n += 32) atomicAdd(&hist[warp][idx[n]], 1);
+  // an expert id outside [0, E) is dropped (no row is sent for it, its position becomes -1 in dispatch)
+  for (int n = c0 + lane; n < c1; n += 32)
+    if (OPK_IDX_OK(idx[n], E) && (unsigned)idx[n] < (unsigned)E) atomicAdd(&hist[warp][idx[n]], 1);
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int run = 0;
@@ -108,7 +111,8 @@ __global__ void __launch_bounds__(1024) ep_count_kernel(const OpkEpGroup g, cons
   __syncthreads();
   for (int base = c0; base < c1; base += 32) {
     const int n = base + lane;
-    const bool valid = n < c1;
+    const bool valid = n < c1 && (unsigned)idx[n < c1 ? n : c0] < (unsigned)E;
+    if (n < c1 && !valid) entry_rank[n] = 0;
     const int e = valid ? idx[n] : -1 - lane;                 // invalid lanes match nobody
     const unsigned m = __match_any_sync(0xffffffffu, e);
     if (valid) {
@@ -204,7 +208,7 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const OpkEpGroup g, co
             pos[u] = entry_pos[n];
           } else {
             const int e = idx[n];
-            pos[u] = ((e / El) << 26) | (base[e] + entry_rank[n]);
+            pos[u] = (unsigned)e < (unsigned)E ? (((e / El) << 26) | (base[e] + entry_rank[n])) : -1;
             if (c == 0) entry_pos[n] = pos[u];
           }
           v[u] = *reinterpret_cast<const uint4*>(x + (long long)(n / k) * ldx + c * 8);
@@ -370,6 +374,7 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const OpkEpGroup g, con
         w[q] = 0.f;
         if (s0 + q < k) {
           const int pos = entry_pos[(long long)t * k + s0 + q];
+          if (pos < 0) continue;                               // dropped entry: contributes nothing
           w[q] = wts ? wts[(long long)t * k + s0 + q] : 1.f;
           const __nv_bfloat16* src =
               reinterpret_cast<const __nv_bfloat16*>(y.p[pos >> 26]) + (long long)(pos & 0x3FFFFFF) * D + c * 8;
@@ -398,6 +403,10 @@ __global__ void __launch_bounds__(256) ep_combine_bwd_kernel(const OpkEpPeers y,
   const int n = (int)((blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
   if (n >= n_entries) return;
   const int pos = entry_pos[n];
+  if (pos < 0) {
+    if (lane == 0) dwts[n] = 0.f;
+    return;
+  }
   const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(dy + (long long)(n / k) * D);
   const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const __nv_bfloat16*>(y.p[pos >> 26]) +
                                                                   (long long)(pos & 0x3FFFFFF) * D);
@@ -424,6 +433,8 @@ bool group_ok(const OpkEpGroup* g) {
   return g && g->world >= 1 && g->world <= MAX_W && g->rank >= 0 && g->rank < g->world && g->n_experts >= g->world &&
          g->n_experts <= MAX_E && g->n_experts % g->world == 0 && g->r_cap > 0 && g->r_cap % 128 == 0 && g->r_cap < (1 << 26);
 }
+
+OPK_DEBUG_BOUNDS_UNIT();
 
 }  // namespace
 

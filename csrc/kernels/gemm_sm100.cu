@@ -1,6 +1,7 @@
 // Host side of the tcgen05 GEMM: builds the TMA tensor maps and launches the persistent kernel.
 #include "gemm2_sm100.cuh"
 #include "opk_api.h"
+#include "debug_bounds.cuh"
 
 #include <cudaTypedefs.h>
 #include <mutex>
@@ -127,6 +128,41 @@ int pick_bn(int N, int epilogue) {
 }  // namespace
 
 extern "C" const char* opk_last_error(void) { return g_err; }
+
+// ---- debug-build index checks: registry of the translation units' records (see debug_bounds.cuh)
+#ifdef OPK_DEBUG_BOUNDS
+namespace opk { namespace dbg {
+struct Unit { ReadFn fn; const char* file; };
+static Unit* units() { static Unit u[16]; return u; }       // function-local: usable from other units' static initialisers
+static int& n_units() { static int n = 0; return n; }
+void register_unit(ReadFn fn, const char* file) {
+  if (n_units() < 16) units()[n_units()++] = Unit{fn, file};
+}
+}}  // namespace opk::dbg
+#endif
+
+extern "C" int opk_debug_bounds_read(int64_t* out4, char* file_out, int file_cap, int reset) {
+#ifdef OPK_DEBUG_BOUNDS
+  using namespace opk::dbg;
+  out4[0] = out4[1] = out4[2] = out4[3] = 0;
+  if (file_out && file_cap > 0) file_out[0] = 0;
+  for (int i = 0; i < n_units(); ++i) {
+    unsigned long long rec[4] = {0, 0, 0, 0};
+    const int e = units()[i].fn(rec, reset);
+    if (e != 0) { set_err(cudaGetErrorString((cudaError_t)e)); return e; }
+    if (rec[0] && !out4[0]) {
+      out4[1] = (int64_t)rec[1]; out4[2] = (int64_t)rec[2]; out4[3] = (int64_t)rec[3];
+      if (file_out && file_cap > 0) snprintf(file_out, (size_t)file_cap, "%s", units()[i].file);
+    }
+    out4[0] += (int64_t)rec[0];
+  }
+  return 0;
+#else
+  (void)out4; (void)file_out; (void)file_cap; (void)reset;
+  set_err("this library was built without OPK_DEBUG_BOUNDS");
+  return -3;
+#endif
+}
 extern "C" int opk_num_sms(void) { return num_sms(); }
 extern "C" void opk_gemm_set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }
 extern "C" int opk_gemm_get_pair_mode(void) { return pair_mode() ? 1 : 0; }

@@ -13,6 +13,7 @@
 #include <stdint.h>
 
 #include "opk_api.h"
+#include "debug_bounds.cuh"
 
 namespace {
 
@@ -144,7 +145,9 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
   __syncthreads();
   const int chunk = ((n_entries + 31) / 32 + 31) / 32 * 32;   // entries per warp, a multiple of 32
   const int c0 = warp * chunk, c1 = min(c0 + chunk, n_entries);
-  for (int n = c0 + lane; n < c1; n += 32) atomicAdd(&hist[warp][idx[n]], 1);
+  // an expert id outside [0, E) is dropped from the plan (its dest stays -1): never an index past the histograms
+  for (int n = c0 + lane; n < c1; n += 32)
+    if (OPK_IDX_OK(idx[n], E) && (unsigned)idx[n] < (unsigned)E) atomicAdd(&hist[warp][idx[n]], 1);
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int run = 0;
@@ -179,7 +182,8 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
   for (int r = total + threadIdx.x; r < r_cap; r += blockDim.x) src_entry[r] = -1;
   for (int base = c0; base < c1; base += 32) {
     const int n = base + lane;
-    const bool valid = n < c1;
+    const bool valid = n < c1 && (unsigned)idx[n < c1 ? n : c0] < (unsigned)E;
+    if (n < c1 && !valid) dest[n] = -1;
     const int e = valid ? idx[n] : -1 - lane;                 // invalid lanes match nobody
     const unsigned m = __match_any_sync(0xffffffffu, e);
     if (valid) {
@@ -240,6 +244,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
     }
     for (int s = 0; s < k; ++s) {
       const int row = dest[(long long)t * k + s];
+      if (row < 0) continue;                                   // entry dropped by the plan (expert id out of range)
       const float w = wts ? wts[(long long)t * k + s] : 1.f;
       const uint4 v = *reinterpret_cast<const uint4*>(y + (long long)row * D + c * 8);
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -261,6 +266,10 @@ __global__ void __launch_bounds__(256) moe_combine_bwd_kernel(const __nv_bfloat1
                                                               float* __restrict__ dwts) {
   const int n = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (n >= n_entries) return;
+  if (dest[n] < 0) {
+    if (lane == 0) dwts[n] = 0.f;
+    return;
+  }
   const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(dy + (long long)(n / k) * D);
   const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(y + (long long)dest[n] * D);
   float s = 0.f;
@@ -277,6 +286,8 @@ inline int grid_for(long long n, int block, int cap = 148 * 8) {
   long long g = (n + block - 1) / block;
   return (int)(g < 1 ? 1 : (g > cap ? cap : g));
 }
+
+OPK_DEBUG_BOUNDS_UNIT();
 
 }  // namespace
 

@@ -51,6 +51,10 @@ int opk_num_sms(void);
 // Two-CTA (cta_group::2) kernel for eligible products: on by default, OPK_GEMM_PAIR=0 or set_pair_mode(0) turns it off.
 void opk_gemm_set_pair_mode(int on);
 int opk_gemm_get_pair_mode(void);
+// Debug-build index checks (library variant built with OPK_DEBUG_BOUNDS): out4 = {failing accesses since the last reset,
+// source line of the first, its index, its bound}; file_out receives the first record's source file. Synchronises the
+// device. Returns -3 from a release build. A failing access is skipped by the kernel, never performed.
+int opk_debug_bounds_read(int64_t* out4, char* file_out, int file_cap, int reset);
 // Bounded-wait self-test: one CTA waits `budget_cycles` on a barrier nobody completes, then sets *err = 3 and returns.
 int opk_wait_selftest(int32_t* err, int64_t budget_cycles, int64_t* waited_cycles, void* stream);
 const char* opk_last_error(void);
@@ -93,7 +97,7 @@ int opk_geglu_bwd(const void* dact, const void* gu, void* dgu, int T, int F, int
 int opk_gelu_fwd(const void* x, void* y, int64_t n, void* stream);
 int opk_gelu_bwd(const void* dy, const void* x, void* dx, int64_t n, void* stream);
 // out[t] = table[tok[t]] (+ pos_table[t] when given)
-int opk_embedding_fwd(const int32_t* tok, const void* table, const void* pos_table, void* out, int T, int D,
+int opk_embedding_fwd(const int32_t* tok, const void* table, const void* pos_table, void* out, int T, int D, int vocab,
                       void* stream);
 // Per-example embedding gradient without a dense [V][D] buffer: rows with equal tokens are summed into the row of
 // their first occurrence. first_pos is an int32 [V] scratch that must hold INT32_MAX on entry and is restored.

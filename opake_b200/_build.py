@@ -17,6 +17,8 @@ CSRC = ROOT / "csrc"
 OUT = Path(__file__).resolve().parent / "_C"
 
 KERNEL_LIB = OUT / "libopake_kernels.so"
+# same sources with -DOPK_DEBUG_BOUNDS: data-dependent indices are checked, a bad one is recorded and its access skipped
+KERNEL_LIB_DEBUG = OUT / "libopake_kernels_debug.so"
 ACCOUNTING_LIB = OUT / ("_opake_accounting" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
 
 NVCC_FLAGS = [
@@ -39,22 +41,25 @@ def _nvcc() -> str:
     return exe
 
 
-def build_kernels(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every ``csrc/kernels/*.cu`` into one shared library for sm_100a."""
+def build_kernels(force: bool = False, verbose: bool = False, debug_bounds: bool = False) -> Path:
+    """Compile every ``csrc/kernels/*.cu`` into one shared library for sm_100a (``debug_bounds``: the checked variant)."""
     src_dir = CSRC / "kernels"
+    target = KERNEL_LIB_DEBUG if debug_bounds else KERNEL_LIB
+    extra = ["-DOPK_DEBUG_BOUNDS"] if debug_bounds else []
+    suffix = ".dbg.o" if debug_bounds else ".o"
     cu = sorted(src_dir.glob("*.cu"))
     deps = cu + sorted(src_dir.glob("*.cuh")) + sorted(src_dir.glob("*.h"))
-    if not force and _newer(KERNEL_LIB, deps):
-        return KERNEL_LIB
+    if not force and _newer(target, deps):
+        return target
     OUT.mkdir(parents=True, exist_ok=True)
     objs = []
     jobs = []
     for f in cu:
-        obj = OUT / (f.stem + ".o")
+        obj = OUT / (f.stem + suffix)
         if not force and _newer(obj, [f] + [d for d in deps if d.suffix in (".cuh", ".h")]):
             objs.append(obj)
             continue
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(f), "-o", str(obj)]
+        cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-c", str(f), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
@@ -66,12 +71,12 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
             print(out)
         if proc.returncode != 0:
             raise RuntimeError(f"nvcc failed for {f.name}:\n{out}")
-    link = [_nvcc(), "-shared", "-o", str(KERNEL_LIB), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a",
+    link = [_nvcc(), "-shared", "-o", str(target), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a",
             "-Xcompiler", "-fPIC"]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}")
-    return KERNEL_LIB
+    return target
 
 
 def build_accounting(force: bool = False) -> Path:
@@ -99,6 +104,7 @@ def build_accounting(force: bool = False) -> Path:
 
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_kernels(force=force, verbose=verbose)
+    build_kernels(force=force, debug_bounds=True)
     build_accounting(force=force)
 
 

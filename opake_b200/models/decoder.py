@@ -38,13 +38,16 @@ class DecoderRuntime:
     """Forward + per-example backward for dense decoders (Llama-style and GPT-2-style blocks)."""
 
     def __init__(self, cfg: DecoderConfig, params: torch.Tensor, *, layout: Layout | None = None,
-                 attn_impl: str = "auto", n_slots: int = 1, wgrad_overlap: bool = True, ep=None):
+                 attn_impl: str = "auto", n_slots: int = 1, wgrad_overlap: bool = True, ep=None,
+                 canaries=None):
         if cfg.n_experts and (cfg.act != "swiglu" or cfg.n_experts > 256 or cfg.top_k > 32 or cfg.d_model % 8):
             raise ValueError("mixture-of-experts layers need SwiGLU experts, at most 256 experts and top_k <= 32")
         self.cfg = cfg
         # expert parallelism: an ``ExpertParallelRuntime`` that owns this rank's experts of every layer (the layout
         # then holds no expert matrices); ``None`` = all experts local, inside the flat parameter buffer
         self.ep = ep
+        # a ``utils.CanaryPool``: gradient slots and workspaces are then allocated between guard bands (debugging aid)
+        self.canaries = canaries
         self.layout = layout or build_layout(cfg, skip_experts=ep is not None)
         self.device = params.device
         self.params = params
@@ -53,7 +56,7 @@ class DecoderRuntime:
         # With two slots the clipped accumulation of example i can run on a side stream while example i+1 is
         # being computed into the other slot.
         self.n_slots = n_slots
-        self.Gs = [torch.empty(self.layout.dense_total, dtype=_bf16, device=self.device) for _ in range(n_slots)]
+        self.Gs = [self._alloc(self.layout.dense_total, dtype=_bf16, name=f"grad_slot{i}") for i in range(n_slots)]
         self.gs = [self.layout.views(G_, dense_only=True) for G_ in self.Gs]
         self.attn_impl = attn_impl
         self.sumsqs = [torch.zeros(1, dtype=torch.float64, device=self.device) for _ in range(n_slots)]
@@ -102,6 +105,11 @@ class DecoderRuntime:
     def norm(self):
         return self.norms[0]
 
+    def _alloc(self, *shape, dtype, name: str) -> torch.Tensor:
+        if self.canaries is not None:
+            return self.canaries.empty(*shape, dtype=dtype, name=name)
+        return torch.empty(*shape, dtype=dtype, device=self.device)
+
     # ------------------------------------------------------------------ workspaces
     def workspace(self, T: int) -> dict:
         ws = self._ws.get(T)
@@ -111,7 +119,7 @@ class DecoderRuntime:
         d, F, L = cfg.d_model, cfg.ffn, cfg.n_layers
 
         def e(*shape, dtype=_bf16):
-            return torch.empty(*shape, dtype=dtype, device=dev)
+            return self._alloc(*shape, dtype=dtype, name=f"workspace[T={T}]#{len(self.canaries) if self.canaries is not None else 0}")
 
         layers = []
         for _ in range(L):

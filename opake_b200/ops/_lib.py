@@ -11,7 +11,9 @@ from functools import lru_cache
 
 import torch
 
-from .._build import KERNEL_LIB, build_kernels
+import os
+
+from .._build import KERNEL_LIB, KERNEL_LIB_DEBUG, build_kernels
 
 
 class GemmArgs(Structure):
@@ -36,10 +38,12 @@ class KernelLibraryError(RuntimeError):
 
 @lru_cache(maxsize=1)
 def lib() -> ctypes.CDLL:
-    path = KERNEL_LIB
+    # OPAKE_B200_DEBUG_KERNELS=1 loads the variant with index checks on data-dependent addresses (see debug_bounds_report)
+    debug = os.environ.get("OPAKE_B200_DEBUG_KERNELS", "0") not in ("", "0")
+    path = KERNEL_LIB_DEBUG if debug else KERNEL_LIB
     if not path.exists():
         try:
-            build_kernels()
+            build_kernels(debug_bounds=debug)
         except Exception as exc:  # pragma: no cover - build environment specific
             raise KernelLibraryError(f"{path} is missing and could not be built: {exc}") from exc
     L = ctypes.CDLL(str(path))
@@ -49,6 +53,8 @@ def lib() -> ctypes.CDLL:
     L.opk_gemm_tiles_n.argtypes = [c_int32, c_int32]
     L.opk_gemm_tiles_n.restype = c_int32
     L.opk_num_sms.restype = c_int32
+    L.opk_debug_bounds_read.argtypes = [POINTER(c_int64), c_char_p, c_int32, c_int32]
+    L.opk_debug_bounds_read.restype = c_int32
     L.opk_gemm_set_pair_mode.argtypes = [c_int32]
     L.opk_gemm_set_pair_mode.restype = None
     L.opk_gemm_get_pair_mode.restype = c_int32
@@ -97,6 +103,21 @@ def err_word(device: torch.device) -> torch.Tensor:
         t = torch.zeros(1, dtype=torch.int32, device=device)
         _ERR[idx] = t
     return t
+
+
+def debug_bounds_report(reset: bool = True) -> dict | None:
+    """Record of the debug library's index checks: ``{"failures", "file", "line", "index", "bound"}`` (the first failing
+    access since the last reset; such accesses were skipped, not performed). ``None`` when the release library is
+    loaded. Synchronises the device."""
+    out = (c_int64 * 4)()
+    buf = ctypes.create_string_buffer(256)
+    code = lib().opk_debug_bounds_read(out, buf, 256, 1 if reset else 0)
+    if code == -3:
+        return None
+    if code != 0:
+        raise KernelLibraryError(f"debug_bounds_read failed (code {code}): {lib().opk_last_error().decode()}")
+    return {"failures": int(out[0]), "file": buf.value.decode("utf-8", "replace"), "line": int(out[1]), "index": int(out[2]),
+            "bound": int(out[3])}
 
 
 def raise_if_device_error(device: torch.device) -> None:

@@ -56,7 +56,7 @@ PROTOTYPES: dict = {
     "opk_geglu_bwd": (I, [P, P, P, I, I, I, P]),
     "opk_gelu_fwd": (I, [P, P, L, P]),
     "opk_gelu_bwd": (I, [P, P, P, L, P]),
-    "opk_embedding_fwd": (I, [P, P, P, P, I, I, P]),
+    "opk_embedding_fwd": (I, [P, P, P, P, I, I, I, P]),
     "opk_embedding_bwd_compact": (I, [P, P, P, P, P, P, I, I, I, P]),
     "opk_embedding_accumulate": (I, [P, P, P, P, P, I, I, P]),
     "opk_lce_finalize": (I, [P, P, P, P, P, P, I, I, P]),

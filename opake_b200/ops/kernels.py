@@ -170,7 +170,7 @@ def embedding_fwd(tok, table, pos_table=None, out=None):
     T, D = tok.numel(), table.shape[1]
     if out is None:
         out = torch.empty(T, D, dtype=_bf16, device=table.device)
-    _chk(_L().opk_embedding_fwd(_p(tok), _p(table), _p(pos_table), _p(out), T, D, _s(table)), "embedding_fwd")
+    _chk(_L().opk_embedding_fwd(_p(tok), _p(table), _p(pos_table), _p(out), T, D, table.shape[0], _s(table)), "embedding_fwd")
     return out
 
 
@@ -368,6 +368,14 @@ class MoePlan:
         self.tile_group = torch.empty(self.R // 128, **i32)
         self.group_k = torch.empty(E, 2, **i32)
         self.counts = torch.empty(E, **i32)
+
+    def build(self, idx: torch.Tensor) -> "MoePlan":
+        """Row plan for expert ids chosen by the caller (``[T, k]`` int32). Ids outside ``[0, E)`` are dropped: their
+        ``dest`` entry becomes -1 and the combine kernels skip them."""
+        self.idx.copy_(idx.reshape(self.T, self.k))
+        _chk(_L().opk_moe_plan(_p(self.idx), self.n, self.E, self.R, _p(self.dest), _p(self.src_entry), _p(self.tile_group),
+                               _p(self.group_k), _p(self.counts), _s(self.idx)), "moe_plan")
+        return self
 
 
 def moe_route(logits, plan: MoePlan, norm_topk: bool = False):

@@ -72,6 +72,8 @@ class EngineConfig:
     # "nccl": the same step with library collectives around a local kernel (reduce_scatter_tensor before, in-place
     # all_gather_into_tensor after): the baseline and fallback implementation of the same interface.
     comm_backend: str = "peer"
+    # debugging aid: gradient slots and workspaces sit between guard bands that are verified after every step
+    debug_canaries: bool = False
 
 
 class ShardedDPEngine:
@@ -143,8 +145,13 @@ class ShardedDPEngine:
             views = self.layout.views(self.params)
             routers = [views[f"layers.{i}.router"] for i in range(model_cfg.n_layers)]
             self.ep = ExpertParallelRuntime(model_cfg, routers, cfg.seq_len, device, init_seed=init_seed)
+        self.canaries = None
+        if cfg.debug_canaries:
+            from ..utils.canary import CanaryPool
+
+            self.canaries = CanaryPool(device)
         self.runtime = DecoderRuntime(model_cfg, self.params, layout=self.layout, attn_impl=cfg.attn_impl, n_slots=self.group,
-                                      ep=self.ep)
+                                      ep=self.ep, canaries=self.canaries)
         self._side = torch.cuda.Stream(device=device)
         self._warm: dict[int, bool] = {}
         self.step_count = 0
@@ -345,6 +352,8 @@ class ShardedDPEngine:
         loss_sum = ws["loss_sum"].clone()
         with nvtx_range("opake::dp_step"):
             self.apply_update()
+        if self.canaries is not None:
+            self.canaries.assert_intact()       # synchronises; raises DeviceIntegrityError naming the damaged buffer
         return loss_sum
 
     def apply_update(self) -> None:

@@ -326,3 +326,80 @@ def test_copy_bytes_and_shared_embedding_accumulate(cuda):
     K.embedding_accumulate(tok, ws, scale, a, T)
     K.embedding_accumulate(tok, ws, scale, b, T, shared=True)
     assert torch.equal(a, b)
+
+
+def test_debug_library_records_and_skips_bad_indices():
+    """The checked library variant (child process: a process loads one variant) records an out-of-range token id,
+    label and expert id with file / line / index / bound, skips the access, and leaves the context usable."""
+    import os
+    import subprocess
+    import sys
+
+    code = r'''
+import torch
+from opake_b200.ops import kernels as K
+from opake_b200.ops._lib import debug_bounds_report
+dev = torch.device("cuda", 0)
+assert debug_bounds_report() == {"failures": 0, "file": "", "line": 0, "index": 0, "bound": 0}
+table = torch.randn(50, 64, device=dev).bfloat16()
+tok = torch.tensor([1, 2, 77, 3], dtype=torch.int32, device=dev)
+out = K.embedding_fwd(tok, table)
+torch.cuda.synchronize()
+assert torch.equal(out[0], table[1]) and torch.equal(out[3], table[3]) and float(out[2].abs().max()) == 0.0
+rep = debug_bounds_report()
+assert rep["failures"] >= 1 and rep["index"] == 77 and rep["bound"] == 50 and rep["file"].endswith("elementwise.cu"), rep
+assert debug_bounds_report()["failures"] == 0          # the read cleared it
+idx = torch.tensor([0, 3, 9, 1, 2, 2], dtype=torch.int32, device=dev)        # 9 >= E = 4
+plan = K.MoePlan(3, 4, 2, dev)
+plan.build(idx)
+torch.cuda.synchronize()
+rep = debug_bounds_report()
+assert rep["failures"] >= 1 and rep["index"] == 9 and rep["bound"] == 4 and rep["file"].endswith("moe.cu"), rep
+assert int(plan.dest.flatten()[2]) == -1
+x = torch.ones(4, device=dev)
+assert float((x + 1).sum()) == 8.0          # the context is alive
+print("DEBUG-BOUNDS-OK")
+'''
+    env = dict(os.environ, OPAKE_B200_DEBUG_KERNELS="1")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert "DEBUG-BOUNDS-OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_release_library_drops_bad_ids_without_touching_memory():
+    from opake_b200.ops._lib import debug_bounds_report
+
+    assert debug_bounds_report() is None            # release build: no record
+    dev = torch.device("cuda", 0)
+    table = torch.randn(50, 64, device=dev).bfloat16()
+    tok = torch.tensor([1, -4, 50, 3], dtype=torch.int32, device=dev)
+    out = K.embedding_fwd(tok, table)
+    assert torch.equal(out[0], table[1]) and float(out[1:3].abs().max()) == 0.0
+    idx = torch.tensor([0, 3, 9, 1, 2, 2], dtype=torch.int32, device=dev)
+    plan = K.MoePlan(3, 4, 2, dev)
+    plan.build(idx)
+    y = torch.randn(plan.R, 64, device=dev).bfloat16()
+    wts = torch.ones(3, 2, device=dev)
+    o = K.moe_combine(y, plan, torch.empty(3, 64, dtype=torch.bfloat16, device=dev), wts)
+    torch.cuda.synchronize()
+    assert int(plan.dest.flatten()[2]) == -1
+    ref = y[plan.dest.flatten()[3].long()].float()           # token 1: slot 0 dropped, slot 1 kept
+    torch.testing.assert_close(o[1].float(), ref, atol=2e-2, rtol=2e-2)
+
+
+def test_engine_step_leaves_every_guard_band_intact():
+    """A whole DP step (forward, backward, clip, accumulate, fused update) with gradient slots and workspaces
+    allocated between guard bands: no kernel writes outside its buffers."""
+    from opake_b200.models.config import tiny_llama
+    from opake_b200.parallel.engine import EngineConfig, ShardedDPEngine
+
+    dev = torch.device("cuda", 0)
+    cfg = tiny_llama()
+    for graph in (False, True):
+        eng = ShardedDPEngine(cfg, EngineConfig(logical_batch=4, noise_multiplier=0.5, use_cuda_graph=graph, debug_canaries=True), dev)
+        tok = torch.randint(0, cfg.vocab_size, (4, 96), dtype=torch.int32).pin_memory()
+        labels = torch.roll(tok, -1, 1).clone()
+        labels[:, -1] = -100
+        for _ in range(2):
+            loss = eng.step(tok, labels).item()
+        assert loss == loss and len(eng.canaries) > 20
+        assert eng.canaries.check() == []
