@@ -21,7 +21,7 @@ import torch
 
 def _peaks() -> dict:
     here = os.path.dirname(os.path.abspath(__file__))
-    path = os.path.join(here, "..", "..", "MEASURED_PEAKS.json")
+    path = os.path.join(here, "..", "MEASURED_PEAKS.json")
     try:
         with open(path, encoding="utf-8") as f:
             raw = json.load(f)

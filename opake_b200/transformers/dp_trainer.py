@@ -278,7 +278,7 @@ class DPTrainer:
         else:
             a = self.args
             self.lr_scheduler = build_lr_schedule(a.lr_scheduler, learning_rate=a.learning_rate, total_steps=total_steps,
-                                                  warmup_steps=a.resolve_warmup(total_steps), kwargs=a.lr_scheduler_kwargs)
+                                                  warmup_steps=a.warmup_steps or 0, kwargs=a.lr_scheduler_kwargs)
         return self.lr_scheduler
 
     def create_optimizer(self):

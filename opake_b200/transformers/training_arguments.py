@@ -32,7 +32,8 @@ MECHANISM_DEFAULTS: dict[str, dict[str, Any]] = {
 }
 _STRATEGIES = ("no", "steps", "epoch")
 _SCHEDULERS = ("linear", "cosine", "cosine_with_restarts", "polynomial", "constant", "constant_with_warmup",
-               "inverse_sqrt", "warmup_stable_decay", "exponential", "one_minus_sqrt")
+               "inverse_sqrt", "warmup_stable_decay", "cosine_with_min_lr", "cosine_warmup_with_min_lr", "exponential",
+               "one_minus_sqrt")
 
 
 def default_delta(dataset_size: int) -> float:
@@ -172,7 +173,10 @@ class TrainingArguments:
             if v not in _STRATEGIES:
                 raise ConfigurationError(f"{name} must be one of {_STRATEGIES}, got {v!r}")
             setattr(self, name, v)
-        if self.lr_scheduler not in _SCHEDULERS:
+        self.lr_scheduler = getattr(self.lr_scheduler, "value", self.lr_scheduler)
+        if callable(self.lr_scheduler) and not isinstance(self.lr_scheduler, str):
+            pass        # a schedule recipe (step -> lr); the scheduler factory checks that no warm-up / kwargs come with it
+        elif self.lr_scheduler not in _SCHEDULERS:
             raise ConfigurationError(f"lr_scheduler must be one of {_SCHEDULERS}, got {self.lr_scheduler!r}")
         if self.clipping_mode not in CLIPPING_MODES:
             raise ConfigurationError(f"clipping_mode must be one of {CLIPPING_MODES}, got {self.clipping_mode!r}")

@@ -299,3 +299,82 @@ def test_hf_and_trl_argument_conversion_report_and_rejections():
     for bad in ({"deepspeed": "ds.json"}, {"packing": True}, {"padding_free": True}):
         with pytest.raises(ConfigurationError):
             convert_hf_training_arguments({"output_dir": "o", **bad}, SFTConfig)
+
+
+def test_lr_schedule_factory_matches_hugging_face_formulas_and_validates():
+    """Every scheduler name against the closed-form Hugging Face lambda, kwargs validation, recipe path."""
+    import math
+
+    from opake_b200.base.exceptions import ConfigurationError
+    from opake_b200.engine.scheduling import cosine_schedule
+    from opake_b200.transformers.scheduler import SUPPORTED_SCHEDULERS, build_lr_schedule, get_warmup_steps
+
+    lr, total, W = 2e-3, 50, 7
+    mk = lambda name, **kw: build_lr_schedule(name, learning_rate=lr, total_steps=total, warmup_steps=W, kwargs=kw)  # noqa: E731
+    prog = lambda s: (s - W) / (total - W)  # noqa: E731
+    hf = {
+        "linear": lambda s: s / W if s < W else max(0.0, (total - s) / (total - W)),
+        "cosine": lambda s: s / W if s < W else max(0.0, 0.5 * (1 + math.cos(math.pi * prog(s)))),
+        "constant_with_warmup": lambda s: s / W if s < W else 1.0,
+        "constant": lambda s: 1.0,
+        "cosine_with_restarts": lambda s: s / W if s < W else (0.0 if prog(s) >= 1 else 0.5 * (1 + math.cos(math.pi * ((3 * prog(s)) % 1.0)))),
+        "inverse_sqrt": lambda s: s / W if s < W else 1.0 / math.sqrt((s - W) / W + 1.0),
+    }
+    kws = {"cosine_with_restarts": {"num_cycles": 3}}
+    for name, f in hf.items():
+        sch = mk(name, **kws.get(name, {}))
+        for s in range(total + 1):          # past the end the upstream cosine lambda oscillates on; ours holds
+            assert sch(s) == pytest.approx(lr * f(s), rel=1e-9, abs=1e-15), (name, s)
+    # polynomial: (lr - end) * (1 - p)^power + end
+    sch = mk("polynomial", lr_end=1e-5, power=2.0)
+    for s in range(W, total + 1):
+        assert sch(s) == pytest.approx((lr - 1e-5) * (1 - prog(s)) ** 2 + 1e-5, rel=1e-9)
+    with pytest.raises(ConfigurationError, match="smaller than initial lr"):
+        mk("polynomial", lr_end=1.0)
+    # cosine with a floor, given either way but not both, and required
+    a, b = mk("cosine_with_min_lr", min_lr=2e-4), mk("cosine_with_min_lr", min_lr_rate=0.1)
+    for s in range(total + 1):
+        assert a(s) == pytest.approx(b(s), rel=1e-12)
+    assert a(total) == pytest.approx(2e-4) and a(W) == pytest.approx(lr)
+    with pytest.raises(ConfigurationError, match="only one"):
+        mk("cosine_with_min_lr", min_lr=1e-4, min_lr_rate=0.1)
+    with pytest.raises(ConfigurationError, match="exactly one"):
+        mk("cosine_with_min_lr")
+    c = mk("cosine_warmup_with_min_lr", min_lr_rate=0.1, warmup_lr_rate=0.25)
+    assert c(0) == pytest.approx(0.25 * lr) and c(W) == pytest.approx(lr) and c(total) == pytest.approx(0.1 * lr)
+    assert all(c(s) < c(s + 1) for s in range(W))
+    # warmup-stable-decay: floor on both ends, stable plateau, decay shape, held at the floor afterwards
+    with pytest.raises(ConfigurationError, match="num_decay_steps"):
+        mk("warmup_stable_decay")
+    with pytest.raises(ConfigurationError, match="decay_type"):
+        mk("warmup_stable_decay", num_decay_steps=10, decay_type="square")
+    w = mk("warmup_stable_decay", num_decay_steps=10, min_lr_ratio=0.1, decay_type="linear")
+    assert w(0) == pytest.approx(0.1 * lr) and w(W) == pytest.approx(lr) and w(W + 32) == pytest.approx(lr)
+    assert w(W + 33 + 5) == pytest.approx(0.1 * lr + 0.9 * lr * 0.5, rel=1e-6) and w(total) == pytest.approx(0.1 * lr) and w(total + 9) == pytest.approx(0.1 * lr)
+    wc = mk("warmup_stable_decay", num_decay_steps=10, num_stable_steps=5, decay_type="cosine")
+    assert wc(W + 5 + 5) == pytest.approx(0.5 * lr) and wc(W + 15) == 0.0 and wc(W + 40) == 0.0
+    ws = mk("warmup_stable_decay", num_decay_steps=16, num_stable_steps=0, decay_type="1-sqrt", warmup_type="cosine")
+    assert ws(W + 4) == pytest.approx(lr * 0.5) and 0 < ws(3) < lr
+    # unknown names / keys
+    with pytest.raises(ConfigurationError, match="unsupported keys"):
+        mk("linear", num_cycles=2)
+    with pytest.raises(ConfigurationError, match="unknown lr_scheduler"):
+        mk("triangular")
+    with pytest.raises(ConfigurationError, match="timescale"):
+        mk("inverse_sqrt", timescale=0)
+    assert set(SUPPORTED_SCHEDULERS) >= {"linear", "cosine", "cosine_with_restarts", "polynomial", "constant", "constant_with_warmup",
+                                         "inverse_sqrt", "cosine_with_min_lr", "cosine_warmup_with_min_lr", "warmup_stable_decay"}
+    # fractions, recipes, argument objects
+    assert get_warmup_steps(100, 0.055) == 6 and get_warmup_steps(100, 12.7) == 12 and get_warmup_steps(100, 0) == 0
+    recipe = cosine_schedule(1e-3, 100)
+    assert build_lr_schedule(recipe, learning_rate=1.0, total_steps=10) is recipe
+    with pytest.raises(ConfigurationError, match="warmup_steps is incompatible"):
+        build_lr_schedule(recipe, learning_rate=1.0, total_steps=10, warmup_steps=3)
+    with pytest.raises(ConfigurationError, match="lr_scheduler_kwargs is incompatible"):
+        build_lr_schedule(recipe, learning_rate=1.0, total_steps=10, kwargs={"num_cycles": 1})
+    from opake_b200.transformers import TrainingArguments
+
+    args = TrainingArguments(output_dir="/tmp/x", lr_scheduler="cosine", warmup_steps=0.1, learning_rate=lr)
+    s1 = build_lr_schedule(args, 50)
+    assert s1(5) == pytest.approx(lr) and s1(2) == pytest.approx(lr * 2 / 5)
+    assert TrainingArguments(output_dir="/tmp/x", lr_scheduler=recipe).lr_scheduler is recipe
