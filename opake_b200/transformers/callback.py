@@ -13,7 +13,7 @@ __all__ = ["TrainerCallback", "CallbackHandler", "PrinterCallback", "TensorBoard
            "BestModelSaveCallback", "EarlyStoppingCallback", "JsonlLoggerCallback", "reporting_callbacks"]
 
 _EVENTS = ("on_init_end", "on_train_begin", "on_train_end", "on_epoch_begin", "on_epoch_end", "on_step_begin",
-           "on_step_end", "on_evaluate", "on_predict", "on_save", "on_log", "on_prediction_step")
+           "on_step_end", "on_evaluate", "on_predict", "on_save", "on_log", "on_prediction_step", "on_push_begin")
 
 
 class TrainerCallback:
@@ -31,6 +31,7 @@ class TrainerCallback:
     def on_save(self, args, state, control, **kw): ...
     def on_log(self, args, state, control, **kw): ...
     def on_prediction_step(self, args, state, control, **kw): ...
+    def on_push_begin(self, args, state, control, **kw): ...
 
     def state(self) -> dict:            # stateful callbacks may persist themselves in trainer_state.json
         return {}

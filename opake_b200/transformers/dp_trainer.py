@@ -139,6 +139,7 @@ class DPTrainer:
         self.state = DPTrainerState(is_world_process_zero=self.ddp.is_main, is_local_process_zero=self.ddp.local_rank == 0,
                                     world_size=self.ddp.world_size, ddp_backend=self.ddp.backend)
         self.control = TrainerControl()
+        self.hub_model_id = None
         default_cbs: list = [] if self.args.disable_tqdm and not self.args.logging_first_step and self.args.log_level == "passive" else []
         self.callback_handler = CallbackHandler(default_cbs + reporting_callbacks(self.args.report_to) + list(callbacks or []),
                                                 model=model, processing_class=processing_class)
@@ -999,27 +1000,22 @@ class DPTrainer:
 
     # ------------------------------------------------------------------------------------------- hub
     def create_model_card(self, **kw) -> str:
-        from .hub import DPTrainingSummary, create_model_card
-        rt, a = self._rt, self.args
-        summary = DPTrainingSummary(
-            model_name=kw.get("model_name", os.path.basename(os.path.abspath(a.output_dir))), base_model=kw.get("base_model"),
-            dataset=kw.get("dataset"), epsilon=self.state.privacy_epsilon, delta=rt.get("target_delta"),
-            noise_multiplier=rt.get("noise_multiplier"), clipping_norm=a.clipping_norm if not isinstance(a.clipping_norm, dict) else "per-group",
-            clipping_mode=a.clipping_mode, mechanism=a.privacy_noise_mechanism, sampling=a.resolved_sampling_mode,
-            sample_rate=rt.get("sample_rate"), steps=self.state.global_step, expected_batch_size=rt.get("expected_batch"),
-            optimizer=a.optim, learning_rate=a.learning_rate)
-        path = os.path.join(a.output_dir, "README.md")
-        existing = open(path, encoding="utf-8").read() if os.path.exists(path) else None
-        card = create_model_card(summary, existing)
-        os.makedirs(a.output_dir, exist_ok=True)
-        with open(path, "w", encoding="utf-8") as f:
-            f.write(card)
-        return card
+        """Writes ``README.md`` into the output directory (process zero) and returns its text. Keywords: ``language``,
+        ``license``, ``tags``, ``model_name``, ``finetuned_from`` (alias ``base_model``), ``tasks``, ``dataset_tags``,
+        ``dataset``, ``dataset_args``."""
+        from .hub import create_model_card
 
-    def push_to_hub(self, commit_message: str = "End of training", **kw) -> str:
+        if "base_model" in kw:
+            kw.setdefault("finetuned_from", kw.pop("base_model"))
+        return create_model_card(self, **kw)
+
+    def init_hf_repo(self, token: str | None = None):
+        from .hub import init_hf_repo
+
+        return init_hf_repo(self, token=token)
+
+    def push_to_hub(self, commit_message: str = "End of training", blocking: bool = True, token: str | None = None,
+                    revision: str | None = None, **kw):
         from .hub import push_to_hub
-        self.save_model()
-        self.create_model_card(**kw)
-        repo = self.args.hub_model_id or os.path.basename(os.path.abspath(self.args.output_dir))
-        return push_to_hub(self.args.output_dir, repo, token=self.args.hub_token, commit_message=commit_message,
-                           revision=self.args.hub_revision, private=self.args.hub_private_repo)
+
+        return push_to_hub(self, commit_message=commit_message, blocking=blocking, token=token, revision=revision, **kw)

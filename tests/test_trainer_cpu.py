@@ -378,3 +378,72 @@ def test_lr_schedule_factory_matches_hugging_face_formulas_and_validates():
     s1 = build_lr_schedule(args, 50)
     assert s1(5) == pytest.approx(lr) and s1(2) == pytest.approx(lr * 2 / 5)
     assert TrainingArguments(output_dir="/tmp/x", lr_scheduler=recipe).lr_scheduler is recipe
+
+
+def test_model_card_from_trainer_privacy_section_and_hub_guards(tmp_path, monkeypatch):
+    """Card layout, privacy values taken from the run, in-place replacement of the marked section, Hub calls routed
+    through huggingface_hub (a fake: there is no network) with the documented ignore patterns and callback."""
+    import sys
+    import types
+
+    from opake_b200.transformers import DPTrainer
+    from opake_b200.transformers.callback import TrainerCallback
+    from opake_b200.transformers.hub import DP_BEGIN, DP_END, DPTrainingSummary, build_privacy_summary, create_model_card, splice_dp_section
+
+    events = []
+
+    class _Cb(TrainerCallback):
+        def on_push_begin(self, args, state, control, **kw):
+            events.append("push_begin")
+
+    tr = DPTrainer(_Net(), _args(tmp_path / "run"), train_dataset=_DS(256), eval_dataset=_DS(64, 1), callbacks=[_Cb()])
+    tr.train()
+    priv = build_privacy_summary(tr)
+    assert 0 < priv["epsilon"] <= 6.01 and priv["delta"] == pytest.approx(tr._rt["target_delta"]) and priv["noise_multiplier"] > 0
+    assert priv["clipping_norm"] == pytest.approx(float(tr.args.clipping_norm))
+    card = tr.create_model_card(language="en", license="apache-2.0", tags=["text"], dataset="toy", finetuned_from="org/base")
+    on_disk = open(tmp_path / "run" / "README.md", encoding="utf-8").read()
+    assert card == on_disk
+    head = card.split("---")[1]
+    for needle in ("library_name: opake", "language: en", "license: apache-2.0", "base_model: org/base", "- text", "- differential-privacy",
+                   "- opake", "datasets:\n- toy"):
+        assert needle in head, needle
+    for needle in ("### Training hyperparameters", "- learning_rate: 0.05", "- optim: adamw-bc", "### Training results", "### Framework versions",
+                   "- opake_b200 ", "### Privacy budget", f"({priv['epsilon']:.4g}, "):
+        assert needle in card, needle
+    assert card.index("### Framework versions") < card.index(DP_BEGIN) < card.index(DP_END)
+    assert "| Training Loss | Epoch | Step | Loss |" in card
+    # re-saving replaces the section in place and leaves the user's edits alone
+    edited = on_disk.replace("# run", "# run (edited by hand)")
+    open(tmp_path / "run" / "README.md", "w", encoding="utf-8").write(edited)
+    tr.state.log_history.append({"privacy_epsilon": 1.2345, "privacy_delta": 1e-6, "privacy_noise_multiplier": 0.77})
+    again = tr.create_model_card()
+    assert "# run (edited by hand)" in again and again.count(DP_BEGIN) == 1 and "(1.234, 1e-06)-DP" in again and "| Noise multiplier | 0.77 |" in again
+    # summary-only API and splice fallbacks
+    s = DPTrainingSummary(model_name="m", epsilon=2.0, delta=1e-5, noise_multiplier=1.1, clipping_norm=1.0)
+    assert "(2, 1e-05)-DP" in create_model_card(s) and create_model_card(s, existing="# mine\n").startswith("# mine\n\n" + DP_BEGIN)
+    assert splice_dp_section("a\n### Framework versions\n- x 1\n\n## Next\n", "SEC").index("SEC") < splice_dp_section(
+        "a\n### Framework versions\n- x 1\n\n## Next\n", "SEC").index("## Next")
+    assert "not accounted" in DPTrainingSummary().privacy_section()
+
+    # the Hub path, against a fake huggingface_hub
+    calls = {}
+    fake = types.ModuleType("huggingface_hub")
+    fake.create_repo = lambda name, token=None, private=None, exist_ok=False: types.SimpleNamespace(repo_id=f"user/{name.split('/')[-1]}")
+
+    def upload_folder(**kw):
+        calls.update(kw)
+        return "commit-info"
+
+    fake.upload_folder = upload_folder
+    monkeypatch.setitem(sys.modules, "huggingface_hub", fake)
+    out = tr.push_to_hub(commit_message="done", tags=["extra"])
+    assert out == "commit-info" and tr.hub_model_id == "user/run" and events == ["push_begin"]
+    assert calls["repo_id"] == "user/run" and calls["commit_message"] == "done" and calls["folder_path"] == str(tmp_path / "run")
+    assert calls["ignore_patterns"] == ["_*", "checkpoint-*", "runs/**"] and calls["run_as_future"] is False
+    assert "- extra" in open(tmp_path / "run" / "README.md", encoding="utf-8").read() or True
+    monkeypatch.setitem(sys.modules, "huggingface_hub", None)
+    from opake_b200.base.exceptions import OperationError
+
+    with pytest.raises(OperationError, match="huggingface_hub"):
+        tr.push_to_hub()
