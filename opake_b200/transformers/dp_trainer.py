@@ -40,7 +40,8 @@ from . import checkpoint as ckpt
 from . import dpftrl as mf
 from .callback import CallbackHandler, PrinterCallback, TrainerCallback, reporting_callbacks
 from .distributed import DDPState, checkpoint_barrier, resolve_ddp_state
-from .eval import EvaluationResult, PredictionAccumulator, PredictionOutput, speed_metrics, with_metric_prefix
+from .eval import (EvaluationResult, EvaluationTelemetry, PredictionAccumulator, PredictionOutput, resolve_eval_num_samples,
+                   speed_metrics, with_metric_prefix)
 from .optim import build_optimizer
 from .precision import autocast_context
 from .scheduler import build_lr_schedule
@@ -774,11 +775,13 @@ class DPTrainer:
         only_loss = (a.prediction_loss_only if prediction_loss_only is None else prediction_loss_only) or self.compute_metrics is None and description == "Evaluation"
         was_training = self.model.training
         self.model.eval()
-        accu = PredictionAccumulator(self.device, a.eval_accumulation_steps, a.eval_do_concat_batches)
+        telemetry = EvaluationTelemetry(self.device)
+        accu = PredictionAccumulator(self.device, a.eval_accumulation_steps, a.eval_do_concat_batches, telemetry=telemetry)
         n = 0
         for batch in dataloader:
             batch = _to_device(batch, self.device)
-            losses, logits, labels = self.prediction_step(batch, only_loss)
+            with telemetry.model():
+                losses, logits, labels = self.prediction_step(batch, only_loss)
             n += max(0, _batch_len(batch))
             accu.add(losses=losses, predictions=None if only_loss else logits, label_ids=None if only_loss else labels)
             self.control = self.callback_handler.call_event("on_prediction_step", a, self.state, self.control)
@@ -788,17 +791,24 @@ class DPTrainer:
         loss_sum = float(np.sum(losses)) if losses is not None else 0.0
         count = int(np.size(losses)) if losses is not None else 0
         if self.ddp.is_distributed:
-            loss_sum = D.reduce_scalar(loss_sum, op="sum", device=self.device)
-            count = int(D.reduce_scalar(count, op="sum", device=self.device))
-            n = int(D.reduce_scalar(n, op="sum", device=self.device))
+            with telemetry.phase("gather"):
+                loss_sum = D.reduce_scalar(loss_sum, op="sum", device=self.device)
+                count = int(D.reduce_scalar(count, op="sum", device=self.device))
+                n = int(D.reduce_scalar(n, op="sum", device=self.device))
+        else:
+            n = max(n, 0) or resolve_eval_num_samples(None, dataloader, n)
         metrics: dict[str, Any] = {}
         if count:
             metrics["loss"] = loss_sum / count
         preds, label_ids = out.get("predictions"), out.get("label_ids")
         if self.compute_metrics is not None and preds is not None:
             from types import SimpleNamespace
-            metrics.update(self.compute_metrics(SimpleNamespace(predictions=preds, label_ids=label_ids, losses=losses)))
-        return EvaluationResult(with_metric_prefix(metrics, metric_key_prefix), n, losses, preds, label_ids)
+            with telemetry.phase("metric"):
+                metrics.update(self.compute_metrics(SimpleNamespace(predictions=preds, label_ids=label_ids, losses=losses)) or {})
+        tele = telemetry.to_dict()
+        metrics.update(tele)        # where the evaluation time went; throughput keys are added by evaluate() / predict()
+        metrics = {k: (v.item() if isinstance(v, (np.generic, torch.Tensor)) and np.size(v) == 1 else v) for k, v in metrics.items()}
+        return EvaluationResult(with_metric_prefix(metrics, metric_key_prefix), n, losses, preds, label_ids, tele)
 
     def evaluate(self, eval_dataset=None, ignore_keys=None, metric_key_prefix: str = "eval") -> dict:
         t0 = time.time()

@@ -447,3 +447,41 @@ def test_model_card_from_trainer_privacy_section_and_hub_guards(tmp_path, monkey
 
     with pytest.raises(OperationError, match="huggingface_hub"):
         tr.push_to_hub()
+
+
+def test_evaluation_telemetry_transfer_pipeline_and_nested_accumulation():
+    from opake_b200.transformers.eval import (PAD_VALUE, EvaluationTelemetry, PredictionAccumulator, TransferPipeline, concat_nested,
+                                              interval_overlap, resolve_eval_num_samples)
+    import numpy as np
+
+    assert interval_overlap([(0, 2), (3, 5)], [(1, 4)]) == pytest.approx(2.0)
+    assert interval_overlap([(0, 1)], [(2, 3)]) == 0.0 and interval_overlap([], [(0, 1)]) == 0.0
+    tel = EvaluationTelemetry("cpu")
+    with tel.model():
+        torch.randn(64, 64) @ torch.randn(64, 64)
+    with tel.phase("metric"):
+        pass
+    acc = PredictionAccumulator(torch.device("cpu"), accumulation_steps=2, concat=True, telemetry=tel)
+    # ragged sequence lengths and a nested prediction payload (two heads)
+    for i, T in enumerate((3, 5, 4)):
+        acc.add(losses=torch.full((2,), float(i)), predictions=(torch.full((2, T, 4), float(i)), {"aux": torch.full((2,), 10.0 + i)}),
+                label_ids=torch.full((2, T), i, dtype=torch.long))
+    out = acc.finalize()
+    assert out["losses"].tolist() == [0, 0, 1, 1, 2, 2]
+    head, extra = out["predictions"]
+    assert head.shape == (6, 5, 4) and (head[0, 3:] == PAD_VALUE).all() and (head[2] == 1).all() and (head[4, 4:] == PAD_VALUE).all()
+    assert extra["aux"].tolist() == [10, 10, 11, 11, 12, 12]
+    assert out["label_ids"].shape == (6, 5) and out["label_ids"][0].tolist() == [0, 0, 0, PAD_VALUE, PAD_VALUE]
+    d = tel.to_dict()
+    assert d["model_time_sec"] > 0 and d["transfer_bytes"] == sum(2 * 4 + 2 * T * 4 * 4 + 2 * 4 + 2 * T * 8 for T in (3, 5, 4))
+    assert set(d) == {"model_time_sec", "gather_time_sec", "transfer_time_sec", "finalization_time_sec", "metric_time_sec",
+                      "transfer_bytes", "transfer_overlap_sec", "transfer_overlap_ratio"}
+    # no concatenation: lists of per-batch payloads
+    acc2 = PredictionAccumulator(torch.device("cpu"), None, concat=False)
+    acc2.add(losses=torch.zeros(2))
+    acc2.add(losses=torch.ones(3))
+    assert [x.tolist() for x in acc2.finalize()["losses"]] == [[0, 0], [1, 1, 1]]
+    pipe = TransferPipeline(None, max_pending=2)
+    assert pipe.submit({"a": torch.ones(2)})[0]["a"].tolist() == [1, 1] and pipe.drain_all() == []
+    assert concat_nested([np.zeros((1, 2)), np.ones((2, 3))]).shape == (3, 3)
+    assert resolve_eval_num_samples([1, 2, 3], None, 2) == 3 and resolve_eval_num_samples(iter(()), None, 7) == 7
