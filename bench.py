@@ -140,7 +140,6 @@ def main() -> None:
     ap.add_argument("--model", default="llama3-8b")
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--batch", type=int, default=256, help="logical batch (sequences per optimizer step, all ranks)")
-    ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (invalidates the number)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--attn", default="auto")
     ap.add_argument("--sigma", type=float, default=0.9)
@@ -149,6 +148,9 @@ def main() -> None:
                     help="what is sharded over the ranks: 'state' = optimizer moments only (replicated bf16 parameters and fp32 "
                          "sums, all-gather by peer stores in the step kernel); 'params' = also the parameters (fetched inside the "
                          "first forward GEMMs after a step); 'full' = parameters and fp32 sums; 'auto' = full when N > 1")
+    ap.add_argument("--comm", default="peer", choices=["peer", "nccl"],
+                    help="optimizer-step collectives: 'peer' = this build's kernels over peer memory; 'nccl' = the library baseline "
+                         "(reduce-scatter, local step, all-gather), with --shard state")
     ap.add_argument("--group", type=int, default=0, help="gradient buffers per accumulation pass (0 = as many as fit)")
     ap.add_argument("--config", default="d", choices=["a", "b", "c", "d", "e"],
                     help="benchmark configuration: d = headline (Llama-3-8B DP-SGD); a = CPU MLP plumbing; b = GPT-2-small "
@@ -180,10 +182,6 @@ def main() -> None:
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     mcfg = PRESETS[args.model]()
-    if args.layers:
-        from dataclasses import replace
-
-        mcfg = replace(mcfg, n_layers=args.layers)
     if args.batch % world:
         raise SystemExit("logical batch must divide evenly over the ranks")
     b_local = args.batch // world
@@ -197,7 +195,8 @@ def main() -> None:
                         noise_bias_correction=True, master_weights=False, use_cuda_graph=not args.no_graph,
                         attn_impl=args.attn, seed=1234, accumulate_group=args.group,
                         shard_params=shard in ("params", "full"), shard_sums=shard == "full",
-                        expert_parallel=bool(mcfg.n_experts) and world > 1, seq_len=args.seq, **blt)
+                        expert_parallel=bool(mcfg.n_experts) and world > 1, seq_len=args.seq,
+                        comm_backend=args.comm, **blt)
     eng = ShardedDPEngine(mcfg, ecfg, dev)
 
     tok = _zipf_tokens(b_local, args.seq, mcfg.vocab_size, seed=1000 + rank)
@@ -256,7 +255,7 @@ def main() -> None:
                            "full": "(full shard: optimizer moments, parameters and fp32 sums; parameters fetched inside the first "
                                    "forward GEMMs after a step, accumulation groups reduce-scattered by reductions over NVLink)",
                        }[shard] + f"; gathered bf16 parameters cached across the {b_local} accumulation micro-steps",
-                       "shard": shard, "expert_parallel": f"ep{world}" if (mcfg.n_experts and world > 1) else None,
+                       "shard": shard, "step_collectives": args.comm, "expert_parallel": f"ep{world}" if (mcfg.n_experts and world > 1) else None,
                        "clip_norm": 1.0, "noise_multiplier": args.sigma, "optimizer": "adamw-bc", "sft_mask": "first 25%",
                        "mechanism": f"dp-ftrl blt x{args.blt_buffers}" if args.blt_buffers else "dp-sgd gaussian",
                        "per_example_microbatch": 1, "cuda_graph": (not args.no_graph) and eng.ep is None,

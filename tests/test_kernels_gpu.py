@@ -366,6 +366,7 @@ print("DEBUG-BOUNDS-OK")
 
 
 def test_release_library_drops_bad_ids_without_touching_memory():
+    from opake_b200.ops import kernels as K
     from opake_b200.ops._lib import debug_bounds_report
 
     assert debug_bounds_report() is None            # release build: no record
