@@ -26,24 +26,56 @@ def is_runtime_patched() -> bool:
     return _RUNTIME["patched"]
 
 
-def apply_runtime_patches(*, performance: bool = True, compat: bool = True, **_kw) -> None:
-    """Idempotent. ``performance``: register the CUDA multi-tensor clip-and-sum as the clipping backend."""
+def apply_runtime_patches(*, performance: bool = True, compat: bool = True, **kw) -> dict:
+    """Idempotent process-wide patches; returns what this call changed.
+
+    ``performance``: registers the CUDA multi-tensor clip-and-sum as the fused clipping backend. ``compat`` turns on,
+    each overridable by keyword: ``vmap_masking`` (mask builders legal under ``vmap(grad)``), ``empty_batches``
+    (collators that survive an empty Poisson batch), ``vmap_grouped_mm`` (grouped expert GEMM gate),
+    ``vmap_checkpointing`` (layer checkpointing under functorch: see ``patches.torch_checkpoint``)."""
+    report = {"fused_clip_backend": False, "masking": 0, "collators": 0, "grouped_mm": False}
     if performance and get_fused_clip_backend() is None:
         from ..ops import clip_sum
         register_fused_clip_backend(clip_sum)
+        report["fused_clip_backend"] = True
+    from .transformers import runtime as R
+    if kw.get("vmap_masking", compat):
+        report["masking"] = R.apply_masking_patches()
+    if kw.get("empty_batches", compat):
+        report["collators"] = R.apply_collator_patches()
+    if kw.get("vmap_grouped_mm", compat):
+        report["grouped_mm"] = R.apply_grouped_mm_patches()
     _RUNTIME["patched"] = True
+    return report
 
 
-def apply_transformers_model_patches(model, *, performance: bool = True, compat: bool = True, kernels: bool = True,
+def apply_transformers_model_patches(model, *, performance: bool = True, compat: bool = True, kernels: bool | None = None,
                                      fused_linear_cross_entropy: bool | None = None, **cfg) -> dict:
-    """Patches a Hugging Face decoder in place; returns a report ``{what: count}``."""
+    """Patches a Hugging Face decoder in place; returns a report ``{what: count}``.
+
+    Umbrella flags and the per-concern keywords they default: ``compat`` -> ``dropout``, ``batchify``,
+    ``eager_attention`` (vmap-safe attention interface); ``performance`` -> ``kv_cache``, ``fused_linear_cross_entropy``
+    (conditional ``loss_only`` forward); ``kernels`` (defaults to ``performance``) -> ``rms_norm``, ``activation``,
+    ``rope``, ``cross_entropy`` (the model's ``loss_function``)."""
     from .transformers import components as C
     spec = family_of(model)
-    report = {"family": spec.model_type if spec else None, "norms": 0, "mlps": 0, "dropouts": 0, "attention": None}
-    if compat:
+    kernels = performance if kernels is None else kernels
+    report = {"family": spec.model_type if spec else None, "norms": 0, "mlps": 0, "dropouts": 0, "attention": None, "kv_cache": 0,
+              "batchify": 0, "rope": 0, "loss_function": 0, "fused_linear_cross_entropy": False}
+    root_cls = type(model)
+    # forward wrappers nest: the fused-loss branch innermost, the batch-dimension shim outermost (each wrapper copies the
+    # marks of what it wraps, so a second application sees all of them on the outermost function)
+    fused = performance if fused_linear_cross_entropy is None else fused_linear_cross_entropy
+    if fused:
+        report["fused_linear_cross_entropy"] = C.apply_fused_linear_ce_patch(model)
+    if cfg.get("dropout", compat):
         report["dropouts"] = C.disable_dropout(model)
-        if cfg.get("kv_cache", True):
-            C.disable_kv_cache(model)
+    if cfg.get("kv_cache", performance):
+        C.disable_kv_cache(model)
+        report["kv_cache"] = C.apply_kv_cache_patch(root_cls, model) if hasattr(model, "config") else 0
+    if cfg.get("batchify", compat) and hasattr(model, "config"):
+        report["batchify"] = C.apply_batchify_patch(root_cls, model)
+    if compat:
         conf = getattr(model, "config", None)
         if conf is not None and hasattr(conf, "_attn_implementation"):
             try:
@@ -63,11 +95,20 @@ def apply_transformers_model_patches(model, *, performance: bool = True, compat:
                 m._opake_offset, m._opake_patched = spec.norm_offset, True
                 m.forward = types.MethodType(C.patched_rms_norm_forward, m)
                 report["norms"] += 1
-            elif cfg.get("activation", True) and spec.mlp_suffixes and cname.endswith(spec.mlp_suffixes) \
-                    and all(hasattr(m, a) for a in ("gate_proj", "up_proj", "down_proj")) and not hasattr(m, "_opake_patched"):
+            elif cfg.get("activation", True) and spec.mlp_suffixes and cname.endswith(spec.mlp_suffixes) and not hasattr(m, "_opake_patched"):
+                if all(hasattr(m, a) for a in ("gate_proj", "up_proj", "down_proj")):
+                    fwd = C.patched_gated_mlp_forward
+                elif spec.fused_gate_up and all(hasattr(m, a) for a in ("gate_up_proj", "down_proj")):
+                    fwd = C.patched_fused_gate_up_mlp_forward
+                else:
+                    continue
                 m._opake_act, m._opake_patched = spec.act, True
-                m.forward = types.MethodType(C.patched_gated_mlp_forward, m)
+                m.forward = types.MethodType(fwd, m)
                 report["mlps"] += 1
+        if cfg.get("rope", True) and spec.rope:
+            report["rope"] = C.apply_rope_patch(model)
+    if kernels and cfg.get("cross_entropy", True) and hasattr(model, "loss_function") and hasattr(model, "lm_head"):
+        report["loss_function"] = C.apply_causal_lm_loss_function_patch(model, root_cls)
     return report
 
 

@@ -14,11 +14,9 @@ import math
 import torch
 import torch.nn.functional as F
 
-from ..kernels.functions import opake_geglu, opake_rms_norm, opake_swiglu
 
 __all__ = ["causal_mask", "sliding_window_mask", "vmap_sdpa_attention_forward", "eager_attention_forward",
-           "softcapped_attention", "patched_rms_norm_forward", "patched_gated_mlp_forward", "disable_dropout",
-           "disable_kv_cache", "repeat_kv"]
+           "softcapped_attention", "SoftcappedAttention", "softcapped_attention_recompute", "repeat_kv"]
 
 
 def causal_mask(q_len: int, kv_len: int, device, dtype=torch.bool, attention_mask: torch.Tensor | None = None):
@@ -68,6 +66,10 @@ def vmap_sdpa_attention_forward(module, query, key, value, attention_mask=None, 
 
 def eager_attention_forward(module, query, key, value, attention_mask=None, scaling: float | None = None, softcap: float | None = None,
                             sliding_window: int | None = None, **_kw):
+    if softcap and attention_mask is None and not _kw.get("output_attentions") and query.shape[-2] == key.shape[-2]:
+        # soft-capped training pass without padding: the recomputing function keeps no [H, T, T] tensor for the backward
+        out = softcapped_attention_recompute(query, key, value, softcap, scaling, sliding_window)
+        return out.transpose(-3, -2).contiguous(), None
     n_rep = query.shape[-3] // key.shape[-3]
     key, value = repeat_kv(key, n_rep), repeat_kv(value, n_rep)
     scale = scaling if scaling is not None else 1.0 / math.sqrt(query.shape[-1])
@@ -106,33 +108,78 @@ def softcapped_attention(query, key, value, softcap: float, scaling: float | Non
     return torch.cat(outs, dim=-2)
 
 
-def patched_rms_norm_forward(self, hidden_states):
-    """Forward for ``*RMSNorm`` modules: fused kernel on CUDA bf16, same formula elsewhere. Modules that store
-    ``weight - 1`` (Gemma) are recognised by ``_opake_offset``."""
-    eps = getattr(self, "variance_epsilon", getattr(self, "eps", 1e-6))
-    return opake_rms_norm(hidden_states, self.weight, eps, getattr(self, "_opake_offset", 0.0))
+class SoftcappedAttention(torch.autograd.Function):
+    """Causal attention with soft-capped logits (``cap * tanh(s / cap)``, Gemma-2) whose backward RECOMPUTES the scores
+    chunk by chunk instead of keeping them: autograd through :func:`softcapped_attention` saves, per layer, the
+    ``[H, T, T]`` pre-cap scores, their tanh and the probabilities; this function saves q, k, v, the output and one
+    log-sum-exp per row. Inputs ``[..., H, T, hd]`` (grouped heads already expanded), optional sliding ``window``.
+    Works under ``vmap`` / ``vmap(grad)`` through the generated batching rule (all internals are batched tensor ops)."""
+
+    generate_vmap_rule = True
+
+    @staticmethod
+    def forward(query, key, value, softcap: float, scale: float, window: int, chunk: int):
+        kv_len, q_len = key.shape[-2], query.shape[-2]
+        outs, lses = [], []
+        for lo in range(0, q_len, chunk):
+            q = query[..., lo:lo + chunk, :]
+            z = _capped_scores(q, key, softcap, scale, lo + kv_len - q_len, window)
+            lse = torch.logsumexp(z, dim=-1)
+            outs.append(torch.matmul(torch.exp(z - lse[..., None]).to(value.dtype), value))
+            lses.append(lse)
+        return torch.cat(outs, dim=-2), torch.cat(lses, dim=-1)
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        query, key, value, softcap, scale, window, chunk = inputs
+        out, lse = output
+        ctx.save_for_backward(query, key, value, out, lse)
+        ctx.cfg = (softcap, scale, window, chunk)
+        ctx.mark_non_differentiable(lse)
+
+    @staticmethod
+    def backward(ctx, d_out, _d_lse):
+        query, key, value, out, lse = ctx.saved_tensors
+        softcap, scale, window, chunk = ctx.cfg
+        kv_len, q_len = key.shape[-2], query.shape[-2]
+        dq = []
+        dk = torch.zeros_like(key, dtype=torch.float32)
+        dv = torch.zeros_like(value, dtype=torch.float32)
+        for lo in range(0, q_len, chunk):
+            sl = slice(lo, lo + chunk)
+            q, do = query[..., sl, :], d_out[..., sl, :]
+            raw = torch.matmul(q.float(), key.float().transpose(-1, -2)) * scale
+            th = torch.tanh(raw / softcap)
+            z = _mask_scores(softcap * th, q.shape[-2], kv_len, lo + kv_len - q_len, window)
+            p = torch.exp(z - lse[..., sl, None])
+            dv = dv + torch.matmul(p.transpose(-1, -2), do.float())
+            dp = torch.matmul(do.float(), value.float().transpose(-1, -2))
+            delta = (do.float() * out[..., sl, :].float()).sum(-1, keepdim=True)
+            ds = p * (dp - delta) * (1.0 - th * th) * scale           # through softmax, then cap * tanh(raw / cap)
+            dq.append(torch.matmul(ds, key.float()).to(query.dtype))
+            dk = dk + torch.matmul(ds.transpose(-1, -2), q.float())
+        return torch.cat(dq, dim=-2), dk.to(key.dtype), dv.to(value.dtype), None, None, None, None
 
 
-def patched_gated_mlp_forward(self, x):
-    act = getattr(self, "_opake_act", "silu")
-    g, u = self.gate_proj(x), self.up_proj(x)
-    return self.down_proj(opake_swiglu(g, u) if act == "silu" else opake_geglu(g, u, approximate=act))
+def _mask_scores(z, q_len: int, kv_len: int, q_offset: int, window: int):
+    qi = torch.arange(q_offset, q_offset + q_len, device=z.device)[:, None]
+    ki = torch.arange(kv_len, device=z.device)[None, :]
+    keep = ki <= qi
+    if window and window < kv_len:
+        keep = keep & (ki > qi - window)
+    return z.masked_fill(~keep, float("-inf"))
 
 
-def disable_dropout(model) -> int:
-    """Sets every dropout probability to zero (per-example randomness under vmap is not defined for module dropout)."""
-    n = 0
-    for m in model.modules():
-        if isinstance(m, torch.nn.Dropout) and m.p:
-            m.p, n = 0.0, n + 1
-    cfg = getattr(model, "config", None)
-    for name in ("attention_dropout", "hidden_dropout", "resid_pdrop", "embd_pdrop", "attn_pdrop", "dropout"):
-        if cfg is not None and isinstance(getattr(cfg, name, None), float) and getattr(cfg, name):
-            setattr(cfg, name, 0.0)
-    return n
+def _capped_scores(q, key, softcap: float, scale: float, q_offset: int, window: int):
+    raw = torch.matmul(q.float(), key.float().transpose(-1, -2)) * scale
+    return _mask_scores(softcap * torch.tanh(raw / softcap), q.shape[-2], key.shape[-2], q_offset, window)
 
 
-def disable_kv_cache(model) -> None:
-    cfg = getattr(model, "config", None)
-    if cfg is not None and getattr(cfg, "use_cache", False):
-        cfg.use_cache = False
+def softcapped_attention_recompute(query, key, value, softcap: float, scaling: float | None = None, sliding_window: int | None = None,
+                                   chunk: int = 1024):
+    """Functional front end of :class:`SoftcappedAttention` (expands grouped heads, fills defaults)."""
+    n_rep = query.shape[-3] // key.shape[-3]
+    key, value = repeat_kv(key, n_rep), repeat_kv(value, n_rep)
+    scale = scaling if scaling is not None else 1.0 / math.sqrt(query.shape[-1])
+    out, _ = SoftcappedAttention.apply(query, key, value, float(softcap), float(scale), int(sliding_window or 0), int(chunk))
+    return out

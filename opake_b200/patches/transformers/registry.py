@@ -20,6 +20,8 @@ class FamilySpec:
     sliding_window: bool = False
     moe: bool = False
     native: bool = False              # lowers to DecoderConfig / NativeCausalLM
+    rope: bool = True                 # rotate-half ``apply_rotary_pos_emb`` in the modeling module (replaced by the kernel)
+    fused_gate_up: bool = False       # MLP stores one ``gate_up_proj`` ([gate | up]) instead of two projections
     notes: str = ""
 
 
@@ -35,19 +37,19 @@ for _s in (
     FamilySpec("llama", native=True), FamilySpec("mistral", sliding_window=True, native=True), FamilySpec("ministral", sliding_window=True),
     FamilySpec("mellum", native=True), FamilySpec("smollm3", native=True), FamilySpec("granite", notes="residual / logit multipliers"),
     FamilySpec("qwen2", notes="q/k/v bias"), FamilySpec("qwen3", notes="q/k norm"), FamilySpec("olmo2", notes="post-norm, q/k norm"),
-    FamilySpec("olmo3", sliding_window=True, notes="post-norm, q/k norm"), FamilySpec("phi3", notes="fused qkv and gate_up"),
-    FamilySpec("glm4", notes="fused gate_up, extra norms"), FamilySpec("exaone4", sliding_window=True, notes="q/k norm"),
+    FamilySpec("olmo3", sliding_window=True, notes="post-norm, q/k norm"), FamilySpec("phi3", fused_gate_up=True, notes="fused qkv and gate_up"),
+    FamilySpec("glm4", fused_gate_up=True, rope=False, notes="fused gate_up, extra norms, interleaved partial rotary"), FamilySpec("exaone4", sliding_window=True, notes="q/k norm"),
     # Cohere's "LayerNorm" subtracts the mean: it is not an RMSNorm and keeps its stock forward
-    FamilySpec("cohere", norm_suffixes=(), notes="parallel block, bias-free mean-subtracting layer norm"),
-    FamilySpec("cohere2", norm_suffixes=(), sliding_window=True),
+    FamilySpec("cohere", norm_suffixes=(), rope=False, notes="parallel block, bias-free mean-subtracting layer norm"),
+    FamilySpec("cohere2", norm_suffixes=(), sliding_window=True, rope=False),
     FamilySpec("gemma", act="tanh", norm_offset=1.0), FamilySpec("gemma2", act="tanh", norm_offset=1.0, softcap=50.0, sliding_window=True),
     FamilySpec("gemma3", act="tanh", norm_offset=1.0, sliding_window=True, notes="q/k norm, local/global rope"),
     FamilySpec("gemma3_text", act="tanh", norm_offset=1.0, sliding_window=True, notes="text tower of gemma3"),
-    FamilySpec("gpt2", norm_suffixes=(), mlp_suffixes=(), act="none", native=True, notes="LayerNorm, learned positions, Conv1D"),
+    FamilySpec("gpt2", norm_suffixes=(), mlp_suffixes=(), act="none", native=True, rope=False, notes="LayerNorm, learned positions, Conv1D"),
     FamilySpec("gpt_oss", moe=True, sliding_window=True, notes="attention sinks, clamped swiglu"),
     FamilySpec("mixtral", moe=True, sliding_window=True), FamilySpec("qwen3_moe", moe=True), FamilySpec("qwen3_5_moe", moe=True),
     FamilySpec("qwen3_next", moe=True, notes="gated delta-net layers stay on the stock path"),
-    FamilySpec("hunyuan_v1_moe", moe=True), FamilySpec("deepseek_v4", moe=True, notes="MLA attention stays on the stock path"),
+    FamilySpec("hunyuan_v1_moe", moe=True), FamilySpec("deepseek_v4", moe=True, rope=False, notes="MLA attention stays on the stock path"),
     FamilySpec("olmoe", moe=True, native=True, notes="not patched by the reference; native MoE runtime target"),
 ):
     register_family(_s)
