@@ -28,8 +28,11 @@ class DecoderConfig:
     top_k: int = 0
     expert_ffn: int = 0
     norm_topk_prob: bool = False
-    # RMSNorm over the whole query / key projection before RoPE (OLMoE: `self_attn.q_norm`, `self_attn.k_norm`)
-    qk_norm: bool = False
+    # RMSNorm of queries and keys before RoPE. True / "proj": over the whole projection (OLMoE, weight [H * hd]);
+    # "head": per head over head_dim with one weight [hd] shared by all heads (Qwen3)
+    qk_norm: bool | str = False
+    # bias on the fused q/k/v projection only (Qwen2); ``bias`` puts one on every projection (GPT-2)
+    qkv_bias: bool = False
     family: str = "llama"
 
     @property

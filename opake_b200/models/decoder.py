@@ -127,6 +127,8 @@ class DecoderRuntime:
                  "x_mid": e(T, d), "xn2": e(T, d)}
             if cfg.qk_norm:      # pre-normalisation queries and keys, needed by the norm's backward
                 a["qk_raw"] = e(T, (cfg.n_heads + cfg.n_kv_heads) * cfg.head_dim)
+                if cfg.qk_norm == "head":   # contiguous per-head rows: [T * heads, hd] views for the row kernels
+                    a["q_raw"], a["k_raw"] = e(T, cfg.n_heads * cfg.head_dim), e(T, cfg.n_kv_heads * cfg.head_dim)
             if cfg.n_experts and self.ep is not None:
                 pass        # token rows, pre-activations and routing state live in the expert-parallel layers
             elif cfg.n_experts:
@@ -259,7 +261,18 @@ class DecoderRuntime:
             wsrc, stg = self._wop(p + "wqkv")
             G.gemm(xn, wsrc, out=a["qkv"], bias=w.get(p + "bqkv"), stage=stg)
             stq = None
-            if cfg.qk_norm:
+            if cfg.qk_norm == "head":
+                nq, nk = H * hd, KV * hd
+                a["q_raw"].copy_(a["qkv"][:, :nq])
+                a["k_raw"].copy_(a["qkv"][:, nq : nq + nk])
+                qn, rq = K.rmsnorm_fwd(a["q_raw"].view(T * H, hd), w[p + "q_norm.weight"], cfg.norm_eps,
+                                       out=a["qk_raw"].view(-1)[: T * nq].view(T * H, hd))
+                kn, rk = K.rmsnorm_fwd(a["k_raw"].view(T * KV, hd), w[p + "k_norm.weight"], cfg.norm_eps,
+                                       out=a["qk_raw"].view(-1)[T * nq : T * (nq + nk)].view(T * KV, hd))
+                a["qkv"][:, :nq].copy_(qn.view(T, nq))
+                a["qkv"][:, nq : nq + nk].copy_(kn.view(T, nk))
+                stq = (rq, rk)
+            elif cfg.qk_norm:
                 nq, nk = H * hd, KV * hd
                 a["qk_raw"].copy_(a["qkv"][:, : nq + nk])
                 _, rq = K.rmsnorm_fwd(a["qk_raw"][:, :nq], w[p + "q_norm.weight"], cfg.norm_eps, out=a["qkv"][:, :nq])
@@ -412,14 +425,26 @@ class DecoderRuntime:
             A.attention_bwd(dattn, a["qkv"], a["attn"], actx, H, KV, hd, dqkv)
             if cfg.pos == "rope":
                 K.rope_(dqkv, self._rope_table(T), H + KV, hd, backward=True)
-            if cfg.qk_norm:      # in place on the query and key columns of dqkv
+            if cfg.qk_norm == "head":
+                nq, nk = H * hd, KV * hd
+                dq_c = a["qk_raw"].view(-1)[: T * nq].view(T, nq)           # the normalised copies are dead by now
+                dk_c = a["qk_raw"].view(-1)[T * nq : T * (nq + nk)].view(T, nk)
+                dq_c.copy_(dqkv[:, :nq])
+                dk_c.copy_(dqkv[:, nq : nq + nk])
+                K.rmsnorm_bwd(dq_c.view(T * H, hd), a["q_raw"].view(T * H, hd), w[p + "q_norm.weight"], stq[0],
+                              dw=self._vec(ws, p + "q_norm.weight"), out=dq_c.view(T * H, hd))
+                K.rmsnorm_bwd(dk_c.view(T * KV, hd), a["k_raw"].view(T * KV, hd), w[p + "k_norm.weight"], stq[1],
+                              dw=self._vec(ws, p + "k_norm.weight"), out=dk_c.view(T * KV, hd))
+                dqkv[:, :nq].copy_(dq_c)
+                dqkv[:, nq : nq + nk].copy_(dk_c)
+            elif cfg.qk_norm:      # in place on the query and key columns of dqkv
                 nq, nk = H * hd, KV * hd
                 K.rmsnorm_bwd(dqkv[:, :nq], a["qk_raw"][:, :nq], w[p + "q_norm.weight"], stq[0],
                               dw=self._vec(ws, p + "q_norm.weight"), out=dqkv[:, :nq])
                 K.rmsnorm_bwd(dqkv[:, nq : nq + nk], a["qk_raw"][:, nq:], w[p + "k_norm.weight"], stq[1],
                               dw=self._vec(ws, p + "k_norm.weight"), out=dqkv[:, nq : nq + nk])
             self._wgrad(dqkv, a["xn"], g[p + "wqkv"], sumsq)
-            if cfg.bias:
+            if cfg.bias or cfg.qkv_bias:
                 K.colsum_(dqkv, self._vec(ws, p + "bqkv"))
             dxn = G.gemm(dqkv, w[p + "wqkv"], b_mn=True, out=ws["dx2"])
             self._wgrad_join()                # dx_mid (read by the wo gradient) is overwritten in place below

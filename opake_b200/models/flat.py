@@ -101,9 +101,12 @@ def build_layout(cfg: DecoderConfig, shard_multiple: int = 1, skip_experts: bool
         if cfg.norm == "layer":
             add(p + "norm1.bias", d)
         add(p + "wqkv", cfg.qkv_dim, d)
-        if cfg.bias:
+        if cfg.bias or cfg.qkv_bias:
             add(p + "bqkv", cfg.qkv_dim)
-        if cfg.qk_norm:
+        if cfg.qk_norm == "head":
+            add(p + "q_norm.weight", cfg.head_dim)
+            add(p + "k_norm.weight", cfg.head_dim)
+        elif cfg.qk_norm:
             add(p + "q_norm.weight", cfg.n_heads * cfg.head_dim)
             add(p + "k_norm.weight", cfg.n_kv_heads * cfg.head_dim)
         add(p + "wo", d, cfg.n_heads * cfg.head_dim)

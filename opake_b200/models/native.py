@@ -144,7 +144,9 @@ def config_from_hf(conf: Any) -> DecoderConfig:
         rope_scaling=get("rope_scaling"), tie_embeddings=bool(get("tie_word_embeddings", False)), bias=False,
         n_experts=int(get("num_local_experts", get("num_experts", 0)) or 0), top_k=int(get("num_experts_per_tok", 0) or 0),
         expert_ffn=int(get("moe_intermediate_size", get("intermediate_size", 0)) or 0) if get("num_local_experts", get("num_experts", 0)) else 0,
-        norm_topk_prob=bool(get("norm_topk_prob", False)), qk_norm=(mt == "olmoe"), family=mt)
+        norm_topk_prob=bool(get("norm_topk_prob", False)),
+        qk_norm=True if mt == "olmoe" else ("head" if mt in ("qwen3", "qwen3_moe") else False),
+        qkv_bias=(mt == "qwen2") or (mt in ("qwen3", "qwen3_moe") and bool(get("attention_bias", False))), family=mt)
 
 
 def _interleave(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -181,6 +183,9 @@ def hf_to_flat_views(cfg: DecoderConfig, sd: Mapping[str, torch.Tensor], w: dict
         put(p + "wqkv", torch.cat([sd[s + "self_attn.q_proj.weight"], sd[s + "self_attn.k_proj.weight"],
                                    sd[s + "self_attn.v_proj.weight"]], dim=0))
         put(p + "wo", sd[s + "self_attn.o_proj.weight"])
+        if cfg.qkv_bias:
+            put(p + "bqkv", torch.cat([sd[s + "self_attn.q_proj.bias"], sd[s + "self_attn.k_proj.bias"],
+                                       sd[s + "self_attn.v_proj.bias"]], dim=0))
         if cfg.qk_norm:
             put(p + "q_norm.weight", sd[s + "self_attn.q_norm.weight"])
             put(p + "k_norm.weight", sd[s + "self_attn.k_norm.weight"])
@@ -225,6 +230,10 @@ def flat_views_to_hf(cfg: DecoderConfig, w: Mapping[str, torch.Tensor]) -> dict[
         out[s + "self_attn.k_proj.weight"] = qkv[H * hd:(H + KV) * hd]
         out[s + "self_attn.v_proj.weight"] = qkv[(H + KV) * hd:]
         out[s + "self_attn.o_proj.weight"] = w[p + "wo"]
+        if cfg.qkv_bias:
+            b = w[p + "bqkv"]
+            out[s + "self_attn.q_proj.bias"], out[s + "self_attn.k_proj.bias"] = b[: H * hd], b[H * hd:(H + KV) * hd]
+            out[s + "self_attn.v_proj.bias"] = b[(H + KV) * hd:]
         if cfg.qk_norm:
             out[s + "self_attn.q_norm.weight"] = w[p + "q_norm.weight"]
             out[s + "self_attn.k_norm.weight"] = w[p + "k_norm.weight"]

@@ -36,10 +36,14 @@ def decoder_hidden(cfg: DecoderConfig, w: dict[str, torch.Tensor], tok: torch.Te
         p = f"layers.{li}."
         xn = _norm(cfg, w, p + "norm1", x)
         qkv = xn @ w[p + "wqkv"].T
-        if cfg.bias:
+        if cfg.bias or cfg.qkv_bias:
             qkv = qkv + w[p + "bqkv"]
         qf, kf = qkv[:, : H * hd], qkv[:, H * hd : (H + KV) * hd]
-        if cfg.qk_norm:
+        if cfg.qk_norm == "head":
+            qh, kh = qf.reshape(T, H, hd), kf.reshape(T, KV, hd)
+            qf = (qh * torch.rsqrt(qh.pow(2).mean(-1, keepdim=True) + cfg.norm_eps) * w[p + "q_norm.weight"]).reshape(T, H * hd)
+            kf = (kh * torch.rsqrt(kh.pow(2).mean(-1, keepdim=True) + cfg.norm_eps) * w[p + "k_norm.weight"]).reshape(T, KV * hd)
+        elif cfg.qk_norm:
             qf = qf * torch.rsqrt(qf.pow(2).mean(-1, keepdim=True) + cfg.norm_eps) * w[p + "q_norm.weight"]
             kf = kf * torch.rsqrt(kf.pow(2).mean(-1, keepdim=True) + cfg.norm_eps) * w[p + "k_norm.weight"]
         q = qf.reshape(T, H, hd)

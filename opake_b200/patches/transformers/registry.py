@@ -36,7 +36,7 @@ def register_family(spec: FamilySpec) -> FamilySpec:
 for _s in (
     FamilySpec("llama", native=True), FamilySpec("mistral", sliding_window=True, native=True), FamilySpec("ministral", sliding_window=True),
     FamilySpec("mellum", native=True), FamilySpec("smollm3", native=True), FamilySpec("granite", notes="residual / logit multipliers"),
-    FamilySpec("qwen2", notes="q/k/v bias"), FamilySpec("qwen3", notes="q/k norm"), FamilySpec("olmo2", notes="post-norm, q/k norm"),
+    FamilySpec("qwen2", native=True, notes="q/k/v bias"), FamilySpec("qwen3", native=True, notes="per-head q/k norm"), FamilySpec("olmo2", notes="post-norm, q/k norm"),
     FamilySpec("olmo3", sliding_window=True, notes="post-norm, q/k norm"), FamilySpec("phi3", fused_gate_up=True, notes="fused qkv and gate_up"),
     FamilySpec("glm4", fused_gate_up=True, rope=False, notes="fused gate_up, extra norms, interleaved partial rotary"), FamilySpec("exaone4", sliding_window=True, notes="q/k norm"),
     # Cohere's "LayerNorm" subtracts the mean: it is not an RMSNorm and keeps its stock forward

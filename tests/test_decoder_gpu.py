@@ -38,7 +38,8 @@ def _oracle(cfg, layout, params, tok, labels, rt):
     return loss.item(), {k: v.grad for k, v in w.items()}
 
 
-@pytest.mark.parametrize("name", ["tiny-llama", "tiny-llama-tied", "tiny-llama-qknorm", "tiny-gpt2", "tiny-moe", "tiny-moe-norm"])
+@pytest.mark.parametrize("name", ["tiny-llama", "tiny-llama-tied", "tiny-llama-qknorm", "tiny-qwen2", "tiny-qwen3", "tiny-gpt2", "tiny-moe",
+                                  "tiny-moe-norm"])
 def test_example_grad_matches_autograd(cuda, name):
     from opake_b200.models import config as C
 
@@ -48,6 +49,10 @@ def test_example_grad_matches_autograd(cuda, name):
         cfg = C.tiny_llama(tie_embeddings=True)
     elif name == "tiny-llama-qknorm":      # RMSNorm over the query / key projections (OLMoE attention)
         cfg = C.tiny_llama(qk_norm=True, name=name)
+    elif name == "tiny-qwen2":             # bias on the fused q/k/v projection only
+        cfg = C.tiny_llama(qkv_bias=True, name=name)
+    elif name == "tiny-qwen3":             # per-head RMSNorm of queries and keys, one [head_dim] weight each
+        cfg = C.tiny_llama(qk_norm="head", name=name)
     elif name.startswith("tiny-moe"):
         cfg = C.tiny_llama(n_experts=8, top_k=2, expert_ffn=128, ffn=0, norm_topk_prob=name.endswith("norm"), name=name)
     else:
