@@ -119,6 +119,38 @@ def _rank_local_sampler_state(saved_state, template_sampler, world_size: int):
     return local
 
 
+def predict_stop_step(prefix_process, step_process, *, target_epsilon: float, delta: float, k0: int, horizon: int) -> int | None:
+    """First accounted step in ``(k0, horizon]`` at which epsilon reaches ``target_epsilon``, or ``None`` (not reached
+    within the horizon, or the epsilon sequence failed the boundary check). After ``k`` steps the accountant holds
+    ``prefix | step_process * (k - k0)``, so a monotone epsilon(k) is bisected with about ``log2(horizon)`` evaluations
+    (packages/opake-transformers/src/opake/api/transformers/trainer/_dp_trainer.py:350-410)."""
+    remaining = horizon - k0
+    if remaining < 1:
+        return None
+    cache: dict[int, float] = {}
+
+    def eps(j: int) -> float:
+        if j not in cache:
+            proc = step_process * j if prefix_process is None else prefix_process | (step_process * j)
+            cache[j] = float(proc.epsilon_at(delta))
+        return cache[j]
+
+    if eps(remaining) < target_epsilon:
+        return None
+    lo, hi = 1, remaining
+    while lo < hi:
+        mid = (lo + hi) // 2
+        if eps(mid) >= target_epsilon:
+            hi = mid
+        else:
+            lo = mid + 1
+    if eps(lo) < target_epsilon or (lo > 1 and eps(lo - 1) >= target_epsilon):
+        warnings.warn(f"stop-at-epsilon: epsilon is not monotone near step {k0 + lo}; checking at log boundaries instead",
+                      stacklevel=2)
+        return None
+    return k0 + lo
+
+
 class DPTrainer:
     def __init__(self, model: nn.Module | None = None, args: TrainingArguments | None = None, data_collator: Callable | None = None,
                  train_dataset=None, eval_dataset=None, processing_class=None, compute_loss_func: Callable | None = None,
@@ -205,7 +237,24 @@ class DPTrainer:
             return False
         return ok
 
+    def is_local_process_zero(self) -> bool:
+        return self.ddp.local_rank == 0
+
+    @property
+    def label_names(self) -> list:
+        return list(self.args.label_names or ["labels"])
+
     # ------------------------------------------------------------------------------------------- loss seam
+    def compute_per_example_loss_and_metrics(self, call: Callable, params, inputs: dict):
+        """``(loss, {name: per-example tensor})`` of ONE example: the seam for objectives that report per-example
+        telemetry (preference rewards, margins). The values ride the clipping transform's ``loss_aux`` channel, are summed
+        over ranks, averaged per logged step and aggregated in the evaluation loop. The default has no telemetry and
+        delegates to :meth:`compute_per_example_loss`; overriding THIS method turns the aux channel on."""
+        return self.compute_per_example_loss(call, params, inputs), {}
+
+    def _overrides_metrics_seam(self) -> bool:
+        return type(self).compute_per_example_loss_and_metrics is not DPTrainer.compute_per_example_loss_and_metrics
+
     def compute_per_example_loss(self, call: Callable, params, inputs: dict) -> torch.Tensor:
         """Loss of ONE example. ``call(params, **inputs)`` runs the model on a batch of one; subclasses override this
         to change the objective (the SFT / DPO trainers do)."""
@@ -399,13 +448,19 @@ class DPTrainer:
         def call(p, **inputs):
             return fmodel({**frozen, **p}, **inputs)
 
+        rt["loss_has_aux"] = self._overrides_metrics_seam()
+
         def loss_fn(p, example):
             batch = tree_map(lambda t: t.unsqueeze(0) if isinstance(t, torch.Tensor) else t, example)
             with autocast_context(a, self.device):
+                if rt["loss_has_aux"]:
+                    loss, tele = self.compute_per_example_loss_and_metrics(call, p, batch)
+                    return loss, {k: v.detach().reshape(()) for k, v in tele.items()}
                 return self.compute_per_example_loss(call, p, batch)
 
         norm = self._resolve_clipping_norm(params)
-        common = dict(normalize_by=rt["expected_batch"], batch_argnums=1, return_aux=True, microbatch_size=self._microbatch)
+        common = dict(has_aux=rt["loss_has_aux"], normalize_by=rt["expected_batch"], batch_argnums=1, return_aux=True,
+                      microbatch_size=self._microbatch)
         compiler = clip_api.CudaGraphChunkCompiler(max_graphs=a.cuda_graphs) if (a.cuda_graphs and self.device.type == "cuda") else None
         ckw = dict(a.clipping_kwargs)
         if a.clipping_mode == "fixed":
@@ -417,7 +472,8 @@ class DPTrainer:
             ckw.setdefault("initial_clipping_norm", float(norm) if not hasattr(norm, "values") else 1.0)
             ckw.setdefault("expected_batch_size", rt["expected_batch"])
             grad_fn, clip_state = clip_api.adaptive_clipped_grad(loss_fn, key=fold_in(make_key(a.seed), "opake.dpsgd.adaptive_clipping"),
-                                                                 normalize_by=rt["expected_batch"], batch_argnums=1, return_aux=True,
+                                                                 has_aux=rt["loss_has_aux"], normalize_by=rt["expected_batch"],
+                                                                 batch_argnums=1, return_aux=True,
                                                                  microbatch_size=self._microbatch, **ckw)
             if rt["step_process"] is not None and a.privacy_noise_mechanism == "gaussian":
                 from ..dpsgd import accounting as SA
@@ -578,7 +634,11 @@ class DPTrainer:
             self.evaluate()
         t0 = time.time()
         self._loss_sum, self._loss_count, self._tokens = 0.0, 0, 0
+        self._tele_sum, self._tele_count = {}, 0
         run_loss, run_count = 0.0, 0
+        stop_at = self._plan_stop_at_epsilon()
+        if stop_at == st.global_step and st.privacy_target_epsilon_reached:        # the resumed accountant is already there
+            total = st.global_step
         it = iter(loader)
         epoch_seen = -1
         while st.global_step < total:
@@ -605,6 +665,12 @@ class DPTrainer:
             run_count += 1
             if self.accountant is not None and rt["step_process"] is not None and rt["per_step_process"]:
                 self.accountant = self.accountant | rt["step_process"]
+            if stop_at is not None and st.global_step >= stop_at:
+                st.privacy_target_epsilon_reached = True
+                self.control.should_training_stop = True
+                self.control.should_log = True
+                if a.save_strategy != "no":
+                    self.control.should_save = True
             self.control = self.callback_handler.call_event("on_step_end", a, st, self.control)
             self._maybe_log_save_evaluate(t0)
             if a.torch_empty_cache_steps and st.global_step % a.torch_empty_cache_steps == 0 and torch.cuda.is_available():
@@ -634,6 +700,29 @@ class DPTrainer:
             self._load_model_weights(st.best_model_checkpoint)
         self.control = self.callback_handler.call_event("on_train_end", a, st, self.control)
         return TrainOutput(st.global_step, metrics["train_loss"], metrics)
+
+    def _plan_stop_at_epsilon(self) -> int | None:
+        """Stop-at-epsilon: with a fixed positive noise multiplier AND a target epsilon, training ends at the first step
+        whose accounted epsilon reaches the target. Accounting is deterministic, so the crossing step is found once, by
+        bisection over the number of steps (``predict_stop_step``); the loop then compares integers. Only defined for
+        independently composed steps (not for whole-horizon mechanisms or Monte-Carlo samplers: those fall back to a
+        check at every log boundary)."""
+        a, rt, st = self.args, self._rt, self.state
+        if not (a.privacy_noise_multiplier and a.privacy_noise_multiplier > 0 and a.privacy_target_epsilon is not None
+                and self.accountant is not None and rt.get("step_process") is not None):
+            return None
+        if not rt["per_step_process"] or a.resolved_sampling_mode in ("b_min_sep", "balls_in_bins"):
+            rt["stop_check_at_log"] = rt["per_step_process"]
+            return None
+        if st.global_step > 0 and self.accountant.epsilon_at(rt["target_delta"]) >= a.privacy_target_epsilon:
+            st.privacy_target_epsilon_reached = True
+            return st.global_step
+        prefix = self.accountant.process if st.global_step > 0 else None
+        stop = predict_stop_step(prefix, rt["step_process"], target_epsilon=a.privacy_target_epsilon, delta=rt["target_delta"],
+                                 k0=st.global_step, horizon=rt["total_steps"])
+        if stop is None:
+            rt["stop_check_at_log"] = True
+        return stop
 
     def _sigterm_agreed(self) -> bool:
         """True on every rank as soon as any rank has received SIGTERM (they must checkpoint together)."""
@@ -665,6 +754,15 @@ class DPTrainer:
             perf.mark("clip")
             loss_sum = float(aux.loss_values.sum()) if getattr(aux, "loss_values", None) is not None and n_local else 0.0
             n_clipped = float(aux.clipping_rate or 0.0) * n_local if getattr(aux, "clipping_rate", None) is not None else 0.0
+            tele = getattr(aux, "loss_aux", None) if rt.get("loss_has_aux") else None
+            if isinstance(tele, dict) and tele:
+                # per-example telemetry: local sums now, one reduction over ranks with the loss, means at the next log
+                sums = {k: float(torch.as_tensor(v).float().sum()) if n_local else 0.0 for k, v in tele.items()}
+                if self.ddp.is_distributed:
+                    sums = {k: D.reduce_scalar(v, op="sum", device=self.device) for k, v in sorted(sums.items())}
+                for k, v in sums.items():
+                    self._tele_sum[k] = self._tele_sum.get(k, 0.0) + v
+                self._tele_count += int(D.reduce_scalar(n_local, op="sum", device=self.device)) if self.ddp.is_distributed else n_local
             if self.ddp.is_distributed:
                 D.sum_gradients_(grads)
                 loss_sum = D.reduce_scalar(loss_sum, op="sum", device=self.device)
@@ -728,6 +826,13 @@ class DPTrainer:
             if eps is not None:
                 logs["privacy_epsilon"] = eps
                 st.privacy_epsilon = eps
+                # fallback of stop-at-epsilon when the crossing step could not be predicted (Monte-Carlo accounting)
+                if self._rt.get("stop_check_at_log") and eps >= a.privacy_target_epsilon:
+                    st.privacy_target_epsilon_reached = True
+                    self.control.should_training_stop = True
+            if getattr(self, "_tele_count", 0):
+                logs.update({k: v / self._tele_count for k, v in self._tele_sum.items()})
+                self._tele_sum, self._tele_count = {}, 0
             self._loss_sum, self._loss_count = 0.0, 0
             self.log(logs)
         do_eval = self.control.should_evaluate or (a.eval_strategy == "steps" and st.eval_steps and step % st.eval_steps == 0) or \

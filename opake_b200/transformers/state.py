@@ -31,6 +31,7 @@ class DPTrainerState:
     stateful_callbacks: dict = field(default_factory=dict)
     # privacy bookkeeping
     privacy_epsilon: float | None = None
+    privacy_target_epsilon_reached: bool = False      # stop-at-epsilon ended the run before max_steps
     privacy_delta: float | None = None
     noise_multiplier: float | None = None
     sample_rate: float | None = None

@@ -187,9 +187,10 @@ class TrainingArguments:
             raise ConfigurationError(f"sampling_mode {self.sampling_mode!r} is not valid for noise mechanism "
                                      f"{self.privacy_noise_mechanism!r}; allowed: "
                                      f"{sorted(ALLOWED_SAMPLING[self.privacy_noise_mechanism])}")
-        if self.privacy_target_epsilon is not None and self.privacy_noise_multiplier is not None:
-            raise ConfigurationError("give either privacy_target_epsilon (noise is calibrated) or "
-                                     "privacy_noise_multiplier (epsilon is reported), not both")
+        # both given: the noise is fixed and training STOPS when the accountant reaches the target (stop-at-epsilon)
+        if self.privacy_target_epsilon is not None and self.privacy_noise_multiplier is not None and self.privacy_noise_multiplier == 0.0:
+            raise ConfigurationError("privacy_noise_multiplier=0.0 is the non-private path; privacy_target_epsilon is "
+                                     "meaningless there")
         if self.privacy_target_epsilon is not None and self.privacy_target_epsilon <= 0:
             raise ConfigurationError("privacy_target_epsilon must be positive")
         if self.privacy_target_delta is not None and not 0 < self.privacy_target_delta < 1:

@@ -162,7 +162,10 @@ class DPOTrainer(DPTrainer):
             losses["rpo_nll"], weights["rpo_nll"] = L.chosen_nll_loss(pc), a.rpo_alpha
         return L.mpo_combine(losses, weights)
 
-    def compute_per_example_loss(self, call, params, inputs):
+    def compute_per_example_loss_and_metrics(self, call, params, inputs):
+        """Loss of one preference pair plus its reward telemetry (``rewards/chosen``, ``rewards/rejected``,
+        ``rewards/accuracies``, ``rewards/margins``), logged as batch means during training. These are statistics of
+        the training data that no mechanism protects: log them for diagnosis, do not publish them."""
         a = self.args
         normalized = any(n in _LENGTH_NORMALISED for n in self._names)
         pc, pr = self._policy_logps(lambda **kw: call(params, **kw), inputs, normalized)
@@ -175,7 +178,13 @@ class DPOTrainer(DPTrainer):
         if rc is None:
             rc, rr = torch.zeros_like(pc), torch.zeros_like(pr)
         loss = self.dpo_loss(pc, pr, rc.to(pc.dtype), rr.to(pr.dtype))
-        return loss[0] if loss.dim() else loss
+        lc, lr_ = (pc - rc).detach().reshape(-1)[0], (pr - rr).detach().reshape(-1)[0]
+        tele = {"rewards/chosen": a.beta * lc, "rewards/rejected": a.beta * lr_, "rewards/accuracies": (lc > lr_).to(lc.dtype),
+                "rewards/margins": a.beta * (lc - lr_)}
+        return (loss[0] if loss.dim() else loss), tele
+
+    def compute_per_example_loss(self, call, params, inputs):
+        return self.compute_per_example_loss_and_metrics(call, params, inputs)[0]
 
     def prediction_step(self, inputs, prediction_loss_only=None):
         with torch.no_grad():

@@ -45,8 +45,8 @@ def test_training_arguments_validation_and_hf_conversion():
     assert TrainingArguments().target_delta(10_000) == pytest.approx(10_000 ** -1.1)
     with pytest.raises(ConfigurationError):
         TrainingArguments(privacy_noise_mechanism="mf_blt", sampling_mode="poisson")
-    with pytest.raises(ConfigurationError):
-        TrainingArguments(privacy_target_epsilon=1.0, privacy_noise_multiplier=1.0)
+    both = TrainingArguments(privacy_target_epsilon=1.0, privacy_noise_multiplier=1.0)      # stop-at-epsilon mode
+    assert both.privacy_target_epsilon == 1.0 and both.privacy_noise_multiplier == 1.0
     with pytest.raises(ConfigurationError):
         TrainingArguments(torch_compile=True)
     b = TrainingArguments.from_hf({"per_device_train_batch_size": 4, "gradient_accumulation_steps": 8, "max_grad_norm": 0.5,
@@ -147,6 +147,10 @@ def test_sft_and_dpo_trainers_on_native_model(tmp_path):
                    train_dataset=Pref(), eval_dataset=Pref())
     assert "ref_chosen_logps" in t.train_dataset[0]
     assert t.train().global_step == 2 and "eval_loss" in t.evaluate()
+    # per-example reward telemetry rides the clipping transform's aux channel into the training logs
+    train_logs = [e for e in t.state.log_history if "rewards/margins" in e and "loss" in e]
+    assert len(train_logs) == 2 and all(0.0 <= e["rewards/accuracies"] <= 1.0 for e in train_logs)
+    assert all(e["rewards/margins"] == pytest.approx(e["rewards/chosen"] - e["rewards/rejected"], abs=1e-5) for e in train_logs)
 
 
 def test_hf_weight_mapping_and_patches_roundtrip():
@@ -485,3 +489,59 @@ def test_evaluation_telemetry_transfer_pipeline_and_nested_accumulation():
     assert pipe.submit({"a": torch.ones(2)})[0]["a"].tolist() == [1, 1] and pipe.drain_all() == []
     assert concat_nested([np.zeros((1, 2)), np.ones((2, 3))]).shape == (3, 3)
     assert resolve_eval_num_samples([1, 2, 3], None, 2) == 3 and resolve_eval_num_samples(iter(()), None, 7) == 7
+
+
+def test_stop_at_epsilon_ends_training_at_the_predicted_step(tmp_path):
+    """Fixed noise AND a target epsilon: the run stops at the first step whose accounted epsilon reaches the target,
+    found once by bisection; a resumed run that is already there does no further step."""
+    from opake_b200 import accounting as acc
+    from opake_b200.dpsgd import accounting as SA
+    from opake_b200.transformers import DPTrainer
+    from opake_b200.transformers.dp_trainer import predict_stop_step
+
+    q, sigma, delta, horizon = 32 / 256, 0.8, 256 ** -1.1, 40
+    step = SA.poisson(SA.gaussian(sigma), q)
+    eps = lambda k: (step * k).epsilon_at(delta)  # noqa: E731
+    target = 0.5 * (eps(9) + eps(10))
+    assert predict_stop_step(None, step, target_epsilon=target, delta=delta, k0=0, horizon=horizon) == 10
+    assert predict_stop_step(None, step, target_epsilon=eps(horizon) + 1.0, delta=delta, k0=0, horizon=horizon) is None
+    # with a prefix of 4 accounted steps the same crossing is found at the same absolute step
+    assert predict_stop_step(step * 4, step, target_epsilon=target, delta=delta, k0=4, horizon=horizon) == 10
+    assert predict_stop_step(None, step, target_epsilon=target, delta=delta, k0=40, horizon=horizon) is None
+
+    args = _args(tmp_path / "run", max_steps=horizon, privacy_target_epsilon=target, privacy_noise_multiplier=sigma,
+                 save_steps=5, eval_strategy="no", logging_steps=5)
+    tr = DPTrainer(_Net(), args, train_dataset=_DS(256))
+    out = tr.train()
+    assert tr.state.global_step == 10 and tr.state.privacy_target_epsilon_reached
+    assert out.metrics["privacy_epsilon"] == pytest.approx(eps(10), rel=1e-6) and out.metrics["privacy_epsilon"] >= target
+    assert os.path.isdir(tmp_path / "run" / "checkpoint-10")                 # the stop forces a checkpoint
+    # resuming from there trains no further
+    tr2 = DPTrainer(_Net(), args, train_dataset=_DS(256))
+    tr2.train(resume_from_checkpoint=True)
+    assert tr2.state.global_step == 10 and tr2.state.privacy_target_epsilon_reached
+    # noise 0 with a target is refused
+    from opake_b200.base.exceptions import ConfigurationError
+    from opake_b200.transformers import TrainingArguments
+
+    with pytest.raises(ConfigurationError, match="non-private"):
+        TrainingArguments(privacy_target_epsilon=1.0, privacy_noise_multiplier=0.0)
+    assert acc is not None
+
+
+def test_per_example_metrics_seam_reaches_the_training_logs(tmp_path):
+    from opake_b200.transformers import DPTrainer
+
+    class T(DPTrainer):
+        def compute_per_example_loss_and_metrics(self, call, params, inputs):
+            loss = self.compute_per_example_loss(call, params, inputs)
+            return loss, {"probe/first_feature": inputs["x"][0, 0], "probe/one": torch.ones(())}
+
+    tr = T(_Net(), _args(tmp_path / "run", max_steps=4, logging_steps=2, eval_strategy="no", save_strategy="no"), train_dataset=_DS(256))
+    assert tr._overrides_metrics_seam() and tr.is_local_process_zero() and tr.label_names == ["labels"]
+    tr.train()
+    logged = [e for e in tr.state.log_history if "probe/one" in e]
+    assert len(logged) == 2 and all(e["probe/one"] == pytest.approx(1.0) for e in logged)
+    assert all(abs(e["probe/first_feature"]) < 1.0 for e in logged)             # a batch mean of N(0, 1) features
+    plain = DPTrainer(_Net(), _args(tmp_path / "run2", max_steps=2, eval_strategy="no", save_strategy="no"), train_dataset=_DS(256))
+    assert not plain._overrides_metrics_seam()
