@@ -92,7 +92,13 @@ def simpo_loss(chosen_logratio, rejected_logratio, *, beta: float, gamma: float 
 
 
 def _log1mexp(x):
-    return torch.where(x > -math.log(2.0), torch.log(-torch.expm1(x)), torch.log1p(-torch.exp(x)))
+    """``log(1 - exp(x))`` for ``x < 0`` (Maechler 2012). Each branch only ever sees arguments from its own side of the
+    split: otherwise the unused branch can be infinite there (``exp(x)`` rounds to 1 in bf16 for small ``|x|``) and its
+    zero-weighted gradient turns into NaN."""
+    near = x > -math.log(2.0)
+    a = torch.where(near, x, torch.full_like(x, -1.0))
+    b = torch.where(near, torch.full_like(x, -1.0), x)
+    return torch.where(near, torch.log(-torch.expm1(a)), torch.log1p(-torch.exp(b)))
 
 
 def odds_ratio_loss(chosen_logp, rejected_logp):
