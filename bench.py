@@ -258,7 +258,7 @@ def main() -> None:
                        "shard": shard, "step_collectives": args.comm, "expert_parallel": f"ep{world}" if (mcfg.n_experts and world > 1) else None,
                        "clip_norm": 1.0, "noise_multiplier": args.sigma, "optimizer": "adamw-bc", "sft_mask": "first 25%",
                        "mechanism": f"dp-ftrl blt x{args.blt_buffers}" if args.blt_buffers else "dp-sgd gaussian",
-                       "per_example_microbatch": 1, "cuda_graph": (not args.no_graph) and eng.ep is None,
+                       "per_example_microbatch": 1, "cuda_graph": not args.no_graph,
                        "accumulate_group": getattr(eng, "group", None),
                        "device_memory_in_use_gib": round((lambda f, t: (t - f) / 2 ** 30)(*torch.cuda.mem_get_info(dev)), 1),
                        "l2_policy": "inputs larger than L2: every example streams all bf16 weights and a full-size bf16 gradient, "

@@ -61,8 +61,13 @@ __device__ __forceinline__ int* ctrl_done(void* ctrl, int W, int E) {
 __device__ __forceinline__ int gpad(int c) { return c <= 64 ? 64 : (c + 63) / 64 * 64; }
 
 // Threads 0..W-1 of the CTA each wait for one source's flag; returns (to every thread) whether all arrived.
+__device__ __forceinline__ int abs_epoch(const OpkEpGroup& g, int phase, int epoch) {
+  return g.epoch_base ? epoch + __ldcg(g.epoch_base + (phase == OPK_EP_PHASE_BARRIER ? 1 : 0)) : epoch;
+}
+
 __device__ bool wait_phase_all(const OpkEpGroup& g, int phase, int epoch) {
   int ok = 1;
+  if (phase >= 0) epoch = abs_epoch(g, phase, epoch);
   if (phase >= 0 && (int)threadIdx.x < g.world) {
     const int* f = ctrl_flags(g.ctrl[g.rank], g.world, g.n_experts, phase) + threadIdx.x;
     if (ld_acquire_sys(f) < epoch) {
@@ -77,6 +82,7 @@ __device__ bool wait_phase_all(const OpkEpGroup& g, int phase, int epoch) {
 
 // Raises flag[phase][my rank] = epoch on every rank. Called by one thread after a system-scope fence.
 __device__ void signal_all(const OpkEpGroup& g, int phase, int epoch) {
+  epoch = abs_epoch(g, phase, epoch);
   for (int r = 0; r < g.world; ++r) st_release_sys(ctrl_flags(g.ctrl[r], g.world, g.n_experts, phase) + g.rank, epoch);
 }
 
@@ -335,6 +341,33 @@ __global__ void ep_signal_kernel(const OpkEpGroup g, int phase, int epoch) {
   if (threadIdx.x == 0) signal_all(g, phase, epoch);
 }
 
+__global__ void ep_advance_kernel(int* base, int d_epoch, int d_barrier) {
+  if (threadIdx.x == 0) { base[0] += d_epoch; base[1] += d_barrier; }
+}
+
+// One CTA of 512 threads: store, fence, signal, bounded wait, ordered sum.
+__global__ void __launch_bounds__(512) ep_allreduce_f64_kernel(const OpkEpGroup g, const OpkEpPeers slots,
+                                                               const double* __restrict__ local, int n, int epoch,
+                                                               double* __restrict__ out, int* err) {
+  for (int t = threadIdx.x; t < g.world * n; t += blockDim.x) {
+    const int r = t / n, i = t - r * n;
+    reinterpret_cast<double*>(slots.p[r])[g.rank * 64 + i] = local[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) signal_all(g, OPK_EP_PHASE_SUMS, epoch);
+  if (!wait_phase_all(g, OPK_EP_PHASE_SUMS, epoch)) {
+    if (threadIdx.x == 0 && err) atomicCAS(err, 0, 1);
+    return;
+  }
+  const volatile double* mine = reinterpret_cast<const volatile double*>(slots.p[g.rank]);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    double s = 0.0;
+    for (int r = 0; r < g.world; ++r) s += mine[r * 64 + i];
+    out[i] = s;
+  }
+}
+
 __global__ void __launch_bounds__(32) ep_wait_kernel(const OpkEpGroup g, int phase, int epoch, int* err) {
   if (!wait_phase_all(g, phase, epoch) && threadIdx.x == 0 && err) atomicCAS(err, 0, 1);
 }
@@ -492,6 +525,19 @@ extern "C" int opk_ep_scale_rows(const void* rows, const int32_t* row_src, const
 extern "C" int opk_ep_signal(const OpkEpGroup* g, int phase, int epoch, void* stream) {
   if (!group_ok(g) || phase < 0 || phase >= N_PHASES) return -1;
   ep_signal_kernel<<<1, 32, 0, ST(stream)>>>(*g, phase, epoch);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int opk_ep_advance(int32_t* epoch_base, int d_epoch, int d_barrier, void* stream) {
+  if (!epoch_base || d_epoch < 0 || d_barrier < 0) return -1;
+  ep_advance_kernel<<<1, 32, 0, ST(stream)>>>(epoch_base, d_epoch, d_barrier);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int opk_ep_allreduce_f64(const OpkEpGroup* g, const OpkEpPeers* slots, const double* local, int n, int epoch, double* out,
+                                    int32_t* err, void* stream) {
+  if (!group_ok(g) || !slots || !local || !out || n < 1 || n > 64) return -1;
+  ep_allreduce_f64_kernel<<<1, 512, 0, ST(stream)>>>(*g, *slots, local, n, epoch, out, err);
   return (int)cudaGetLastError();
 }
 

@@ -165,17 +165,22 @@ int opk_clip_apply_sum(const void* tiles, int n_tiles, int B, const float* f_bf1
 
 // ---- expert-parallel dispatch / combine over peer memory (csrc/kernels/ep.cu) ------------------------------------
 #define OPK_EP_MAX_RANKS 8
-#define OPK_EP_PHASES 6
+#define OPK_EP_PHASES 7
 #define OPK_EP_PHASE_COUNTS 0   // routing histograms have been stored into the peers' control blocks
 #define OPK_EP_PHASE_ROWS 1     // forward rows have been stored into the owners' receive buffers
 #define OPK_EP_PHASE_OUT 2      // expert outputs are complete in the owner's buffer
 #define OPK_EP_PHASE_DROWS 3    // backward: upstream-gradient rows have been stored
 #define OPK_EP_PHASE_DOUT 4     // backward: input-gradient rows are complete in the owner's buffer
 #define OPK_EP_PHASE_BARRIER 5  // plain group barrier (buffer reuse)
+#define OPK_EP_PHASE_SUMS 6     // small all-reduce: every rank's vector has been stored into the peers' slots
 typedef struct {
   int32_t world, rank, n_experts;
   int32_t r_cap;                      // rows of every rank's row buffers (multiple of 128)
   void* ctrl[OPK_EP_MAX_RANKS];       // device address of every rank's control block (opk_ep_ctrl_ints int32, zeroed once)
+  // Optional device int32[2]: {base of the exchange epochs, base of the barrier epochs}. Every `epoch` argument below is
+  // then RELATIVE to the base read on the device, so a captured launch sequence (frozen arguments) can be replayed:
+  // opk_ep_advance moves the bases forward at the end of the sequence. Null: epochs are absolute.
+  const int32_t* epoch_base;
 } OpkEpGroup;
 typedef struct { void* p[OPK_EP_MAX_RANKS]; } OpkEpPeers;   // the same row buffer on every rank
 int opk_ep_ctrl_ints(int world, int n_experts);
@@ -194,6 +199,13 @@ int opk_ep_prepare(const OpkEpGroup* g, int wait_phase, int epoch, int32_t* tile
 int opk_ep_zero_pad(void* rows, const int32_t* row_src, const int32_t* rows_total, int r_cap, int D, void* stream);
 int opk_ep_scale_rows(const void* rows, const int32_t* row_src, const float* scale, int r_cap, int D, void* out, void* stream);
 int opk_ep_signal(const OpkEpGroup* g, int phase, int epoch, void* stream);
+// epoch_base[0] += d_epoch, epoch_base[1] += d_barrier (one thread; stream-ordered after the sequence that used them).
+int opk_ep_advance(int32_t* epoch_base, int d_epoch, int d_barrier, void* stream);
+// out[i] = sum over ranks of that rank's local[i], i < n <= 64 (fp64). `slots` is an [world][64] double buffer on
+// every rank: each rank stores its vector into slot [its rank] of every peer, raises OPK_EP_PHASE_SUMS, waits (bounded)
+// for all peers and adds the slots in rank order, so every rank gets the same bits.
+int opk_ep_allreduce_f64(const OpkEpGroup* g, const OpkEpPeers* slots, const double* local, int n, int epoch, double* out,
+                         int32_t* err, void* stream);
 int opk_ep_wait(const OpkEpGroup* g, int phase, int epoch, int32_t* err, void* stream);
 int opk_ep_combine(const OpkEpGroup* g, const OpkEpPeers* y, const int32_t* entry_pos, const float* wts, int k,
                    const void* residual, int T, int D, void* out, int wait_phase, int epoch, int32_t* err, void* stream);

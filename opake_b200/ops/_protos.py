@@ -21,7 +21,8 @@ class DpStepArgs(Structure):
 
 
 class EpGroup(Structure):
-    _fields_ = [("world", c_int32), ("rank", c_int32), ("n_experts", c_int32), ("r_cap", c_int32), ("ctrl", c_void_p * 8)]
+    _fields_ = [("world", c_int32), ("rank", c_int32), ("n_experts", c_int32), ("r_cap", c_int32), ("ctrl", c_void_p * 8),
+                ("epoch_base", c_void_p)]
 
 
 class EpPeers(Structure):
@@ -39,6 +40,8 @@ PROTOTYPES: dict = {
     "opk_ep_zero_pad": (I, [P, P, P, I, I, P]),
     "opk_ep_scale_rows": (I, [P, P, P, I, I, P, P]),
     "opk_ep_signal": (I, [_G, I, I, P]),
+    "opk_ep_advance": (I, [P, I, I, P]),
+    "opk_ep_allreduce_f64": (I, [_G, _PE, P, I, I, P, P, P]),
     "opk_ep_wait": (I, [_G, I, I, P, P]),
     "opk_ep_combine": (I, [_G, _PE, P, P, I, P, I, I, P, I, I, P, P]),
     "opk_ep_combine_bwd": (I, [_PE, P, P, I, I, I, P, P]),

@@ -265,6 +265,7 @@ class ShardedDPEngine:
                                           widest_leaf=max(rt._widest, self.ep.n_wgu), counters=rt.clip_count)
             rt.scales[slot].copy_(scales[self.rank : self.rank + 1])
             self.ep.accumulate_clipped()
+            self.ep.end_example()
         else:
             rt.clip_factor(cfg.clip_norm, auto=cfg.auto_clip, gamma=cfg.auto_gamma, slot=slot)
         ws["loss_sum"].add_(st.loss.reshape(1))
@@ -285,9 +286,7 @@ class ShardedDPEngine:
             self._stale = False
         ws["toks"][slot].copy_(tok_host, non_blocking=True)
         ws["labels"].copy_(labels_host, non_blocking=True)
-        if not self.cfg.use_cuda_graph or self.ep is not None:
-            # expert-parallel layers pass a new epoch number to their exchange kernels on every call, which a captured
-            # graph would freeze: those examples are launched directly
+        if not self.cfg.use_cuda_graph:
             self._example_body(ws, slot, drain, refresh)
             return
         key = (T, slot, drain, refresh)
@@ -306,6 +305,9 @@ class ShardedDPEngine:
                 torch.cuda.synchronize(self.device)
                 ws["loss_sum"].copy_(saved[0])
                 self.runtime.clip_count.zero_()
+                if self.ep is not None:
+                    # warm-ups only ever happen on the first example of a step, where the expert sums are still zero
+                    self.ep.acc.zero_()
                 self._warm[(T, refresh)] = True
             g = torch.cuda.CUDAGraph()
             before = _lib.LAUNCHES[0]

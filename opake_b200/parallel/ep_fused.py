@@ -58,10 +58,43 @@ class EpContext:
         if self.world > 1:                 # every control block is zero before anyone raises a flag in it
             torch.cuda.synchronize(device)
             dist.barrier(group)
-        self.g = EpGroup(self.world, self.rank, n_experts, self.r_cap, (ctypes.c_void_p * 8)(*self.ctrl.ptrs))
+        # Epoch numbers handed to the kernels are RELATIVE to two counters in device memory (exchange epochs, barrier
+        # epochs): ``end_sequence`` adds what a sequence of calls consumed, on the stream. A captured CUDA graph of one
+        # example therefore replays with fresh absolute epochs although its kernel arguments are frozen.
+        self.epoch_dev = torch.zeros(2, dtype=torch.int32, device=device)
+        self.g = EpGroup(self.world, self.rank, n_experts, self.r_cap, (ctypes.c_void_p * 8)(*self.ctrl.ptrs),
+                         self.epoch_dev.data_ptr())
         self.epoch = 0
         self.barrier_epoch = 0
         self.err = _lib.err_word(device)
+        # slots of the small fp64 all-reduce (per-example norms): [world][64] doubles on every rank
+        self._sum_slots = comm.alloc_peer_buffer(8 * 64, torch.float64, device, group)
+        self._sum_slots.local.zero_()
+        self._sum_peers = EpPeers((ctypes.c_void_p * 8)(*self._sum_slots.ptrs))
+        if self.world > 1:
+            torch.cuda.synchronize(device)
+            dist.barrier(group)
+
+    def begin_sequence(self) -> None:
+        """Start of a launch sequence that every rank issues identically (one example): relative epochs restart."""
+        self.epoch = 0
+        self.barrier_epoch = 0
+
+    def end_sequence(self) -> None:
+        """Moves the device-side epoch bases past the epochs this sequence used (stream-ordered)."""
+        _lib.check(_L().opk_ep_advance(self.epoch_dev.data_ptr(), self.epoch, self.barrier_epoch, self._s()), "ep_advance")
+        self.epoch = 0
+        self.barrier_epoch = 0
+
+    def allreduce_f64(self, local: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """``out = sum over ranks of local`` for a float64 vector of at most 64 entries, on the exchange kernels (plain
+        peer stores, bounded wait; capturable, no library collective)."""
+        if local.dtype != torch.float64 or out.dtype != torch.float64 or local.numel() > 64 or out.numel() != local.numel():
+            raise ValueError("allreduce_f64 takes float64 vectors of at most 64 entries")
+        self.epoch += 1
+        _lib.check(_L().opk_ep_allreduce_f64(self.g, self._sum_peers, _p(local), local.numel(), self.epoch, _p(out), _p(self.err),
+                                             self._s()), "ep_allreduce_f64")
+        return out
 
     def rows(self, width: int) -> tuple[torch.Tensor, EpPeers]:
         """A ``[r_cap, width]`` bf16 row buffer that every rank of the group can address."""

@@ -52,6 +52,7 @@ class ExpertParallelRuntime:
             self.layers.append(FusedExpertParallelLayer(self.ctx, router_weights[li], wgu, wd, tokens, cfg.top_k,
                                                         cfg.norm_topk_prob))
         self.norms = torch.zeros(self.world, dtype=torch.float64, device=device)       # per source example
+        self._norms_sum = torch.zeros(self.world, dtype=torch.float64, device=device)
         self.scales = torch.zeros(self.world, dtype=torch.float32, device=device)
         self._norm_parts: list[torch.Tensor] = []
 
@@ -74,6 +75,10 @@ class ExpertParallelRuntime:
     # ------------------------------------------------------------------ per example
     def begin_example(self) -> None:
         self._norm_parts.clear()
+        self.ctx.begin_sequence()
+
+    def end_example(self) -> None:
+        self.ctx.end_sequence()
 
     def forward(self, li: int, x: torch.Tensor, residual: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         return self.layers[li].forward(x, residual=residual, out=out)
@@ -93,7 +98,8 @@ class ExpertParallelRuntime:
             self.norms.add_(part)
         self.norms[self.rank : self.rank + 1].add_(dense_sumsq.reshape(1))
         if self.world > 1:
-            dist.all_reduce(self.norms, group=self.ctx.group)
+            self.ctx.allreduce_f64(self.norms, self._norms_sum)
+            self.norms.copy_(self._norms_sum)
         for r in range(self.world):
             K.clip_scale(self.norms[r : r + 1], clip, scale_out=self.scales[r : r + 1], auto=auto, gamma=gamma, n_leaves=n_leaves,
                          widest_leaf=widest_leaf, counters=counters if r == self.rank else None, reset=False)
