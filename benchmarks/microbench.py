@@ -7,7 +7,8 @@ prints one JSON line per shape with the achieved rate and the fraction of the me
 that a profiler capture of the same command ends quickly; ``--once`` runs a single launch per shape after warm-up.
 
 Cases: ``gemm`` (forward / dgrad / wgrad shapes of a decoder layer), ``attention`` (causal GQA forward + backward),
-``dp_step`` (fused noise + AdamW-BC on a parameter shard), ``clip_accumulate``, ``rmsnorm``, ``lce``, ``clip_sum``.
+``dp_step`` (fused noise + AdamW-BC on a parameter shard), ``clip_accumulate``, ``rmsnorm``, ``lce``, ``clip_sum``, ``moe``
+(one mixture-of-experts layer on one GPU).
 """
 from __future__ import annotations
 
@@ -191,7 +192,40 @@ def case_clip_sum(t: _Timer, a) -> None:
     _emit("clip_sum", {"B": B, "elements": n}, us, bytes_=2.0 * B * n * 2 + 4 * n)
 
 
-CASES = {"gemm": case_gemm, "attention": case_attention, "dp_step": case_dp_step, "clip_accumulate": case_clip_accumulate,
+def case_moe(t: _Timer, a) -> None:
+    """One mixture-of-experts layer on one GPU (OLMoE shape): router product, top-k routing and row plan, gather by
+    expert, grouped gate/up GEMM with the SwiGLU epilogue, grouped down GEMM, weighted combine with the residual."""
+    from opake_b200.ops import gemm as G, kernels as K
+    dev = t.device
+    T, d, E, k, I = (1024, 1024, 32, 4, 512) if a.small else (2048, 2048, 64, 8, 1024)
+    x = (torch.randn(T, d, device=dev) * 0.5).to(torch.bfloat16)
+    router = (torch.randn(E, d, device=dev) * 0.05).to(torch.bfloat16)
+    wgu = (torch.randn(E, 2 * I, d, device=dev) * 0.03).to(torch.bfloat16)
+    wd = (torch.randn(E, d, I, device=dev) * 0.03).to(torch.bfloat16)
+    plan = K.MoePlan(T, E, k, dev)
+    e = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)  # noqa: E731
+    rl, xs, gu, act, ye, out = e(T, E), e(plan.R, d), e(plan.R, 2 * I), e(plan.R, I), e(plan.R, d), e(T, d)
+
+    def route():
+        G.gemm(x, router, out=rl)
+        K.moe_route(rl, plan, False)
+
+    def experts():
+        K.moe_gather(x, plan, xs)
+        G.gemm(xs, wgu, out=gu, epilogue=G.EPI_SWIGLU, act=act, tile_group=plan.tile_group)
+        G.gemm(act, wd, out=ye, tile_group=plan.tile_group)
+        K.moe_combine(ye, plan, out, wts=plan.wts, residual=x)
+
+    route()
+    us_r = t.run(route, a.iters)
+    _emit("moe", {"kind": "router + top-k + row plan", "T": T, "E": E, "k": k}, us_r, flops=2.0 * T * d * E)
+    us_e = t.run(experts, a.iters)
+    # useful work: every token visits k experts, each 3 * I * d multiply-adds (gate, up, down)
+    _emit("moe", {"kind": "gather + grouped GEMMs (SwiGLU epilogue) + combine", "T": T, "d": d, "E": E, "k": k, "ffn": I, "rows": plan.R},
+          us_e, flops=2.0 * T * k * 3 * I * d)
+
+
+CASES = {"moe": case_moe, "gemm": case_gemm, "attention": case_attention, "dp_step": case_dp_step, "clip_accumulate": case_clip_accumulate,
          "rmsnorm": case_rmsnorm, "lce": case_lce, "clip_sum": case_clip_sum}
 
 

@@ -171,22 +171,37 @@ __global__ void __launch_bounds__(RMS_BWD_NT) rmsnorm_bwd_kernel(const __nv_bflo
       for (int j = 0; j < 8; ++j) wv[it][j] += w_off;
     }
   }
-  for (long long row = blockIdx.x; row < T; row += gridDim.x) {
+  // The loads of the NEXT row are issued before the block-wide reduction of the current one, so every thread keeps two
+  // rows of 16-byte loads in flight across the two barriers of the reduction (the kernel is bound by memory latency:
+  // one row per CTA and iteration leaves the memory system half idle).
+  bf16x8 g_raw[ITERS], x_raw[ITERS];
+  float rs_next = 0.f;
+  auto fetch = [&](long long row) {
     const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + row * ld_dy);
     const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * ldx);
-    const float rs = rstd[row];
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int v = threadIdx.x + it * RMS_BWD_NT;
+      if (v < nv) { g_raw[it] = dyr[v]; x_raw[it] = xr[v]; }
+    }
+    rs_next = rstd[row];
+  };
+  if (blockIdx.x < T) fetch(blockIdx.x);
+  for (long long row = blockIdx.x; row < T; row += gridDim.x) {
+    const float rs = rs_next;
     float g[ITERS][8], xv[ITERS][8];
     float dot = 0.f;
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
       const int v = threadIdx.x + it * RMS_BWD_NT;
       if (v < nv) {
-        unpack8(dyr[v], g[it]);
-        unpack8(xr[v], xv[it]);
+        unpack8(g_raw[it], g[it]);
+        unpack8(x_raw[it], xv[it]);
 #pragma unroll
         for (int j = 0; j < 8; ++j) dot += g[it][j] * wv[it][j] * xv[it][j];
       }
     }
+    if (row + gridDim.x < T) fetch(row + gridDim.x);
     const float mean_dot = block_sum<RMS_BWD_NT>(dot, sh) * rs / (float)D;
     const bf16x8* drr = dres ? reinterpret_cast<const bf16x8*>(dres + row * ld_dx) : nullptr;
     bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + row * ld_dx);
