@@ -231,6 +231,59 @@ inline std::vector<double> cholesky(std::vector<double> A, int64_t b) {
   return L;
 }
 
+// Cholesky factor of a CYCLICALLY banded Gram matrix (packages/opake-accounting/src/amplification/balls_in_bins/
+// cyclic_cholesky.rs). The Gram over bins of a Toeplitz strategy is banded modulo b: G_ij is non-zero only for
+// min(|i-j|, b-|i-j|) <= p, corner blocks included. Eliminating a column couples the band rows below it and the p
+// corner rows at the bottom, so L keeps the band in rows 0 .. b-p-1 (columns i-p .. i) and fills the last p rows
+// densely. `lo[i]` is the first possibly non-zero column of row i; factorisation costs O(b p^2) and a product L z
+// costs O(b p) instead of O(b^3) / O(b^2). A matrix without such structure (2p + 1 >= b) gets lo = 0: the dense factor.
+struct CyclicCholesky {
+  int64_t b = 0, p = 0;
+  std::vector<double> L;        // row-major [b][b]; entries left of lo[i] are exactly zero
+  std::vector<int64_t> lo;
+
+  static int64_t cyclic_bandwidth(const std::vector<double>& G, int64_t b) {
+    double dmax = 0.0;
+    for (int64_t i = 0; i < b; ++i) dmax = std::max(dmax, std::fabs(G[(size_t)(i * b + i)]));
+    const double tol = 1e-14 * dmax;
+    int64_t p = 0;
+    for (int64_t i = 0; i < b; ++i)
+      for (int64_t j = 0; j < i; ++j)
+        if (std::fabs(G[(size_t)(i * b + j)]) > tol) p = std::max(p, std::min(i - j, b - (i - j)));
+    return p;
+  }
+
+  static CyclicCholesky factor(const std::vector<double>& G, int64_t b) {
+    CyclicCholesky c;
+    c.b = b;
+    c.p = cyclic_bandwidth(G, b);
+    const bool dense = 2 * c.p + 1 >= b;
+    const int64_t n_band = dense ? 0 : b - c.p;
+    c.lo.assign((size_t)b, 0);
+    for (int64_t i = 0; i < n_band; ++i) c.lo[(size_t)i] = std::max<int64_t>(0, i - c.p);
+    c.L.assign((size_t)(b * b), 0.0);
+    for (int64_t i = 0; i < b; ++i)
+      for (int64_t j = c.lo[(size_t)i]; j <= i; ++j) {
+        double s = G[(size_t)(i * b + j)];
+        for (int64_t t = std::max(c.lo[(size_t)i], c.lo[(size_t)j]); t < j; ++t) s -= c.L[(size_t)(i * b + t)] * c.L[(size_t)(j * b + t)];
+        if (i == j) c.L[(size_t)(i * b + i)] = std::sqrt(std::max(s, 1e-14));
+        else c.L[(size_t)(i * b + j)] = s / c.L[(size_t)(j * b + j)];
+      }
+    return c;
+  }
+
+  // y = scale * L z
+  template <class Z>
+  void apply(const Z* z, double scale, double* y) const {
+    for (int64_t r = 0; r < b; ++r) {
+      double s = 0.0;
+      const double* row = &L[(size_t)(r * b)];
+      for (int64_t t = lo[(size_t)r]; t <= r; ++t) s += row[t] * (double)z[t];
+      y[r] = scale * s;
+    }
+  }
+};
+
 // Empirical PLD from privacy-loss samples of both directions (pessimistic rounding up to the grid).
 inline Pld pld_from_loss_samples(const std::vector<double>& rem, const std::vector<double>& add, const Config& cfg) {
   auto build = [&](const std::vector<double>& v, double h) {
@@ -292,7 +345,7 @@ inline Pld bnb_pld_from_corpus(const BnbCorpus& c, const std::vector<double>& G,
   const int64_t b = c.b;
   if ((int64_t)G.size() != b * b) throw std::invalid_argument("gram must have num_bins^2 entries");
   if (!(sigma > 0)) throw std::invalid_argument("sigma must be positive");
-  const auto L = cholesky(G, b);
+  const CyclicCholesky chol = CyclicCholesky::factor(G, b);
   const size_t n = c.bin.size();
   std::vector<double> rem(n), add(n);
   const double s2 = sigma * sigma, logb = std::log((double)b);
@@ -301,11 +354,7 @@ inline Pld bnb_pld_from_corpus(const BnbCorpus& c, const std::vector<double>& G,
     std::vector<double> y((size_t)b);
     for (size_t i = a; i < e; ++i) {
       // y_i = <m_i, noise> = sigma * (L z)_i
-      for (int64_t r = 0; r < b; ++r) {
-        double s = 0.0;
-        for (int64_t t = 0; t <= r; ++t) s += L[(size_t)(r * b + t)] * (double)c.z[i * (size_t)b + (size_t)t];
-        y[(size_t)r] = sigma * s;
-      }
+      chol.apply(&c.z[i * (size_t)b], sigma, y.data());
       const int64_t J = c.bin[i];
       // loss(x) = log mean_i exp((<m_i, x> - G_ii / 2) / s2); under P: <m_i, x> = G_iJ + y_i, under Q: y_i
       double lp = -kInf, lq = -kInf;

@@ -242,5 +242,11 @@ PYBIND11_MODULE(_opake_accounting, m) {
         }, py::arg("strategy_coef"), py::arg("n_steps"), py::arg("min_sep") = 1, py::arg("max_participations") = py::none(),
         py::arg("normalized") = true);
   m.def("bisr_strategy_coefficients", &bisr_strategy_coefficients, py::arg("coefficients"), py::arg("n"));
+  // Factor of a cyclically banded Gram matrix as the balls-in-bins sampler uses it: (cyclic bandwidth, row-major L).
+  m.def("cyclic_banded_cholesky", [](const std::vector<double>& gram, int64_t b) {
+          if (b < 1 || (int64_t)gram.size() != b * b) throw std::invalid_argument("gram must have num_bins^2 entries");
+          const CyclicCholesky c = CyclicCholesky::factor(gram, b);
+          return py::make_tuple(c.p, c.L);
+        }, py::arg("gram"), py::arg("num_bins"));
   m.def("adaclip_sensitivity", &adaclip_sensitivity, py::arg("noise_multiplier"), py::arg("quantile_noise_std"), py::arg("num_groups") = 1);
 }

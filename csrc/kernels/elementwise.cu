@@ -104,8 +104,10 @@ __global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __
 }
 
 // One warp per row, the row held in registers (VPL vectors of 8 per lane): one pass over memory, no block barrier.
+// (Without the opaque barrier below the compiler keeps the row UNPACKED across the reduction, 255 registers per thread at
+// 16 vectors per lane: one CTA per SM and 12 % of the warp slots in use. Packed, the row is 64 registers.)
 template <int VPL>
-__global__ void __launch_bounds__(256) rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(256, VPL >= 16 ? 2 : 4) rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x,
                                                                const __nv_bfloat16* __restrict__ w,
                                                                __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int T,
                                                                float eps, float w_off, long long ldx, long long ldy) {
@@ -131,6 +133,12 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_warp_kernel(const __nv_bfloat
   if (lane == 0 && rstd) rstd[row] = rs;
   const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
   bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * ldy);
+  // the packed words pass through an empty asm: the floats computed for the reduction cannot be reused below
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) asm volatile("" : "+r"(*reinterpret_cast<uint32_t*>(&v[i].h[q])));
+  }
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     float f[8], g[8];
@@ -171,38 +179,35 @@ __global__ void __launch_bounds__(RMS_BWD_NT) rmsnorm_bwd_kernel(const __nv_bflo
       for (int j = 0; j < 8; ++j) wv[it][j] += w_off;
     }
   }
-  // The loads of the NEXT row are issued before the block-wide reduction of the current one, so every thread keeps two
-  // rows of 16-byte loads in flight across the two barriers of the reduction (the kernel is bound by memory latency:
-  // one row per CTA and iteration leaves the memory system half idle).
-  bf16x8 g_raw[ITERS], x_raw[ITERS];
-  float rs_next = 0.f;
-  auto fetch = [&](long long row) {
+  int par = 0;
+  for (long long row = blockIdx.x; row < T; row += gridDim.x) {
     const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + row * ld_dy);
     const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * ldx);
-#pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-      const int v = threadIdx.x + it * RMS_BWD_NT;
-      if (v < nv) { g_raw[it] = dyr[v]; x_raw[it] = xr[v]; }
-    }
-    rs_next = rstd[row];
-  };
-  if (blockIdx.x < T) fetch(blockIdx.x);
-  for (long long row = blockIdx.x; row < T; row += gridDim.x) {
-    const float rs = rs_next;
+    const float rs = rstd[row];
     float g[ITERS][8], xv[ITERS][8];
     float dot = 0.f;
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
       const int v = threadIdx.x + it * RMS_BWD_NT;
       if (v < nv) {
-        unpack8(g_raw[it], g[it]);
-        unpack8(x_raw[it], xv[it]);
+        unpack8(dyr[v], g[it]);
+        unpack8(xr[v], xv[it]);
 #pragma unroll
         for (int j = 0; j < 8; ++j) dot += g[it][j] * wv[it][j] * xv[it][j];
       }
     }
-    if (row + gridDim.x < T) fetch(row + gridDim.x);
-    const float mean_dot = block_sum<RMS_BWD_NT>(dot, sh) * rs / (float)D;
+    // one barrier per row: warp sums go to one of two alternating sets of slots and every thread adds the sixteen
+    // partials itself (a set is rewritten two rows later, after the barrier of the row in between)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    float* slots = sh + par * (RMS_BWD_NT / 32);
+    par ^= 1;
+    if ((threadIdx.x & 31) == 0) slots[threadIdx.x >> 5] = dot;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int wq = 0; wq < RMS_BWD_NT / 32; ++wq) tot += slots[wq];
+    const float mean_dot = tot * rs / (float)D;
     const bf16x8* drr = dres ? reinterpret_cast<const bf16x8*>(dres + row * ld_dx) : nullptr;
     bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + row * ld_dx);
 #pragma unroll

@@ -88,15 +88,9 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const opk::GemmParams& 
 }
 
 // Pair mode: eligible products (256-wide column tiles, no grouped tables, at least 256 rows) run on the two-CTA
-// kernel. -1 = not decided yet (environment variable OPK_GEMM_PAIR, default on).
-int g_pair_mode = -1;
-bool pair_mode() {
-  if (g_pair_mode < 0) {
-    const char* e = getenv("OPK_GEMM_PAIR");
-    g_pair_mode = (e && e[0] == '0') ? 0 : 1;
-  }
-  return g_pair_mode == 1;
-}
+// kernel. On by default; opk_gemm_set_pair_mode selects the single-CTA kernel (the tests run both).
+int g_pair_mode = 1;
+bool pair_mode() { return g_pair_mode == 1; }
 
 template <bool A_MN, bool B_MN, int EPI, bool STAGE = false>
 int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const opk::GemmParams& p, int max_ctas, cudaStream_t st) {

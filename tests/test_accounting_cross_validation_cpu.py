@@ -243,3 +243,43 @@ def test_learning_rate_weighted_gram_functions_raise_like_the_reference():
         N.bisr_gram_matrix_lr([1.0, 0.5], 0.0, 8, 2, None, True, [1.0] * 8)
     with pytest.raises(ValueError):
         N.lambda_cgd_gram_matrix_lr(0.5, 0.0, 8, 2, None, True, [1.0] * 8)
+
+
+def test_cyclic_banded_cholesky_matches_the_dense_factor():
+    """The balls-in-bins sampler factors the Gram matrix over bins, which is banded modulo the number of bins (corner
+    blocks included). The structured factor keeps the band plus dense trailing rows; it must reproduce the dense
+    Cholesky factor, detect the CYCLIC (not the linear) bandwidth, and fall back to dense for unstructured input."""
+    import numpy as np
+
+    from opake_b200.accounting._native import native
+
+    N = native()
+
+    def cyclic_gram(b, width):
+        # G = C^T C for a circulant C with `width` sub-diagonals (wrapping around): cyclic bandwidth `width`, and
+        # positive definite because C is strictly diagonally dominant
+        col = np.zeros(b)
+        col[0] = 3.0
+        col[1 : width + 1] = 0.9 ** np.arange(1, width + 1)
+        C = np.stack([np.roll(col, j) for j in range(b)], axis=1)
+        return C.T @ C
+
+    for b, width in ((24, 3), (40, 5), (17, 2)):
+        G = cyclic_gram(b, width)
+        assert np.linalg.eigvalsh(G).min() > 0
+        p, L = N.cyclic_banded_cholesky(G.reshape(-1).tolist(), b)
+        L = np.asarray(L).reshape(b, b)
+        assert p == width                                                   # the corner entries count with distance b - |i-j|
+        assert np.allclose(L, np.linalg.cholesky(G), atol=1e-10)
+        assert np.allclose(L @ L.T, G, atol=1e-10)
+        # structure: band rows hold nothing left of the band, the last `width` rows are dense
+        for i in range(b - width):
+            assert np.all(L[i, : max(0, i - width)] == 0.0)
+        assert np.abs(L[b - 1, :width]).max() > 0                           # the corner block fills in
+    rng = np.random.default_rng(0)
+    A = rng.normal(size=(9, 9))
+    G = A @ A.T + 9 * np.eye(9)
+    p, L = N.cyclic_banded_cholesky(G.reshape(-1).tolist(), 9)
+    assert p == 4 and np.allclose(np.asarray(L).reshape(9, 9), np.linalg.cholesky(G), atol=1e-10)
+    with pytest.raises(ValueError):
+        N.cyclic_banded_cholesky([1.0, 0.0, 0.0], 2)
