@@ -101,7 +101,7 @@ def _ep_train(rank: int, world: int, dev: torch.device, a) -> None:
     # plain SGD: the update is linear in the summed gradient, so differences in summation order stay small (Adam's
     # normalised update flips sign on near-zero gradient entries)
     ecfg = EngineConfig(logical_batch=a.batch, noise_multiplier=0.0, clip_norm=0.5, lr=20.0, optimizer="sgd", weight_decay=0.0,
-                        seed=5, use_cuda_graph=False, accumulate_group=2, expert_parallel=True, seq_len=T)
+                        seed=5, use_cuda_graph=a.graph, accumulate_group=2, expert_parallel=True, seq_len=T)
     eng = ShardedDPEngine(cfg, ecfg, dev)
     def snapshot():
         views = eng.layout.views(eng.params)

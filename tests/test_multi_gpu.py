@@ -80,14 +80,17 @@ def test_two_ranks_match_one_rank_toeplitz(tmp_path):
     assert diff <= 2e-2 * one["params"].abs().max().item(), diff
 
 
-def test_expert_parallel_training_matches_local_experts(tmp_path):
+@pytest.mark.parametrize("graph", [False, True])
+def test_expert_parallel_training_matches_local_experts(tmp_path, graph):
     """Two ranks with sharded experts (tokens exchanged over NVLink, per-example norms combined across ranks, clipped
-    expert gradients formed in a second pass) train to the same losses and weights as one rank holding every expert."""
+    expert gradients formed in a second pass) train to the same losses and weights as one rank holding every expert.
+    ``graph``: every example replayed from a CUDA graph on the two-rank side (exchange epochs relative to device-side
+    counters); the one-rank side stays eager, so the two implementations are compared, not two replays."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     extra = ("--ep-train", "--steps", "3", "--batch", "8")
     one = _run(1, str(tmp_path / "w1.pt"), extra)
-    two = _run(2, str(tmp_path / "w2.pt"), extra)
+    two = _run(2, str(tmp_path / "w2.pt"), extra + (("--graph",) if graph else ()))
     assert one["clipped"] > 0 and two["clipped"] == one["clipped"]          # the clip factors were exercised
     assert one["losses"] == pytest.approx(two["losses"], rel=3e-3)
     for name in ("routers", "wgu", "wd", "wqkv"):
