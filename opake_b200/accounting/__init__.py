@@ -1,5 +1,5 @@
 """Privacy accounting: process algebra, budgets, calibration, and the native PLD engine (torch-free)."""
-from . import budgets, calibration, codec, core, discretization  # noqa: F401
+from . import amplification, budgets, calibration, codec, core, discretization  # noqa: F401
 from .accountant import Accountant  # noqa: F401
 from .budgets import (advantage_budget, beta_budget, delta_budget, epsilon_budget, register_budget_serializer,  # noqa: F401
                       risk_budget)

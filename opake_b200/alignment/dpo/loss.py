@@ -13,7 +13,10 @@ import torch.nn.functional as F
 from ...base.exceptions import ConfigurationError
 from ..logprob import _compute_dtype
 
+from ..logprob import fused_sequence_logp, sequence_logp  # noqa: E402,F401  (same names as the reference's dpo.loss)
+
 __all__ = [
+    "sequence_logp", "fused_sequence_logp",
     "sigmoid_loss", "hinge_loss", "robust_loss", "ipo_loss", "discopop_loss", "chosen_nll_loss", "apo_zero_loss",
     "apo_down_loss", "exo_loss", "nca_loss", "bco_loss", "sppo_loss", "simpo_loss", "odds_ratio_loss",
     "f_divergence_remap", "f_divergence_logits", "mpo_combine", "wpo_weights", "ld_dpo_split", "LOSS_HEADS",

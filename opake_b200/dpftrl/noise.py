@@ -245,4 +245,7 @@ def _register():
 
 _register()
 
+from .strategies import (band_mf_strategy, bisr_strategy, blt_strategy, bsr_strategy, identity_strategy,  # noqa: E402,F401
+                         lambda_cgd_strategy)
+
 __all__ = ["MFNoiseState", "mf_gaussian_noise", "MF_STREAM_FOLD", "sync_mf_noise_state", "iid_normal_like"]

@@ -58,6 +58,14 @@ def apply_transformers_model_patches(model, *, performance: bool = True, compat:
     (conditional ``loss_only`` forward); ``kernels`` (defaults to ``performance``) -> ``rms_norm``, ``activation``,
     ``rope``, ``cross_entropy`` (the model's ``loss_function``)."""
     from .transformers import components as C
+    from .transformers.family import family_name, get_family_apply_fn
+
+    user_apply = get_family_apply_fn(family_name(model))
+    if user_apply is not None:          # a family registered with an apply function handles itself
+        out = user_apply(model, performance=performance, compat=compat, kernels=kernels,
+                         fused_linear_cross_entropy=performance if fused_linear_cross_entropy is None else fused_linear_cross_entropy,
+                         **cfg)
+        return out if isinstance(out, dict) else {"family": family_name(model)}
     spec = family_of(model)
     kernels = performance if kernels is None else kernels
     report = {"family": spec.model_type if spec else None, "norms": 0, "mlps": 0, "dropouts": 0, "attention": None, "kv_cache": 0,

@@ -8,10 +8,14 @@ from .training_arguments import TrainingArguments
 
 __all__ = ["DPTrainer", "TrainOutput", "TrainingArguments", "DPTrainerState", "TrainerControl", "TrainerCallback",
            "PrinterCallback", "JsonlLoggerCallback", "TensorBoardCallback", "WandbCallback", "BestModelSaveCallback",
-           "EarlyStoppingCallback", "SFTTrainer", "SFTConfig", "DPOTrainer", "DPOConfig"]
+           "EarlyStoppingCallback", "SFTTrainer", "SFTConfig", "DPOTrainer", "DPOConfig", "trl"]
 
 
 def __getattr__(name):
+    if name == "trl":
+        import importlib
+
+        return importlib.import_module(".trl", __name__)
     if name in ("SFTTrainer", "SFTConfig"):
         from .trl import sft_trainer as m
         return getattr(m, name)

@@ -244,3 +244,102 @@ def test_runtime_patches_collators_grouped_gemm_and_dropout():
     model.extra = drop
     assert disable_dropout(model) >= 2
     assert drop.p == 0.0 and model.model.layers[0].self_attn.attention_dropout == 0.0 and model.config.attention_dropout == 0.0
+
+
+def test_user_registered_family_goes_through_the_factories():
+    """A model type that is not built in: module-level patches from ``make_apply_family_patches``, per-role forwards by
+    kind from ``make_apply_model_patches`` (activation, RMSNorm, fused add + RMSNorm decoder layer, loss), routed by
+    ``register_family``; losses and per-example gradients agree with the stock model."""
+    from opake_b200 import patches
+    from opake_b200.base.exceptions import ConfigurationError
+    from opake_b200.patches import transformers as PT
+
+    class MyConfig(transformers.LlamaConfig):
+        model_type = "my_llama"
+
+    torch.manual_seed(5)
+    model = transformers.LlamaForCausalLM(MyConfig(vocab_size=97, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                                                   num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64,
+                                                   tie_word_embeddings=False)).eval()
+    assert PT.family_name(model) == "my_llama" and "my_llama" not in PT.supported_families()
+    stock = copy.deepcopy(model)
+    seen = []
+
+    def my_act(original):                                    # a custom kind: same math, observable
+        def forward(self, x):
+            seen.append("act")
+            return self.down_proj(torch.nn.functional.silu(self.gate_proj(x)) * self.up_proj(x))
+        return forward
+
+    PT.register_activation_kind("my_swiglu", my_act)
+    path = "transformers.models.llama.modeling_llama"
+    fam = PT.make_apply_family_patches(family="my_llama", module_path=path)
+    with pytest.raises(ConfigurationError, match="unknown kind"):
+        PT.make_apply_model_patches(family="my_llama", family_apply=fam, module_path=path, classes={}, activation_kind="nope")
+    apply = PT.make_apply_model_patches(family="my_llama", family_apply=fam, module_path=path,
+                                        classes={"mlp": "LlamaMLP", "rms_norm": "LlamaRMSNorm", "decoder_layer": "LlamaDecoderLayer",
+                                                 "causal_lm": "LlamaForCausalLM"},
+                                        activation_kind="my_swiglu", rms_norm_kind="llama", fused_add_rms_kind="llama")
+    PT.register_family("my_llama", apply)
+    assert "my_llama" in PT.supported_families() and apply.__name__ == "apply_my_llama_patches"
+    rep = patches.apply_model_patches(model)
+    assert rep["family"] == "my_llama" and rep["mlps"] == 2 and rep["norms"] == 5 and rep["decoder_layers"] == 2
+    assert rep["loss_function"] == 1
+    ids = torch.randint(1, 97, (3, 10))
+    with torch.no_grad():
+        want = torch.stack([stock(ids[b : b + 1], labels=ids[b : b + 1]).loss for b in range(3)])
+        got = torch.stack([model(ids[b : b + 1], labels=ids[b : b + 1]).loss for b in range(3)])
+    assert torch.allclose(got, want, rtol=1e-4, atol=1e-5) and seen
+    params = {k: v.detach() for k, v in model.named_parameters()}
+    loss = lambda p, x: functional_call(model, p, (x,), {"labels": x}).loss  # noqa: E731
+    g_v = vmap(grad(loss), in_dims=(None, 0))(params, ids)
+    sparams = {k: v.detach() for k, v in stock.named_parameters()}
+    for b in range(3):
+        g_1 = grad(lambda p: functional_call(stock, p, (ids[b : b + 1],), {"labels": ids[b : b + 1]}).loss)(sparams)
+        for k in g_1:
+            assert torch.allclose(g_v[k][b], g_1[k], rtol=5e-4, atol=5e-6), (k, b)
+    # second application: nothing new
+    rep2 = patches.apply_model_patches(model)
+    assert rep2["mlps"] == 0 and rep2["norms"] == 0 and rep2["decoder_layers"] == 0
+
+
+def test_public_namespaces_match_the_reference_layout():
+    """``from opake import random, scheduling, ...`` style imports resolve under this package's name."""
+    import importlib
+
+    surface = {
+        "exceptions": "ConfigurationError OpakeError PrivacyBudgetError", "serialization": "state_dict from_state_dict register_serializer",
+        "random": "key fold_in split generator_from_key", "scheduling": "cosine_schedule with_warmup warmup_stable_decay",
+        "functional": "make_functional with_batch_dim empty_collate", "distributed": "sum_gradients_ local_shard sync is_main_process",
+        "profiling": "step_perf PerfTracker get_memory_stats", "device": "device_capabilities fused_kernels_available",
+        "accounting": "amplification calibration composition mechanisms Accountant calibrate epsilon_budget",
+        "dpftrl": "clipping clipped_grad BallsInBinsSampler blt_strategy mf_gaussian_noise", "dpftrl.clipping": "clipped_grad per_group",
+        "dpftrl.noise": "band_mf_strategy mf_gaussian_noise", "dpsgd": "clipped_grad gaussian_noise PoissonSampler",
+        "alignment.dpo.loss": "sequence_logp fused_sequence_logp sigmoid_loss", "patches.torch": "apply_checkpoint_patch is_checkpoint_patched",
+        "patches.kernels": "opake_rope opake_slow_rope opake_lora_qkv opake_geglu_exact ACTIVATION_SWIGLU opake_cross_entropy_loss",
+        "patches.transformers": "register_family make_apply_model_patches supported_families family_name",
+        "patches.transformers.runtime": "apply_collator_patches apply_grouped_mm_patches apply_masking_patches",
+        "transformers": "DPTrainer TrainingArguments trl", "transformers.trl": "SFTTrainer DPOTrainer SFTConfig DPOConfig",
+    }
+    for mod, names in surface.items():
+        m = importlib.import_module("opake_b200." + mod)
+        assert not [n for n in names.split() if not hasattr(m, n)], mod
+
+
+def test_checkpoint_patch_routes_only_inside_transforms():
+    import torch.utils.checkpoint as tuc
+
+    from opake_b200.patches.torch import apply_checkpoint_patch, is_checkpoint_patched
+
+    apply_checkpoint_patch()
+    assert is_checkpoint_patched() and apply_checkpoint_patch() is False
+    lin = torch.nn.Linear(6, 6)
+    f = lambda x: torch.tanh(lin(x)).pow(2).sum()  # noqa: E731
+    x = torch.randn(4, 6)
+    # outside a transform: the stock checkpoint
+    y = tuc.checkpoint(lambda t: torch.tanh(lin(t)), x[0].clone().requires_grad_(), use_reentrant=False)
+    assert y.requires_grad
+    # inside vmap(grad): the functional recomputation
+    g_ck = vmap(grad(lambda t: tuc.checkpoint(lambda u: torch.tanh(lin(u)), t, use_reentrant=False).pow(2).sum()))(x)
+    g_pl = vmap(grad(f))(x)
+    assert torch.allclose(g_ck, g_pl, atol=1e-6)
