@@ -64,7 +64,7 @@ MODEL_SHAPES = {
 def run(args) -> None:
     pkgs = _paths()
     if len(pkgs) < 5:
-        _say({"impl": "reference", "unavailable": "baseline/_ref holds no installed reference packages (run the pip install recorded in DESIGN.md)"})
+        _say({"impl": "reference", "unavailable": "baseline/_ref holds no installed reference packages (install each reference sub-project with pip --no-deps --target baseline/_ref/opake-<name>)"})
         return
     sys.path[:0] = pkgs
     try:
