@@ -891,4 +891,192 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, 1);
 }
 
+// ------------------------------------------------------------------------------------------------ dQ, 128-key tiles
+// Same contract as attn_dq_kernel with key tiles of 128 instead of sub-tiles of 64: per tile the three products are
+// 8 + 8 + 8 `tcgen05.mma` of 128x128x16 instead of 2 x (8 + 8 + 4) of 128x64x16 / 128x128x16, and every instruction
+// with M = 128 costs about 45 cycles on top of its arithmetic whatever its width, so the wider tile nearly halves the
+// tensor-pipe time per key. S and dP are single-buffered in TMEM (128 + 128 columns, dQ in another 128): the softmax
+// warps release them as soon as the second half of their columns is in registers, i.e. after about half of their
+// work on the tile, and the score products of the next tile run under the rest.
+// Shared memory (head_dim 128: 224 KB): K(i) stays resident until dQ(i) has completed, i.e. across the score products of
+// tile i+1, and its refill needs a TMA round trip on top, so K has THREE stages; V(i) is dead as soon as dP(i) has
+// completed and has ONE stage: V(i+1) is requested then and is first needed a whole tile later (S(i+1) goes first).
+template <int HD>
+struct Dq128Smem {
+  static constexpr int NS = 3;                            // K ring depth (V: one stage)
+  static constexpr int Q_TILE = 128 * HD * 2;
+  static constexpr int KV_TILE = 128 * HD * 2;
+  static constexpr int Q_OFF = 0;
+  static constexpr int DO_OFF = Q_TILE;
+  static constexpr int K_OFF = 2 * Q_TILE;                // NS stages
+  static constexpr int V_OFF = K_OFF + NS * KV_TILE;      // one stage
+  static constexpr int DS_OFF = V_OFF + KV_TILE;          // [128 q][128 keys] bf16 as two 64-key chunks of 16 KB
+  static constexpr int BAR_OFF = DS_OFF + 32768;
+  static constexpr int USED = BAR_OFF + 256;
+  static constexpr int BYTES = USED + 1024;
+  static_assert(BYTES <= 232448, "dQ (128-key tiles) shared-memory layout does not fit");
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
+                  const __grid_constant__ CUtensorMap tm_do, const AttnParams p) {
+  using SM = Dq128Smem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if ((int)(smem - smem_raw) + SM::USED > SM::BYTES) {   // uniform over the CTA; nothing has been set up yet
+    if (threadIdx.x == 0 && p.err) atomicExch(p.err, 2);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
+  constexpr int NS = SM::NS;
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;             // [NS]
+  uint64_t* k_empty = k_full + NS;         // [NS]
+  uint64_t* v_full = k_empty + NS;
+  uint64_t* v_empty = v_full + 1;
+  uint64_t* s_full = v_empty + 1;
+  uint64_t* s_free = s_full + 1;
+  uint64_t* ds_full = s_free + 1;
+  uint64_t* ds_free = ds_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ds_free + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = (p.T + 127) / 128;
+  const int h = blockIdx.x % p.H;
+  const int qt = n_qt - 1 - (int)(blockIdx.x / p.H);     // heavy (late) query tiles first
+  const int g = h / (p.H / p.KV);
+  const int n_it = qt + 1;                               // key tiles 0 .. qt; the last one is the causal diagonal
+  const int q_col = h * HD, k_col = (p.H + g) * HD, v_col = (p.H + p.KV + g) * HD;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < NS; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    mbar_init(s_full, 1);
+    mbar_init(s_free, kSoftmaxWarps);
+    mbar_init(ds_full, kSoftmaxWarps);
+    mbar_init(ds_free, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t S_COL = 0, DP_COL = 128, DQ_COL = 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_kv); tma_prefetch_desc(&tm_do);
+      mbar_expect_tx(q_full, 2 * SM::Q_TILE);
+      for (int c = 0; c < HD / 64; ++c) {
+        tma_load_2d(smem + SM::Q_OFF + c * 16384, &tm_q, q_full, q_col + c * 64, qt * 128);
+        tma_load_2d(smem + SM::DO_OFF + c * 16384, &tm_do, q_full, q_col + c * 64, qt * 128);
+      }
+      for (int i = 0; i < n_it; ++i) {
+        const int s = i % NS;
+        if (!mbar_wait(&k_empty[s], (uint32_t)((i / NS) & 1) ^ 1u, abort_flag)) break;
+        mbar_expect_tx(&k_full[s], SM::KV_TILE);
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_2d(smem + SM::K_OFF + s * SM::KV_TILE + c * 16384, &tm_kv, &k_full[s], k_col + c * 64, i * 128);
+        if (!mbar_wait(v_empty, (uint32_t)(i & 1) ^ 1u, abort_flag)) break;
+        mbar_expect_tx(v_full, SM::KV_TILE);
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_2d(smem + SM::V_OFF + c * 16384, &tm_kv, v_full, v_col + c * 64, i * 128);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t q_s = smem_u32(smem + SM::Q_OFF), do_s = smem_u32(smem + SM::DO_OFF);
+      const uint32_t ds_s = smem_u32(smem + SM::DS_OFF);
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      auto scores = [&](int i) -> bool {
+        const int sk = i % NS;
+        if (!mbar_wait(&k_full[sk], (i / NS) & 1, abort_flag)) return false;
+        if (!mbar_wait(s_free, (uint32_t)(i & 1) ^ 1u, abort_flag)) return false;   // tile i-1's scores are in registers
+        tc_fence_after();
+        issue_product<false, false>(tmem + S_COL, q_s, 128, smem_u32(smem + SM::K_OFF + sk * SM::KV_TILE), 128, 128, HD, false);
+        if (!mbar_wait(v_full, i & 1, abort_flag)) return false;
+        tc_fence_after();
+        issue_product<false, false>(tmem + DP_COL, do_s, 128, smem_u32(smem + SM::V_OFF), 128, 128, HD, false);
+        umma_commit(v_empty);        // V(i) is dead once dP(i) has completed
+        umma_commit(s_full);
+        return true;
+      };
+      if (ok) ok = scores(0);
+      for (int i = 0; i < n_it && ok; ++i) {
+        if (i + 1 < n_it) ok = scores(i + 1);
+        if (!ok) break;
+        const int sk = i % NS;
+        if (!mbar_wait(ds_full, i & 1, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t k_s = smem_u32(smem + SM::K_OFF + sk * SM::KV_TILE);
+        // dQ[q x HD] += dS[q x 128 keys] * K[128 keys x HD]   (B rows = keys: MN-major)
+        issue_product<false, true>(tmem + DQ_COL, ds_s, 128, k_s, 128, HD, 128, i > 0);
+        umma_commit(&k_empty[sk]);
+        umma_commit(ds_free);
+      }
+    }
+    __syncwarp();
+  } else {
+    // 8 softmax warps: (warp & 3) picks the 32 query rows (TMEM lanes), `half` 64 of the 128 keys of the tile
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int r = quad * 32 + lane;
+    const int qrow = qt * 128 + r;
+    const int c0 = half * 64;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    const float c2 = p.scale * 1.4426950408889634f;
+    const bool qvalid = qrow < p.T;
+    const float nl_r = qvalid ? p.nlse2[(long long)h * p.T64 + qrow] : -INFINITY;   // invalid rows give P = 0
+    const float d_r = qvalid ? p.dsum[(long long)h * p.T64 + qrow] : 0.f;
+    uint8_t* ds_chunk = smem + SM::DS_OFF + half * 16384;       // this warp's 64 keys are one 64-column chunk
+    bool ok = true;
+    for (int i = 0; i < n_it && ok; ++i) {
+      if (!warp_wait(s_full, i & 1, abort_flag, lane)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t dw0[16], dw1[16];
+      const bool masked = (i == qt);              // the tile on the causal diagonal
+      {
+        uint32_t sraw[32], draw[32];
+        __syncwarp();
+        tmem_ld32(tmem + lane_base + S_COL + c0, sraw);
+        tmem_ld32(tmem + lane_base + DP_COL + c0, draw);
+        tc_wait_ld();
+        if (masked) dq_chunk<true>(sraw, draw, c2, nl_r, d_r, r - c0, dw0);
+        else dq_chunk<false>(sraw, draw, c2, nl_r, d_r, 0, dw0);
+        __syncwarp();
+        tmem_ld32(tmem + lane_base + S_COL + c0 + 32, sraw);
+        tmem_ld32(tmem + lane_base + DP_COL + c0 + 32, draw);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);        // all of this warp's scores are in registers
+        if (masked) dq_chunk<true>(sraw, draw, c2, nl_r, d_r, r - (c0 + 32), dw1);
+        else dq_chunk<false>(sraw, draw, c2, nl_r, d_r, 0, dw1);
+      }
+      if (i > 0 && !warp_wait(ds_free, (i - 1) & 1, abort_flag, lane)) { ok = false; break; }
+      store_row32(ds_chunk, r, 0, dw0);
+      store_row32(ds_chunk, r, 32, dw1);
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);
+    }
+    if (ok && warp_wait(ds_free, (n_it - 1) & 1, abort_flag, lane)) {
+      tc_fence_after();
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.dqkv) + (long long)qrow * p.ld + q_col + half * (HD / 2);
+      store_acc_rows<HD / 2>(tmem + lane_base + DQ_COL + half * (HD / 2), dst, qvalid, p.scale);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+  if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, 1);
+}
+
 }  // namespace opk
