@@ -49,18 +49,28 @@ extern "C" int opk_attn_fwd(const void* qkv, void* out, float* lse, int T, int H
   if ((ldo % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) return -1;
   CUtensorMap tm;
   if (!map2d(&tm, qkv, (uint64_t)(H + 2 * KV) * hd, (uint64_t)T, (uint64_t)ld, 128)) return -2;
+  CUtensorMap tm_out;   // output rows leave through TMA stores of {64 columns, 32 rows} boxes (head_dim 128)
+  if (!map2d(&tm_out, out, (uint64_t)H * hd, (uint64_t)T, (uint64_t)ldo, 32)) return -2;
   opk::AttnParams p{};
   p.T = T; p.H = H; p.KV = KV; p.hd = hd; p.ld = ld; p.ldo = ldo; p.out = out; p.lse = lse; p.scale = scale; p.err = err;
-  const int grid = ((T + 127) / 128) * H;
+  // persistent CTAs, one per SM, each walking its share of the (query tile, head) items
+  static const int n_sm = [] {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 0;
+    return n;
+  }();
+  if (n_sm <= 0) return -3;
+  const int n_items = ((T + 127) / 128) * H;
+  const int grid = n_items < n_sm ? n_items : n_sm;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (hd == 128) {
     static bool once = set_smem(opk::attn_fwd_kernel<128>, opk::FwdSmem<128>::BYTES);
     if (!once) return -3;
-    opk::attn_fwd_kernel<128><<<grid, opk::kAttnThreads, opk::FwdSmem<128>::BYTES, st>>>(tm, p);
+    opk::attn_fwd_kernel<128><<<grid, opk::kFwdThreads, opk::FwdSmem<128>::BYTES, st>>>(tm, tm_out, p);
   } else {
     static bool once = set_smem(opk::attn_fwd_kernel<64>, opk::FwdSmem<64>::BYTES);
     if (!once) return -3;
-    opk::attn_fwd_kernel<64><<<grid, opk::kAttnThreads, opk::FwdSmem<64>::BYTES, st>>>(tm, p);
+    opk::attn_fwd_kernel<64><<<grid, opk::kFwdThreads, opk::FwdSmem<64>::BYTES, st>>>(tm, tm_out, p);
   }
   return (int)cudaGetLastError();
 }

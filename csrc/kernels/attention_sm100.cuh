@@ -3,8 +3,8 @@
 // (H+KV+g)*hd. head_dim is 64 or 128. One example (sequence) per launch; heads are the parallel dimension.
 //
 // Shared design of the three kernels (forward, dK/dV, dQ):
-//   * 192 threads: warp 0 = TMA producer, warp 1 = TMEM owner + UMMA issuer, warps 2..5 = softmax / epilogue with
-//     thread <-> TMEM lane (= row of the 128-row tile),
+//   * 320 threads: warp 0 = TMA producer, warp 1 = TMEM owner + UMMA issuer, warps 2..9 = softmax / epilogue with
+//     thread <-> TMEM lane (= row of the 128-row tile; warps w and w+4 share a lane quarter),
 //   * operand tiles are TMA boxes of 64 columns x R rows with 128-byte swizzle; a tile of hd columns is hd/64 such
 //     boxes. The same bytes serve as a K-major operand (rows = M/N index) or as an MN-major operand (rows = reduction
 //     index), which is what lets P^T / dS^T / K / Q / dO be reused across the five products without transposes,
@@ -45,6 +45,16 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// 2-D TMA store of a {64 cols, rows} box from shared memory (rows outside the tensor are clipped), as one bulk group.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// The calling thread's bulk stores have finished reading shared memory.
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
 // Issue the UMMAs of one product D[128 x N] (+)= A[128 x Kred] * B[N x Kred]^T.
 //   A_MN / B_MN select the operand interpretation; a_rows / b_rows = rows of one 64-column chunk of that operand
 //   (chunk stride in bytes = rows * 128).
@@ -73,21 +83,45 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 // ------------------------------------------------------------------------------------------------ forward
-// CTA = (query tile of 128 rows, head). KV tiles of 128 keys, double-buffered K and V stages, S double-buffered in
-// TMEM. O accumulates in TMEM across KV tiles; the running maximum is updated lazily: rows are rescaled (TMEM
-// load-multiply-store by the softmax warps) only when their maximum grew by more than 2^8, otherwise the stale
-// maximum stays in use (probabilities may then exceed 1 by at most 2^8, harmless in bf16 / fp32). The softmax of a
-// tile is a single pass over registers: 128 fmax, 128 ffma + ex2.approx, 64 packs, 16 shared stores per thread.
+// CTA = (query tile of 128 rows, head). KV tiles of 128 keys, double-buffered K and V stages. The key tiles are split
+// between two softmax groups of four warps: even tiles go to group 0, odd tiles to group 1, and each group has its own
+// score buffer and its own output accumulator in TMEM (4 x 128 columns), its own probability buffer in shared memory
+// and its own running maximum and row sum, as if the keys had been split in two; the two partial results are merged
+// once, in the epilogue. One group's exponentials therefore run under the other group's waits and under the tensor
+// core's work on the other buffers. The running maximum is updated lazily: rows are rescaled (TMEM
+// load-multiply-store) only when their maximum grew by more than 2^8, otherwise the stale maximum stays in use
+// (probabilities may then exceed 1 by at most 2^8, harmless in bf16 / fp32). A thread owns one row and all 128 keys of
+// a tile: pass 1 reads the scores from TMEM for the maximum, pass 2 reads them again 32 at a time for ffma +
+// ex2.approx, pack and the swizzled store.
 #ifdef OPK_ATTN_TRACE
 // Debug-only timeline of CTA 0 (clock64 stamps per role / tile / event); never compiled into the library.
 __device__ long long g_attn_trace[3 * 1024];
+#ifndef OPK_TRACE_K
+#define OPK_TRACE_K 0
+#endif
 #define OPK_TRACE(role, j, e) do { if (blockIdx.x == 0) g_attn_trace[(role) * 1024 + (j) * 8 + (e)] = clock64(); } while (0)
+// Per-item record (SM id, start and end in globaltimer nanoseconds) of up to 1024 work items.
+__device__ long long g_attn_cta[1024 * 4];
+__device__ __forceinline__ long long opk_globaltimer() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ int opk_smid() {
+  int v;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(v));
+  return v;
+}
+#define OPK_TRACE_ITEM(w, e) do { if ((w) < 1024) { g_attn_cta[(w) * 4 + (e)] = opk_globaltimer(); g_attn_cta[(w) * 4 + 3] = opk_smid(); } } while (0)
 #else
+#define OPK_TRACE_K 0
 #define OPK_TRACE(role, j, e) do { } while (0)
+#define OPK_TRACE_ITEM(w, e) do { } while (0)
 #endif
 
 constexpr int kSoftmaxWarps = 8;                       // warps 2..9; warps 0 / 1 drive TMA / MMA
 constexpr int kAttnThreads = (2 + kSoftmaxWarps) * 32;
+constexpr int kFwdThreads = kAttnThreads + 64;          // forward: two more warps, the V producer and the P*V issuer
 
 template <int HD>
 struct FwdSmem {
@@ -104,16 +138,31 @@ struct FwdSmem {
   static constexpr int BYTES = (USED + 1024 <= 232448) ? USED + 1024 : 232448;
 };
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 // Maximum of 64 scores (columns col0 .. col0+63 of the tile) with four independent chains; MASKED drops columns > r.
 template <bool MASKED>
 __device__ __forceinline__ float row_max64(const uint32_t (&a)[32], const uint32_t (&b)[32], int col0, int r) {
   float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+  if (!MASKED) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {   // three-input maximum: two columns per instruction
+      m0 = fmax3(m0, __uint_as_float(a[i]), __uint_as_float(a[i + 1]));
+      m1 = fmax3(m1, __uint_as_float(a[i + 2]), __uint_as_float(a[i + 3]));
+      m2 = fmax3(m2, __uint_as_float(b[i]), __uint_as_float(b[i + 1]));
+      m3 = fmax3(m3, __uint_as_float(b[i + 2]), __uint_as_float(b[i + 3]));
+    }
+    return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+  }
 #pragma unroll
   for (int i = 0; i < 32; i += 2) {
-    if (!MASKED || col0 + i <= r) m0 = fmaxf(m0, __uint_as_float(a[i]));
-    if (!MASKED || col0 + i + 1 <= r) m1 = fmaxf(m1, __uint_as_float(a[i + 1]));
-    if (!MASKED || col0 + 32 + i <= r) m2 = fmaxf(m2, __uint_as_float(b[i]));
-    if (!MASKED || col0 + 33 + i <= r) m3 = fmaxf(m3, __uint_as_float(b[i + 1]));
+    if (col0 + i <= r) m0 = fmaxf(m0, __uint_as_float(a[i]));
+    if (col0 + i + 1 <= r) m1 = fmaxf(m1, __uint_as_float(a[i + 1]));
+    if (col0 + 32 + i <= r) m2 = fmaxf(m2, __uint_as_float(b[i]));
+    if (col0 + 33 + i <= r) m3 = fmaxf(m3, __uint_as_float(b[i + 1]));
   }
   return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
@@ -154,9 +203,25 @@ __device__ __forceinline__ float softmax_chunk(const uint32_t (&x)[32], int col0
   return sum;
 }
 
+// One work item of the forward kernel: (query tile, head), decoded from its rank in the heavy-first order.
+struct FwdItem {
+  int qt, h, g, n_kv;
+};
+__device__ __forceinline__ FwdItem fwd_item(int w, int n_qt, int H, int KV) {
+  FwdItem it;
+  it.qt = n_qt - 1 - w / H;
+  it.h = w % H;
+  it.g = it.h / (H / KV);
+  it.n_kv = it.qt + 1;
+  return it;
+}
+// Rank of the k-th item of CTA c out of G: boustrophedon over the heavy-first list, so that every CTA gets nearly the
+// same number of key tiles. Monotone in k; the CTA is done at the first rank >= the number of items.
+__device__ __forceinline__ int fwd_rank(int k, int c, int G) { return (k & 1) ? (k + 1) * G - 1 - c : k * G + c; }
+
 template <int HD>
-__global__ void __launch_bounds__(kAttnThreads, 1)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
+__global__ void __launch_bounds__(kFwdThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tm_out, const AttnParams p) {
   using SM = FwdSmem<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -166,216 +231,385 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
   uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;    // [2]
-  uint64_t* k_empty = bars + 3;   // [2]
-  uint64_t* v_full = bars + 5;    // [2]
-  uint64_t* v_empty = bars + 7;   // [2]
-  uint64_t* s_full = bars + 9;    // [2]
-  uint64_t* s_free = bars + 11;   // [2]
-  uint64_t* p_full = bars + 13;   // [2]
-  uint64_t* o_done = bars + 15;   // [2] P*V of a tile has completed (its P buffer is reusable, O is consistent)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  uint64_t* q_empty = bars + 1;   // every score product of the item has completed: Q may be replaced
+  uint64_t* k_full = bars + 2;    // [2]
+  uint64_t* k_empty = bars + 4;   // [2]
+  uint64_t* v_full = bars + 6;    // [2]
+  uint64_t* v_empty = bars + 8;   // [2]
+  uint64_t* s_full = bars + 10;   // [2]
+  uint64_t* s_free = bars + 12;   // [2]
+  uint64_t* p_full = bars + 14;   // [2]
+  uint64_t* o_done = bars + 16;   // [2] P*V of a tile has completed (its P buffer is reusable, its accumulator consistent)
+  uint64_t* o_free = bars + 18;   // all eight softmax warps have read the item's accumulators (and the exchange area)
+  uint64_t* x_bar = bars + 19;    // [4] rendezvous of the two warps of a TMEM lane quarter before the merge
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  uint64_t* x_bar = bars + 20;    // [2 tiles][4 quads] pair rendezvous for the row maxima; [8..11]: final row sums
-  float* xchg = reinterpret_cast<float*>(bars + 32);   // [2 tiles][2 halves][128 rows] partial maxima (row sums at the end)
+  float* xchg = reinterpret_cast<float*>(bars + 32);   // [2 groups][128 rows] running maxima, then [2][128] row sums
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qt = (p.T + 127) / 128;
-  const int h = blockIdx.x % p.H;
-  const int qt = n_qt - 1 - (int)(blockIdx.x / p.H);   // heavy (late) query tiles first
-  const int g = h / (p.H / p.KV);
-  const int n_kv = qt + 1;
-  const int q_col = h * HD, k_col = (p.H + g) * HD, v_col = (p.H + p.KV + g) * HD;
+  const int n_items = n_qt * p.H;
+  const int G = (int)gridDim.x, cta = (int)blockIdx.x;
+  const int k_col0 = p.H * HD, v_col0 = (p.H + p.KV) * HD;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    mbar_init(q_full, 1); mbar_init(q_empty, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], kSoftmaxWarps);
-      mbar_init(&p_full[i], kSoftmaxWarps); mbar_init(&o_done[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], kSoftmaxWarps / 2);
+      mbar_init(&p_full[i], kSoftmaxWarps / 2); mbar_init(&o_done[i], 1);
     }
-    for (int i = 0; i < 12; ++i) mbar_init(&x_bar[i], 2);
+    mbar_init(o_free, kSoftmaxWarps);
+    for (int i = 0; i < 4; ++i) mbar_init(&x_bar[i], 2);
     *abort_flag = 0;
     fence_barrier_init();
+    // The producer thread starts the loads of Q and of the first K tile of its first item before the CTA-wide setup
+    // barrier: their latency then runs under the TMEM allocation.
+    const FwdItem it = fwd_item(fwd_rank(0, cta, G), n_qt, p.H, p.KV);
+    tma_prefetch_desc(&tm);
+    mbar_expect_tx(q_full, SM::TILE);
+    for (int c = 0; c < HD / 64; ++c) tma_load_2d(smem + SM::Q_OFF + c * 16384, &tm, q_full, it.h * HD + c * 64, it.qt * 128);
+    mbar_expect_tx(&k_full[0], SM::TILE);
+    for (int c = 0; c < HD / 64; ++c) tma_load_2d(smem + SM::K_OFF + c * 16384, &tm, &k_full[0], k_col0 + it.g * HD + c * 64, 0);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t S_COL = 0, O_COL = 256;   // S buffers at 0 / 128, O accumulator at 256
+  const uint32_t S_COL = 0, O_COL = 256;   // score buffers at 0 / 128, the two output accumulators at 256 / 384
 
+  // All roles walk the same stream of key tiles: the items of this CTA one after the other, tile t of the stream
+  // using K / V stage, score buffer, probability buffer, accumulator and softmax group t & 1 with barrier phase
+  // (t >> 1) & 1. Nothing but the item-level hand-offs (Q, accumulators) separates one item from the next, so the
+  // loads and score products of an item start under the last tiles and the epilogue of the one before.
   if (warp == 0) {
+    // Q and K producer. K(t+2) is requested as soon as the score product of tile t has completed.
     if (lane == 0) {
-      tma_prefetch_desc(&tm);
-      mbar_expect_tx(q_full, SM::TILE);
-      for (int c = 0; c < HD / 64; ++c) tma_load_2d(smem + SM::Q_OFF + c * 16384, &tm, q_full, q_col + c * 64, qt * 128);
-      // K(j) is issued one tile ahead of V(j-1): the K stage frees when S(j-2) has completed, well before the V
-      // stage (which waits for P*V of tile j-3), so neither wait holds the other load back.
-      for (int j = 0; j <= n_kv; ++j) {
-        if (j < n_kv) {
-          const int s = j & 1;
-          const uint32_t ph = (j >> 1) & 1;
-          if (!mbar_wait(&k_empty[s], ph ^ 1u, abort_flag)) break;
-          OPK_TRACE(0, j, 0);
+      tma_prefetch_desc(&tm_out);
+      int t_base = 0;
+      bool alive = true;
+      for (int k = 0; alive; ++k) {
+        const int w = fwd_rank(k, cta, G);
+        if (w >= n_items) break;
+        const FwdItem it = fwd_item(w, n_qt, p.H, p.KV);
+        const int q_col = it.h * HD, k_col = k_col0 + it.g * HD;
+        if (k > 0) {
+          if (!mbar_wait(q_empty, (uint32_t)((k - 1) & 1), abort_flag)) break;
+          mbar_expect_tx(q_full, SM::TILE);
+          for (int c = 0; c < HD / 64; ++c) tma_load_2d(smem + SM::Q_OFF + c * 16384, &tm, q_full, q_col + c * 64, it.qt * 128);
+        }
+        for (int j = (k == 0 ? 1 : 0); j < it.n_kv; ++j) {   // K(0) of the first item was requested during the setup
+          const int t = t_base + j, s = t & 1;
+          const uint32_t ph = (t >> 1) & 1;
+          if (!mbar_wait(&k_empty[s], ph ^ 1u, abort_flag)) { alive = false; break; }
+          if (k == OPK_TRACE_K) OPK_TRACE(0, j, 0);
           mbar_expect_tx(&k_full[s], SM::TILE);
           for (int c = 0; c < HD / 64; ++c)
             tma_load_2d(smem + SM::K_OFF + s * SM::TILE + c * 16384, &tm, &k_full[s], k_col + c * 64, j * 128);
         }
-        if (j >= 1) {
-          const int jv = j - 1, s = jv & 1;
-          const uint32_t ph = (jv >> 1) & 1;
-          if (!mbar_wait(&v_empty[s], ph ^ 1u, abort_flag)) break;
-          OPK_TRACE(0, jv, 1);
+        t_base += it.n_kv;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 2 + kSoftmaxWarps) {
+    // V producer, on a warp of its own so that a wait for a V stage (freed by a P*V) never delays a K request.
+    if (lane == 0) {
+      int t_base = 0;
+      bool alive = true;
+      for (int k = 0; alive; ++k) {
+        const int w = fwd_rank(k, cta, G);
+        if (w >= n_items) break;
+        const FwdItem it = fwd_item(w, n_qt, p.H, p.KV);
+        const int v_col = v_col0 + it.g * HD;
+        for (int j = 0; j < it.n_kv; ++j) {
+          const int t = t_base + j, s = t & 1;
+          const uint32_t ph = (t >> 1) & 1;
+          if (!mbar_wait(&v_empty[s], ph ^ 1u, abort_flag)) { alive = false; break; }
+          if (k == OPK_TRACE_K) OPK_TRACE(0, j, 1);
           mbar_expect_tx(&v_full[s], SM::TILE);
           for (int c = 0; c < HD / 64; ++c)
-            tma_load_2d(smem + SM::V_OFF + s * SM::TILE + c * 16384, &tm, &v_full[s], v_col + c * 64, jv * 128);
+            tma_load_2d(smem + SM::V_OFF + s * SM::TILE + c * 16384, &tm, &v_full[s], v_col + c * 64, j * 128);
+        }
+        t_base += it.n_kv;
+      }
+    }
+#ifdef OPK_ATTN_TRACE
+    // observers: arrival times of the K and V tiles of the first item
+    if (lane == 1 || lane == 2) {
+      int tb = 0;
+      for (int kk = 0; kk < OPK_TRACE_K; ++kk) tb += fwd_item(fwd_rank(kk, cta, G), n_qt, p.H, p.KV).n_kv;
+      const int n0 = fwd_item(fwd_rank(OPK_TRACE_K, cta, G), n_qt, p.H, p.KV).n_kv;
+      for (int jj = 0; jj < tb + n0; ++jj) {
+        const int j = jj - tb;
+        if (!mbar_wait(lane == 1 ? &k_full[jj & 1] : &v_full[jj & 1], (uint32_t)((jj >> 1) & 1), abort_flag)) break;
+        if (j >= 0) OPK_TRACE(0, j, 1 + lane);
+      }
+    }
+#endif
+    __syncwarp();
+  } else if (warp == 1) {
+    // Score-product issuer. The two kinds of products are issued by two threads of different warps: a thread's
+    // barrier probes queue up behind the tensor-core instructions it has issued itself, so a single issuer that
+    // alternates "wait, 8 x mma, commit" for both kinds leaves the tensor core idle during its waits, whereas
+    // two issuers fill each other's gaps. S(t) only needs K(t) and score buffer t & 1 (free once softmax t-2 has read it).
+    if (lane == 0) {
+      const uint32_t q_s = smem_u32(smem + SM::Q_OFF);
+      int t = 0;
+      bool ok = true;
+      for (int k = 0; ok; ++k) {
+        const int w = fwd_rank(k, cta, G);
+        if (w >= n_items) break;
+        const int n_kv = n_qt - w / p.H;
+        if (!mbar_wait(q_full, (uint32_t)(k & 1), abort_flag)) break;
+        for (int j = 0; j < n_kv; ++j, ++t) {
+          const int s = t & 1;
+          const uint32_t ph = (t >> 1) & 1;
+          if (k == OPK_TRACE_K) OPK_TRACE(1, j, 6);
+          if (!mbar_wait(&k_full[s], ph, abort_flag)) { ok = false; break; }
+          if (k == OPK_TRACE_K) OPK_TRACE(1, j, 0);
+          if (!mbar_wait(&s_free[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+          if (k == OPK_TRACE_K) OPK_TRACE(1, j, 1);
+          tc_fence_after();
+          issue_product<false, false>(tmem + S_COL + s * 128, q_s, 128, smem_u32(smem + SM::K_OFF + s * SM::TILE), 128, 128,
+                                      HD, false);
+          umma_commit(&k_empty[s]);
+          umma_commit(&s_full[s]);
+          if (j == n_kv - 1) umma_commit(q_empty);
+          if (k == OPK_TRACE_K) OPK_TRACE(1, j, 7);
         }
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
+  } else if (warp == 3 + kSoftmaxWarps) {
+    // P*V issuer: O_s[128 x HD] (+)= P[128 x 128 keys] * V[keys x HD], B MN-major (rows = keys); the first tile of
+    // each group in an item (j = 0, 1) starts its accumulator afresh.
     if (lane == 0) {
-      const uint32_t q_s = smem_u32(smem + SM::Q_OFF), p_s = smem_u32(smem + SM::P_OFF);
-      bool ok = mbar_wait(q_full, 0, abort_flag);
-      auto issue_s = [&](int j) -> bool {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_full[s], ph, abort_flag)) return false;
-        OPK_TRACE(1, j, 0);
-        if (!mbar_wait(&s_free[s], ph ^ 1u, abort_flag)) return false;
-        OPK_TRACE(1, j, 1);
-        tc_fence_after();
-        issue_product<false, false>(tmem + S_COL + s * 128, q_s, 128, smem_u32(smem + SM::K_OFF + s * SM::TILE), 128, 128,
-                                    HD, false);
-        umma_commit(&k_empty[s]);
-        umma_commit(&s_full[s]);
-        return true;
-      };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) ok = issue_s(j + 1);
-        if (!ok) break;
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        OPK_TRACE(1, j, 2);
-        if (!mbar_wait(&v_full[s], ph, abort_flag)) break;
-        OPK_TRACE(1, j, 3);
-        if (!mbar_wait(&p_full[s], ph, abort_flag)) break;
-        OPK_TRACE(1, j, 4);
-        tc_fence_after();
-        // O[128 x HD] += P[128 x 128 keys] * V[keys x HD]: B is MN-major (rows = keys)
-        issue_product<false, true>(tmem + O_COL, p_s + s * SM::P_BYTES, 128, smem_u32(smem + SM::V_OFF + s * SM::TILE), 128, HD, 128, j > 0);
-        umma_commit(&v_empty[s]);
-        umma_commit(&o_done[s]);
-        OPK_TRACE(1, j, 5);
+      const uint32_t p_s = smem_u32(smem + SM::P_OFF);
+      int t = 0;
+      bool ok = true;
+      for (int k = 0; ok; ++k) {
+        const int w = fwd_rank(k, cta, G);
+        if (w >= n_items) break;
+        const int n_kv = n_qt - w / p.H;
+        // the accumulators of the previous item must have been read before this item's first P*V overwrites one
+        if (k > 0 && !mbar_wait(o_free, (uint32_t)((k - 1) & 1), abort_flag)) break;
+        for (int j = 0; j < n_kv; ++j, ++t) {
+          const int s = t & 1;
+          const uint32_t ph = (t >> 1) & 1;
+          if (k == OPK_TRACE_K) OPK_TRACE(1, j, 2);
+          if (!mbar_wait(&v_full[s], ph, abort_flag)) { ok = false; break; }
+          if (k == OPK_TRACE_K) OPK_TRACE(1, j, 3);
+          if (!mbar_wait(&p_full[s], ph, abort_flag)) { ok = false; break; }
+          if (k == OPK_TRACE_K) OPK_TRACE(1, j, 4);
+          tc_fence_after();
+          issue_product<false, true>(tmem + O_COL + s * 128, p_s + s * SM::P_BYTES, 128, smem_u32(smem + SM::V_OFF + s * SM::TILE), 128, HD, 128, j > 1);
+          umma_commit(&v_empty[s]);
+          umma_commit(&o_done[s]);
+          if (k == OPK_TRACE_K) OPK_TRACE(1, j, 5);
+        }
       }
     }
     __syncwarp();
   } else {
-    // 8 softmax warps: warps with the same (warp & 3) share 32 TMEM lanes (rows); `half` selects 64 of the 128 keys.
+    // Two softmax groups of four warps. Group g owns the stream tiles with t & 1 == g together with score buffer g,
+    // probability buffer g and output accumulator g, and keeps its own running maximum and row sum, so the groups
+    // never synchronise inside an item: while one waits for its next score tile the other one computes.
+    // Thread <-> row of the query tile; warps with the same (warp & 3) share a TMEM lane quarter.
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int grp = (warp - 2) >> 2;
     const int r = quad * 32 + lane;            // row inside the query tile
-    const int row = qt * 128 + r;
-    const int col0 = half * 64;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    const uint32_t s_addr = tmem + lane_base + S_COL + grp * 128;
+    const uint32_t o_addr = tmem + lane_base + O_COL + grp * 128;
+    uint8_t* p_smem = smem + SM::P_OFF + grp * SM::P_BYTES;
     const float c2 = p.scale * 1.4426950408889634f;
-    float m_run = -INFINITY, l_run = 0.f;      // m_run: maximum in use (possibly stale); l_run: this half's row sum
+    int t_base = 0;
     bool ok = true;
-    for (int j = 0; j < n_kv && ok; ++j) {
-      const int s = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      uint8_t* p_smem = smem + SM::P_OFF + s * SM::P_BYTES;
-      if (warp == 2 && lane == 0) OPK_TRACE(2, j, 0);
-      if (!warp_wait(&s_full[s], ph, abort_flag, lane)) { ok = false; break; }
-      if (warp == 2 && lane == 0) OPK_TRACE(2, j, 1);
-      tc_fence_after();
-      uint32_t x0[32], x1[32];
-      __syncwarp();
-      const uint32_t sa = tmem + lane_base + S_COL + s * 128 + col0;
-      tmem_ld32(sa, x0); tmem_ld32(sa + 32, x1);
-      tc_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[s]);   // S lives in registers now
-      if (warp == 2 && lane == 0) OPK_TRACE(2, j, 2);
-      const bool diag = (j == qt);
-      float mx = diag ? row_max64<true>(x0, x1, col0, r) : row_max64<false>(x0, x1, col0, r);
-      // combine with the other half of the row (through shared memory, 64-thread named barrier)
-      float* xm = xchg + s * 256;
-      xm[half * 128 + r] = mx;
-      if (!pair_sync(&x_bar[s * 4 + quad], ph, abort_flag, lane)) { ok = false; break; }
-      mx = fmaxf(fmaxf(mx, xm[(half ^ 1) * 128 + r]), m_run);
-      if (warp == 2 && lane == 0) OPK_TRACE(2, j, 3);
-      // lazy rescale: adopt the new maximum only if it grew by more than 8 in the exponent domain
-      const bool grow = (mx - m_run) * c2 > 8.f;   // true on the first tile (m_run = -inf)
-      const unsigned any_grow = __ballot_sync(0xffffffffu, grow);
-      // P buffer s was last read by the P*V of tile j-2
-      if (j > 1 && !warp_wait(&o_done[s], ph ^ 1u, abort_flag, lane)) { ok = false; break; }
-      float alpha = 1.f;
-      if (grow) {
-        alpha = ex2_approx((m_run - mx) * c2);     // 0 when m_run = -inf
-        l_run *= alpha;
-        m_run = mx;
+    for (int k = 0; ok; ++k) {
+      const int w = fwd_rank(k, cta, G);
+      if (w >= n_items) break;
+      const FwdItem it = fwd_item(w, n_qt, p.H, p.KV);
+      const int qt = it.qt, h = it.h, n_kv = it.n_kv;
+      const int row = qt * 128 + r;
+      if (quad == 2 && lane == 0 && grp == 0) OPK_TRACE_ITEM(w, 0);
+      if (HD == 128) {                         // this warp's output slab of the previous item has left shared memory
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
       }
-      if (any_grow && j > 0) {
-        // O may only be touched once the P*V of tile j-1 has completed; the next one waits for this warp's P
-        if (!warp_wait(&o_done[s ^ 1], ((j - 1) >> 1) & 1, abort_flag, lane)) { ok = false; break; }
+      float m_run = -INFINITY, l_run = 0.f;    // m_run: maximum in use (possibly stale); l_run: this group's row sum
+      const int j0 = ((t_base & 1) == grp) ? 0 : 1;   // first tile of the item that belongs to this group
+      bool first_tile = true;
+      for (int j = j0; j < n_kv && ok; j += 2) {
+        const int t = t_base + j;
+        const uint32_t ph = (t >> 1) & 1;
+        if (k == OPK_TRACE_K && quad == 2 && lane == 0) OPK_TRACE(2, j, 0);
+        if (!warp_wait(&s_full[grp], ph, abort_flag, lane)) { ok = false; break; }
+        if (k == OPK_TRACE_K && quad == 2 && lane == 0) OPK_TRACE(2, j, 1);
         tc_fence_after();
+#ifdef OPK_FWD_SKIP_SOFTMAX
+        if (t > 1 && !warp_wait(&o_done[grp], ph ^ 1u, abort_flag, lane)) { ok = false; break; }
+        first_tile = false;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free[grp]);
+#else
+        uint32_t x0[32], x1[32];
+        if (j == qt) {
+          // causal diagonal: the scores right of the diagonal are replaced by -inf in TMEM once, so that the two
+          // passes below need no masked variant (exp2 of -inf is 0 and the maximum ignores it)
+#pragma unroll 1
+          for (int c0 = 0; c0 < 128; c0 += 32) {
+            if (c0 + 31 <= (quad * 32)) continue;          // whole chunk left of the diagonal for every row of this warp
+            __syncwarp();
+            tmem_ld32(s_addr + c0, x0);
+            tc_wait_ld();
 #pragma unroll
-        for (int c0 = 0; c0 < HD / 2; c0 += 32) {
-          uint32_t o[32];
-          __syncwarp();
-          tmem_ld32(tmem + lane_base + O_COL + half * (HD / 2) + c0, o);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(tmem + lane_base + O_COL + half * (HD / 2) + c0, o);
+            for (int i = 0; i < 32; ++i)
+              if (c0 + i > r) x0[i] = 0xff800000u;
+            tmem_st32(s_addr + c0, x0);
+          }
+          tc_wait_st();
         }
-        tc_wait_st();
+        // pass 1: row maximum over the 128 keys (the scores stay in TMEM and are read again in pass 2)
+        float mx = m_run;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 64) {
+          __syncwarp();
+          tmem_ld32(s_addr + c0, x0); tmem_ld32(s_addr + c0 + 32, x1);
+          tc_wait_ld();
+          mx = fmaxf(mx, row_max64<false>(x0, x1, c0, r));
+        }
+        __syncwarp();
+        tmem_ld32(s_addr, x0);                     // first chunk of pass 2, in flight during the bookkeeping below
+        if (k == OPK_TRACE_K && quad == 2 && lane == 0) OPK_TRACE(2, j, 2);
+        // lazy rescale: adopt the new maximum only if it grew by more than 8 in the exponent domain
+        const bool grow = (mx - m_run) * c2 > 8.f;   // true on the group's first tile of the item (m_run = -inf)
+        const unsigned any_grow = __ballot_sync(0xffffffffu, grow);
+        // P buffer and accumulator of this group were last used by the P*V of stream tile t-2
+        if (t > 1 && !warp_wait(&o_done[grp], ph ^ 1u, abort_flag, lane)) { tc_wait_ld(); ok = false; break; }
+        float alpha = 1.f;
+        if (grow) {
+          alpha = ex2_approx((m_run - mx) * c2);     // 0 when m_run = -inf
+          l_run *= alpha;
+          m_run = mx;
+        }
+        if (any_grow && !first_tile) {
+          tc_fence_after();
+#pragma unroll 1
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            __syncwarp();
+            tmem_ld32(o_addr + c0, x1);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x1[i] = __float_as_uint(__uint_as_float(x1[i]) * alpha);
+            tmem_st32(o_addr + c0, x1);
+          }
+          tc_wait_st();
+        }
+        first_tile = false;
+        if (k == OPK_TRACE_K && quad == 2 && lane == 0) OPK_TRACE(2, j, 3);
+        const float mc = m_run * c2;
+        // pass 2: exp2, pack, store; the load of the next chunk is in flight while a chunk is computed
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 64) {
+          tc_wait_ld();
+          __syncwarp();
+          tmem_ld32(s_addr + c0 + 32, x1);
+          l_run += softmax_chunk<false>(x0, c0, r, c2, mc, p_smem);
+          tc_wait_ld();
+          __syncwarp();
+          if (c0 == 0) {
+            tmem_ld32(s_addr + 64, x0);
+          } else {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_free[grp]);   // the whole score tile has been read
+          }
+          l_run += softmax_chunk<false>(x1, c0 + 32, r, c2, mc, p_smem);
+        }
+#endif
+        if (k == OPK_TRACE_K && quad == 2 && lane == 0) OPK_TRACE(2, j, 5);
+        fence_proxy_async();           // make the generic-proxy writes of P visible to the tensor core
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[grp]);
+        if (k == OPK_TRACE_K && quad == 2 && lane == 0) OPK_TRACE(2, j, 6);
       }
-      if (warp == 2 && lane == 0) OPK_TRACE(2, j, 4);
-      const float mc = m_run * c2;
-      if (diag) l_run += softmax_chunk<true>(x0, col0, r, c2, mc, p_smem) + softmax_chunk<true>(x1, col0 + 32, r, c2, mc, p_smem);
-      else l_run += softmax_chunk<false>(x0, col0, r, c2, mc, p_smem) + softmax_chunk<false>(x1, col0 + 32, r, c2, mc, p_smem);
-      if (warp == 2 && lane == 0) OPK_TRACE(2, j, 5);
-      tc_fence_before();
-      fence_proxy_async();           // make the generic-proxy writes of P visible to the tensor core
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[s]);
-      if (warp == 2 && lane == 0) OPK_TRACE(2, j, 6);
-    }
-    if (ok && warp_wait(&o_done[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort_flag, lane)) {
+      if (!ok) break;
+      // The group's last tile of the item has been accumulated: exchange (maximum, row sum) with the other group and
+      // merge the two accumulators, O = (a * O_0 + b * O_1) / (a * l_0 + b * l_1), a, b = 2^(c2 * (m_g - max(m_0, m_1))).
+      // Group g writes output columns [g * HD/2, (g+1) * HD/2).
+      const int n_mine = (n_kv - j0 + 1) / 2;      // tiles of this item that this group processed
+      if (n_mine > 0) {
+        const int t_last = t_base + j0 + 2 * (n_mine - 1);
+        if (!warp_wait(&o_done[grp], (uint32_t)((t_last >> 1) & 1), abort_flag, lane)) { ok = false; break; }
+      }
+      // the exchange area is rewritten only after every warp has read the previous item's values
+      if (k > 0 && !warp_wait(o_free, (uint32_t)((k - 1) & 1), abort_flag, lane)) { ok = false; break; }
+      if (k == OPK_TRACE_K && quad == 2 && lane == 0) OPK_TRACE(2, 100 + grp, 0);
       tc_fence_after();
-      // total row sum = both halves (same running maximum on both sides)
-      float* xl = xchg + (n_kv & 1) * 256;      // the buffer the last tile did not use
-      xl[half * 128 + r] = l_run;
-      const bool both = pair_sync(&x_bar[8 + quad], 0, abort_flag, lane);
-      const float l_tot = l_run + xl[(half ^ 1) * 128 + r];
-      const float inv = both ? 1.f / l_tot : 0.f;
-      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ldo + h * HD + half * (HD / 2);
+      xchg[grp * 128 + r] = m_run;
+      xchg[256 + grp * 128 + r] = l_run;
+      if (!pair_sync(&x_bar[quad], (uint32_t)(k & 1), abort_flag, lane)) { ok = false; break; }
+      tc_fence_after();
+      const float m_o = xchg[(grp ^ 1) * 128 + r], l_o = xchg[256 + (grp ^ 1) * 128 + r];
+      const float m_tot = fmaxf(m_run, m_o);
+      const float w_me = ex2_approx((m_run - m_tot) * c2), w_o = ex2_approx((m_o - m_tot) * c2);
+      const float l_tot = w_me * l_run + w_o * l_o;
+      const float inv = 1.f / l_tot;
+      const float w0 = (grp == 0 ? w_me : w_o) * inv, w1 = (grp == 0 ? w_o : w_me) * inv;
+      // with a single key tile only the accumulator of the group that owned it was written
+      const bool has0 = n_kv > 1 || (t_base & 1) == 0, has1 = n_kv > 1 || (t_base & 1) == 1;
+      const uint32_t o0 = tmem + lane_base + O_COL + grp * (HD / 2), o1 = o0 + 128;
+      // HD = 128: the group's 64 output columns are staged in its probability buffer (free now) in the swizzled
+      // row layout and each warp stores its 32 rows with one TMA store, which clips the rows past T.
+      // HD = 64: 32 columns per group, written directly.
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ldo + h * HD + grp * (HD / 2);
 #pragma unroll
       for (int c0 = 0; c0 < HD / 2; c0 += 32) {
-        uint32_t raw[32];
+        uint32_t ra[32], rb[32];
         __syncwarp();
-        tmem_ld32(tmem + lane_base + O_COL + half * (HD / 2) + c0, raw);
+        tmem_ld32(o0 + c0, ra);                 // an accumulator without a tile holds stale bits: dropped below
+        tmem_ld32(o1 + c0, rb);
         tc_wait_ld();
-        if (row < p.T) {
+        if (c0 + 32 >= HD / 2) {                  // last accumulator read of the item by this warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(o_free);
+        }
+        if (HD == 128 || row < p.T) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              v[i] = __uint_as_float(has0 ? ra[8 * q + i] : 0u) * w0;
+              v[i] = fmaf(__uint_as_float(has1 ? rb[8 * q + i] : 0u), w1, v[i]);
+            }
             uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(raw[8 * q + 0]) * inv, __uint_as_float(raw[8 * q + 1]) * inv);
-            o.y = pack_bf16x2(__uint_as_float(raw[8 * q + 2]) * inv, __uint_as_float(raw[8 * q + 3]) * inv);
-            o.z = pack_bf16x2(__uint_as_float(raw[8 * q + 4]) * inv, __uint_as_float(raw[8 * q + 5]) * inv);
-            o.w = pack_bf16x2(__uint_as_float(raw[8 * q + 6]) * inv, __uint_as_float(raw[8 * q + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c0 + q * 8) = o;
+            o.x = pack_bf16x2(v[0], v[1]);
+            o.y = pack_bf16x2(v[2], v[3]);
+            o.z = pack_bf16x2(v[4], v[5]);
+            o.w = pack_bf16x2(v[6], v[7]);
+            if (HD == 128) *reinterpret_cast<uint4*>(p_smem + swz_off(r, c0 + q * 8)) = o;
+            else *reinterpret_cast<uint4*>(orow + c0 + q * 8) = o;
           }
         }
       }
-      if (half == 0 && row < p.T) p.lse[(long long)h * p.T + row] = m_run * p.scale + logf(l_tot);
+      if (HD == 128) {
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0 && qt * 128 + quad * 32 < p.T)
+          tma_store_2d(&tm_out, p_smem + quad * 32 * 128, h * HD + grp * 64, qt * 128 + quad * 32);
+        __syncwarp();
+      }
+      if (grp == 0 && row < p.T) p.lse[(long long)h * p.T + row] = m_tot * p.scale + logf(l_tot);
+      if (k == OPK_TRACE_K && quad == 2 && lane == 0) OPK_TRACE(2, 100 + grp, 1);
+      if (quad == 2 && lane == 0 && grp == 0) OPK_TRACE_ITEM(w, 1);
+      t_base += n_kv;
     }
+    if (HD == 128 && lane == 0) tma_store_wait_read();   // shared memory must outlive the stores' reads
   }
   tc_fence_before();
   __syncthreads();
