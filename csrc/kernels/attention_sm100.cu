@@ -105,14 +105,14 @@ extern "C" int opk_attn_bwd(const void* qkv, const void* out, const void* dout, 
     static bool once = set_smem(opk::attn_dkv_kernel<128>, opk::DkvSmem<128>::BYTES) &&
                        set_smem(opk::attn_dq128_kernel<128>, opk::Dq128Smem<128>::BYTES);
     if (!once) return -3;
-    opk::attn_dkv_kernel<128><<<dkv_grid, opk::kAttnThreads, opk::DkvSmem<128>::BYTES, st>>>(tm128, tm64, tmdo64, p);
-    opk::attn_dq128_kernel<128><<<n_kt * H, opk::kAttnThreads, opk::Dq128Smem<128>::BYTES, st>>>(tm128, tm128, tmdo128, p);
+    opk::attn_dkv_kernel<128><<<dkv_grid, opk::kBwdThreads, opk::DkvSmem<128>::BYTES, st>>>(tm128, tm64, tmdo64, p);
+    opk::attn_dq128_kernel<128><<<n_kt * H, opk::kBwdThreads, opk::Dq128Smem<128>::BYTES, st>>>(tm128, tm128, tmdo128, p);
   } else {
     static bool once = set_smem(opk::attn_dkv_kernel<64>, opk::DkvSmem<64>::BYTES) &&
                        set_smem(opk::attn_dq128_kernel<64>, opk::Dq128Smem<64>::BYTES);
     if (!once) return -3;
-    opk::attn_dkv_kernel<64><<<dkv_grid, opk::kAttnThreads, opk::DkvSmem<64>::BYTES, st>>>(tm128, tm64, tmdo64, p);
-    opk::attn_dq128_kernel<64><<<n_kt * H, opk::kAttnThreads, opk::Dq128Smem<64>::BYTES, st>>>(tm128, tm128, tmdo128, p);
+    opk::attn_dkv_kernel<64><<<dkv_grid, opk::kBwdThreads, opk::DkvSmem<64>::BYTES, st>>>(tm128, tm64, tmdo64, p);
+    opk::attn_dq128_kernel<64><<<n_kt * H, opk::kBwdThreads, opk::Dq128Smem<64>::BYTES, st>>>(tm128, tm128, tmdo128, p);
   }
   if (p.part) {
     const int kvw = KV * hd;

@@ -122,6 +122,7 @@ __device__ __forceinline__ int opk_smid() {
 constexpr int kSoftmaxWarps = 8;                       // warps 2..9; warps 0 / 1 drive TMA / MMA
 constexpr int kAttnThreads = (2 + kSoftmaxWarps) * 32;
 constexpr int kFwdThreads = kAttnThreads + 64;          // forward: two more warps, the V producer and the P*V issuer
+constexpr int kBwdThreads = kAttnThreads + 64;          // backward: two more warps, the second issuer and (dQ) the V producer
 
 template <int HD>
 struct FwdSmem {
@@ -771,7 +772,7 @@ __device__ __forceinline__ void dkv_chunk(const uint32_t (&sraw)[32], const uint
 }
 
 template <int HD>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_q,
                 const __grid_constant__ CUtensorMap tm_do, const AttnParams p) {
   using SM = DkvSmem<HD>;
@@ -852,7 +853,6 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t k_s = smem_u32(smem + SM::K_OFF), v_s = smem_u32(smem + SM::V_OFF);
-      const uint32_t pt_s = smem_u32(smem + SM::PT_OFF), dst_s = smem_u32(smem + SM::DST_OFF);
       bool ok = mbar_wait(kv_full, 0, abort_flag);
       auto scores = [&](int i) -> bool {
         const int s = i & 1, sq = i % NS;
@@ -866,10 +866,16 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
         umma_commit(&st_full[s]);
         return true;
       };
-      if (ok) ok = scores(0);
-      for (int i = 0; i < n_it && ok; ++i) {
-        if (i + 1 < n_it) ok = scores(i + 1);
-        if (!ok) break;
+      // The score products and the gradient products are issued by two threads of different warps: a thread's
+      // barrier probes queue up behind the tensor-core instructions it has issued itself, so one issuer that
+      // alternates between the two kinds leaves the tensor core idle during its waits.
+      for (int i = 0; i < n_it && ok; ++i) ok = scores(i);
+    }
+    __syncwarp();
+  } else if (warp == 2 + kSoftmaxWarps) {
+    if (lane == 0) {
+      const uint32_t pt_s = smem_u32(smem + SM::PT_OFF), dst_s = smem_u32(smem + SM::DST_OFF);
+      for (int i = 0; i < n_it; ++i) {
         const int sq = i % NS;
         if (!mbar_wait(pd_full, i & 1, abort_flag)) break;
         tc_fence_after();
@@ -882,6 +888,8 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
       }
     }
     __syncwarp();
+  } else if (warp > 2 + kSoftmaxWarps) {
+    // spare warp of the common backward launch shape
   } else {
     // 8 softmax warps: (warp & 3) picks the 32 key rows (TMEM lanes), `half` 32 of the 64 queries of the sub-tile
     const int quad = warp & 3;
@@ -946,25 +954,14 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
 }
 
 // ------------------------------------------------------------------------------------------------ dQ
-// CTA = (query tile of 128 rows, head). Iterates over 64-key sub-tiles up to the diagonal; dQ accumulates in TMEM.
-//   S = Q K^T [q x 64 keys]   dP = dO V^T [q x 64 keys]   dS = P * (dP - D) * scale   dQ += dS K
-template <int HD>
-struct DqSmem {
-  static constexpr int NS = 4;                            // K / V ring depth (see DkvSmem)
-  static constexpr int Q_TILE = 128 * HD * 2;
-  static constexpr int KV_TILE = 64 * HD * 2;
-  static constexpr int Q_OFF = 0;
-  static constexpr int DO_OFF = Q_TILE;
-  static constexpr int K_OFF = 2 * Q_TILE;                // NS stages
-  static constexpr int V_OFF = K_OFF + NS * KV_TILE;      // NS stages
-  static constexpr int DS_OFF = V_OFF + NS * KV_TILE;     // [128][64] bf16
-  static constexpr int BAR_OFF = DS_OFF + 16384;
-  static constexpr int BYTES = BAR_OFF + 256 + 1024;
-  static_assert(BYTES <= 232448, "dQ shared-memory layout does not fit");
-};
-
-// One 32-key chunk of the backward softmax for a query row: dS = exp2(S*c2 + nlse2) * (dP - D); keys with local
-// index above `lim` are masked (causal diagonal).
+// CTA = (query tile of 128 rows, head). Iterates over key tiles of 128 up to the diagonal; dQ accumulates in TMEM.
+//   S = Q K^T [q x 128 keys]   dP = dO V^T [q x 128 keys]   dS = P * (dP - D) * scale   dQ += dS K
+// per tile 8 + 8 + 8 `tcgen05.mma` of 128x128x16. S and dP are single-buffered in TMEM (128 + 128 columns, dQ in
+// another 128): the softmax warps release them as soon as the second half of their columns is in registers, i.e.
+// after about half of their work on the tile, and the score products of the next tile run under the rest.
+// Shared memory (head_dim 128: 224 KB): K(i) stays resident until dQ(i) has completed, i.e. across the score products of
+// tile i+1, and its refill needs a TMA round trip on top, so K has THREE stages; V(i) is dead as soon as dP(i) has
+// completed and has ONE stage: V(i+1) is requested then and is first needed a whole tile later (S(i+1) goes first).
 template <bool MASKED>
 __device__ __forceinline__ void dq_chunk(const uint32_t (&sraw)[32], const uint32_t (&draw)[32], float c2, float nl,
                                          float d, int lim, uint32_t* dw) {
@@ -980,161 +977,6 @@ __device__ __forceinline__ void dq_chunk(const uint32_t (&sraw)[32], const uint3
   }
 }
 
-template <int HD>
-__global__ void __launch_bounds__(kAttnThreads, 1)
-attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
-               const __grid_constant__ CUtensorMap tm_do, const AttnParams p) {
-  using SM = DqSmem<HD>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
-  constexpr int NS = SM::NS;
-  uint64_t* q_full = bars + 0;
-  uint64_t* kv_full = bars + 1;            // [NS]
-  uint64_t* kv_empty = kv_full + NS;       // [NS]
-  uint64_t* s_full = kv_empty + NS;        // [2]
-  uint64_t* s_free = s_full + 2;           // [2]
-  uint64_t* ds_full = s_free + 2;
-  uint64_t* ds_free = ds_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ds_free + 1);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_qt = (p.T + 127) / 128;
-  const int h = blockIdx.x % p.H;
-  const int qt = n_qt - 1 - (int)(blockIdx.x / p.H);
-  const int g = h / (p.H / p.KV);
-  const int n_it = min(2 * qt + 2, (p.T + 63) / 64);
-  const int q_col = h * HD, k_col = (p.H + g) * HD, v_col = (p.H + p.KV + g) * HD;
-
-  if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    for (int i = 0; i < NS; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], kSoftmaxWarps); }
-    mbar_init(ds_full, kSoftmaxWarps);
-    mbar_init(ds_free, 1);
-    *abort_flag = 0;
-    fence_barrier_init();
-  }
-  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  const uint32_t S_COL = 0, DP_COL = 128, DQ_COL = 256;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_kv); tma_prefetch_desc(&tm_do);
-      mbar_expect_tx(q_full, 2 * SM::Q_TILE);
-      for (int c = 0; c < HD / 64; ++c) {
-        tma_load_2d(smem + SM::Q_OFF + c * 16384, &tm_q, q_full, q_col + c * 64, qt * 128);
-        tma_load_2d(smem + SM::DO_OFF + c * 16384, &tm_do, q_full, q_col + c * 64, qt * 128);
-      }
-      for (int i = 0; i < n_it; ++i) {
-        const int s = i % NS;
-        const uint32_t ph = (i / NS) & 1;
-        if (!mbar_wait(&kv_empty[s], ph ^ 1u, abort_flag)) break;
-        mbar_expect_tx(&kv_full[s], 2 * SM::KV_TILE);
-        for (int c = 0; c < HD / 64; ++c) {
-          tma_load_2d(smem + SM::K_OFF + s * SM::KV_TILE + c * 8192, &tm_kv, &kv_full[s], k_col + c * 64, i * 64);
-          tma_load_2d(smem + SM::V_OFF + s * SM::KV_TILE + c * 8192, &tm_kv, &kv_full[s], v_col + c * 64, i * 64);
-        }
-      }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t q_s = smem_u32(smem + SM::Q_OFF), do_s = smem_u32(smem + SM::DO_OFF);
-      const uint32_t ds_s = smem_u32(smem + SM::DS_OFF);
-      bool ok = mbar_wait(q_full, 0, abort_flag);
-      auto scores = [&](int i) -> bool {
-        const int s = i & 1, sk = i % NS;
-        const uint32_t ph = (i >> 1) & 1;
-        if (!mbar_wait(&kv_full[sk], (i / NS) & 1, abort_flag)) return false;
-        if (!mbar_wait(&s_free[s], ph ^ 1u, abort_flag)) return false;
-        tc_fence_after();
-        const uint32_t k_s = smem_u32(smem + SM::K_OFF + sk * SM::KV_TILE), v_s = smem_u32(smem + SM::V_OFF + sk * SM::KV_TILE);
-        issue_product<false, false>(tmem + S_COL + s * 64, q_s, 128, k_s, 64, 64, HD, false);
-        issue_product<false, false>(tmem + DP_COL + s * 64, do_s, 128, v_s, 64, 64, HD, false);
-        umma_commit(&s_full[s]);
-        return true;
-      };
-      if (ok) ok = scores(0);
-      for (int i = 0; i < n_it && ok; ++i) {
-        if (i + 1 < n_it) ok = scores(i + 1);
-        if (!ok) break;
-        const int sk = i % NS;
-        if (!mbar_wait(ds_full, i & 1, abort_flag)) break;
-        tc_fence_after();
-        const uint32_t k_s = smem_u32(smem + SM::K_OFF + sk * SM::KV_TILE);
-        // dQ[q x HD] += dS[q x 64 keys] * K[64 keys x HD]   (B rows = keys: MN-major)
-        issue_product<false, true>(tmem + DQ_COL, ds_s, 128, k_s, 64, HD, 64, i > 0);
-        umma_commit(&kv_empty[sk]);
-        umma_commit(ds_free);
-      }
-    }
-    __syncwarp();
-  } else {
-    // 8 softmax warps: (warp & 3) picks the 32 query rows (TMEM lanes), `half` 32 of the 64 keys of the sub-tile
-    const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
-    const int r = quad * 32 + lane;
-    const int qrow = qt * 128 + r;
-    const int c0 = half * 32;
-    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-    const float c2 = p.scale * 1.4426950408889634f;
-    const bool qvalid = qrow < p.T;
-    const float nl_r = qvalid ? p.nlse2[(long long)h * p.T64 + qrow] : -INFINITY;   // invalid rows give P = 0
-    const float d_r = qvalid ? p.dsum[(long long)h * p.T64 + qrow] : 0.f;
-    bool ok = true;
-    for (int i = 0; i < n_it && ok; ++i) {
-      const int s = i & 1;
-      const uint32_t ph = (i >> 1) & 1;
-      if (!warp_wait(&s_full[s], ph, abort_flag, lane)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t dw[16];
-      const bool masked = i >= 2 * qt;          // the two sub-tiles on the causal diagonal
-      {
-        uint32_t sraw[32], draw[32];
-        __syncwarp();
-        tmem_ld32(tmem + lane_base + S_COL + s * 64 + c0, sraw);
-        tmem_ld32(tmem + lane_base + DP_COL + s * 64 + c0, draw);
-        tc_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s_free[s]);      // scores are in registers
-        if (masked) dq_chunk<true>(sraw, draw, c2, nl_r, d_r, qrow - (i * 64 + c0), dw);
-        else dq_chunk<false>(sraw, draw, c2, nl_r, d_r, 0, dw);
-      }
-      if (i > 0 && !warp_wait(ds_free, (i - 1) & 1, abort_flag, lane)) { ok = false; break; }
-      store_row32(smem + SM::DS_OFF, r, c0, dw);
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(ds_full);
-    }
-    if (ok && warp_wait(ds_free, (n_it - 1) & 1, abort_flag, lane)) {
-      tc_fence_after();
-      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.dqkv) + (long long)qrow * p.ld + q_col + half * (HD / 2);
-      store_acc_rows<HD / 2>(tmem + lane_base + DQ_COL + half * (HD / 2), dst, qvalid, p.scale);
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
-  if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, 1);
-}
-
-// ------------------------------------------------------------------------------------------------ dQ, 128-key tiles
-// Same contract as attn_dq_kernel with key tiles of 128 instead of sub-tiles of 64: per tile the three products are
-// 8 + 8 + 8 `tcgen05.mma` of 128x128x16 instead of 2 x (8 + 8 + 4) of 128x64x16 / 128x128x16, and every instruction
-// with M = 128 costs about 45 cycles on top of its arithmetic whatever its width, so the wider tile nearly halves the
-// tensor-pipe time per key. S and dP are single-buffered in TMEM (128 + 128 columns, dQ in another 128): the softmax
-// warps release them as soon as the second half of their columns is in registers, i.e. after about half of their
-// work on the tile, and the score products of the next tile run under the rest.
-// Shared memory (head_dim 128: 224 KB): K(i) stays resident until dQ(i) has completed, i.e. across the score products of
-// tile i+1, and its refill needs a TMA round trip on top, so K has THREE stages; V(i) is dead as soon as dP(i) has
-// completed and has ONE stage: V(i+1) is requested then and is first needed a whole tile later (S(i+1) goes first).
 template <int HD>
 struct Dq128Smem {
   static constexpr int NS = 3;                            // K ring depth (V: one stage)
@@ -1152,7 +994,7 @@ struct Dq128Smem {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                   const __grid_constant__ CUtensorMap tm_do, const AttnParams p) {
   using SM = Dq128Smem<HD>;
@@ -1217,6 +1059,13 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mbar_expect_tx(&k_full[s], SM::KV_TILE);
         for (int c = 0; c < HD / 64; ++c)
           tma_load_2d(smem + SM::K_OFF + s * SM::KV_TILE + c * 16384, &tm_kv, &k_full[s], k_col + c * 64, i * 128);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 3 + kSoftmaxWarps) {
+    // V producer, on a warp of its own: the wait for the single V stage never delays a K request
+    if (lane == 0) {
+      for (int i = 0; i < n_it; ++i) {
         if (!mbar_wait(v_empty, (uint32_t)(i & 1) ^ 1u, abort_flag)) break;
         mbar_expect_tx(v_full, SM::KV_TILE);
         for (int c = 0; c < HD / 64; ++c)
@@ -1227,7 +1076,6 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t q_s = smem_u32(smem + SM::Q_OFF), do_s = smem_u32(smem + SM::DO_OFF);
-      const uint32_t ds_s = smem_u32(smem + SM::DS_OFF);
       bool ok = mbar_wait(q_full, 0, abort_flag);
       auto scores = [&](int i) -> bool {
         const int sk = i % NS;
@@ -1242,10 +1090,15 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         umma_commit(s_full);
         return true;
       };
-      if (ok) ok = scores(0);
-      for (int i = 0; i < n_it && ok; ++i) {
-        if (i + 1 < n_it) ok = scores(i + 1);
-        if (!ok) break;
+      // The score products and the dQ products are issued by two threads of different warps (a thread's barrier
+      // probes queue up behind the tensor-core instructions it has issued itself).
+      for (int i = 0; i < n_it && ok; ++i) ok = scores(i);
+    }
+    __syncwarp();
+  } else if (warp == 2 + kSoftmaxWarps) {
+    if (lane == 0) {
+      const uint32_t ds_s = smem_u32(smem + SM::DS_OFF);
+      for (int i = 0; i < n_it; ++i) {
         const int sk = i % NS;
         if (!mbar_wait(ds_full, i & 1, abort_flag)) break;
         tc_fence_after();
