@@ -96,8 +96,9 @@ extern "C" int opk_attn_bwd(const void* qkv, const void* out, const void* dout, 
   const int dkv_grid = ((T + 127) / 128) * (p.part ? H : KV);
   p.dout = dout; p.dqkv = dqkv; p.scale = scale; p.err = err;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const long long warps = (long long)T64 * H;
-  opk::attn_dsum_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(dout) & 15)) return -1;
+  const long long dsum_threads = (long long)T64 * H * (hd / 8);   // hd / 8 lanes per (t, h) row, 16 bytes each
+  opk::attn_dsum_kernel<<<(unsigned)((dsum_threads + 255) / 256), 256, 0, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), lse, dsum,
       dsum + (long long)H * T64, T, T64, H, hd, ldo);
   const int n_kt = (T + 127) / 128;

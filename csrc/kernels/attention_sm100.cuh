@@ -625,25 +625,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ 
 __global__ void attn_dsum_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                                  const float* __restrict__ lse, float* __restrict__ dsum, float* __restrict__ nlse2,
                                  int T, int T64, int H, int hd, long long ldo) {
-  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (w >= T64 * H) return;
-  const int t = w / H, h = w % H;
-  if (t >= T) {
-    if (lane == 0) { dsum[(long long)h * T64 + t] = 0.f; nlse2[(long long)h * T64 + t] = -INFINITY; }
-    return;
-  }
-  const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(o + (long long)t * ldo + h * hd);
-  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(dout + (long long)t * ldo + h * hd);
+  // hd / 8 consecutive lanes share one (t, h) row and each takes 16 bytes of O and of dO
+  const int lpr = hd >> 3;                                  // 8 or 16 lanes per row
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gid / lpr;
+  const int sub = (int)(gid % lpr);
+  const bool live = row < (long long)T64 * H;
+  const int t = live ? (int)(row / H) : 0, h = live ? (int)(row % H) : 0;
   float s = 0.f;
-  for (int i = lane; i < hd / 2; i += 32) {
-    const float2 x = __bfloat1622float2(a[i]), y = __bfloat1622float2(b[i]);
-    s += x.x * y.x + x.y * y.y;
-  }
+  if (live && t < T) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + (long long)t * ldo + h * hd + sub * 8);
+    const uint4 b = *reinterpret_cast<const uint4*>(dout + (long long)t * ldo + h * hd + sub * 8);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) {
-    dsum[(long long)h * T64 + t] = s;
-    nlse2[(long long)h * T64 + t] = -lse[(long long)h * T + t] * 1.4426950408889634f;
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
+      const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[i]));
+      s = fmaf(x.x, y.x, fmaf(x.y, y.y, s));
+    }
+  }
+  // the rows of a warp are aligned groups of lpr lanes: xor offsets below lpr stay inside the group
+  for (int off = lpr >> 1; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (live && sub == 0) {
+    dsum[(long long)h * T64 + t] = t < T ? s : 0.f;
+    nlse2[(long long)h * T64 + t] = t < T ? -lse[(long long)h * T + t] * 1.4426950408889634f : -INFINITY;
   }
 }
 
@@ -727,17 +732,18 @@ template <int HD>
 struct DkvSmem {
   // The Q / dO ring is deeper than the two score buffers in TMEM: a stage stays occupied from the score products of
   // its sub-tile until the dK product of the same sub-tile has completed (about two iterations), and the refill needs
-  // a full TMA round trip on top, so two stages leave that round trip exposed in every iteration.
-  static constexpr int NS = 4;
+  // a full TMA round trip on top, so two stages leave that round trip exposed in every iteration. Pt and dSt are
+  // double-buffered: the softmax warps store sub-tile i+1 while the gradient products of sub-tile i run.
+  static constexpr int NS = 3;
   static constexpr int KV_TILE = 128 * HD * 2;
   static constexpr int Q_TILE = 64 * HD * 2;
   static constexpr int K_OFF = 0;
   static constexpr int V_OFF = KV_TILE;
   static constexpr int Q_OFF = 2 * KV_TILE;               // NS stages
   static constexpr int DO_OFF = Q_OFF + NS * Q_TILE;      // NS stages
-  static constexpr int PT_OFF = DO_OFF + NS * Q_TILE;     // [128][64] bf16
-  static constexpr int DST_OFF = PT_OFF + 16384;
-  static constexpr int ROW_OFF = DST_OFF + 16384;         // NS stages x (64 nlse2 + 64 dsum) floats
+  static constexpr int PT_OFF = DO_OFF + NS * Q_TILE;     // 2 x [128][64] bf16
+  static constexpr int DST_OFF = PT_OFF + 2 * 16384;      // 2 x [128][64] bf16
+  static constexpr int ROW_OFF = DST_OFF + 2 * 16384;     // NS stages x (64 nlse2 + 64 dsum) floats
   static constexpr int BAR_OFF = ROW_OFF + NS * 512;
   static constexpr int USED = BAR_OFF + 256;
   // up to 1 KB of alignment padding in front; at HD = 128 the layout only fits when the padding is below 768 bytes,
@@ -789,9 +795,9 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
   uint64_t* q_empty = q_full + NS;         // [NS]
   uint64_t* st_full = q_empty + NS;        // [2]
   uint64_t* st_free = st_full + 2;         // [2]
-  uint64_t* pd_full = st_free + 2;
-  uint64_t* pd_free = pd_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pd_free + 1);
+  uint64_t* pd_full = st_free + 2;         // [2]
+  uint64_t* pd_free = pd_full + 2;         // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pd_free + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -813,9 +819,10 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int i = 0; i < NS; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_free[i], kSoftmaxWarps); }
-    mbar_init(pd_full, kSoftmaxWarps);
-    mbar_init(pd_free, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&st_full[i], 1); mbar_init(&st_free[i], kSoftmaxWarps);
+      mbar_init(&pd_full[i], kSoftmaxWarps); mbar_init(&pd_free[i], 1);
+    }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -876,15 +883,15 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
     if (lane == 0) {
       const uint32_t pt_s = smem_u32(smem + SM::PT_OFF), dst_s = smem_u32(smem + SM::DST_OFF);
       for (int i = 0; i < n_it; ++i) {
-        const int sq = i % NS;
-        if (!mbar_wait(pd_full, i & 1, abort_flag)) break;
+        const int sq = i % NS, b = i & 1;
+        if (!mbar_wait(&pd_full[b], (uint32_t)((i >> 1) & 1), abort_flag)) break;
         tc_fence_after();
         const uint32_t q_s = smem_u32(smem + SM::Q_OFF + sq * SM::Q_TILE), do_s = smem_u32(smem + SM::DO_OFF + sq * SM::Q_TILE);
         // dV[keys x HD] += Pt[keys x 64 q] * dO[64 q x HD]   (B rows = queries: MN-major)
-        issue_product<false, true>(tmem + DV_COL, pt_s, 128, do_s, 64, HD, 64, i > 0);
-        issue_product<false, true>(tmem + DK_COL, dst_s, 128, q_s, 64, HD, 64, i > 0);
+        issue_product<false, true>(tmem + DV_COL, pt_s + b * 16384, 128, do_s, 64, HD, 64, i > 0);
+        issue_product<false, true>(tmem + DK_COL, dst_s + b * 16384, 128, q_s, 64, HD, 64, i > 0);
         umma_commit(&q_empty[sq]);
-        umma_commit(pd_free);
+        umma_commit(&pd_free[b]);
       }
     }
     __syncwarp();
@@ -925,14 +932,16 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
         if (masked) dkv_chunk<true>(sraw, draw, nl4, d4, c2, key - (q64 * 64 + c0), pw, dw);
         else dkv_chunk<false>(sraw, draw, nl4, d4, c2, 0, pw, dw);
       }
-      if (i > 0 && !warp_wait(pd_free, (i - 1) & 1, abort_flag, lane)) { ok = false; break; }
-      store_row32(smem + SM::PT_OFF, r, c0, pw);
-      store_row32(smem + SM::DST_OFF, r, c0, dw);
+      // buffer s of Pt / dSt was last read by the gradient products of sub-tile i-2
+      if (i > 1 && !warp_wait(&pd_free[s], ph ^ 1u, abort_flag, lane)) { ok = false; break; }
+      store_row32(smem + SM::PT_OFF + s * 16384, r, c0, pw);
+      store_row32(smem + SM::DST_OFF + s * 16384, r, c0, dw);
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(pd_full);
+      if (lane == 0) mbar_arrive(&pd_full[s]);
     }
-    if (ok && warp_wait(pd_free, (n_it - 1) & 1, abort_flag, lane)) {
+    // the gradient products complete in issue order: the last one done means all done
+    if (ok && warp_wait(&pd_free[(n_it - 1) & 1], (uint32_t)(((n_it - 1) >> 1) & 1), abort_flag, lane)) {
       tc_fence_after();
       if (split) {
         const long long kvw = (long long)p.KV * HD;
@@ -956,9 +965,9 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
 // ------------------------------------------------------------------------------------------------ dQ
 // CTA = (query tile of 128 rows, head). Iterates over key tiles of 128 up to the diagonal; dQ accumulates in TMEM.
 //   S = Q K^T [q x 128 keys]   dP = dO V^T [q x 128 keys]   dS = P * (dP - D) * scale   dQ += dS K
-// per tile 8 + 8 + 8 `tcgen05.mma` of 128x128x16. S and dP are single-buffered in TMEM (128 + 128 columns, dQ in
-// another 128): the softmax warps release them as soon as the second half of their columns is in registers, i.e.
-// after about half of their work on the tile, and the score products of the next tile run under the rest.
+// per tile 8 + 8 + 8 `tcgen05.mma` of 128x128x16. TMEM: S double-buffered (2 x 128 columns), dP single (128), dQ 128.
+// The softmax warps take their 64 dP columns into registers first and release the dP buffer at once, so dP of the
+// next tile is computed under their work on this one; S of the next tile was issued even earlier.
 // Shared memory (head_dim 128: 224 KB): K(i) stays resident until dQ(i) has completed, i.e. across the score products of
 // tile i+1, and its refill needs a TMA round trip on top, so K has THREE stages; V(i) is dead as soon as dP(i) has
 // completed and has ONE stage: V(i+1) is requested then and is first needed a whole tile later (S(i+1) goes first).
@@ -1011,9 +1020,11 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint64_t* k_empty = k_full + NS;         // [NS]
   uint64_t* v_full = k_empty + NS;
   uint64_t* v_empty = v_full + 1;
-  uint64_t* s_full = v_empty + 1;
-  uint64_t* s_free = s_full + 1;
-  uint64_t* ds_full = s_free + 1;
+  uint64_t* s_full = v_empty + 1;          // [2]
+  uint64_t* s_free = s_full + 2;           // [2]
+  uint64_t* dp_full = s_free + 2;
+  uint64_t* dp_free = dp_full + 1;
+  uint64_t* ds_full = dp_free + 1;
   uint64_t* ds_free = ds_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ds_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -1031,8 +1042,9 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     for (int i = 0; i < NS; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
     mbar_init(v_full, 1);
     mbar_init(v_empty, 1);
-    mbar_init(s_full, 1);
-    mbar_init(s_free, kSoftmaxWarps);
+    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], kSoftmaxWarps); }
+    mbar_init(dp_full, 1);
+    mbar_init(dp_free, kSoftmaxWarps);
     mbar_init(ds_full, kSoftmaxWarps);
     mbar_init(ds_free, 1);
     *abort_flag = 0;
@@ -1043,7 +1055,7 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t S_COL = 0, DP_COL = 128, DQ_COL = 256;
+  const uint32_t S_COL = 0, DP_COL = 256, DQ_COL = 384;   // two S buffers at 0 / 128
 
   if (warp == 0) {
     if (lane == 0) {
@@ -1077,17 +1089,26 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (lane == 0) {
       const uint32_t q_s = smem_u32(smem + SM::Q_OFF), do_s = smem_u32(smem + SM::DO_OFF);
       bool ok = mbar_wait(q_full, 0, abort_flag);
+      // S is double-buffered, dP single: S(i+1) is issued right behind dP(i) and is long complete when the softmax
+      // warps get to it; dP(i+1) waits until they have taken dP(i) into registers, which is the first thing they do.
       auto scores = [&](int i) -> bool {
-        const int sk = i % NS;
+        const int sk = i % NS, b = i & 1;
         if (!mbar_wait(&k_full[sk], (i / NS) & 1, abort_flag)) return false;
-        if (!mbar_wait(s_free, (uint32_t)(i & 1) ^ 1u, abort_flag)) return false;   // tile i-1's scores are in registers
+        OPK_TRACE(1, i, 0);
+        if (!mbar_wait(&s_free[b], (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag)) return false;   // tile i-2's scores were read
+        OPK_TRACE(1, i, 1);
         tc_fence_after();
-        issue_product<false, false>(tmem + S_COL, q_s, 128, smem_u32(smem + SM::K_OFF + sk * SM::KV_TILE), 128, 128, HD, false);
+        issue_product<false, false>(tmem + S_COL + b * 128, q_s, 128, smem_u32(smem + SM::K_OFF + sk * SM::KV_TILE), 128, 128, HD, false);
+        umma_commit(&s_full[b]);
+        OPK_TRACE(1, i, 2);
         if (!mbar_wait(v_full, i & 1, abort_flag)) return false;
+        if (!mbar_wait(dp_free, (uint32_t)(i & 1) ^ 1u, abort_flag)) return false;           // tile i-1's dP is in registers
+        OPK_TRACE(1, i, 3);
         tc_fence_after();
         issue_product<false, false>(tmem + DP_COL, do_s, 128, smem_u32(smem + SM::V_OFF), 128, 128, HD, false);
         umma_commit(v_empty);        // V(i) is dead once dP(i) has completed
-        umma_commit(s_full);
+        umma_commit(dp_full);
+        OPK_TRACE(1, i, 4);
         return true;
       };
       // The score products and the dQ products are issued by two threads of different warps (a thread's barrier
@@ -1101,12 +1122,14 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       for (int i = 0; i < n_it; ++i) {
         const int sk = i % NS;
         if (!mbar_wait(ds_full, i & 1, abort_flag)) break;
+        OPK_TRACE(0, i, 0);
         tc_fence_after();
         const uint32_t k_s = smem_u32(smem + SM::K_OFF + sk * SM::KV_TILE);
         // dQ[q x HD] += dS[q x 128 keys] * K[128 keys x HD]   (B rows = keys: MN-major)
         issue_product<false, true>(tmem + DQ_COL, ds_s, 128, k_s, 128, HD, 128, i > 0);
         umma_commit(&k_empty[sk]);
         umma_commit(ds_free);
+        OPK_TRACE(0, i, 1);
       }
     }
     __syncwarp();
@@ -1125,34 +1148,50 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     uint8_t* ds_chunk = smem + SM::DS_OFF + half * 16384;       // this warp's 64 keys are one 64-column chunk
     bool ok = true;
     for (int i = 0; i < n_it && ok; ++i) {
-      if (!warp_wait(s_full, i & 1, abort_flag, lane)) { ok = false; break; }
+      const int b = i & 1;
+      if (warp == 2 && lane == 0) OPK_TRACE(2, i, 0);
+      if (!warp_wait(dp_full, i & 1, abort_flag, lane)) { ok = false; break; }
+      if (warp == 2 && lane == 0) OPK_TRACE(2, i, 1);
       tc_fence_after();
       uint32_t dw0[16], dw1[16];
       const bool masked = (i == qt);              // the tile on the causal diagonal
       {
-        uint32_t sraw[32], draw[32];
+        // dP first, all 64 columns of this warp at once: the single dP buffer is free for tile i+1 right away
+        uint32_t draw0[32], draw1[32], sraw[32];
         __syncwarp();
-        tmem_ld32(tmem + lane_base + S_COL + c0, sraw);
-        tmem_ld32(tmem + lane_base + DP_COL + c0, draw);
-        tc_wait_ld();
-        if (masked) dq_chunk<true>(sraw, draw, c2, nl_r, d_r, r - c0, dw0);
-        else dq_chunk<false>(sraw, draw, c2, nl_r, d_r, 0, dw0);
-        __syncwarp();
-        tmem_ld32(tmem + lane_base + S_COL + c0 + 32, sraw);
-        tmem_ld32(tmem + lane_base + DP_COL + c0 + 32, draw);
+        tmem_ld32(tmem + lane_base + DP_COL + c0, draw0);
+        tmem_ld32(tmem + lane_base + DP_COL + c0 + 32, draw1);
         tc_wait_ld();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(s_free);        // all of this warp's scores are in registers
-        if (masked) dq_chunk<true>(sraw, draw, c2, nl_r, d_r, r - (c0 + 32), dw1);
-        else dq_chunk<false>(sraw, draw, c2, nl_r, d_r, 0, dw1);
+        if (lane == 0) mbar_arrive(dp_free);
+        if (warp == 2 && lane == 0) OPK_TRACE(2, i, 2);
+        if (!warp_wait(&s_full[b], (uint32_t)((i >> 1) & 1), abort_flag, lane)) { ok = false; break; }
+        tc_fence_after();
+        __syncwarp();
+        tmem_ld32(tmem + lane_base + S_COL + b * 128 + c0, sraw);
+        tc_wait_ld();
+        if (masked) dq_chunk<true>(sraw, draw0, c2, nl_r, d_r, r - c0, dw0);
+        else dq_chunk<false>(sraw, draw0, c2, nl_r, d_r, 0, dw0);
+        __syncwarp();
+        tmem_ld32(tmem + lane_base + S_COL + b * 128 + c0 + 32, sraw);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free[b]);    // all of this warp's scores are in registers
+        if (warp == 2 && lane == 0) OPK_TRACE(2, i, 3);
+        if (masked) dq_chunk<true>(sraw, draw1, c2, nl_r, d_r, r - (c0 + 32), dw1);
+        else dq_chunk<false>(sraw, draw1, c2, nl_r, d_r, 0, dw1);
       }
+      if (warp == 2 && lane == 0) OPK_TRACE(2, i, 4);
       if (i > 0 && !warp_wait(ds_free, (i - 1) & 1, abort_flag, lane)) { ok = false; break; }
+      if (warp == 2 && lane == 0) OPK_TRACE(2, i, 5);
       store_row32(ds_chunk, r, 0, dw0);
       store_row32(ds_chunk, r, 32, dw1);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(ds_full);
+      if (warp == 2 && lane == 0) OPK_TRACE(2, i, 6);
     }
     if (ok && warp_wait(ds_free, (n_it - 1) & 1, abort_flag, lane)) {
       tc_fence_after();
