@@ -3,8 +3,11 @@
 // (H+KV+g)*hd. head_dim is 64 or 128. One example (sequence) per launch; heads are the parallel dimension.
 //
 // Shared design of the three kernels (forward, dK/dV, dQ):
-//   * 320 threads: warp 0 = TMA producer, warp 1 = TMEM owner + UMMA issuer, warps 2..9 = softmax / epilogue with
-//     thread <-> TMEM lane (= row of the 128-row tile; warps w and w+4 share a lane quarter),
+//   * 384 threads: warp 0 = TMA producer (Q, K), warp 1 = TMEM owner + issuer of the score products, warps 2..9 =
+//     softmax / epilogue with thread <-> TMEM lane (= row of the 128-row tile; warps w and w+4 share a lane quarter),
+//     warps 10 and 11 = issuer of the second kind of products (P*V; dV and dK; dQ) and V producer (forward, dQ).
+//     Two issuing threads because a thread's barrier probes queue up behind the tensor-core instructions it has
+//     issued itself: one issuer alternating between the two kinds leaves the tensor core idle during its waits,
 //   * operand tiles are TMA boxes of 64 columns x R rows with 128-byte swizzle; a tile of hd columns is hd/64 such
 //     boxes. The same bytes serve as a K-major operand (rows = M/N index) or as an MN-major operand (rows = reduction
 //     index), which is what lets P^T / dS^T / K / Q / dO be reused across the five products without transposes,

@@ -33,6 +33,27 @@ def test_flash_forward(cuda, T, H, KV, hd):
     assert (out.float() - o_ref).abs().max().item() < 3e-2 * o_ref.abs().max().item() + 1e-3
 
 
+@pytest.mark.parametrize("T,H,KV,hd", [(1024, 4, 2, 128), (640, 4, 4, 64)])
+def test_flash_forward_growing_scores(cuda, T, H, KV, hd):
+    """Keys whose magnitude grows with the position: the row maxima jump by far more than the lazy-rescale
+    threshold from one key tile to the next, so the running maximum is replaced, the accumulators are rescaled and
+    a tile whose exponentials were taken against a stale maximum is done again."""
+    from opake_b200.ops.flash import flash_fwd
+    from opake_b200.ops._lib import raise_if_device_error
+
+    torch.manual_seed(2)
+    x = torch.randn(T, (H + 2 * KV) * hd, device=cuda)
+    ramp = torch.linspace(1.0, 30.0, T, device=cuda)[:, None]
+    x[:, H * hd : (H + KV) * hd] *= ramp
+    qkv = x.to(torch.bfloat16)
+    out, lse = flash_fwd(qkv, H, KV, hd)
+    raise_if_device_error(cuda)
+    _, o_ref, lse_ref = _ref(qkv, H, KV, hd)
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    assert (lse - lse_ref).abs().max().item() < 2e-2 + 2e-3 * lse_ref.abs().max().item()
+    assert (out.float() - o_ref).abs().max().item() < 3e-2 * o_ref.abs().max().item() + 1e-3
+
+
 @pytest.mark.parametrize("split", [True, False])
 @pytest.mark.parametrize("T,H,KV,hd", [(128, 2, 1, 128), (384, 4, 2, 128), (300, 4, 4, 64), (1024, 8, 2, 128)])
 def test_flash_backward(cuda, T, H, KV, hd, split):
