@@ -36,6 +36,19 @@ bool map2d(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint6
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// fp32 [slices][rows][cols] map with a {32 floats, 32 rows, 1} box and 128-byte swizzle (partial dK / dV stores)
+bool map3d_f32(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t slices) {
+  EncodeFn enc = encoder();
+  if (!enc || (reinterpret_cast<uintptr_t>(base) & 15) || (cols * 4) % 16) return false;
+  cuuint64_t dims[3] = {cols, rows, slices};
+  cuuint64_t strides[2] = {cols * 4, rows * cols * 4};
+  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, es,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <class K>
 bool set_smem(K kern, int bytes) {
   return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
@@ -94,6 +107,8 @@ extern "C" int opk_attn_bwd(const void* qkv, const void* out, const void* dout, 
   if (part && (reinterpret_cast<uintptr_t>(part) & 15)) return -1;
   p.part = (H > KV) ? part : nullptr;       // without grouping every CTA already owns its dK / dV tile
   const int dkv_grid = ((T + 127) / 128) * (p.part ? H : KV);
+  CUtensorMap tm_part = tm128;              // placeholder when there is no partial buffer (never dereferenced then)
+  if (p.part && !map3d_f32(&tm_part, p.part, (uint64_t)KV * hd, (uint64_t)T, (uint64_t)2 * (H / KV))) return -2;
   p.dout = dout; p.dqkv = dqkv; p.scale = scale; p.err = err;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(dout) & 15)) return -1;
@@ -106,13 +121,13 @@ extern "C" int opk_attn_bwd(const void* qkv, const void* out, const void* dout, 
     static bool once = set_smem(opk::attn_dkv_kernel<128>, opk::DkvSmem<128>::BYTES) &&
                        set_smem(opk::attn_dq128_kernel<128>, opk::Dq128Smem<128>::BYTES);
     if (!once) return -3;
-    opk::attn_dkv_kernel<128><<<dkv_grid, opk::kBwdThreads, opk::DkvSmem<128>::BYTES, st>>>(tm128, tm64, tmdo64, p);
+    opk::attn_dkv_kernel<128><<<dkv_grid, opk::kBwdThreads, opk::DkvSmem<128>::BYTES, st>>>(tm128, tm64, tmdo64, tm_part, p);
     opk::attn_dq128_kernel<128><<<n_kt * H, opk::kBwdThreads, opk::Dq128Smem<128>::BYTES, st>>>(tm128, tm128, tmdo128, p);
   } else {
     static bool once = set_smem(opk::attn_dkv_kernel<64>, opk::DkvSmem<64>::BYTES) &&
                        set_smem(opk::attn_dq128_kernel<64>, opk::Dq128Smem<64>::BYTES);
     if (!once) return -3;
-    opk::attn_dkv_kernel<64><<<dkv_grid, opk::kBwdThreads, opk::DkvSmem<64>::BYTES, st>>>(tm128, tm64, tmdo64, p);
+    opk::attn_dkv_kernel<64><<<dkv_grid, opk::kBwdThreads, opk::DkvSmem<64>::BYTES, st>>>(tm128, tm64, tmdo64, tm_part, p);
     opk::attn_dq128_kernel<64><<<n_kt * H, opk::kBwdThreads, opk::Dq128Smem<64>::BYTES, st>>>(tm128, tm128, tmdo128, p);
   }
   if (p.part) {

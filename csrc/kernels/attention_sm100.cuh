@@ -55,6 +55,14 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
                : "memory");
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
+// 3-D TMA store of one box (the tensor map fixes its shape), joined to the calling thread's current bulk group by
+// the next commit.
+__device__ __forceinline__ void tma_store_3d_nocommit(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // The calling thread's bulk stores have finished reading shared memory.
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
@@ -783,7 +791,8 @@ __device__ __forceinline__ void dkv_chunk(const uint32_t (&sraw)[32], const uint
 template <int HD>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_q,
-                const __grid_constant__ CUtensorMap tm_do, const AttnParams p) {
+                const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_part,
+                const AttnParams p) {
   using SM = DkvSmem<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -947,11 +956,41 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
     if (ok && warp_wait(&pd_free[(n_it - 1) & 1], (uint32_t)(((n_it - 1) >> 1) & 1), abort_flag, lane)) {
       tc_fence_after();
       if (split) {
-        const long long kvw = (long long)p.KV * HD;
-        float* pk = p.part + ((long long)(h_first % G) * p.T + key) * kvw + g * HD + half * (HD / 2);
-        float* pv = pk + (long long)G * p.T * kvw;
-        store_acc_rows_f32<HD / 2>(tmem + lane_base + DK_COL + half * (HD / 2), pk, key < p.T, p.scale);
-        store_acc_rows_f32<HD / 2>(tmem + lane_base + DV_COL + half * (HD / 2), pv, key < p.T, 1.f);
+        // fp32 partials part[dK | dV][query head of the group][t][KV * HD]: each warp stages its 32 key rows x HD/2
+        // columns of both matrices in the (now dead) Q / dO ring as {32 floats, 32 rows} boxes with 128-byte swizzle
+        // and stores them with TMA, which also clips the rows past T.
+        constexpr int NB = HD / 64;                                  // boxes per matrix and warp
+        uint8_t* stage = smem + SM::Q_OFF + (warp - 2) * (2 * NB * 4096);
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+          const float mul = m == 0 ? p.scale : 1.f;
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            uint32_t raw[32];
+            __syncwarp();
+            tmem_ld32(tmem + lane_base + (m == 0 ? DK_COL : DV_COL) + half * (HD / 2) + b * 32, raw);
+            tc_wait_ld();
+            uint8_t* box = stage + (m * NB + b) * 4096 + lane * 128;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<float4*>(box + ((q ^ (lane & 7)) << 4)) =
+                  make_float4(__uint_as_float(raw[4 * q]) * mul, __uint_as_float(raw[4 * q + 1]) * mul,
+                              __uint_as_float(raw[4 * q + 2]) * mul, __uint_as_float(raw[4 * q + 3]) * mul);
+          }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0 && kt * 128 + quad * 32 < p.T) {
+#pragma unroll
+          for (int m = 0; m < 2; ++m)
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+              tma_store_3d_nocommit(&tm_part, stage + (m * NB + b) * 4096, g * HD + half * (HD / 2) + b * 32,
+                                    kt * 128 + quad * 32, m * G + (h_first % G));
+          tma_store_commit();
+          tma_store_wait_read();
+        }
+        __syncwarp();
       } else {
         __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.dqkv) + (long long)key * p.ld + half * (HD / 2);
         store_acc_rows<HD / 2>(tmem + lane_base + DV_COL + half * (HD / 2), base + v_col, key < p.T, 1.f);
