@@ -107,6 +107,8 @@ extern "C" int opk_attn_bwd(const void* qkv, const void* out, const void* dout, 
   if (part && (reinterpret_cast<uintptr_t>(part) & 15)) return -1;
   p.part = (H > KV) ? part : nullptr;       // without grouping every CTA already owns its dK / dV tile
   const int dkv_grid = ((T + 127) / 128) * (p.part ? H : KV);
+  CUtensorMap tm_dq;                        // dQ rows leave through TMA stores of {64 columns, 32 rows} boxes (head_dim 128)
+  if (!map2d(&tm_dq, dqkv, cols, (uint64_t)T, (uint64_t)ld, 32)) return -2;
   CUtensorMap tm_part = tm128;              // placeholder when there is no partial buffer (never dereferenced then)
   if (p.part && !map3d_f32(&tm_part, p.part, (uint64_t)KV * hd, (uint64_t)T, (uint64_t)2 * (H / KV))) return -2;
   p.dout = dout; p.dqkv = dqkv; p.scale = scale; p.err = err;
@@ -122,13 +124,13 @@ extern "C" int opk_attn_bwd(const void* qkv, const void* out, const void* dout, 
                        set_smem(opk::attn_dq128_kernel<128>, opk::Dq128Smem<128>::BYTES);
     if (!once) return -3;
     opk::attn_dkv_kernel<128><<<dkv_grid, opk::kBwdThreads, opk::DkvSmem<128>::BYTES, st>>>(tm128, tm64, tmdo64, tm_part, p);
-    opk::attn_dq128_kernel<128><<<n_kt * H, opk::kBwdThreads, opk::Dq128Smem<128>::BYTES, st>>>(tm128, tm128, tmdo128, p);
+    opk::attn_dq128_kernel<128><<<n_kt * H, opk::kBwdThreads, opk::Dq128Smem<128>::BYTES, st>>>(tm128, tm128, tmdo128, tm_dq, p);
   } else {
     static bool once = set_smem(opk::attn_dkv_kernel<64>, opk::DkvSmem<64>::BYTES) &&
                        set_smem(opk::attn_dq128_kernel<64>, opk::Dq128Smem<64>::BYTES);
     if (!once) return -3;
     opk::attn_dkv_kernel<64><<<dkv_grid, opk::kBwdThreads, opk::DkvSmem<64>::BYTES, st>>>(tm128, tm64, tmdo64, tm_part, p);
-    opk::attn_dq128_kernel<64><<<n_kt * H, opk::kBwdThreads, opk::Dq128Smem<64>::BYTES, st>>>(tm128, tm128, tmdo128, p);
+    opk::attn_dq128_kernel<64><<<n_kt * H, opk::kBwdThreads, opk::Dq128Smem<64>::BYTES, st>>>(tm128, tm128, tmdo128, tm_dq, p);
   }
   if (p.part) {
     const int kvw = KV * hd;

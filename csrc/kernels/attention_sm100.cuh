@@ -837,6 +837,14 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
     }
     *abort_flag = 0;
     fence_barrier_init();
+    // K, V and the first Q / dO sub-tile are requested before the CTA-wide set-up barrier: their latency runs under
+    // the TMEM allocation.
+    tma_prefetch_desc(&tm_kv); tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_do);
+    mbar_expect_tx(kv_full, 2 * SM::KV_TILE);
+    for (int c = 0; c < HD / 64; ++c) {
+      tma_load_2d(smem + SM::K_OFF + c * 16384, &tm_kv, kv_full, k_col + c * 64, kt * 128);
+      tma_load_2d(smem + SM::V_OFF + c * 16384, &tm_kv, kv_full, v_col + c * 64, kt * 128);
+    }
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -848,12 +856,7 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant
 
   if (warp == 0) {
     if (lane == 0) {
-      tma_prefetch_desc(&tm_kv); tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_do);
-      mbar_expect_tx(kv_full, 2 * SM::KV_TILE);
-      for (int c = 0; c < HD / 64; ++c) {
-        tma_load_2d(smem + SM::K_OFF + c * 16384, &tm_kv, kv_full, k_col + c * 64, kt * 128);
-        tma_load_2d(smem + SM::V_OFF + c * 16384, &tm_kv, kv_full, v_col + c * 64, kt * 128);
-      }
+      tma_prefetch_desc(&tm_part);
       for (int i = 0; i < n_it; ++i) {
         const int s = i % NS;
         const uint32_t ph = (i / NS) & 1;
@@ -1047,7 +1050,8 @@ struct Dq128Smem {
 template <int HD>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
-                  const __grid_constant__ CUtensorMap tm_do, const AttnParams p) {
+                  const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_dq,
+                  const AttnParams p) {
   using SM = Dq128Smem<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -1091,6 +1095,16 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     mbar_init(ds_free, 1);
     *abort_flag = 0;
     fence_barrier_init();
+    // Q, dO and the first K tile are requested before the CTA-wide set-up barrier: their latency runs under the
+    // TMEM allocation.
+    tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_kv); tma_prefetch_desc(&tm_do);
+    mbar_expect_tx(q_full, 2 * SM::Q_TILE);
+    for (int c = 0; c < HD / 64; ++c) {
+      tma_load_2d(smem + SM::Q_OFF + c * 16384, &tm_q, q_full, q_col + c * 64, qt * 128);
+      tma_load_2d(smem + SM::DO_OFF + c * 16384, &tm_do, q_full, q_col + c * 64, qt * 128);
+    }
+    mbar_expect_tx(&k_full[0], SM::KV_TILE);
+    for (int c = 0; c < HD / 64; ++c) tma_load_2d(smem + SM::K_OFF + c * 16384, &tm_kv, &k_full[0], k_col + c * 64, 0);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -1101,13 +1115,8 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
   if (warp == 0) {
     if (lane == 0) {
-      tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_kv); tma_prefetch_desc(&tm_do);
-      mbar_expect_tx(q_full, 2 * SM::Q_TILE);
-      for (int c = 0; c < HD / 64; ++c) {
-        tma_load_2d(smem + SM::Q_OFF + c * 16384, &tm_q, q_full, q_col + c * 64, qt * 128);
-        tma_load_2d(smem + SM::DO_OFF + c * 16384, &tm_do, q_full, q_col + c * 64, qt * 128);
-      }
-      for (int i = 0; i < n_it; ++i) {
+      tma_prefetch_desc(&tm_dq);
+      for (int i = 1; i < n_it; ++i) {          // K(0) was requested during the set-up
         const int s = i % NS;
         if (!mbar_wait(&k_empty[s], (uint32_t)((i / NS) & 1) ^ 1u, abort_flag)) break;
         mbar_expect_tx(&k_full[s], SM::KV_TILE);
@@ -1237,8 +1246,37 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
     if (ok && warp_wait(ds_free, (n_it - 1) & 1, abort_flag, lane)) {
       tc_fence_after();
-      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.dqkv) + (long long)qrow * p.ld + q_col + half * (HD / 2);
-      store_acc_rows<HD / 2>(tmem + lane_base + DQ_COL + half * (HD / 2), dst, qvalid, p.scale);
+      if (HD == 128) {
+        // this warp's 32 rows x 64 columns are staged in the (now dead) dS buffer in the swizzled row layout and
+        // leave with one TMA store, which clips the rows past T
+        uint8_t* chunk = smem + SM::DS_OFF + half * 16384;
+#pragma unroll
+        for (int cc = 0; cc < 64; cc += 32) {
+          uint32_t raw[32];
+          __syncwarp();
+          tmem_ld32(tmem + lane_base + DQ_COL + half * 64 + cc, raw);
+          tc_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(raw[8 * q + 0]) * p.scale, __uint_as_float(raw[8 * q + 1]) * p.scale);
+            o.y = pack_bf16x2(__uint_as_float(raw[8 * q + 2]) * p.scale, __uint_as_float(raw[8 * q + 3]) * p.scale);
+            o.z = pack_bf16x2(__uint_as_float(raw[8 * q + 4]) * p.scale, __uint_as_float(raw[8 * q + 5]) * p.scale);
+            o.w = pack_bf16x2(__uint_as_float(raw[8 * q + 6]) * p.scale, __uint_as_float(raw[8 * q + 7]) * p.scale);
+            *reinterpret_cast<uint4*>(chunk + swz_off(r, cc + q * 8)) = o;
+          }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0 && qt * 128 + quad * 32 < p.T) {
+          tma_store_2d(&tm_dq, chunk + quad * 32 * 128, q_col + half * 64, qt * 128 + quad * 32);
+          tma_store_wait_read();
+        }
+        __syncwarp();
+      } else {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.dqkv) + (long long)qrow * p.ld + q_col + half * (HD / 2);
+        store_acc_rows<HD / 2>(tmem + lane_base + DQ_COL + half * (HD / 2), dst, qvalid, p.scale);
+      }
     }
   }
   tc_fence_before();
