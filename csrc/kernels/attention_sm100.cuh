@@ -253,8 +253,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ 
   uint64_t* p_full = bars + 14;   // [2]
   uint64_t* o_done = bars + 16;   // [2] P*V of a tile has completed (its P buffer is reusable, its accumulator consistent)
   uint64_t* o_free = bars + 18;   // all eight softmax warps have read the item's accumulators (and the exchange area)
-  uint64_t* x_bar = bars + 19;    // [4] rendezvous of the two warps of a TMEM lane quarter before the merge
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
+  uint64_t* xr = bars + 19;       // [2 groups][4 quads] the warp's (maximum, row sum) of the item are in the exchange
+                                  // area and, if its group owns the item's last tile, that tile's P*V has completed
+  uint64_t* stage_free = bars + 27;   // [2] the other group has read its staged output out of group b's buffer
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 29);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* xchg = reinterpret_cast<float*>(bars + 32);   // [2 groups][128 rows] running maxima, then [2][128] row sums
 
@@ -273,7 +275,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ 
       mbar_init(&p_full[i], kSoftmaxWarps / 2); mbar_init(&o_done[i], 1);
     }
     mbar_init(o_free, kSoftmaxWarps);
-    for (int i = 0; i < 4; ++i) mbar_init(&x_bar[i], 2);
+    for (int i = 0; i < 8; ++i) mbar_init(&xr[i], 1);
+    for (int i = 0; i < 2; ++i) mbar_init(&stage_free[i], kSoftmaxWarps / 2);
     *abort_flag = 0;
     fence_barrier_init();
     // The producer thread starts the loads of Q and of the first K tile of its first item before the CTA-wide setup
@@ -439,12 +442,97 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ 
     const float c2 = p.scale * 1.4426950408889634f;
     int t_base = 0;
     bool ok = true;
+    // An item ends with an epilogue that merges the two groups' accumulators. The group that owns the item's last key
+    // tile runs it as soon as that tile's P*V has completed. The other group is done a tile earlier: instead of
+    // waiting it publishes its (maximum, row sum), goes on with the first tile of the next item (whose P*V the issuer
+    // holds back until both groups have read the accumulators) and runs the deferred epilogue right after it.
+    bool pend = false;              // a deferred epilogue: item rank, index, first stream tile, tiles, this group's state
+    int pend_w = 0, pend_k = 0, pend_tb = 0, pend_n = 0;
+    float pend_m = 0.f, pend_l = 0.f;
+    bool stage_wait = false;        // the other group staged its output in this group's buffer: wait before writing P
+    int own_cnt = 0;                // items so far whose last tile this group owned (phase of stage_free[grp])
+    uint32_t stage_par = 0;
+    // Merge and store the output rows of item (e_w, e_k) whose stream started at tile e_tb with e_n tiles; e_m / e_l are
+    // this group's maximum and row sum. O = (a * O_0 + b * O_1) / (a * l_0 + b * l_1), a, b = 2^(c2 * (m_g - max)).
+    // Group g writes output columns [g * HD/2, (g+1) * HD/2).
+    auto epilogue = [&](int e_w, int e_k, int e_tb, int e_n, float e_m, float e_l) -> bool {
+      const FwdItem eit = fwd_item(e_w, n_qt, p.H, p.KV);
+      const int qt = eit.qt, h = eit.h;
+      const int row = qt * 128 + r;
+      const bool owner = ((e_tb + e_n - 1) & 1) == grp;
+      // the other group's values; from the owner they also tell that every P*V of the item has completed
+      if (!warp_wait(&xr[(grp ^ 1) * 4 + quad], (uint32_t)(e_k & 1), abort_flag, lane)) return false;
+      if (e_k == OPK_TRACE_K && quad == 2 && lane == 0) OPK_TRACE(2, 100 + grp, 0);
+      tc_fence_after();
+      const float m_o = xchg[(grp ^ 1) * 128 + r], l_o = xchg[256 + (grp ^ 1) * 128 + r];
+      const float m_tot = fmaxf(e_m, m_o);
+      const float w_me = ex2_approx((e_m - m_tot) * c2), w_o = ex2_approx((m_o - m_tot) * c2);
+      const float l_tot = w_me * e_l + w_o * l_o;
+      const float inv = 1.f / l_tot;
+      const float w0 = (grp == 0 ? w_me : w_o) * inv, w1 = (grp == 0 ? w_o : w_me) * inv;
+      // with a single key tile only the accumulator of the group that owned it was written
+      const bool has0 = e_n > 1 || (e_tb & 1) == 0, has1 = e_n > 1 || (e_tb & 1) == 1;
+      const uint32_t o0 = tmem + lane_base + O_COL + grp * (HD / 2), o1 = o0 + 128;
+      // HD = 128: the group's 64 output columns are staged in the swizzled row layout and each warp stores its 32
+      // rows with one TMA store, which clips the rows past T. The owner stages in the first half of its own
+      // probability buffer (free: its last P*V is complete); the other group's own buffer already holds the
+      // probabilities of the next item, so it borrows the second half of the owner's. HD = 64: written directly.
+      uint8_t* stage = owner ? p_smem : smem + SM::P_OFF + (grp ^ 1) * SM::P_BYTES + 16384;
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ldo + h * HD + grp * (HD / 2);
+#pragma unroll
+      for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+        uint32_t ra[32], rb[32];
+        __syncwarp();
+        tmem_ld32(o0 + c0, ra);                 // an accumulator without a tile holds stale bits: dropped below
+        tmem_ld32(o1 + c0, rb);
+        tc_wait_ld();
+        if (c0 + 32 >= HD / 2) {                  // last accumulator read of the item by this warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(o_free);
+        }
+        if (HD == 128 || row < p.T) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              v[i] = __uint_as_float(has0 ? ra[8 * q + i] : 0u) * w0;
+              v[i] = fmaf(__uint_as_float(has1 ? rb[8 * q + i] : 0u), w1, v[i]);
+            }
+            uint4 o;
+            o.x = pack_bf16x2(v[0], v[1]);
+            o.y = pack_bf16x2(v[2], v[3]);
+            o.z = pack_bf16x2(v[4], v[5]);
+            o.w = pack_bf16x2(v[6], v[7]);
+            if (HD == 128) *reinterpret_cast<uint4*>(stage + swz_off(r, c0 + q * 8)) = o;
+            else *reinterpret_cast<uint4*>(orow + c0 + q * 8) = o;
+          }
+        }
+      }
+      if (HD == 128) {
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0 && qt * 128 + quad * 32 < p.T)
+          tma_store_2d(&tm_out, stage + quad * 32 * 128, h * HD + grp * 64, qt * 128 + quad * 32);
+      }
+      if (!owner) {                               // hand the borrowed half back once the store has read it
+        if (lane == 0) {
+          if (HD == 128) tma_store_wait_read();
+          mbar_arrive(&stage_free[grp ^ 1]);
+        }
+      }
+      __syncwarp();
+      if (grp == 0 && row < p.T) p.lse[(long long)h * p.T + row] = m_tot * p.scale + logf(l_tot);
+      if (e_k == OPK_TRACE_K && quad == 2 && lane == 0) OPK_TRACE(2, 100 + grp, 1);
+      if (quad == 2 && lane == 0 && grp == 0) OPK_TRACE_ITEM(e_w, 1);
+      return true;
+    };
     for (int k = 0; ok; ++k) {
       const int w = fwd_rank(k, cta, G);
       if (w >= n_items) break;
       const FwdItem it = fwd_item(w, n_qt, p.H, p.KV);
-      const int qt = it.qt, h = it.h, n_kv = it.n_kv;
-      const int row = qt * 128 + r;
+      const int qt = it.qt, n_kv = it.n_kv;
       if (quad == 2 && lane == 0 && grp == 0) OPK_TRACE_ITEM(w, 0);
       if (HD == 128) {                         // this warp's output slab of the previous item has left shared memory
         if (lane == 0) tma_store_wait_read();
@@ -501,6 +589,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ 
         const unsigned any_grow = __ballot_sync(0xffffffffu, grow);
         // P buffer and accumulator of this group were last used by the P*V of stream tile t-2
         if (t > 1 && !warp_wait(&o_done[grp], ph ^ 1u, abort_flag, lane)) { tc_wait_ld(); ok = false; break; }
+        if (stage_wait) {          // ... and its second half by the other group's staged output of an earlier item
+          if (!warp_wait(&stage_free[grp], stage_par, abort_flag, lane)) { tc_wait_ld(); ok = false; break; }
+          stage_wait = false;
+        }
         float alpha = 1.f;
         if (grow) {
           alpha = ex2_approx((m_run - mx) * c2);     // 0 when m_run = -inf
@@ -547,78 +639,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[grp]);
         if (k == OPK_TRACE_K && quad == 2 && lane == 0) OPK_TRACE(2, j, 6);
+        if (pend) {                // the previous item's epilogue, deferred past this group's first tile of this item
+          pend = false;
+          if (!epilogue(pend_w, pend_k, pend_tb, pend_n, pend_m, pend_l)) { ok = false; break; }
+        }
       }
       if (!ok) break;
-      // The group's last tile of the item has been accumulated: exchange (maximum, row sum) with the other group and
-      // merge the two accumulators, O = (a * O_0 + b * O_1) / (a * l_0 + b * l_1), a, b = 2^(c2 * (m_g - max(m_0, m_1))).
-      // Group g writes output columns [g * HD/2, (g+1) * HD/2).
+      // This group's tiles of the item are done: publish (maximum, row sum), then run the epilogue now or defer it.
       const int n_mine = (n_kv - j0 + 1) / 2;      // tiles of this item that this group processed
-      if (n_mine > 0) {
+      const bool owner = ((t_base + n_kv - 1) & 1) == grp;
+      if (owner) {                                 // the owner's publication also vouches for the last P*V
         const int t_last = t_base + j0 + 2 * (n_mine - 1);
         if (!warp_wait(&o_done[grp], (uint32_t)((t_last >> 1) & 1), abort_flag, lane)) { ok = false; break; }
       }
       // the exchange area is rewritten only after every warp has read the previous item's values
       if (k > 0 && !warp_wait(o_free, (uint32_t)((k - 1) & 1), abort_flag, lane)) { ok = false; break; }
-      if (k == OPK_TRACE_K && quad == 2 && lane == 0) OPK_TRACE(2, 100 + grp, 0);
-      tc_fence_after();
       xchg[grp * 128 + r] = m_run;
       xchg[256 + grp * 128 + r] = l_run;
-      if (!pair_sync(&x_bar[quad], (uint32_t)(k & 1), abort_flag, lane)) { ok = false; break; }
-      tc_fence_after();
-      const float m_o = xchg[(grp ^ 1) * 128 + r], l_o = xchg[256 + (grp ^ 1) * 128 + r];
-      const float m_tot = fmaxf(m_run, m_o);
-      const float w_me = ex2_approx((m_run - m_tot) * c2), w_o = ex2_approx((m_o - m_tot) * c2);
-      const float l_tot = w_me * l_run + w_o * l_o;
-      const float inv = 1.f / l_tot;
-      const float w0 = (grp == 0 ? w_me : w_o) * inv, w1 = (grp == 0 ? w_o : w_me) * inv;
-      // with a single key tile only the accumulator of the group that owned it was written
-      const bool has0 = n_kv > 1 || (t_base & 1) == 0, has1 = n_kv > 1 || (t_base & 1) == 1;
-      const uint32_t o0 = tmem + lane_base + O_COL + grp * (HD / 2), o1 = o0 + 128;
-      // HD = 128: the group's 64 output columns are staged in its probability buffer (free now) in the swizzled
-      // row layout and each warp stores its 32 rows with one TMA store, which clips the rows past T.
-      // HD = 64: 32 columns per group, written directly.
-      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ldo + h * HD + grp * (HD / 2);
-#pragma unroll
-      for (int c0 = 0; c0 < HD / 2; c0 += 32) {
-        uint32_t ra[32], rb[32];
-        __syncwarp();
-        tmem_ld32(o0 + c0, ra);                 // an accumulator without a tile holds stale bits: dropped below
-        tmem_ld32(o1 + c0, rb);
-        tc_wait_ld();
-        if (c0 + 32 >= HD / 2) {                  // last accumulator read of the item by this warp
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(o_free);
-        }
-        if (HD == 128 || row < p.T) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              v[i] = __uint_as_float(has0 ? ra[8 * q + i] : 0u) * w0;
-              v[i] = fmaf(__uint_as_float(has1 ? rb[8 * q + i] : 0u), w1, v[i]);
-            }
-            uint4 o;
-            o.x = pack_bf16x2(v[0], v[1]);
-            o.y = pack_bf16x2(v[2], v[3]);
-            o.z = pack_bf16x2(v[4], v[5]);
-            o.w = pack_bf16x2(v[6], v[7]);
-            if (HD == 128) *reinterpret_cast<uint4*>(p_smem + swz_off(r, c0 + q * 8)) = o;
-            else *reinterpret_cast<uint4*>(orow + c0 + q * 8) = o;
-          }
-        }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&xr[grp * 4 + quad]);
+      if (owner) {
+        // before this group writes probabilities again, the other group's staged rows must have left its buffer
+        stage_wait = true;
+        stage_par = (uint32_t)(own_cnt & 1);
+        ++own_cnt;
+        if (!epilogue(w, k, t_base, n_kv, m_run, l_run)) { ok = false; break; }
+      } else if (fwd_rank(k + 1, cta, G) < n_items) {
+        pend = true;
+        pend_w = w; pend_k = k; pend_tb = t_base; pend_n = n_kv; pend_m = m_run; pend_l = l_run;
+      } else {
+        if (!epilogue(w, k, t_base, n_kv, m_run, l_run)) { ok = false; break; }
       }
-      if (HD == 128) {
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0 && qt * 128 + quad * 32 < p.T)
-          tma_store_2d(&tm_out, p_smem + quad * 32 * 128, h * HD + grp * 64, qt * 128 + quad * 32);
-        __syncwarp();
-      }
-      if (grp == 0 && row < p.T) p.lse[(long long)h * p.T + row] = m_tot * p.scale + logf(l_tot);
-      if (k == OPK_TRACE_K && quad == 2 && lane == 0) OPK_TRACE(2, 100 + grp, 1);
-      if (quad == 2 && lane == 0 && grp == 0) OPK_TRACE_ITEM(w, 1);
       t_base += n_kv;
     }
     if (HD == 128 && lane == 0) tma_store_wait_read();   // shared memory must outlive the stores' reads
