@@ -94,8 +94,10 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 // ------------------------------------------------------------------------------------------------ forward
-// CTA = (query tile of 128 rows, head). KV tiles of 128 keys, double-buffered K and V stages. The key tiles are split
-// between two softmax groups of four warps: even tiles go to group 0, odd tiles to group 1, and each group has its own
+// Work item = (query tile of 128 rows, head). One persistent CTA per SM walks a balanced share of the items, heavy
+// ones first; the key tiles of its items form one stream, so the loads and score products of an item start under the
+// tail of the one before. KV tiles of 128 keys, double-buffered K and V stages. The key tiles are split
+// between two softmax groups of four warps: even tiles of the stream go to group 0, odd tiles to group 1, and each group has its own
 // score buffer and its own output accumulator in TMEM (4 x 128 columns), its own probability buffer in shared memory
 // and its own running maximum and row sum, as if the keys had been split in two; the two partial results are merged
 // once, in the epilogue. One group's exponentials therefore run under the other group's waits and under the tensor
