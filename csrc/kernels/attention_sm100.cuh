@@ -157,41 +157,22 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
-// Maximum of 64 scores (columns col0 .. col0+63 of the tile) with four independent chains; MASKED drops columns > r.
-template <bool MASKED>
-__device__ __forceinline__ float row_max64(const uint32_t (&a)[32], const uint32_t (&b)[32], int col0, int r) {
+// Maximum of 64 scores with four independent chains of three-input maxima (two columns per instruction). The causal
+// mask needs no variant here: the forward kernel writes -inf over the masked scores of a diagonal tile beforehand.
+__device__ __forceinline__ float row_max64(const uint32_t (&a)[32], const uint32_t (&b)[32]) {
   float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-  if (!MASKED) {
 #pragma unroll
-    for (int i = 0; i < 32; i += 4) {   // three-input maximum: two columns per instruction
-      m0 = fmax3(m0, __uint_as_float(a[i]), __uint_as_float(a[i + 1]));
-      m1 = fmax3(m1, __uint_as_float(a[i + 2]), __uint_as_float(a[i + 3]));
-      m2 = fmax3(m2, __uint_as_float(b[i]), __uint_as_float(b[i + 1]));
-      m3 = fmax3(m3, __uint_as_float(b[i + 2]), __uint_as_float(b[i + 3]));
-    }
-    return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-  }
-#pragma unroll
-  for (int i = 0; i < 32; i += 2) {
-    if (col0 + i <= r) m0 = fmaxf(m0, __uint_as_float(a[i]));
-    if (col0 + i + 1 <= r) m1 = fmaxf(m1, __uint_as_float(a[i + 1]));
-    if (col0 + 32 + i <= r) m2 = fmaxf(m2, __uint_as_float(b[i]));
-    if (col0 + 33 + i <= r) m3 = fmaxf(m3, __uint_as_float(b[i + 1]));
+  for (int i = 0; i < 32; i += 4) {
+    m0 = fmax3(m0, __uint_as_float(a[i]), __uint_as_float(a[i + 1]));
+    m1 = fmax3(m1, __uint_as_float(a[i + 2]), __uint_as_float(a[i + 3]));
+    m2 = fmax3(m2, __uint_as_float(b[i]), __uint_as_float(b[i + 1]));
+    m3 = fmax3(m3, __uint_as_float(b[i + 2]), __uint_as_float(b[i + 3]));
   }
   return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
 
-// Rendezvous of the two warps that share a TMEM lane quarter, on an mbarrier of count 2 (bounded like every wait
-// here; a named bar.sync would hang the partner if one side had given up). Shared-memory writes made before the
-// call are visible to the partner after it.
-__device__ __forceinline__ bool pair_sync(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane) {
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar);
-  return warp_wait(bar, parity, abort_flag, lane);
-}
-
 // exp2(x * c2 - mc) for 32 columns starting at col0, packed to bf16 and stored swizzled; returns the partial row sum.
-template <bool MASKED>
+// Masked scores arrive as -inf and come out as exact zeros.
 __device__ __forceinline__ float softmax_chunk(const uint32_t (&x)[32], int col0, int r, float c2, float mc,
                                                uint8_t* p_smem) {
   float sum0 = 0.f, sum1 = 0.f;
@@ -200,10 +181,6 @@ __device__ __forceinline__ float softmax_chunk(const uint32_t (&x)[32], int col0
   for (int i = 0; i < 32; i += 2) {
     float e0 = ex2_approx(fmaf(__uint_as_float(x[i]), c2, -mc));
     float e1 = ex2_approx(fmaf(__uint_as_float(x[i + 1]), c2, -mc));
-    if (MASKED) {
-      if (col0 + i > r) e0 = 0.f;
-      if (col0 + i + 1 > r) e1 = 0.f;
-    }
     sum0 += e0;
     sum1 += e1;
     packed[i >> 1] = pack_bf16x2(e0, e1);
@@ -581,7 +558,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ 
           __syncwarp();
           tmem_ld32(s_addr + c0, x0); tmem_ld32(s_addr + c0 + 32, x1);
           tc_wait_ld();
-          mx = fmaxf(mx, row_max64<false>(x0, x1, c0, r));
+          mx = fmaxf(mx, row_max64(x0, x1));
         }
         __syncwarp();
         tmem_ld32(s_addr, x0);                     // first chunk of pass 2, in flight during the bookkeeping below
@@ -623,7 +600,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ 
           tc_wait_ld();
           __syncwarp();
           tmem_ld32(s_addr + c0 + 32, x1);
-          l_run += softmax_chunk<false>(x0, c0, r, c2, mc, p_smem);
+          l_run += softmax_chunk(x0, c0, r, c2, mc, p_smem);
           tc_wait_ld();
           __syncwarp();
           if (c0 == 0) {
@@ -633,7 +610,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ 
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_free[grp]);   // the whole score tile has been read
           }
-          l_run += softmax_chunk<false>(x1, c0 + 32, r, c2, mc, p_smem);
+          l_run += softmax_chunk(x1, c0 + 32, r, c2, mc, p_smem);
         }
 #endif
         if (k == OPK_TRACE_K && quad == 2 && lane == 0) OPK_TRACE(2, j, 5);
@@ -742,25 +719,6 @@ __device__ __forceinline__ void store_acc_rows(uint32_t tmem_addr, __nv_bfloat16
         o.w = pack_bf16x2(__uint_as_float(raw[8 * q + 6]) * mul, __uint_as_float(raw[8 * q + 7]) * mul);
         *reinterpret_cast<uint4*>(dst + c0 + q * 8) = o;
       }
-    }
-  }
-}
-
-// Same, keeping fp32 (partial results that a later kernel sums).
-template <int NCOLS>
-__device__ __forceinline__ void store_acc_rows_f32(uint32_t tmem_addr, float* dst, bool valid, float mul) {
-#pragma unroll
-  for (int c0 = 0; c0 < NCOLS; c0 += 32) {
-    uint32_t raw[32];
-    __syncwarp();
-    tmem_ld32(tmem_addr + c0, raw);
-    tc_wait_ld();
-    if (valid) {
-#pragma unroll
-      for (int q = 0; q < 8; ++q)
-        *reinterpret_cast<float4*>(dst + c0 + q * 4) =
-            make_float4(__uint_as_float(raw[4 * q]) * mul, __uint_as_float(raw[4 * q + 1]) * mul,
-                        __uint_as_float(raw[4 * q + 2]) * mul, __uint_as_float(raw[4 * q + 3]) * mul);
     }
   }
 }
