@@ -107,6 +107,8 @@ extern "C" int opk_attn_bwd(const void* qkv, const void* out, const void* dout, 
   if (part && (reinterpret_cast<uintptr_t>(part) & 15)) return -1;
   p.part = (H > KV) ? part : nullptr;       // without grouping every CTA already owns its dK / dV tile
   const int dkv_grid = ((T + 127) / 128) * (p.part ? H : KV);
+  CUtensorMap tm_o128;                      // O tiles for the row sums of dO * O (taken in the dQ kernel)
+  if (!map2d(&tm_o128, out, (uint64_t)H * hd, (uint64_t)T, (uint64_t)ldo, 128)) return -2;
   CUtensorMap tm_dq;                        // dQ rows leave through TMA stores of {64 columns, 32 rows} boxes (head_dim 128)
   if (!map2d(&tm_dq, dqkv, cols, (uint64_t)T, (uint64_t)ld, 32)) return -2;
   CUtensorMap tm_part = tm128;              // placeholder when there is no partial buffer (never dereferenced then)
@@ -114,23 +116,20 @@ extern "C" int opk_attn_bwd(const void* qkv, const void* out, const void* dout, 
   p.dout = dout; p.dqkv = dqkv; p.scale = scale; p.err = err;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(dout) & 15)) return -1;
-  const long long dsum_threads = (long long)T64 * H * (hd / 8);   // hd / 8 lanes per (t, h) row, 16 bytes each
-  opk::attn_dsum_kernel<<<(unsigned)((dsum_threads + 255) / 256), 256, 0, st>>>(
-      reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), lse, dsum,
-      dsum + (long long)H * T64, T, T64, H, hd, ldo);
   const int n_kt = (T + 127) / 128;
   if (hd == 128) {
     static bool once = set_smem(opk::attn_dkv_kernel<128>, opk::DkvSmem<128>::BYTES) &&
                        set_smem(opk::attn_dq128_kernel<128>, opk::Dq128Smem<128>::BYTES);
     if (!once) return -3;
+    // the dQ kernel goes first: it also writes the row statistics (dsum, nlse2) that the dK/dV kernel reads
+    opk::attn_dq128_kernel<128><<<n_kt * H, opk::kBwdThreads, opk::Dq128Smem<128>::BYTES, st>>>(tm128, tm128, tmdo128, tm_dq, tm_o128, p);
     opk::attn_dkv_kernel<128><<<dkv_grid, opk::kBwdThreads, opk::DkvSmem<128>::BYTES, st>>>(tm128, tm64, tmdo64, tm_part, p);
-    opk::attn_dq128_kernel<128><<<n_kt * H, opk::kBwdThreads, opk::Dq128Smem<128>::BYTES, st>>>(tm128, tm128, tmdo128, tm_dq, p);
   } else {
     static bool once = set_smem(opk::attn_dkv_kernel<64>, opk::DkvSmem<64>::BYTES) &&
                        set_smem(opk::attn_dq128_kernel<64>, opk::Dq128Smem<64>::BYTES);
     if (!once) return -3;
+    opk::attn_dq128_kernel<64><<<n_kt * H, opk::kBwdThreads, opk::Dq128Smem<64>::BYTES, st>>>(tm128, tm128, tmdo128, tm_dq, tm_o128, p);
     opk::attn_dkv_kernel<64><<<dkv_grid, opk::kBwdThreads, opk::DkvSmem<64>::BYTES, st>>>(tm128, tm64, tmdo64, tm_part, p);
-    opk::attn_dq128_kernel<64><<<n_kt * H, opk::kBwdThreads, opk::Dq128Smem<64>::BYTES, st>>>(tm128, tm128, tmdo128, tm_dq, p);
   }
   if (p.part) {
     const int kvw = KV * hd;

@@ -660,39 +660,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ 
 }
 
 // ------------------------------------------------------------------------------------------------ backward helpers
-// Backward preprocessing, one warp per (t, h) with t < T64 (T rounded up to a multiple of 64):
-//   dsum[h][t] = sum_d dO[t][h*hd + d] * O[t][h*hd + d]        nlse2[h][t] = -lse[h][t] * log2(e)
-// Rows t >= T get dsum = 0 and nlse2 = -inf, so that exp2(s * c + nlse2) is exactly 0 for padded queries.
-__global__ void attn_dsum_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
-                                 const float* __restrict__ lse, float* __restrict__ dsum, float* __restrict__ nlse2,
-                                 int T, int T64, int H, int hd, long long ldo) {
-  // hd / 8 consecutive lanes share one (t, h) row and each takes 16 bytes of O and of dO
-  const int lpr = hd >> 3;                                  // 8 or 16 lanes per row
-  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long row = gid / lpr;
-  const int sub = (int)(gid % lpr);
-  const bool live = row < (long long)T64 * H;
-  const int t = live ? (int)(row / H) : 0, h = live ? (int)(row % H) : 0;
-  float s = 0.f;
-  if (live && t < T) {
-    const uint4 a = *reinterpret_cast<const uint4*>(o + (long long)t * ldo + h * hd + sub * 8);
-    const uint4 b = *reinterpret_cast<const uint4*>(dout + (long long)t * ldo + h * hd + sub * 8);
-    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
-      const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[i]));
-      s = fmaf(x.x, y.x, fmaf(x.y, y.y, s));
-    }
-  }
-  // the rows of a warp are aligned groups of lpr lanes: xor offsets below lpr stay inside the group
-  for (int off = lpr >> 1; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (live && sub == 0) {
-    dsum[(long long)h * T64 + t] = t < T ? s : 0.f;
-    nlse2[(long long)h * T64 + t] = t < T ? -lse[(long long)h * T + t] * 1.4426950408889634f : -INFINITY;
-  }
-}
-
 // Write 32 packed bf16 values (16 words) of row r, columns col0 .. col0+31, into a [128 rows][64 cols] swizzled chunk.
 __device__ __forceinline__ void store_row32(uint8_t* chunk, int r, int col0, const uint32_t (&w)[16]) {
 #pragma unroll
@@ -1062,7 +1029,7 @@ template <int HD>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                   const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_dq,
-                  const AttnParams p) {
+                  const __grid_constant__ CUtensorMap tm_o, const AttnParams p) {
   using SM = Dq128Smem<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -1083,7 +1050,9 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint64_t* dp_free = dp_full + 1;
   uint64_t* ds_full = dp_free + 1;
   uint64_t* ds_free = ds_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ds_free + 1);
+  uint64_t* o_full = ds_free + 1;          // the O tile (parked in the dS buffer) has arrived
+  uint64_t* o_read = o_full + 1;           // all softmax warps have taken their row sums of dO * O from it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_read + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1104,6 +1073,8 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     mbar_init(dp_free, kSoftmaxWarps);
     mbar_init(ds_full, kSoftmaxWarps);
     mbar_init(ds_free, 1);
+    mbar_init(o_full, 1);
+    mbar_init(o_read, kSoftmaxWarps);
     *abort_flag = 0;
     fence_barrier_init();
     // Q, dO and the first K tile are requested before the CTA-wide set-up barrier: their latency runs under the
@@ -1116,6 +1087,9 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
     mbar_expect_tx(&k_full[0], SM::KV_TILE);
     for (int c = 0; c < HD / 64; ++c) tma_load_2d(smem + SM::K_OFF + c * 16384, &tm_kv, &k_full[0], k_col + c * 64, 0);
+    // the O tile of these rows goes into the dS buffer, which is idle until the first score gradients are stored
+    mbar_expect_tx(o_full, SM::Q_TILE);
+    for (int c = 0; c < HD / 64; ++c) tma_load_2d(smem + SM::DS_OFF + c * 16384, &tm_o, o_full, q_col + c * 64, qt * 128);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -1205,10 +1179,39 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     const float c2 = p.scale * 1.4426950408889634f;
     const bool qvalid = qrow < p.T;
-    const float nl_r = qvalid ? p.nlse2[(long long)h * p.T64 + qrow] : -INFINITY;   // invalid rows give P = 0
-    const float d_r = qvalid ? p.dsum[(long long)h * p.T64 + qrow] : 0.f;
     uint8_t* ds_chunk = smem + SM::DS_OFF + half * 16384;       // this warp's 64 keys are one 64-column chunk
     bool ok = true;
+    // Row statistics of the backward pass, computed here and published for the dK/dV kernel that follows:
+    //   dsum[h][t] = sum_d dO[t][d] * O[t][d]      nlse2[h][t] = -lse[h][t] * log2(e)
+    // Rows t >= T (up to the padded length T64) get dsum = 0 and nlse2 = -inf, so that exp2(s * c + nlse2) is exactly
+    // 0 for padded queries. Every thread sums its whole row (the two warps of a lane quarter do the same work).
+    float d_r = 0.f;
+    if (!warp_wait(q_full, 0, abort_flag, lane) || !warp_wait(o_full, 0, abort_flag, lane)) ok = false;
+    if (ok) {
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint4 a = *reinterpret_cast<const uint4*>(smem + SM::DO_OFF + c * 16384 + swz_off(r, 8 * j));
+          const uint4 o = *reinterpret_cast<const uint4*>(smem + SM::DS_OFF + c * 16384 + swz_off(r, 8 * j));
+          const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[e]));
+            const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ow[e]));
+            d_r = fmaf(x.x, y.x, fmaf(x.y, y.y, d_r));
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(o_read);
+    const float nl_r = qvalid ? -p.lse[(long long)h * p.T + qrow] * 1.4426950408889634f : -INFINITY;   // invalid rows give P = 0
+    if (!qvalid) d_r = 0.f;
+    if (half == 0 && qrow < p.T64) {
+      const_cast<float*>(p.dsum)[(long long)h * p.T64 + qrow] = d_r;
+      const_cast<float*>(p.nlse2)[(long long)h * p.T64 + qrow] = nl_r;
+    }
     for (int i = 0; i < n_it && ok; ++i) {
       const int b = i & 1;
       if (warp == 2 && lane == 0) OPK_TRACE(2, i, 0);
@@ -1247,6 +1250,7 @@ attn_dq128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       if (warp == 2 && lane == 0) OPK_TRACE(2, i, 4);
       if (i > 0 && !warp_wait(ds_free, (i - 1) & 1, abort_flag, lane)) { ok = false; break; }
+      if (i == 0 && !warp_wait(o_read, 0, abort_flag, lane)) { ok = false; break; }   // the O tile is no longer needed
       if (warp == 2 && lane == 0) OPK_TRACE(2, i, 5);
       store_row32(ds_chunk, r, 0, dw0);
       store_row32(ds_chunk, r, 32, dw1);
