@@ -133,8 +133,8 @@ extern "C" int opk_attn_bwd(const void* qkv, const void* out, const void* dout, 
   }
   if (p.part) {
     const int kvw = KV * hd;
-    const long long n4 = (long long)T * (kvw / 4) * 2;
-    const unsigned blocks = (unsigned)((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
+    const long long n8 = (long long)T * (kvw / 8) * 2;
+    const unsigned blocks = (unsigned)((n8 + 255) / 256 < 148 * 8 ? (n8 + 255) / 256 : 148 * 8);
     opk::attn_dkv_reduce_kernel<<<blocks, 256, 0, st>>>(p.part, reinterpret_cast<__nv_bfloat16*>(dqkv), T, H / KV, kvw, ld,
                                                          H * hd);
   }
